@@ -1,0 +1,54 @@
+"""Device tensors behind the cache manager's page numbers and state slots.
+
+One allocation per group: [entries, pages, 2 (k, v), kv heads, page_size, head_dim]
+in the runtime dtype, so that one page's keys for one KV head are a contiguous
+``page_size x head_dim`` tile. Fixed-size state: one tensor [slots, *shape] per
+schedule entry that asks for it (the reference allocates conv/ssm state per
+recurrent layer the same way, app/runtime/mamba_cache.py:63-70).
+"""
+
+from __future__ import annotations
+
+import torch
+
+from matricxon_b200.models.decoder import CachePlan
+
+
+class CacheStorage:
+    def __init__(self, plan: CachePlan, pages_per_group: list[int], page_size: int,
+                 dtype: torch.dtype, device: torch.device, num_state_slots: int,
+                 poison: bool = False) -> None:
+        self.plan = plan
+        self.page_size = page_size
+        self.groups: list[torch.Tensor] = []
+        for group, pages in zip(plan.groups, pages_per_group):
+            shape = (len(group.entries), pages, 2, group.request.num_kv_heads, page_size,
+                     group.request.head_dim)
+            tensor = torch.empty(shape, dtype=dtype, device=device)
+            # NaN everywhere when asked: a read of a slot that was never written then shows
+            tensor.fill_(float("nan")) if poison else tensor.zero_()
+            self.groups.append(tensor)
+        self.states: list[torch.Tensor | None] = []
+        for request in plan.state_of_entry:
+            if request is None:
+                self.states.append(None)
+            else:
+                self.states.append(torch.zeros((num_state_slots, *request.shape),
+                                               dtype=request.dtype, device=device))
+
+    def zero_state(self, slot: int) -> None:
+        """A slot handed to a new request starts from zero."""
+        for state in self.states:
+            if state is not None:
+                state[slot].zero_()
+
+    def bytes(self) -> int:
+        total = sum(t.numel() * t.element_size() for t in self.groups)
+        total += sum(t.numel() * t.element_size() for t in self.states if t is not None)
+        return total
+
+
+def bytes_per_token(plan: CachePlan, dtype: torch.dtype) -> int:
+    width = torch.empty((), dtype=dtype).element_size()
+    return sum(len(g.entries) * 2 * g.request.num_kv_heads * g.request.head_dim * width
+               for g in plan.groups)

@@ -1,0 +1,351 @@
+// Grouped-query attention of a flattened batch of query tokens over a paged cache.
+//
+// Visibility rule (the reference's windowed decode attention, app/native/src/mx_attention.c:36-39,
+// and its masks, app/architectures/qwen_layers.py:12-17, app/architectures/gemma4_layers.py:17-34):
+// the query at absolute position p sees key j iff j <= p and (window == 0 or j > p - window).
+// Scores are q.k * scale, softmax is max-subtracted, query head h reads KV head h / (heads / kv heads)
+// (app/native/src/mx_attention.c:16-68). Scores, softmax and the weighted sum are float whatever T is.
+//
+// One block handles (query token, KV head, group of up to 16 query heads, key split). Keys are
+// walked in chunks of 32 absolute positions (one key per lane); a split owns a contiguous run of
+// chunks. With more than one split each block writes an unnormalised partial (max, sum, weighted
+// values) and mx_attention_merge combines them in a fixed order.
+//
+// Cache layout: [page][2 (k, v)][kv head][page_size][head_dim]; block_tables[seq][logical page]
+// gives the physical page, negative when the request holds none there.
+#include <math.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int ATT_THREADS = 128;
+constexpr int ATT_WARPS = ATT_THREADS / 32;
+constexpr int KEYS = 32;      // keys per chunk
+constexpr int GH = 16;        // query heads per block at most
+constexpr int HEADS_PER_WARP = GH / ATT_WARPS;
+
+struct AttnParams {
+    const void* q;            // [n_tokens][q_stride], head h at h * head_dim
+    const void* cache;
+    void* out;                // [n_tokens][out_stride]
+    float* part_o;            // [n_tokens][n_heads][n_splits][head_dim]
+    float* part_ml;           // [n_tokens][n_heads][n_splits][2]
+    const int* block_tables;  // [n_seqs][bt_stride]
+    const int* tok_seq;       // [n_tokens]
+    const int* positions;     // [n_tokens]
+    int* status;
+    long long n_pages;
+    int q_stride, out_stride, bt_stride;
+    int n_heads, n_kv_heads, head_dim, page_size, window, n_splits;
+    float scale;
+};
+
+template <typename T> struct Vec16;  // 16 bytes of T
+template <> struct Vec16<float> { static constexpr int E = 4; };
+template <> struct Vec16<__nv_bfloat16> { static constexpr int E = 8; };
+
+template <typename T>
+__device__ __forceinline__ void unpack16(const uint4& raw, float* f);
+template <>
+__device__ __forceinline__ void unpack16<float>(const uint4& raw, float* f) {
+    f[0] = __uint_as_float(raw.x); f[1] = __uint_as_float(raw.y);
+    f[2] = __uint_as_float(raw.z); f[3] = __uint_as_float(raw.w);
+}
+template <>
+__device__ __forceinline__ void unpack16<__nv_bfloat16>(const uint4& raw, float* f) {
+    const unsigned w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        f[2 * i] = __uint_as_float(w[i] << 16);
+        f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+}
+
+template <typename T, int HD_SLOTS>
+__global__ void __launch_bounds__(ATT_THREADS)
+paged_attention_kernel(const AttnParams p) {
+    constexpr int E = Vec16<T>::E;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int hd = p.head_dim;
+    const int cpr = hd / E;                                   // 16-byte chunks per row
+    const int swz_mask = (cpr % 8 == 0) ? 7 : 0;
+    float* q_s = reinterpret_cast<float*>(smem_raw);          // [GH][hd]
+    float* p_s = q_s + GH * hd;                               // [GH][KEYS]
+    float* alpha_s = p_s + GH * KEYS;                         // [GH]
+    float* m_s = alpha_s + GH;                                // [GH]
+    float* l_s = m_s + GH;                                    // [GH]
+    uint4* k_s = reinterpret_cast<uint4*>(l_s + GH);          // [KEYS][cpr] (swizzled)
+    uint4* v_s = k_s + KEYS * cpr;                            // [KEYS][cpr]
+
+    const int t = blockIdx.x;
+    const int group = p.n_heads / p.n_kv_heads;
+    const int n_hgroups = (group + GH - 1) / GH;
+    const int kh = blockIdx.y / n_hgroups, hg = blockIdx.y - kh * n_hgroups;
+    const int split = blockIdx.z;
+    const int head0 = kh * group + hg * GH;
+    const int gc = min(GH, group - hg * GH);                  // heads this block handles
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+    const int seq = p.tok_seq[t];
+    if (seq < 0) {  // a padding row of a fixed-size batch: defined output, no cache access
+        if (split == 0) {
+            T* orow = reinterpret_cast<T*>(p.out) + (size_t)t * p.out_stride + (size_t)head0 * hd;
+            for (int i = tid; i < gc * hd; i += ATT_THREADS) orow[i] = from_float<T>(0.f);
+        }
+        if (p.n_splits > 1) {
+            for (int h = 0; h < gc; ++h) {
+                const size_t base = ((size_t)t * p.n_heads + head0 + h) * p.n_splits + split;
+                for (int d = tid; d < hd; d += ATT_THREADS) p.part_o[base * hd + d] = 0.f;
+                if (tid == 0) { p.part_ml[base * 2] = 0.f; p.part_ml[base * 2 + 1] = 1.f; }
+            }
+        }
+        return;
+    }
+    const int pos = p.positions[t];
+    const int hi = pos;
+    const int lo = (p.window > 0) ? max(0, pos - p.window + 1) : 0;
+    const int first_chunk = lo / KEYS, last_chunk = hi / KEYS;
+    const int n_chunks = last_chunk - first_chunk + 1;
+    const int per_split = (n_chunks + p.n_splits - 1) / p.n_splits;
+    const int c_begin = first_chunk + split * per_split;
+    const int c_end = min(last_chunk + 1, c_begin + per_split);
+
+    const T* qrow = reinterpret_cast<const T*>(p.q) + (size_t)t * p.q_stride + (size_t)head0 * hd;
+    for (int i = tid; i < gc * hd; i += ATT_THREADS) q_s[i] = to_float(qrow[i]);
+
+    float acc[GH][HD_SLOTS];
+#pragma unroll
+    for (int h = 0; h < GH; ++h)
+#pragma unroll
+        for (int s = 0; s < HD_SLOTS; ++s) acc[h][s] = 0.f;
+    float m_run[HEADS_PER_WARP], l_run[HEADS_PER_WARP];
+#pragma unroll
+    for (int hs = 0; hs < HEADS_PER_WARP; ++hs) { m_run[hs] = -INFINITY; l_run[hs] = 0.f; }
+
+    const int* bt = p.block_tables + (size_t)seq * p.bt_stride;
+    const T* cache = reinterpret_cast<const T*>(p.cache);
+    const size_t head_stride = (size_t)p.page_size * hd;
+
+    for (int ci = c_begin; ci < c_end; ++ci) {
+        const int c0 = ci * KEYS;
+        // ---- stage the chunk's K and V rows (zero for keys outside [lo, hi])
+        for (int item = tid; item < KEYS * cpr; item += ATT_THREADS) {
+            const int j = item / cpr, c = item - j * cpr;
+            const int kpos = c0 + j;
+            uint4 kv = make_uint4(0, 0, 0, 0), vv = make_uint4(0, 0, 0, 0);
+            if (kpos >= lo && kpos <= hi) {
+                const int lp = kpos / p.page_size;
+                const long long page = (lp < p.bt_stride) ? bt[lp] : -1;
+                if (page < 0 || page >= p.n_pages) {
+                    if (c == 0) atomicOr(p.status, MX_STATUS_BAD_PAGE);
+                } else {
+                    const int off = kpos - lp * p.page_size;
+                    const T* kptr = cache + ((size_t)page * 2 * p.n_kv_heads + kh) * head_stride +
+                                    (size_t)off * hd + (size_t)c * E;
+                    const T* vptr = kptr + (size_t)p.n_kv_heads * head_stride;
+                    kv = *reinterpret_cast<const uint4*>(kptr);
+                    vv = *reinterpret_cast<const uint4*>(vptr);
+                }
+            }
+            k_s[j * cpr + (c ^ (j & swz_mask))] = kv;
+            v_s[j * cpr + c] = vv;
+        }
+        __syncthreads();
+
+        // ---- scores: lane = key, this warp's heads are warp, warp + 4, ...
+        {
+            const int kpos = c0 + lane;
+            const bool valid = (kpos >= lo && kpos <= hi);
+            float s[HEADS_PER_WARP];
+#pragma unroll
+            for (int hs = 0; hs < HEADS_PER_WARP; ++hs) s[hs] = 0.f;
+            for (int c = 0; c < cpr; ++c) {
+                float kf[E];
+                unpack16<T>(k_s[lane * cpr + (c ^ (lane & swz_mask))], kf);
+#pragma unroll
+                for (int hs = 0; hs < HEADS_PER_WARP; ++hs) {
+                    const int h = warp + hs * ATT_WARPS;
+                    if (h < gc) {
+                        const float4* qv = reinterpret_cast<const float4*>(q_s + h * hd + c * E);
+#pragma unroll
+                        for (int e4 = 0; e4 < E / 4; ++e4) {
+                            const float4 qq = qv[e4];
+                            s[hs] = fmaf(qq.x, kf[4 * e4 + 0], s[hs]);
+                            s[hs] = fmaf(qq.y, kf[4 * e4 + 1], s[hs]);
+                            s[hs] = fmaf(qq.z, kf[4 * e4 + 2], s[hs]);
+                            s[hs] = fmaf(qq.w, kf[4 * e4 + 3], s[hs]);
+                        }
+                    }
+                }
+            }
+#pragma unroll
+            for (int hs = 0; hs < HEADS_PER_WARP; ++hs) {
+                const int h = warp + hs * ATT_WARPS;
+                if (h < gc) {
+                    const float sv = valid ? s[hs] * p.scale : -INFINITY;
+                    const float m_new = fmaxf(m_run[hs], warp_max(sv));
+                    const float pj = valid ? expf(sv - m_new) : 0.f;
+                    const float alpha = (m_run[hs] == -INFINITY) ? 0.f : expf(m_run[hs] - m_new);
+                    l_run[hs] = l_run[hs] * alpha + warp_sum(pj);
+                    m_run[hs] = m_new;
+                    p_s[h * KEYS + lane] = pj;
+                    if (lane == 0) alpha_s[h] = alpha;
+                }
+            }
+        }
+        __syncthreads();
+
+        // ---- weighted values: thread = output dim(s), all heads
+#pragma unroll
+        for (int slot = 0; slot < HD_SLOTS; ++slot) {
+            const int d = tid + slot * ATT_THREADS;
+            if (d < hd) {
+#pragma unroll
+                for (int h = 0; h < GH; ++h)
+                    if (h < gc) acc[h][slot] *= alpha_s[h];
+                const T* vcol = reinterpret_cast<const T*>(v_s) + d;
+                for (int j = 0; j < KEYS; j += 4) {
+                    const float v0 = to_float(vcol[(size_t)(j + 0) * hd]);
+                    const float v1 = to_float(vcol[(size_t)(j + 1) * hd]);
+                    const float v2 = to_float(vcol[(size_t)(j + 2) * hd]);
+                    const float v3 = to_float(vcol[(size_t)(j + 3) * hd]);
+#pragma unroll
+                    for (int h = 0; h < GH; ++h) {
+                        if (h < gc) {
+                            const float4 pp = *reinterpret_cast<const float4*>(p_s + h * KEYS + j);
+                            float a = acc[h][slot];
+                            a = fmaf(pp.x, v0, a);
+                            a = fmaf(pp.y, v1, a);
+                            a = fmaf(pp.z, v2, a);
+                            a = fmaf(pp.w, v3, a);
+                            acc[h][slot] = a;
+                        }
+                    }
+                }
+            }
+        }
+        __syncthreads();
+    }
+
+    // ---- hand the running max / sum of each head to every thread
+#pragma unroll
+    for (int hs = 0; hs < HEADS_PER_WARP; ++hs) {
+        const int h = warp + hs * ATT_WARPS;
+        if (h < gc && lane == 0) { m_s[h] = m_run[hs]; l_s[h] = l_run[hs]; }
+    }
+    __syncthreads();
+
+    if (p.n_splits == 1) {
+        T* orow = reinterpret_cast<T*>(p.out) + (size_t)t * p.out_stride + (size_t)head0 * hd;
+#pragma unroll
+        for (int slot = 0; slot < HD_SLOTS; ++slot) {
+            const int d = tid + slot * ATT_THREADS;
+            if (d < hd) {
+#pragma unroll
+                for (int h = 0; h < GH; ++h)
+                    if (h < gc) orow[(size_t)h * hd + d] = from_float<T>(acc[h][slot] / l_s[h]);
+            }
+        }
+    } else {
+#pragma unroll
+        for (int h = 0; h < GH; ++h) {
+            if (h < gc) {
+                const size_t base = ((size_t)t * p.n_heads + head0 + h) * p.n_splits + split;
+#pragma unroll
+                for (int slot = 0; slot < HD_SLOTS; ++slot) {
+                    const int d = tid + slot * ATT_THREADS;
+                    if (d < hd) p.part_o[base * hd + d] = acc[h][slot];
+                }
+                if (tid == 0) { p.part_ml[base * 2] = m_s[h]; p.part_ml[base * 2 + 1] = l_s[h]; }
+            }
+        }
+    }
+}
+
+template <typename T>
+__global__ void attention_merge_kernel(const float* __restrict__ part_o,
+                                       const float* __restrict__ part_ml, T* __restrict__ out,
+                                       int out_stride, int n_heads, int head_dim, int n_splits) {
+    const int t = blockIdx.x, h = blockIdx.y;
+    const size_t base = ((size_t)t * n_heads + h) * n_splits;
+    float m = -INFINITY;
+    for (int s = 0; s < n_splits; ++s) m = fmaxf(m, part_ml[(base + s) * 2]);
+    float total = 0.f;
+    for (int s = 0; s < n_splits; ++s) {
+        const float ms = part_ml[(base + s) * 2];
+        if (ms != -INFINITY) total += part_ml[(base + s) * 2 + 1] * expf(ms - m);
+    }
+    for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
+        float o = 0.f;
+        for (int s = 0; s < n_splits; ++s) {
+            const float ms = part_ml[(base + s) * 2];
+            if (ms != -INFINITY) o += part_o[(base + s) * head_dim + d] * expf(ms - m);
+        }
+        out[(size_t)t * out_stride + (size_t)h * head_dim + d] = from_float<T>(o / total);
+    }
+}
+
+template <typename T>
+size_t attention_smem_bytes(int head_dim) {
+    return (size_t)GH * head_dim * 4 + (size_t)GH * KEYS * 4 + 3 * GH * 4 +
+           2 * (size_t)KEYS * head_dim * sizeof(T);
+}
+
+template <typename T, int HD_SLOTS>
+int launch_attention(const AttnParams& p, int n_tokens, cudaStream_t stream) {
+    const size_t smem = attention_smem_bytes<T>(p.head_dim);
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(paged_attention_kernel<T, HD_SLOTS>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) MX_REFUSE("attention: cannot reserve %zu bytes of shared memory", smem);
+    }
+    const int group = p.n_heads / p.n_kv_heads;
+    const int n_hgroups = (group + GH - 1) / GH;
+    dim3 grid(n_tokens, p.n_kv_heads * n_hgroups, p.n_splits);
+    paged_attention_kernel<T, HD_SLOTS><<<grid, ATT_THREADS, smem, stream>>>(p);
+    int rc = mx_launch_status();
+    if (rc != MX_OK || p.n_splits == 1) return rc;
+    dim3 mgrid(n_tokens, p.n_heads);
+    attention_merge_kernel<T><<<mgrid, 128, 0, stream>>>(p.part_o, p.part_ml, (T*)p.out, p.out_stride,
+                                                        p.n_heads, p.head_dim, p.n_splits);
+    return mx_launch_status();
+}
+
+}  // namespace
+
+// Bytes of scratch the split path needs: partial values plus (max, sum) per split.
+extern "C" long long mx_attention_scratch_bytes(int n_tokens, int n_heads, int head_dim, int n_splits) {
+    if (n_splits <= 1) return 0;
+    return (long long)n_tokens * n_heads * n_splits * (head_dim + 2) * (long long)sizeof(float);
+}
+
+extern "C" int mx_paged_attention(const void* q, int dtype, int q_stride, const void* cache,
+                                  long long n_pages, int page_size, const int* block_tables,
+                                  int bt_stride, const int* tok_seq, const int* positions,
+                                  int n_tokens, int n_heads, int n_kv_heads, int head_dim,
+                                  int window, float scale, void* out, int out_stride,
+                                  int n_splits, float* scratch, int* status, cudaStream_t stream) {
+    if (n_tokens <= 0) return MX_OK;
+    if (n_kv_heads <= 0 || n_heads % n_kv_heads != 0)
+        MX_REFUSE("attention: %d heads are not a multiple of %d kv heads", n_heads, n_kv_heads);
+    if (head_dim % 16 != 0 || head_dim < 16 || head_dim > 256)
+        MX_REFUSE("attention: head_dim %d is not a multiple of 16 in [16, 256]", head_dim);
+    if (page_size <= 0) MX_REFUSE("attention: page size %d", page_size);
+    if (n_splits < 1) MX_REFUSE("attention: n_splits %d", n_splits);
+    if (n_splits > 1 && scratch == nullptr) MX_REFUSE("attention: split path without scratch memory");
+    if (n_splits > 65535) MX_REFUSE("attention: %d splits exceed the grid's third dimension", n_splits);
+    AttnParams p;
+    p.q = q; p.cache = cache; p.out = out;
+    p.part_o = scratch;
+    p.part_ml = scratch ? scratch + (size_t)n_tokens * n_heads * n_splits * head_dim : nullptr;
+    p.block_tables = block_tables; p.tok_seq = tok_seq; p.positions = positions; p.status = status;
+    p.n_pages = n_pages; p.q_stride = q_stride; p.out_stride = out_stride; p.bt_stride = bt_stride;
+    p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.head_dim = head_dim; p.page_size = page_size;
+    p.window = window; p.n_splits = n_splits; p.scale = scale;
+    const bool two = head_dim > ATT_THREADS;
+    if (dtype == MX_DTYPE_F32)
+        return two ? launch_attention<float, 2>(p, n_tokens, stream) : launch_attention<float, 1>(p, n_tokens, stream);
+    return two ? launch_attention<__nv_bfloat16, 2>(p, n_tokens, stream)
+               : launch_attention<__nv_bfloat16, 1>(p, n_tokens, stream);
+}

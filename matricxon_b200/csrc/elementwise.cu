@@ -1,0 +1,240 @@
+// Embedding lookup, LayerNorm, rotary encoding with the cache write, and the
+// bias / activation / residual epilogue used behind a library matrix product.
+//
+// Formulas follow the reference's modules: token_embd lookup
+// (app/architectures/starcoder2.py:218), nn.LayerNorm with biased variance
+// (app/architectures/starcoder2_layers.py:45,56), NeoX rotate-half RoPE with fp32
+// angles (app/architectures/rope.py:18-29,152-169; app/native/src/mx_fused_ops.c:20-34),
+// K cached already rotated (app/architectures/qwen_layers.py:80-86), tanh GELU
+// (app/architectures/starcoder2_layers.py:23).
+#include <stdarg.h>
+#include <stdio.h>
+
+#include "common.cuh"
+
+static thread_local char g_error[512] = "";
+extern "C" const char* mx_last_error_message() { return g_error; }
+void mx_set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof(g_error), fmt, ap);
+    va_end(ap);
+}
+
+// ---------------------------------------------------------------- embedding
+template <typename T>
+__global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ table,
+                             float* __restrict__ out, int hidden, int vocab, int* status) {
+    const int row = blockIdx.x;
+    const int id = ids[row];
+    float* o = out + (size_t)row * hidden;
+    if (id < 0 || id >= vocab) {
+        if (threadIdx.x == 0) atomicOr(status, MX_STATUS_BAD_TOKEN_ID);
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = 0.f;
+        return;
+    }
+    const T* src = table + (size_t)id * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = to_float(src[i]);
+}
+
+extern "C" int mx_embed(const int* ids, const void* table, int dtype, float* out, int n_tokens,
+                        int hidden, int vocab, int* status, cudaStream_t stream) {
+    if (n_tokens <= 0) return MX_OK;
+    const int threads = hidden >= 1024 ? 256 : 128;
+    if (dtype == MX_DTYPE_F32)
+        embed_kernel<float><<<n_tokens, threads, 0, stream>>>(ids, (const float*)table, out, hidden,
+                                                              vocab, status);
+    else
+        embed_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>(
+            ids, (const __nv_bfloat16*)table, out, hidden, vocab, status);
+    return mx_launch_status();
+}
+
+// ---------------------------------------------------------------- LayerNorm
+// One block per output row. The row (float) is staged in shared memory; mean, then the
+// mean of squared deviations (two passes, so no cancellation), all in float.
+template <typename TOut>
+__global__ void layernorm_kernel(const float* __restrict__ x, const int* __restrict__ rows,
+                                 const float* __restrict__ weight, const float* __restrict__ bias,
+                                 TOut* __restrict__ out, int hidden, float eps) {
+    extern __shared__ float row_cache[];
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    const int src_row = rows ? rows[r] : r;
+    const float* xr = x + (size_t)src_row * hidden;
+    float s = 0.f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        const float v = xr[i];
+        row_cache[i] = v;
+        s += v;
+    }
+    const float mean = block_sum(s, scratch) / (float)hidden;
+    float q = 0.f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        const float d = row_cache[i] - mean;
+        q += d * d;
+    }
+    const float var = block_sum(q, scratch) / (float)hidden;
+    const float rstd = 1.0f / sqrtf(var + eps);
+    TOut* o = out + (size_t)r * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        float v = (row_cache[i] - mean) * rstd * weight[i];
+        if (bias) v += bias[i];
+        o[i] = from_float<TOut>(v);
+    }
+}
+
+extern "C" int mx_layernorm(const float* x, const int* rows, const float* weight, const float* bias,
+                            void* out, int out_dtype, int n_rows, int hidden, float eps,
+                            cudaStream_t stream) {
+    if (n_rows <= 0) return MX_OK;
+    const size_t smem = (size_t)hidden * sizeof(float);
+    if (smem > 200 * 1024) MX_REFUSE("layernorm: hidden size %d exceeds the 51200 this kernel stages", hidden);
+    const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+    if (out_dtype == MX_DTYPE_F32) {
+        if (smem > 48 * 1024)
+            cudaFuncSetAttribute(layernorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        layernorm_kernel<float><<<n_rows, threads, smem, stream>>>(x, rows, weight, bias, (float*)out, hidden, eps);
+    } else {
+        if (smem > 48 * 1024)
+            cudaFuncSetAttribute(layernorm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        layernorm_kernel<__nv_bfloat16><<<n_rows, threads, smem, stream>>>(x, rows, weight, bias, (__nv_bfloat16*)out, hidden, eps);
+    }
+    return mx_launch_status();
+}
+
+// ---------------------------------------------------------------- rotary + cache write
+// qkv rows are [q heads | k heads | v heads], each head `head_dim` wide. q is rotated in
+// place; k is rotated and stored, v is stored, at `slot = page * page_size + offset` of a
+// cache laid out [page][2 (k,v)][kv head][page_size][head_dim]. Angles and the rotation
+// are float; one rounding to T at the end. With write_cache == 0 only q is rotated. A slot of
+// -1 marks a padding row (rotated, not stored); any other slot outside the pool sets the
+// status bit MX_STATUS_BAD_SLOT.
+template <typename T>
+__global__ void rope_kv_write_kernel(T* __restrict__ qkv, int row_stride,
+                                     const int* __restrict__ positions,
+                                     const float* __restrict__ inv_freq,
+                                     const int* __restrict__ slots, T* __restrict__ cache,
+                                     int n_heads, int n_kv_heads, int head_dim, int rotary_dim,
+                                     int page_size, long long n_slots, int write_cache,
+                                     int* status) {
+    extern __shared__ float cs[];  // cos[half], sin[half]
+    const int t = blockIdx.x;
+    const int half = rotary_dim >> 1;
+    const float pos = (float)positions[t];
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        const float angle = pos * inv_freq[i];
+        cs[i] = cosf(angle);
+        cs[half + i] = sinf(angle);
+    }
+    __syncthreads();
+    T* row = qkv + (size_t)t * row_stride;
+
+    // q heads: rotate in place
+    for (int item = threadIdx.x; item < n_heads * half; item += blockDim.x) {
+        const int h = item / half, i = item - h * half;
+        T* p = row + (size_t)h * head_dim;
+        const float x1 = to_float(p[i]), x2 = to_float(p[i + half]);
+        const float c = cs[i], s = cs[half + i];
+        p[i] = from_float<T>(x1 * c - x2 * s);
+        p[i + half] = from_float<T>(x2 * c + x1 * s);
+    }
+    if (!write_cache) return;
+
+    const long long slot = slots[t];
+    if (slot == -1) return;  // a padding row of a fixed-size batch: nothing to store
+    if (slot < 0 || slot >= n_slots) {
+        if (threadIdx.x == 0) atomicOr(status, MX_STATUS_BAD_SLOT);
+        return;
+    }
+    const long long page = slot / page_size;
+    const int offset = (int)(slot - page * page_size);
+    const size_t head_stride = (size_t)page_size * head_dim;
+    T* kbase = cache + ((size_t)page * 2 * n_kv_heads) * head_stride + (size_t)offset * head_dim;
+    T* vbase = kbase + (size_t)n_kv_heads * head_stride;
+    const T* krow = row + (size_t)n_heads * head_dim;
+    const T* vrow = krow + (size_t)n_kv_heads * head_dim;
+
+    for (int item = threadIdx.x; item < n_kv_heads * half; item += blockDim.x) {
+        const int h = item / half, i = item - h * half;
+        const T* p = krow + (size_t)h * head_dim;
+        const float x1 = to_float(p[i]), x2 = to_float(p[i + half]);
+        const float c = cs[i], s = cs[half + i];
+        T* dst = kbase + (size_t)h * head_stride;
+        dst[i] = from_float<T>(x1 * c - x2 * s);
+        dst[i + half] = from_float<T>(x2 * c + x1 * s);
+    }
+    // dims beyond the rotary width pass through unrotated
+    const int tail = head_dim - rotary_dim;
+    for (int item = threadIdx.x; item < n_kv_heads * tail; item += blockDim.x) {
+        const int h = item / tail, i = rotary_dim + (item - h * tail);
+        kbase[(size_t)h * head_stride + i] = krow[(size_t)h * head_dim + i];
+    }
+    for (int item = threadIdx.x; item < n_kv_heads * head_dim; item += blockDim.x) {
+        const int h = item / head_dim, i = item - h * head_dim;
+        vbase[(size_t)h * head_stride + i] = vrow[(size_t)h * head_dim + i];
+    }
+}
+
+extern "C" int mx_rope_kv_write(void* qkv, int dtype, int row_stride, const int* positions,
+                                const float* inv_freq, const int* slots, void* cache, int n_tokens,
+                                int n_heads, int n_kv_heads, int head_dim, int rotary_dim,
+                                int page_size, long long n_pages, int write_cache, int* status,
+                                cudaStream_t stream) {
+    if (n_tokens <= 0) return MX_OK;
+    if (rotary_dim % 2 != 0 || rotary_dim > head_dim || rotary_dim < 0)
+        MX_REFUSE("rope: rotary width %d must be even and at most head_dim %d", rotary_dim, head_dim);
+    const size_t smem = (size_t)rotary_dim * sizeof(float);
+    if (smem > 48 * 1024) MX_REFUSE("rope: rotary width %d is too large", rotary_dim);
+    const int work = n_heads * (rotary_dim / 2);
+    const int threads = work >= 1024 ? 256 : 128;
+    const long long n_slots = n_pages * page_size;
+    if (dtype == MX_DTYPE_F32)
+        rope_kv_write_kernel<float><<<n_tokens, threads, smem, stream>>>(
+            (float*)qkv, row_stride, positions, inv_freq, slots, (float*)cache, n_heads, n_kv_heads,
+            head_dim, rotary_dim, page_size, n_slots, write_cache, status);
+    else
+        rope_kv_write_kernel<__nv_bfloat16><<<n_tokens, threads, smem, stream>>>(
+            (__nv_bfloat16*)qkv, row_stride, positions, inv_freq, slots, (__nv_bfloat16*)cache,
+            n_heads, n_kv_heads, head_dim, rotary_dim, page_size, n_slots, write_cache, status);
+    return mx_launch_status();
+}
+
+// ---------------------------------------------------------------- epilogue behind a library GEMM
+// mode 0: out(T)  = acc + bias
+// mode 1: out(T)  = gelu_tanh(acc + bias)
+// mode 2: out(f32) = residual + acc + bias     (out may alias residual)
+// mode 3: out(f32) = acc + bias
+template <typename TAcc, typename TOut>
+__global__ void epilogue_kernel(const TAcc* __restrict__ acc, const float* __restrict__ bias,
+                                const float* residual, TOut* out, long long total, int n_cols,
+                                int mode) {
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+        float v = to_float(acc[i]);
+        if (bias) v += bias[(int)(i % n_cols)];
+        if (mode == 1) v = gelu_tanh(v);
+        if (mode == 2) v += residual[i];
+        out[i] = from_float<TOut>(v);
+    }
+}
+
+extern "C" int mx_epilogue(const void* acc, int acc_dtype, const float* bias, const float* residual,
+                           void* out, int out_dtype, long long n_rows, int n_cols, int mode,
+                           cudaStream_t stream) {
+    const long long total = n_rows * n_cols;
+    if (total <= 0) return MX_OK;
+    if (mode < 0 || mode > 3) MX_REFUSE("epilogue: unknown mode %d", mode);
+    if (mode == 2 && residual == nullptr) MX_REFUSE("epilogue: residual mode without a residual");
+    const int threads = 256;
+    long long blocks = (total + threads - 1) / threads;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+#define MX_EPI(TA, TO) \
+    epilogue_kernel<TA, TO><<<(int)blocks, threads, 0, stream>>>((const TA*)acc, bias, residual, (TO*)out, total, n_cols, mode)
+    if (acc_dtype == MX_DTYPE_F32 && out_dtype == MX_DTYPE_F32) MX_EPI(float, float);
+    else if (acc_dtype == MX_DTYPE_F32) MX_EPI(float, __nv_bfloat16);
+    else if (out_dtype == MX_DTYPE_F32) MX_EPI(__nv_bfloat16, float);
+    else MX_EPI(__nv_bfloat16, __nv_bfloat16);
+#undef MX_EPI
+    return mx_launch_status();
+}

@@ -1,0 +1,173 @@
+"""Tensor-level faces of the CUDA kernels.
+
+Each function checks device, dtype and layout, then launches on torch's current
+stream. Nothing here computes with torch: a tensor that is not on a CUDA device
+is an error, not a cue to fall back.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from matricxon_b200.ops.library import KernelLibraryError, check, library
+
+F32, BF16 = 0, 1
+EPILOGUE_NONE, EPILOGUE_GELU, EPILOGUE_RESIDUAL, EPILOGUE_F32 = 0, 1, 2, 3
+
+STATUS_BITS = {1: "a token id outside the vocabulary", 2: "a cache slot outside the pool",
+               4: "a block-table entry that names no page", 8: "a device-side wait ran out"}
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return F32
+    if dtype == torch.bfloat16:
+        return BF16
+    raise KernelLibraryError(f"kernels take float32 or bfloat16, not {dtype}")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def _need(t: torch.Tensor, name: str, dtype: torch.dtype | None = None, contiguous: bool = True):
+    if not t.is_cuda:
+        raise KernelLibraryError(f"{name} must be a CUDA tensor (there is no CPU path)")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelLibraryError(f"{name} must be {dtype}, got {t.dtype}")
+    if contiguous and not t.is_contiguous():
+        raise KernelLibraryError(f"{name} must be contiguous")
+
+
+def describe_status(word: int) -> str:
+    return "; ".join(text for bit, text in STATUS_BITS.items() if word & bit) or "no error"
+
+
+def embed(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, status: torch.Tensor) -> None:
+    _need(ids, "ids", torch.int32)
+    _need(table, "table")
+    _need(out, "out", torch.float32)
+    _need(status, "status", torch.int32)
+    n, hidden = out.shape
+    assert ids.numel() == n and table.shape[1] == hidden
+    check(library().mx_embed(_ptr(ids), _ptr(table), dtype_code(table.dtype), _ptr(out), n, hidden,
+                             table.shape[0], _ptr(status), _stream()), "embed")
+
+
+def layernorm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, eps: float,
+              out: torch.Tensor, rows: torch.Tensor | None = None) -> None:
+    """out[r] = LayerNorm(x[rows[r]] if rows is given else x[r]); x is the float residual stream."""
+    _need(x, "x", torch.float32)
+    _need(weight, "weight", torch.float32)
+    if bias is not None:
+        _need(bias, "bias", torch.float32)
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
+    _need(out, "out")
+    n_rows, hidden = out.shape
+    assert x.shape[1] == hidden and weight.numel() == hidden
+    assert rows is None or rows.numel() == n_rows
+    assert rows is not None or x.shape[0] == n_rows
+    check(library().mx_layernorm(_ptr(x), _ptr(rows), _ptr(weight), _ptr(bias), _ptr(out),
+                                 dtype_code(out.dtype), n_rows, hidden, float(eps), _stream()),
+          "layernorm")
+
+
+def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor,
+                  slots: torch.Tensor | None, cache: torch.Tensor | None, n_heads: int,
+                  n_kv_heads: int, head_dim: int, rotary_dim: int, page_size: int,
+                  status: torch.Tensor) -> None:
+    """Rotates q (and k) of each row of ``qkv`` in float; writes k and v to the cache pages.
+
+    ``cache`` is [pages, 2, kv heads, page_size, head_dim]; None rotates q only."""
+    _need(qkv, "qkv")
+    _need(positions, "positions", torch.int32)
+    _need(inv_freq, "inv_freq", torch.float32)
+    _need(status, "status", torch.int32)
+    n = qkv.shape[0]
+    assert qkv.shape[1] == (n_heads + 2 * n_kv_heads) * head_dim
+    assert inv_freq.numel() == rotary_dim // 2
+    write = cache is not None
+    n_pages = 0
+    if write:
+        _need(cache, "cache", qkv.dtype)
+        _need(slots, "slots", torch.int32)
+        assert tuple(cache.shape[1:]) == (2, n_kv_heads, page_size, head_dim), cache.shape
+        n_pages = cache.shape[0]
+    check(library().mx_rope_kv_write(_ptr(qkv), dtype_code(qkv.dtype), qkv.stride(0),
+                                     _ptr(positions), _ptr(inv_freq), _ptr(slots), _ptr(cache), n,
+                                     n_heads, n_kv_heads, head_dim, rotary_dim, page_size, n_pages,
+                                     1 if write else 0, _ptr(status), _stream()), "rope_kv_write")
+
+
+def epilogue(acc: torch.Tensor, bias: torch.Tensor | None, residual: torch.Tensor | None,
+             out: torch.Tensor, mode: int) -> None:
+    _need(acc, "acc")
+    _need(out, "out")
+    n_rows, n_cols = acc.shape
+    check(library().mx_epilogue(_ptr(acc), dtype_code(acc.dtype), _ptr(bias), _ptr(residual),
+                                _ptr(out), dtype_code(out.dtype), n_rows, n_cols, mode, _stream()),
+          "epilogue")
+
+
+def gemm_simt(a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None,
+              residual: torch.Tensor | None, out: torch.Tensor, mode: int) -> None:
+    """out = epilogue(a @ w.T + bias) with float accumulation on the FP32 cores."""
+    _need(a, "a", contiguous=False)
+    _need(w, "w")
+    _need(out, "out")
+    if a.stride(1) != 1:
+        raise KernelLibraryError("a must have unit stride along K")
+    m, k = a.shape
+    n = w.shape[0]
+    assert w.shape[1] == k and tuple(out.shape) == (m, n), (a.shape, w.shape, out.shape)
+    assert w.dtype == a.dtype
+    if bias is not None:
+        _need(bias, "bias", torch.float32)
+        assert bias.numel() == n
+    if residual is not None:
+        _need(residual, "residual", torch.float32)
+        assert tuple(residual.shape) == (m, n)
+    check(library().mx_gemm_simt(_ptr(a), _ptr(w), dtype_code(a.dtype), _ptr(bias), _ptr(residual),
+                                 _ptr(out), dtype_code(out.dtype), m, n, k, a.stride(0), w.stride(0),
+                                 out.stride(0), mode, _stream()), "gemm_simt")
+
+
+def attention_scratch_bytes(n_tokens: int, n_heads: int, head_dim: int, n_splits: int) -> int:
+    return int(library().mx_attention_scratch_bytes(n_tokens, n_heads, head_dim, n_splits))
+
+
+def paged_attention(q: torch.Tensor, q_stride: int, cache: torch.Tensor, block_tables: torch.Tensor,
+                    tok_seq: torch.Tensor, positions: torch.Tensor, n_tokens: int, n_heads: int,
+                    n_kv_heads: int, head_dim: int, window: int | None, scale: float,
+                    out: torch.Tensor, status: torch.Tensor, n_splits: int = 1,
+                    scratch: torch.Tensor | None = None) -> None:
+    """Attention of ``n_tokens`` query rows over the paged cache.
+
+    ``q`` points at the first query head of row 0 and rows are ``q_stride`` elements apart
+    (so the q part of a fused qkv buffer can be used in place). ``out`` is [tokens, heads * dim].
+    """
+    _need(q, "q", contiguous=False)
+    _need(cache, "cache", q.dtype)
+    _need(block_tables, "block_tables", torch.int32)
+    _need(tok_seq, "tok_seq", torch.int32)
+    _need(positions, "positions", torch.int32)
+    _need(out, "out", q.dtype)
+    _need(status, "status", torch.int32)
+    page_size = cache.shape[3]
+    assert tuple(cache.shape[1:]) == (2, n_kv_heads, page_size, head_dim), cache.shape
+    assert out.shape[1] == n_heads * head_dim and out.shape[0] >= n_tokens
+    if n_splits > 1:
+        need = attention_scratch_bytes(n_tokens, n_heads, head_dim, n_splits)
+        if scratch is None or scratch.numel() * scratch.element_size() < need:
+            raise KernelLibraryError(f"attention with {n_splits} splits needs {need} bytes of scratch")
+        _need(scratch, "scratch", torch.float32)
+    check(library().mx_paged_attention(
+        _ptr(q), dtype_code(q.dtype), q_stride, _ptr(cache), cache.shape[0], page_size,
+        _ptr(block_tables), block_tables.stride(0), _ptr(tok_seq), _ptr(positions), n_tokens,
+        n_heads, n_kv_heads, head_dim, int(window or 0), float(scale), _ptr(out), out.stride(0),
+        n_splits, _ptr(scratch), _ptr(status), _stream()), "paged_attention")

@@ -1,0 +1,131 @@
+"""Descriptions of parts: plain data that an architecture's configuration produces.
+
+A model is described without naming the architecture it came from: a list of
+layers, each naming the kind and the constants of its mixer, feed-forward and
+norms, and a schedule that says in which order layers run. The reference
+passes the same constants as constructor arguments
+(app/architectures/starcoder2_layers.py:34-43, app/architectures/qwen_layers.py:35-45,
+app/architectures/rope.py:16); here they are data so that a layer list can mix kinds.
+
+A spec class only needs a string attribute ``kind``; the class registered under
+that kind (parts/registry.py) is built from it. New kinds need no change here.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any
+
+
+@dataclass(frozen=True)
+class LayerNormSpec:
+    """``(x - mean) / sqrt(var + eps) * weight (+ bias)`` over the last axis."""
+
+    size: int
+    eps: float
+    bias: bool = True
+    kind: str = "layernorm"
+
+
+@dataclass(frozen=True)
+class RotarySpec:
+    """Rotary position encoding, halves paired as (i, i + rotary_dim/2)."""
+
+    rotary_dim: int
+    theta: float
+    kind: str = "rotary_neox"
+
+
+@dataclass(frozen=True)
+class AttentionSpec:
+    """Grouped-query attention over a paged cache.
+
+    ``window`` is None for plain causal attention; otherwise the query at
+    absolute position p sees key j iff ``j <= p and j > p - window``.
+    """
+
+    hidden_size: int
+    num_heads: int
+    num_kv_heads: int
+    head_dim: int
+    bias: bool
+    window: int | None
+    scale: float
+    position: Any | None = None
+    kind: str = "attention"
+
+
+@dataclass(frozen=True)
+class MlpSpec:
+    """``down(act(up(x)))`` without a gate."""
+
+    hidden_size: int
+    intermediate_size: int
+    bias: bool
+    activation: str = "gelu_tanh"
+    up_name: str = "c_fc"
+    down_name: str = "c_proj"
+    kind: str = "mlp"
+
+
+@dataclass(frozen=True)
+class LayerSpec:
+    """One decoder layer: which block arrangement holds which parts."""
+
+    mixer: Any
+    feed_forward: Any
+    mixer_norm: Any
+    ffn_norm: Any
+    block: str = "pre_norm_sequential"
+    # weight-name fragments under "model.layers.{i}."
+    mixer_name: str = "self_attn"
+    feed_forward_name: str = "mlp"
+    mixer_norm_name: str = "input_layernorm"
+    ffn_norm_name: str = "post_attention_layernorm"
+
+
+@dataclass(frozen=True)
+class ScheduleEntry:
+    """One execution of a layer.
+
+    ``layer`` indexes ``ModelSpec.layers`` (a layer may be named by several
+    entries: its weights are then shared, each execution keeps a cache of its
+    own). ``cache_of`` names an earlier schedule entry whose cache this
+    execution reads instead of owning one; it then writes nothing.
+    """
+
+    layer: int
+    cache_of: int | None = None
+
+
+@dataclass(frozen=True)
+class ModelSpec:
+    hidden_size: int
+    vocab_size: int
+    layers: tuple[LayerSpec, ...]
+    schedule: tuple[ScheduleEntry, ...]
+    final_norm: Any
+    tie_word_embeddings: bool
+    max_position_embeddings: int
+    embedding_name: str = "model.embed_tokens"
+    layer_prefix: str = "model.layers"
+    final_norm_name: str = "model.norm"
+    head_name: str = "lm_head"
+    extra: dict = field(default_factory=dict, compare=False, hash=False)
+
+    def __post_init__(self) -> None:
+        for position, entry in enumerate(self.schedule):
+            if not 0 <= entry.layer < len(self.layers):
+                raise ValueError(f"schedule entry {position} names layer {entry.layer}, "
+                                 f"but the model has {len(self.layers)} layers")
+            if entry.cache_of is not None:
+                if not 0 <= entry.cache_of < position:
+                    raise ValueError(f"schedule entry {position} reads the cache of entry "
+                                     f"{entry.cache_of}, which does not run before it")
+                if self.schedule[entry.cache_of].cache_of is not None:
+                    raise ValueError(f"schedule entry {position} reads the cache of entry "
+                                     f"{entry.cache_of}, which owns no cache itself")
+
+
+def sequential_schedule(num_layers: int) -> tuple[ScheduleEntry, ...]:
+    return tuple(ScheduleEntry(layer=i) for i in range(num_layers))
