@@ -115,7 +115,7 @@ class DecoderModel:
     def __init__(self, spec: ModelSpec, runtime: Runtime) -> None:
         self.spec = spec
         self.runtime = runtime
-        self.layers = [build_part("block", layer, runtime, f"{spec.layer_prefix}.{index}.")
+        self.layers = [part_class("block", layer.block)(layer, runtime, f"{spec.layer_prefix}.{index}.")
                        for index, layer in enumerate(spec.layers)]
         self.final_norm = build_part("norm", spec.final_norm, runtime, f"{spec.final_norm_name}.")
         self.cache_plan = plan_cache(spec)

@@ -1,0 +1,329 @@
+"""Each CUDA kernel alone against a plain float64 reference, at sizes other than the engine's."""
+
+import math
+
+import pytest
+import torch
+
+from plain_reference import (
+    plain_apply_rope,
+    plain_attention_core,
+    plain_gelu_tanh,
+    plain_layernorm,
+    plain_rope_tables,
+)
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+def kernels():
+    from matricxon_b200.ops import kernels as k
+
+    return k
+
+
+def status():
+    return torch.zeros(1, dtype=torch.int32, device=DEV)
+
+
+def tol(dtype):
+    return dict(atol=2e-5, rtol=1e-5) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
+
+
+# ------------------------------------------------------------------ embedding
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embed(dtype):
+    k = kernels()
+    table = torch.randn(1000, 96, device=DEV).to(dtype)
+    ids = torch.tensor([0, 999, 17, 17, 500], dtype=torch.int32, device=DEV)
+    out = torch.empty(5, 96, device=DEV)
+    st = status()
+    k.embed(ids, table, out, st)
+    assert torch.equal(out, table[ids.long()].float()) and st.item() == 0
+    bad = torch.tensor([3, 1000, -1], dtype=torch.int32, device=DEV)
+    out = torch.empty(3, 96, device=DEV)
+    k.embed(bad, table, out, st)
+    assert st.item() == 1 and torch.all(out[1:] == 0) and torch.equal(out[0], table[3].float())
+
+
+# ------------------------------------------------------------------ LayerNorm
+@pytest.mark.parametrize("hidden", [16, 100, 3072, 6144])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_layernorm(hidden, dtype):
+    k = kernels()
+    torch.manual_seed(hidden)
+    x = (torch.randn(37, hidden, device=DEV) * 3 + 5)        # a mean far from zero
+    w = 1 + 0.1 * torch.randn(hidden, device=DEV)
+    b = 0.1 * torch.randn(hidden, device=DEV)
+    out = torch.empty(37, hidden, dtype=dtype, device=DEV)
+    k.layernorm(x, w, b, 1e-6, out)
+    ref = plain_layernorm(x.double().cpu(), w.double().cpu(), b.double().cpu(), 1e-6)
+    assert torch.allclose(out.double().cpu(), ref, **tol(dtype))
+    # without bias, and on gathered rows
+    rows = torch.tensor([36, 0, 5], dtype=torch.int32, device=DEV)
+    out = torch.empty(3, hidden, dtype=dtype, device=DEV)
+    k.layernorm(x, w, None, 1e-5, out, rows)
+    ref = plain_layernorm(x.double().cpu()[[36, 0, 5]], w.double().cpu(), None, 1e-5)
+    assert torch.allclose(out.double().cpu(), ref, **tol(dtype))
+
+
+# ------------------------------------------------------------------ FP32-core GEMM
+@pytest.mark.parametrize("m,n,k_dim", [(1, 1000, 96), (7, 130, 352), (65, 64, 17), (200, 3584, 300)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_gemm_simt_all_epilogues(m, n, k_dim, dtype):
+    k = kernels()
+    torch.manual_seed(m * n)
+    a = torch.randn(m, k_dim, device=DEV).to(dtype)
+    w = (torch.randn(n, k_dim, device=DEV) / math.sqrt(k_dim)).to(dtype)
+    bias = torch.randn(n, device=DEV)
+    residual = torch.randn(m, n, device=DEV)
+    acc = a.double().cpu() @ w.double().cpu().T + bias.double().cpu()
+    out = torch.empty(m, n, dtype=dtype, device=DEV)
+    k.gemm_simt(a, w, bias, None, out, k.EPILOGUE_NONE)
+    assert torch.allclose(out.double().cpu(), acc, **tol(dtype))
+    k.gemm_simt(a, w, bias, None, out, k.EPILOGUE_GELU)
+    assert torch.allclose(out.double().cpu(), plain_gelu_tanh(acc), **tol(dtype))
+    out32 = residual.clone()
+    k.gemm_simt(a, w, bias, out32, out32, k.EPILOGUE_RESIDUAL)          # in place
+    assert torch.allclose(out32.double().cpu(), acc + residual.double().cpu(), atol=2e-5, rtol=1e-5)
+    k.gemm_simt(a, w, None, None, out32, k.EPILOGUE_F32)
+    assert torch.allclose(out32.double().cpu(), acc - bias.double().cpu(), atol=2e-5, rtol=1e-5)
+
+
+def test_gemm_simt_row_result_does_not_depend_on_the_batch():
+    k = kernels()
+    a = torch.randn(70, 300, device=DEV)
+    w = torch.randn(130, 300, device=DEV)
+    whole = torch.empty(70, 130, device=DEV)
+    k.gemm_simt(a, w, None, None, whole, k.EPILOGUE_F32)
+    one = torch.empty(1, 130, device=DEV)
+    k.gemm_simt(a[33:34], w, None, None, one, k.EPILOGUE_F32)
+    assert torch.equal(one[0], whole[33])
+
+
+@pytest.mark.parametrize("mode", [0, 1, 2, 3])
+def test_library_product_with_epilogue(mode):
+    from matricxon_b200.ops.linear import linear
+
+    torch.manual_seed(mode)
+    a = torch.randn(33, 96, device=DEV).bfloat16()
+    w = (torch.randn(1000, 96, device=DEV) / 10).bfloat16()
+    bias = torch.randn(1000, device=DEV)
+    residual = torch.randn(33, 1000, device=DEV)
+    acc = a.double().cpu() @ w.double().cpu().T + bias.double().cpu()
+    expected = [acc, plain_gelu_tanh(acc), acc + residual.double().cpu(), acc][mode]
+    out = linear(a, w, bias, mode, residual=residual.clone() if mode == 2 else None, backend="library")
+    assert out.dtype == (torch.float32 if mode >= 2 else torch.bfloat16)
+    assert torch.allclose(out.double().cpu(), expected, atol=3e-2, rtol=2e-2)
+
+
+# ------------------------------------------------------------------ rotary + cache write
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads,kv_heads,dim,rot", [(4, 2, 16, 16), (3, 1, 32, 32), (6, 3, 48, 32), (24, 2, 128, 128)])
+def test_rope_kv_write(dtype, heads, kv_heads, dim, rot):
+    k = kernels()
+    torch.manual_seed(dim)
+    n, page_size, pages = 9, 4, 7
+    theta = 100000.0
+    qkv = torch.randn(n, (heads + 2 * kv_heads) * dim, device=DEV).to(dtype)
+    original = qkv.clone()
+    positions = torch.tensor([0, 1, 2, 3, 500, 4095, 16000, 7, 8], dtype=torch.int32, device=DEV)
+    slots = torch.tensor([5, 6, 7, 0, 27, 13, 12, 1, 2], dtype=torch.int32, device=DEV)
+    inv_freq = (1.0 / (theta ** (torch.arange(0, rot, 2, dtype=torch.float32) / rot))).to(DEV)
+    cache = torch.full((pages, 2, kv_heads, page_size, dim), float("nan"), dtype=dtype, device=DEV)
+    st = status()
+    k.rope_kv_write(qkv, positions, inv_freq, slots, cache, heads, kv_heads, dim, rot, page_size, st)
+    assert st.item() == 0
+
+    src = original.double().cpu()
+    q = src[:, : heads * dim].view(n, heads, dim).transpose(0, 1)
+    kk = src[:, heads * dim: (heads + kv_heads) * dim].view(n, kv_heads, dim).transpose(0, 1)
+    vv = src[:, (heads + kv_heads) * dim:].view(n, kv_heads, dim).transpose(0, 1)
+    cos, sin = plain_rope_tables(positions.cpu(), rot, theta)
+
+    def rotate(x):
+        out = x.clone()
+        out[..., :rot] = plain_apply_rope(x[..., :rot], cos, sin)
+        return out
+
+    q_ref, k_ref = rotate(q), rotate(kk)
+    got_q = qkv[:, : heads * dim].double().cpu().view(n, heads, dim).transpose(0, 1)
+    assert torch.allclose(got_q, q_ref, **tol(dtype))
+    # v part of the row is untouched, k part of the row is untouched (only the cache gets rotated k)
+    assert torch.equal(qkv[:, heads * dim:], original[:, heads * dim:])
+    for t in range(n):
+        page, off = divmod(int(slots[t]), page_size)
+        assert torch.allclose(cache[page, 0, :, off].double().cpu(), k_ref[:, t], **tol(dtype))
+        assert torch.equal(cache[page, 1, :, off].double().cpu(), vv[:, t])
+    written = torch.zeros(pages * page_size, dtype=torch.bool)
+    written[slots.cpu().long()] = True
+    flat = cache.permute(0, 3, 1, 2, 4).reshape(pages * page_size, -1)
+    assert torch.isnan(flat[~written]).all() and not torch.isnan(flat[written]).any()
+
+
+def test_rope_bad_slot_sets_status_and_padding_slot_is_silent():
+    k = kernels()
+    qkv = torch.randn(3, 4 * 16, device=DEV)
+    positions = torch.zeros(3, dtype=torch.int32, device=DEV)
+    inv_freq = torch.ones(8, device=DEV)
+    cache = torch.zeros(2, 2, 1, 4, 16, device=DEV)
+    st = status()
+    k.rope_kv_write(qkv, positions, inv_freq, torch.tensor([0, -1, 1], dtype=torch.int32, device=DEV),
+                    cache, 2, 1, 16, 16, 4, st)
+    assert st.item() == 0
+    k.rope_kv_write(qkv, positions, inv_freq, torch.tensor([0, 8, 1], dtype=torch.int32, device=DEV),
+                    cache, 2, 1, 16, 16, 4, st)
+    assert st.item() == 2
+
+
+# ------------------------------------------------------------------ paged attention
+def paged_case(dtype, heads, kv_heads, dim, page_size, seq_lens, q_lens, seed, scale_up=None):
+    """Random K/V for several sequences scattered over shuffled pages; the last q_len positions
+    of each sequence are the queries. Returns kernel inputs and dense per-sequence tensors."""
+    generator = torch.Generator().manual_seed(seed)
+    n_seq = len(seq_lens)
+    pages_per_seq = [(length + page_size - 1) // page_size for length in seq_lens]
+    total_pages = sum(pages_per_seq) + 3
+    order = torch.randperm(total_pages, generator=generator).tolist()
+    width = max(pages_per_seq) + 1
+    tables = torch.full((n_seq, width), -1, dtype=torch.int32)
+    cache = torch.full((total_pages, 2, kv_heads, page_size, dim), float("nan"))
+    dense = []
+    cursor = 0
+    for s, length in enumerate(seq_lens):
+        ks = torch.randn(kv_heads, length, dim, generator=generator)
+        vs = torch.randn(kv_heads, length, dim, generator=generator)
+        qs = torch.randn(heads, q_lens[s], dim, generator=generator)
+        if scale_up is not None:
+            scale_up(s, qs, ks, vs)
+        ks, vs, qs = ks.to(dtype).float(), vs.to(dtype).float(), qs.to(dtype).float()
+        dense.append((qs, ks, vs))
+        for lp in range(pages_per_seq[s]):
+            page = order[cursor]
+            cursor += 1
+            tables[s, lp] = page
+            lo, hi = lp * page_size, min(length, (lp + 1) * page_size)
+            cache[page, 0, :, : hi - lo] = ks[:, lo:hi]
+            cache[page, 1, :, : hi - lo] = vs[:, lo:hi]
+    q_rows, tok_seq, positions = [], [], []
+    for s, (qs, _, _) in enumerate(dense):
+        for i in range(q_lens[s]):
+            q_rows.append(qs[:, i].reshape(-1))
+            tok_seq.append(s)
+            positions.append(seq_lens[s] - q_lens[s] + i)
+    q = torch.stack(q_rows)
+    return (q.to(dtype).to(DEV), cache.to(dtype).to(DEV), tables.to(DEV),
+            torch.tensor(tok_seq, dtype=torch.int32, device=DEV),
+            torch.tensor(positions, dtype=torch.int32, device=DEV), dense)
+
+
+def reference_attention(dense, q_lens, seq_lens, scale, window):
+    rows = []
+    for (qs, ks, vs), q_len, length in zip(dense, q_lens, seq_lens):
+        out = plain_attention_core(qs.double(), ks.double(), vs.double(), scale, window,
+                                   offset=length - q_len)
+        rows.append(out.transpose(0, 1).reshape(q_len, -1))
+    return torch.cat(rows)
+
+
+def run_attention(k, q, cache, tables, tok_seq, positions, heads, kv_heads, dim, window, scale, n_splits):
+    n = q.shape[0]
+    out = torch.full((n, heads * dim), float("nan"), dtype=q.dtype, device=DEV)
+    st = status()
+    scratch = None
+    if n_splits > 1:
+        need = k.attention_scratch_bytes(n, heads, dim, n_splits)
+        scratch = torch.full((need // 4,), float("nan"), device=DEV)
+    k.paged_attention(q, q.stride(0), cache, tables, tok_seq, positions, n, heads, kv_heads, dim,
+                      window, scale, out, st, n_splits=n_splits, scratch=scratch)
+    return out, st.item()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads,kv_heads,dim,page_size", [
+    (4, 2, 16, 16), (3, 1, 32, 16), (24, 2, 128, 16), (5, 5, 48, 8), (40, 2, 64, 32), (2, 1, 256, 16)])
+@pytest.mark.parametrize("window", [None, 24, 100])
+def test_paged_attention_mixed_batch(dtype, heads, kv_heads, dim, page_size, window):
+    k = kernels()
+    seq_lens, q_lens = [1, 37, 130, 64, 301], [1, 37, 1, 5, 2]
+    scale = dim ** -0.5
+    q, cache, tables, tok_seq, positions, dense = paged_case(
+        dtype, heads, kv_heads, dim, page_size, seq_lens, q_lens, seed=dim + heads)
+    ref = reference_attention(dense, q_lens, seq_lens, scale, window)
+    for n_splits in (1, 3, 16):
+        out, st = run_attention(k, q, cache, tables, tok_seq, positions, heads, kv_heads, dim,
+                                window, scale, n_splits)
+        assert st == 0
+        assert torch.allclose(out.double().cpu(), ref, **tol(dtype)), (n_splits, (out.double().cpu() - ref).abs().max())
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("edge", ["window_first_visible", "just_outside_window", "page_last_slot",
+                                  "page_first_slot", "self", "far_key_full_attention"])
+def test_paged_attention_one_key_stands_out(dtype, edge):
+    """One key gets a score far above the rest, so the output is (almost) that key's value if
+    it is visible and unchanged by it if it is not: a wrong mask edge or page offset shows."""
+    k = kernels()
+    heads, kv_heads, dim, page_size = 4, 2, 32, 16
+    length, window = 400, 96
+    p = length - 1
+    target = {"window_first_visible": p - window + 1, "just_outside_window": p - window,
+              "page_last_slot": 367, "page_first_slot": 368, "self": p,
+              "far_key_full_attention": 3}[edge]
+    use_window = None if edge == "far_key_full_attention" else window
+
+    def scale_up(s, qs, ks, vs):
+        ks[:, target] = qs[0::2, 0] * 4.0 if kv_heads == 2 else qs[0, 0] * 4.0   # aligned with the query
+        qs *= 3.0
+
+    scale = dim ** -0.5
+    q, cache, tables, tok_seq, positions, dense = paged_case(
+        dtype, heads, kv_heads, dim, page_size, [length], [1], seed=7, scale_up=scale_up)
+    ref = reference_attention(dense, [1], [length], scale, use_window)
+    for n_splits in (1, 4):
+        out, st = run_attention(k, q, cache, tables, tok_seq, positions, heads, kv_heads, dim,
+                                use_window, scale, n_splits)
+        assert st == 0
+        assert torch.allclose(out.double().cpu(), ref, **tol(dtype))
+    qs, ks, vs = dense[0]
+    head0 = ref[0, :dim]
+    if edge == "just_outside_window":
+        assert (head0 - vs[0, target].double()).abs().max() > 0.3
+    else:
+        assert (head0 - vs[0, target].double()).abs().max() < 0.05
+
+
+def test_paged_attention_missing_page_sets_status():
+    k = kernels()
+    q, cache, tables, tok_seq, positions, _ = paged_case(torch.float32, 2, 1, 16, 16, [40], [1], seed=1)
+    tables[0, 1] = -1
+    _, st = run_attention(k, q, cache, tables, tok_seq, positions, 2, 1, 16, None, 0.25, 1)
+    assert st == 4
+
+
+def test_paged_attention_padding_rows_are_zero():
+    k = kernels()
+    q, cache, tables, tok_seq, positions, dense = paged_case(torch.float32, 2, 1, 16, 16, [40, 9], [1, 1], seed=2)
+    tok_seq[1] = -1
+    for n_splits in (1, 2):
+        out, st = run_attention(k, q, cache, tables, tok_seq, positions, 2, 1, 16, None, 0.25, n_splits)
+        assert st == 0 and torch.all(out[1] == 0)
+        ref = reference_attention(dense[:1], [1], [40], 0.25, None)
+        assert torch.allclose(out[:1].double().cpu(), ref, atol=2e-5)
+
+
+def test_kernels_refuse_unsupported_sizes():
+    from matricxon_b200.ops.library import KernelLibraryError
+
+    k = kernels()
+    q = torch.zeros(1, 2 * 24, device=DEV)
+    cache = torch.zeros(1, 2, 1, 16, 24, device=DEV)
+    tables = torch.zeros(1, 1, dtype=torch.int32, device=DEV)
+    zeros = torch.zeros(1, dtype=torch.int32, device=DEV)
+    with pytest.raises(KernelLibraryError, match="head_dim 24"):
+        k.paged_attention(q, 48, cache, tables, zeros, zeros, 1, 2, 1, 24, None, 1.0,
+                          torch.zeros(1, 48, device=DEV), status())
+    with pytest.raises(KernelLibraryError, match="CUDA tensor"):
+        k.layernorm(torch.zeros(2, 8), torch.ones(8), None, 1e-5, torch.zeros(2, 8))
