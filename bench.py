@@ -1,0 +1,351 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the engine on one B200, StarCoder2-3B layer sizes.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+Prints ONE JSON line. A "step" is one decode step of a batch of 8 requests at the context
+length of the benchmark configuration (random bf16 weights, random token ids). ``value`` is
+decoded tokens per second timed on the device with CUDA events around K steps; ``e2e`` is the
+same through the Python entry point (``ChatEngine.step``: host token ids in, sampled ids back
+on the host each step). ``prefill`` is one 2,048-token prompt in one step; ``roofline``
+relates the decode step's necessary bytes (every weight once plus the live cache) to its
+time; ``points`` adds decoding at batch 1 and 64. Between timed iterations the working set
+(6 GB of weights) is larger than L2, so nothing is flushed explicitly.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+STARCODER2_3B = {
+    "model_type": "starcoder2", "architectures": ["Starcoder2ForCausalLM"],
+    "num_hidden_layers": 30, "hidden_size": 3072, "num_attention_heads": 24,
+    "num_key_value_heads": 2, "head_dim": 128, "intermediate_size": 12288, "vocab_size": 49152,
+    "rope_theta": 999999.4420358813, "sliding_window": 4096, "max_position_embeddings": 16384,
+    "norm_epsilon": 1e-5, "use_bias": True, "tie_word_embeddings": True,
+    "hidden_act": "gelu_pytorch_tanh",
+}
+CONTEXT = 4096           # tokens per request in the benchmark configuration
+PREFILL_TOKENS = 2048
+PAGE_SIZE = 16
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def load_peaks() -> tuple[dict, str]:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        try:
+            with open(path) as handle:
+                raw = json.load(handle)
+            peaks = dict(FALLBACK_PEAKS)
+            for key in peaks:
+                if isinstance(raw.get(key), (int, float)):
+                    peaks[key] = float(raw[key])
+            return peaks, "measured"
+        except (OSError, ValueError):
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self) -> None:
+        self.rows: list[list[str]] = []
+        self.proc = None
+
+    def start(self) -> None:
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        threading.Thread(target=self._read, daemon=True).start()
+
+    def _read(self) -> None:
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) >= 6:
+                self.rows.append(parts)
+
+    def mark(self) -> int:
+        return len(self.rows)
+
+    def stop(self) -> None:
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self, begin: int = 0, end: int | None = None) -> dict:
+        rows = self.rows[begin:end] or self.rows
+        clocks = sorted(int(r[0]) for r in rows if r[0].isdigit())
+        if not clocks:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no nvidia-smi samples"]}
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [name for i, name in enumerate(names) if any(r[2 + i].lower() == "active" for r in rows)]
+        return {"sm_mhz": clocks[len(clocks) // 2], "sm_max_mhz": int(rows[0][1]) if rows[0][1].isdigit() else None,
+                "reasons": reasons, "samples": len(clocks)}
+
+
+def reference_arm(args) -> int:
+    """The unmodified reference through its own API, if it is installed under baseline/_ref."""
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_dir, "app")):
+        print(json.dumps({"impl": "reference",
+                          "unavailable": "nesmind/matricxon is not installed under baseline/_ref "
+                                         "(pip install --no-index of /root/reference: see DESIGN.md)"}))
+        return 0
+    from baseline.reference_arm import run_reference     # imported only when the install exists
+
+    print(json.dumps(run_reference(args, STARCODER2_3B, CONTEXT)))
+    return 0
+
+
+def build_engine(config_dict: dict, n_layers: int, max_active: int, cache_tokens: int,
+                 max_batched_tokens: int):
+    import torch
+
+    from matricxon_b200 import ChatEngine
+    from matricxon_b200.config.registry import config_from_dict
+    from matricxon_b200.engine.core import build_model
+    from matricxon_b200.weights.random_init import RandomInit, RandomSource, weight_specs_for
+
+    raw = dict(config_dict)
+    raw["num_hidden_layers"] = n_layers
+    config = config_from_dict(raw)
+    source = RandomSource(weight_specs_for(config), seed=0,
+                          init=RandomInit(weight_std=0.02, bias_std=0.02), device="cuda:0",
+                          store_dtype=torch.bfloat16)
+    model = build_model(config, source, "bfloat16", "cuda:0", PAGE_SIZE)
+    engine = ChatEngine(model, max_cache_tokens=cache_tokens, max_active=max_active,
+                        max_batched_tokens=max_batched_tokens, prefill_chunk=PREFILL_TOKENS,
+                        max_model_len=CONTEXT)
+    return config, model, engine
+
+
+def fill_cache(engine, batch: int, context: int, vocab: int):
+    """Gives ``batch`` requests ``context`` cached tokens each by running real prefill steps."""
+    import torch
+
+    from matricxon_b200.engine.step import StepEntry
+
+    generator = torch.Generator().manual_seed(1)
+    ids = []
+    for b in range(batch):
+        rid = f"bench-{b}"
+        engine.core.cache.add_request(rid)
+        ids.append(rid)
+        done = 0
+        while done < context:
+            n = min(PREFILL_TOKENS, context - done)
+            tokens = torch.randint(0, vocab, (n,), generator=generator).tolist()
+            engine.core.runner.run([StepEntry(rid, tokens, [])])
+            done += n
+    engine.core.runner.check_status()
+    return ids
+
+
+def time_decode(engine, ids, vocab, steps, warmup):
+    """K decode steps of the whole batch, timed on the device. Every step appends one token
+    per request, so the context grows from ``context`` by K."""
+    import torch
+
+    from matricxon_b200.engine.step import StepEntry
+
+    generator = torch.Generator().manual_seed(2)
+    def one_step():
+        tokens = torch.randint(0, vocab, (len(ids),), generator=generator).tolist()
+        return engine.core.runner.run([StepEntry(rid, [tok], [0]) for rid, tok in zip(ids, tokens)])
+    for _ in range(warmup):
+        one_step()
+    torch.cuda.synchronize()
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    begin.record()
+    for _ in range(steps):
+        one_step()
+    end.record()
+    torch.cuda.synchronize()
+    engine.core.runner.check_status()
+    return begin.elapsed_time(end) / steps
+
+
+def decode_bytes(config, n_layers, batch, context, model) -> float:
+    """Bytes one decode step must read: every weight once, and the cache of the live requests."""
+    h, i, v = config.hidden_size, config.intermediate_size, config.vocab_size
+    q, kv = config.num_attention_heads * config.head_dim, config.num_key_value_heads * config.head_dim
+    per_layer = (h * (q + 2 * kv) + q * h + 2 * h * i) * 2 + ((q + 2 * kv) + h + i + h + 4 * h) * 4
+    head = v * h * 2
+    window = config.sliding_window or context
+    cache = batch * min(context, window) * n_layers * 2 * kv * 2
+    return n_layers * per_layer + head + cache
+
+
+def prefill_flops(config, n_layers, tokens) -> float:
+    h, i, v = config.hidden_size, config.intermediate_size, config.vocab_size
+    q, kv = config.num_attention_heads * config.head_dim, config.num_key_value_heads * config.head_dim
+    gemm = 2.0 * tokens * (h * (q + 2 * kv) + q * h + 2 * h * i)
+    attention = 2.0 * 2.0 * q * tokens * (tokens + 1) / 2.0          # causal QK^T and PV
+    return n_layers * (gemm + attention) + 2.0 * v * h               # one row of logits
+
+
+def main() -> int:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=64)
+    parser.add_argument("--warmup", type=int, default=8)
+    parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    parser.add_argument("--layers", type=int, default=STARCODER2_3B["num_hidden_layers"])
+    parser.add_argument("--batch", type=int, default=8)
+    parser.add_argument("--context", type=int, default=CONTEXT - 1024,
+                        help="cached tokens per request when decode timing starts")
+    parser.add_argument("--skip-points", action="store_true")
+    args = parser.parse_args()
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    if args.impl == "reference":
+        return reference_arm(args)
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import torch
+
+    from matricxon_b200 import GenerationRequest, SamplingConfig
+
+    if not torch.cuda.is_available():
+        print("bench.py: no CUDA device")
+        return 1
+    peaks, peak_source = load_peaks()
+    n_layers = args.layers
+    clocks = ClockSampler()
+    clocks.start()
+
+    # ---- the headline: decode at batch 8
+    batch = args.batch
+    cache_tokens = 64 * CONTEXT
+    config, model, engine = build_engine(STARCODER2_3B, n_layers, 64, cache_tokens, 8192)
+    vocab = config.vocab_size
+    context = min(args.context, CONTEXT - args.steps - args.warmup - 1)
+    ids = fill_cache(engine, batch, context, vocab)
+    mark_a = clocks.mark()
+    ms_step = time_decode(engine, ids, vocab, args.steps, args.warmup)
+    mark_b = clocks.mark()
+    mean_context = context + args.warmup + args.steps / 2
+    necessary = decode_bytes(config, n_layers, batch, mean_context, model)
+    achieved_gbs = necessary / (ms_step * 1e-3) / 1e9
+    launches = None
+    for rid in ids:
+        engine.core.cache.free_request(rid)
+
+    # ---- other batch sizes
+    points = {}
+    if not args.skip_points:
+        for b in (1, 64):
+            ids_b = fill_cache(engine, b, context, vocab)
+            ms = time_decode(engine, ids_b, vocab, max(8, args.steps // 2), args.warmup)
+            points[f"decode_b{b}"] = round(b / (ms * 1e-3), 1)
+            points[f"decode_b{b}_hbm_frac"] = round(
+                decode_bytes(config, n_layers, b, mean_context, model) / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 4)
+            for rid in ids_b:
+                engine.core.cache.free_request(rid)
+
+    # ---- prefill of 2,048 tokens in one step
+    from matricxon_b200.engine.step import StepEntry
+
+    generator = torch.Generator().manual_seed(3)
+    prompt = torch.randint(0, vocab, (PREFILL_TOKENS,), generator=generator).tolist()
+    prefill_ms = []
+    for rep in range(5):
+        engine.core.cache.add_request("prefill")
+        torch.cuda.synchronize()
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        engine.core.runner.run([StepEntry("prefill", prompt, [PREFILL_TOKENS - 1])])
+        end.record()
+        torch.cuda.synchronize()
+        engine.core.cache.free_request("prefill")
+        if rep >= 2:
+            prefill_ms.append(begin.elapsed_time(end))
+    pf_ms = sorted(prefill_ms)[len(prefill_ms) // 2]
+    pf_flops = prefill_flops(config, n_layers, PREFILL_TOKENS)
+    pf_frac = pf_flops / (pf_ms * 1e-3) / (peaks["bf16_tflops"] * 1e12)
+
+    # ---- end to end through the entry point: host ids in, sampled ids out, every step
+    sampling = SamplingConfig(temperature=0.0, num_predict=args.steps + args.warmup, num_ctx=CONTEXT)
+    e2e_context = context
+    prompts = [torch.randint(0, vocab, (e2e_context,), generator=generator).tolist() for _ in range(batch)]
+    rids = [engine.add_request(p, sampling) for p in prompts]
+    produced = 0
+    while produced < batch * args.warmup:                       # prefill + warm-up decode steps
+        produced += len(engine.step())
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    tokens_out = 0
+    e2e_steps = 0
+    while engine.has_unfinished():
+        tokens_out += len(engine.step())
+        e2e_steps += 1
+    torch.cuda.synchronize()
+    e2e_seconds = time.perf_counter() - t0
+    for rid in rids:
+        engine.result(rid)
+    e2e_value = tokens_out / e2e_seconds if e2e_seconds > 0 else 0.0
+    h2d_bytes = engine.core.runner.last_upload_bytes
+    d2h_bytes = batch * 4 + 4
+
+    clocks.stop()
+    launches = engine.core.runner.launches_per_step
+    value = batch / (ms_step * 1e-3)
+    record = {
+        "metric": "decode tok/s @ batch 8 (StarCoder2-3B bf16, one B200)",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(ms_step, 4), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: seeded random weights N(0,0.02), uniform random token ids",
+        "impl": "ours",
+        "config": {
+            "model": "StarCoder2-3B layer sizes", "layers": n_layers, "layers_in_model": 30,
+            "hidden": config.hidden_size, "heads": config.num_attention_heads,
+            "kv_heads": config.num_key_value_heads, "head_dim": config.head_dim,
+            "intermediate": config.intermediate_size, "vocab": config.vocab_size,
+            "window": config.sliding_window, "tied": config.tie_word_embeddings,
+            "bias": config.use_bias, "global_batch": batch, "seq_len": CONTEXT,
+            "decode_context": int(mean_context), "page_size": PAGE_SIZE,
+            "cache_pool_tokens": cache_tokens, "parallelism": "single GPU",
+            "l2": "working set (weights) exceeds L2; no flush", "peaks": peak_source,
+        },
+        "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "steps": e2e_steps,
+                "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes},
+        "gpu_launches": launches * args.steps if launches else None,
+        "prefill": {"value": round(PREFILL_TOKENS / (pf_ms * 1e-3), 1), "tokens": PREFILL_TOKENS,
+                    "ms": round(pf_ms, 3), "frac": round(pf_frac, 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved_gbs, 1), "peak": peaks["hbm_gbs"],
+                     "unit": "GB/s", "frac": round(achieved_gbs / peaks["hbm_gbs"], 4)},
+        "points": points,
+        "clocks": clocks.summary(mark_a, mark_b),
+    }
+    print(json.dumps(record))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,117 @@
+"""The Python entry point: prompts in, generated token ids out.
+
+Named and shaped after the reference's ``ChatEngine`` (app/runtime/chat_engine.py:17-210):
+``ChatEngine(model, eos_token_ids)``, ``generate(GenerationRequest) -> GenerationResult``,
+``stream(request)`` yielding token ids. Where the reference runs one request per call and
+leaves batching to its worker thread (app/models/worker.py:148-183), this engine owns the
+scheduler: ``generate_batch`` and the ``add_request`` / ``step`` pair run many requests
+through shared steps, prompt portions beside decode tokens.
+"""
+
+from __future__ import annotations
+
+import itertools
+from pathlib import Path
+from typing import Iterable, Iterator
+
+import torch
+
+from matricxon_b200.engine.core import EngineCore, load_model
+from matricxon_b200.engine.request import GenerationRequest, GenerationResult, as_token_list
+from matricxon_b200.engine.scheduler import FINISHED, Scheduler, SchedulerConfig, Sequence
+from matricxon_b200.engine.step import StepEntry
+from matricxon_b200.sampling.config import SamplingConfig
+from matricxon_b200.sampling.sampler import BatchSampler
+
+
+class ChatEngine:
+    """``model`` is a model folder (config.json + model.safetensors) or a model built by
+    ``matricxon_b200.engine.core`` (for instance from random weights in memory)."""
+
+    def __init__(self, model, eos_token_ids: Iterable[int] = (), dtype: str = "bfloat16",
+                 device: str = "cuda:0", max_cache_tokens: int | None = None, max_active: int = 8,
+                 max_batched_tokens: int = 2048, prefill_chunk: int = 256,
+                 max_model_len: int | None = None, page_size: int = 16,
+                 gemm_backend: str = "auto") -> None:
+        if isinstance(model, (str, Path)):
+            _, model = load_model(model, dtype=dtype, device=device, page_size=page_size,
+                                  gemm_backend=gemm_backend)
+        self.model = model
+        limit = max_model_len or model.spec.max_position_embeddings
+        if max_cache_tokens is None:
+            max_cache_tokens = max_active * limit
+        self.core = EngineCore(model, max_cache_tokens=max_cache_tokens, max_requests=max_active,
+                               max_step_tokens=max(max_batched_tokens, 1))
+        self.scheduler = Scheduler(
+            self.core.cache,
+            SchedulerConfig(max_num_seqs=max_active, max_num_batched_tokens=max_batched_tokens,
+                            prefill_chunk=prefill_chunk, max_model_len=limit),
+            set(eos_token_ids))
+        self.sampler = BatchSampler(model.runtime.device, model.spec.vocab_size)
+        self._ids = itertools.count()
+        self.steps = 0
+
+    # ------------------------------------------------------------------ low level
+    def add_request(self, input_ids, sampling: SamplingConfig | None = None,
+                    request_id: str | None = None) -> str:
+        request_id = request_id if request_id is not None else f"req-{next(self._ids)}"
+        self.scheduler.add(request_id, as_token_list(input_ids), sampling or SamplingConfig())
+        return request_id
+
+    def cancel(self, request_id: str) -> bool:
+        return self.scheduler.cancel(request_id)
+
+    def has_unfinished(self) -> bool:
+        return self.scheduler.has_work()
+
+    def step(self) -> list[tuple[str, int, bool]]:
+        """One scheduled step. Returns (request id, new token, finished) for every request
+        that produced a token."""
+        plan = self.scheduler.schedule()
+        if not plan.entries:
+            return []
+        entries = []
+        samplers = []
+        for planned in plan.entries:
+            tokens = planned.sequence.token_slice(planned.start, planned.count)
+            samples = planned.samples
+            entries.append(StepEntry(planned.sequence.request_id, tokens,
+                                     [planned.count - 1] if samples else []))
+            if samples:
+                samplers.append(planned.sequence.sampler)
+        logits = self.core.runner.run(entries)
+        sampled = self.sampler.sample(logits, samplers) if samplers else []
+        self.core.runner.check_status()
+        produced = self.scheduler.step_done(plan, sampled)
+        self.steps += 1
+        return [(seq.request_id, token, seq.status == FINISHED) for seq, token in produced]
+
+    def result(self, request_id: str) -> GenerationResult:
+        sequence: Sequence = self.scheduler.finished.pop(request_id)
+        return GenerationResult(token_ids=list(sequence.outputs),
+                                finish_reason=sequence.finish_reason)
+
+    # ------------------------------------------------------------------ the reference's calls
+    def stream(self, request: GenerationRequest) -> Iterator[int]:
+        """Yields one generated token id at a time (app/runtime/chat_engine.py:83-107)."""
+        request_id = self.add_request(request.input_ids, request.sampling)
+        try:
+            while request_id not in self.scheduler.finished:
+                for rid, token, _ in self.step():
+                    if rid == request_id:
+                        yield token
+        finally:
+            if request_id not in self.scheduler.finished:
+                self.cancel(request_id)
+            self.scheduler.finished.pop(request_id, None)
+
+    def generate(self, request: GenerationRequest) -> GenerationResult:
+        """Runs one request to its end (app/runtime/chat_engine.py:207-210)."""
+        return self.generate_batch([request])[0]
+
+    def generate_batch(self, requests: list[GenerationRequest]) -> list[GenerationResult]:
+        """Runs the requests together through shared steps; results in the order given."""
+        ids = [self.add_request(r.input_ids, r.sampling) for r in requests]
+        while any(rid not in self.scheduler.finished for rid in ids):
+            self.step()
+        return [self.result(rid) for rid in ids]

@@ -1,0 +1,273 @@
+"""Which requests run in the next step, with how many tokens each.
+
+The reference's worker admits replies in arrival order up to ``max_active``
+(app/models/worker.py:164-172), advances every prefilling reply by one 256-token piece per
+round and then runs one batched decode (worker.py:177-179; app/runtime/chat_engine.py:36,
+158-182), finishes on an EOS token (which is emitted) or after ``num_predict`` tokens bounded
+by ``num_ctx`` (chat_engine.py:153-154,191-196), and can never run out of cache because each
+request's cache is allocated whole up front (app/runtime/kv_cache.py:31-38).
+
+Here one step holds decode tokens and prompt portions together, under a token budget:
+  1. every running request that has one token left to compute (a decode) gets it first;
+  2. the rest of the budget goes to prompt portions, running requests before waiting ones,
+     in arrival order, each at most ``prefill_chunk`` tokens and cut to the remaining budget;
+  3. waiting requests are admitted while fewer than ``max_num_seqs`` run and pages are free.
+When pages run out: portions are skipped first (nothing is admitted or advanced); if a decode
+token cannot get its page, the most recently admitted running request is preempted: its pages
+are freed, it keeps its sampled tokens and returns to the front of the queue, and is later
+recomputed as one prompt of (prompt + sampled tokens). Its random stream is a function of
+(seed, token index), so the tokens it goes on to sample are unchanged. A request that cannot
+fit in the empty pool is refused when it is added.
+"""
+
+from __future__ import annotations
+
+from collections import deque
+from dataclasses import dataclass, field
+
+from matricxon_b200.cache.manager import CacheManager
+from matricxon_b200.sampling.config import SamplingConfig
+from matricxon_b200.sampling.sampler import RequestSampler
+
+WAITING, RUNNING, FINISHED = "waiting", "running", "finished"
+
+
+class RequestRefused(ValueError):
+    """A request that can never run under the engine's limits."""
+
+
+@dataclass
+class SchedulerConfig:
+    max_num_seqs: int = 8                  # the reference's max_active default (app/config.py:87)
+    max_num_batched_tokens: int = 2048
+    prefill_chunk: int = 256               # the reference's PLAIN_PREFILL_CHUNK
+    max_model_len: int = 4096
+
+
+@dataclass(eq=False)
+class Sequence:
+    request_id: str
+    prompt: list[int]
+    sampling: SamplingConfig
+    max_new_tokens: int
+    sampler: RequestSampler
+    outputs: list[int] = field(default_factory=list)
+    computed: int = 0                      # tokens of prompt + outputs already in the cache
+    status: str = WAITING
+    finish_reason: str | None = None
+    preemptions: int = 0
+    order: int = 0                         # admission order among running requests
+
+    @property
+    def tokens(self) -> list[int]:
+        return self.prompt + self.outputs
+
+    def token_slice(self, start: int, count: int) -> list[int]:
+        """Tokens [start, start + count) of prompt + outputs without joining the two lists."""
+        n_prompt = len(self.prompt)
+        if start >= n_prompt:
+            return self.outputs[start - n_prompt:start - n_prompt + count]
+        if start + count <= n_prompt:
+            return self.prompt[start:start + count]
+        return self.prompt[start:] + self.outputs[:start + count - n_prompt]
+
+    @property
+    def remaining(self) -> int:
+        return len(self.prompt) + len(self.outputs) - self.computed
+
+
+@dataclass
+class PlannedEntry:
+    sequence: Sequence
+    start: int
+    count: int
+
+    @property
+    def samples(self) -> bool:
+        """The portion reaches the request's last token: its logits choose the next one."""
+        seq = self.sequence
+        return self.start + self.count == len(seq.prompt) + len(seq.outputs)
+
+
+@dataclass
+class StepPlan:
+    entries: list[PlannedEntry] = field(default_factory=list)
+    preempted: list[Sequence] = field(default_factory=list)
+
+    @property
+    def num_tokens(self) -> int:
+        return sum(entry.count for entry in self.entries)
+
+
+class Scheduler:
+    def __init__(self, cache: CacheManager, config: SchedulerConfig,
+                 eos_token_ids: set[int] | None = None) -> None:
+        self.cache = cache
+        self.config = config
+        self.eos_token_ids = set(eos_token_ids or ())
+        self.waiting: deque[Sequence] = deque()
+        self.running: list[Sequence] = []
+        self.finished: dict[str, Sequence] = {}
+        self._admitted = 0
+        self.num_preemptions = 0
+
+    # ------------------------------------------------------------------ requests
+    def add(self, request_id: str, prompt: list[int], sampling: SamplingConfig) -> Sequence:
+        if not prompt:
+            raise RequestRefused("a request needs at least one prompt token")
+        limit = min(sampling.num_ctx, self.config.max_model_len)
+        if len(prompt) > limit:
+            raise RequestRefused(f"prompt of {len(prompt)} tokens exceeds the context of {limit}")
+        room = max(limit - len(prompt), 0)
+        max_new = room if sampling.num_predict < 0 else min(sampling.num_predict, room)
+        most_pages = (len(prompt) + max_new + self.cache.page_size - 1) // self.cache.page_size
+        for group, pool in enumerate(self.cache.pools):
+            if self.cache.rules[group].window is None and most_pages > pool.num_pages:
+                raise RequestRefused(
+                    f"request needs {most_pages} pages in group {group}, the pool has {pool.num_pages}")
+        sequence = Sequence(request_id, list(prompt), sampling, max_new, RequestSampler(sampling))
+        if max_new == 0:
+            sequence.status, sequence.finish_reason = FINISHED, "length"
+            self.finished[request_id] = sequence
+            return sequence
+        self.waiting.append(sequence)
+        return sequence
+
+    def cancel(self, request_id: str) -> bool:
+        """Stops a request between steps; False if it is neither waiting nor running."""
+        for sequence in list(self.waiting):
+            if sequence.request_id == request_id:
+                self.waiting.remove(sequence)
+                self._finish(sequence, "cancelled")
+                return True
+        for sequence in self.running:
+            if sequence.request_id == request_id:
+                self._finish(sequence, "cancelled")
+                return True
+        return False
+
+    def has_work(self) -> bool:
+        return bool(self.waiting or self.running)
+
+    # ------------------------------------------------------------------ planning
+    def _fits(self, sequence: Sequence, count: int, planned: list[int]) -> bool:
+        needed = self.cache.pages_needed(sequence.request_id, count)
+        free = self.cache.free_pages()
+        return all(n + p <= f for n, p, f in zip(needed, planned, free))
+
+    def _plan(self, plan: StepPlan, sequence: Sequence, count: int, planned: list[int]) -> None:
+        for group, n in enumerate(self.cache.pages_needed(sequence.request_id, count)):
+            planned[group] += n
+        plan.entries.append(PlannedEntry(sequence, sequence.computed, count))
+
+    def _preempt(self, sequence: Sequence, plan: StepPlan) -> None:
+        self.cache.free_request(sequence.request_id)
+        self.running.remove(sequence)
+        sequence.status = WAITING
+        sequence.computed = 0
+        sequence.preemptions += 1
+        self.num_preemptions += 1
+        self.waiting.appendleft(sequence)
+        plan.preempted.append(sequence)
+
+    def schedule(self) -> StepPlan:
+        plan = StepPlan()
+        planned = [0] * len(self.cache.pools)
+        budget = self.config.max_num_batched_tokens
+
+        # 1. decode tokens, oldest request first; preempt the youngest when a page is missing
+        decodes = [s for s in self.running if s.remaining == 1]
+        for sequence in decodes:
+            if sequence.status != RUNNING or budget <= 0:
+                continue
+            while not self._fits(sequence, 1, planned):
+                victims = [s for s in self.running if s is not sequence
+                           and all(e.sequence is not s for e in plan.entries)]
+                if not victims:
+                    break
+                self._preempt(max(victims, key=lambda s: s.order), plan)
+            if sequence.status == RUNNING and self._fits(sequence, 1, planned):
+                self._plan(plan, sequence, 1, planned)
+                budget -= 1
+            elif sequence.status == RUNNING and len(self.running) == 1 and not plan.entries:
+                # alone and still no page: the request has reached what the pool can hold
+                self._finish(sequence, "length")
+
+        # 2. prompt portions of running requests, in admission order
+        def portion(sequence: Sequence) -> int:
+            count = min(self.config.prefill_chunk, sequence.remaining, budget)
+            while count > 0 and not self._fits(sequence, count, planned):
+                count //= 2                    # a shorter portion may still fit the free pages
+            return count
+
+        blocked = False
+        for sequence in sorted(self.running, key=lambda s: s.order):
+            if sequence.remaining <= 1 or any(e.sequence is sequence for e in plan.entries):
+                continue
+            if budget <= 0:
+                break
+            count = portion(sequence)
+            if count <= 0:
+                blocked = True
+                break
+            self._plan(plan, sequence, count, planned)
+            budget -= count
+
+        # 3. admit waiting requests in order
+        while self.waiting and not blocked and budget > 0 \
+                and len(self.running) < self.config.max_num_seqs:
+            sequence = self.waiting[0]
+            if any(s is sequence for s in plan.preempted):
+                break                          # a request preempted in this step waits a step
+            if self.cache.slots.free_count == 0:
+                break
+            self.cache.add_request(sequence.request_id)
+            count = portion(sequence)
+            if count <= 0:
+                self.cache.free_request(sequence.request_id)
+                if not self.running:
+                    self.waiting.popleft()
+                    self._finish(sequence, "cancelled")
+                    raise RequestRefused(
+                        f"request {sequence.request_id!r} does not fit in the empty cache pool")
+                break
+            self.waiting.popleft()
+            sequence.status = RUNNING
+            sequence.order = self._admitted
+            self._admitted += 1
+            self.running.append(sequence)
+            self._plan(plan, sequence, count, planned)
+            budget -= count
+        return plan
+
+    # ------------------------------------------------------------------ after a step
+    def _finish(self, sequence: Sequence, reason: str) -> None:
+        if sequence.status == RUNNING:
+            self.cache.free_request(sequence.request_id)
+            self.running.remove(sequence)
+        sequence.status, sequence.finish_reason = FINISHED, reason
+        self.finished[sequence.request_id] = sequence
+
+    def step_done(self, plan: StepPlan, sampled: list[int]) -> list[tuple[Sequence, int]]:
+        """Records a finished step: ``sampled`` holds one token per sampling entry, in plan
+        order. Returns (sequence, new token) pairs; finished requests have given up their
+        pages when this returns."""
+        produced: list[tuple[Sequence, int]] = []
+        tokens = iter(sampled)
+        for entry in plan.entries:
+            sequence = entry.sequence
+            samples = entry.samples
+            sequence.computed = entry.start + entry.count
+            if not samples:
+                continue
+            token = int(next(tokens))
+            if sequence.status != RUNNING:
+                continue                       # cancelled while the step ran
+            sequence.outputs.append(token)
+            sequence.sampler.accept(token)
+            produced.append((sequence, token))
+            if token in self.eos_token_ids:
+                self._finish(sequence, "stop")
+            elif len(sequence.outputs) >= sequence.max_new_tokens:
+                self._finish(sequence, "length")
+        return produced

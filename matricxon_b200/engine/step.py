@@ -113,6 +113,8 @@ class StepRunner:
         self._upload_done: torch.cuda.Event | None = None
         self.steps_run = 0
         self.tokens_run = 0
+        self.last_upload_bytes = 0        # host-to-device bytes of the latest step's metadata
+        self.launches_per_step = 0        # this library's kernel launches in the latest step
         model.bind_cache(storage.groups, storage.states)
 
     # ------------------------------------------------------------------ buffers
@@ -233,6 +235,7 @@ class StepRunner:
             self._upload_done.synchronize()      # the pinned buffer may still be in flight
         host[:total].copy_(flat_all)
         dev[:total].copy_(host[:total], non_blocking=True)
+        self.last_upload_bytes = total * 4
         if self._upload_done is None:
             self._upload_done = torch.cuda.Event()
         self._upload_done.record()
@@ -259,6 +262,7 @@ class StepRunner:
         """Runs the entries as one batch and commits them. Returns float32 logits
         [wanted, vocab] in the order of the entries and of each ``want``, or None."""
         ctx = self.build(entries)
+        launches_before = kernels.launch_count
         try:
             hidden = self.model.forward(ctx)
             logits = None
@@ -272,6 +276,7 @@ class StepRunner:
             self.cache.commit(entry.request_id, len(entry.tokens))
         self.steps_run += 1
         self.tokens_run += ctx.n_tokens
+        self.launches_per_step = kernels.launch_count - launches_before
         return logits
 
     def check_status(self) -> None:

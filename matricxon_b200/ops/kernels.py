@@ -14,6 +14,14 @@ from matricxon_b200.ops.library import KernelLibraryError, check, library
 F32, BF16 = 0, 1
 EPILOGUE_NONE, EPILOGUE_GELU, EPILOGUE_RESIDUAL, EPILOGUE_F32 = 0, 1, 2, 3
 
+launch_count = 0      # kernels of this library launched so far in this process
+
+
+def _launched(n: int = 1) -> None:
+    global launch_count
+    launch_count += n
+
+
 STATUS_BITS = {1: "a token id outside the vocabulary", 2: "a cache slot outside the pool",
                4: "a block-table entry that names no page", 8: "a device-side wait ran out"}
 
@@ -56,6 +64,7 @@ def embed(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, status: tor
     assert ids.numel() == n and table.shape[1] == hidden
     check(library().mx_embed(_ptr(ids), _ptr(table), dtype_code(table.dtype), _ptr(out), n, hidden,
                              table.shape[0], _ptr(status), _stream()), "embed")
+    _launched()
 
 
 def layernorm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, eps: float,
@@ -75,6 +84,7 @@ def layernorm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, 
     check(library().mx_layernorm(_ptr(x), _ptr(rows), _ptr(weight), _ptr(bias), _ptr(out),
                                  dtype_code(out.dtype), n_rows, hidden, float(eps), _stream()),
           "layernorm")
+    _launched()
 
 
 def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor,
@@ -102,6 +112,7 @@ def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Te
                                      _ptr(positions), _ptr(inv_freq), _ptr(slots), _ptr(cache), n,
                                      n_heads, n_kv_heads, head_dim, rotary_dim, page_size, n_pages,
                                      1 if write else 0, _ptr(status), _stream()), "rope_kv_write")
+    _launched()
 
 
 def epilogue(acc: torch.Tensor, bias: torch.Tensor | None, residual: torch.Tensor | None,
@@ -112,6 +123,7 @@ def epilogue(acc: torch.Tensor, bias: torch.Tensor | None, residual: torch.Tenso
     check(library().mx_epilogue(_ptr(acc), dtype_code(acc.dtype), _ptr(bias), _ptr(residual),
                                 _ptr(out), dtype_code(out.dtype), n_rows, n_cols, mode, _stream()),
           "epilogue")
+    _launched()
 
 
 def gemm_simt(a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None,
@@ -135,6 +147,7 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None,
     check(library().mx_gemm_simt(_ptr(a), _ptr(w), dtype_code(a.dtype), _ptr(bias), _ptr(residual),
                                  _ptr(out), dtype_code(out.dtype), m, n, k, a.stride(0), w.stride(0),
                                  out.stride(0), mode, _stream()), "gemm_simt")
+    _launched()
 
 
 def attention_scratch_bytes(n_tokens: int, n_heads: int, head_dim: int, n_splits: int) -> int:
@@ -171,3 +184,4 @@ def paged_attention(q: torch.Tensor, q_stride: int, cache: torch.Tensor, block_t
         _ptr(block_tables), block_tables.stride(0), _ptr(tok_seq), _ptr(positions), n_tokens,
         n_heads, n_kv_heads, head_dim, int(window or 0), float(scale), _ptr(out), out.stride(0),
         n_splits, _ptr(scratch), _ptr(status), _stream()), "paged_attention")
+    _launched(2 if n_splits > 1 else 1)

@@ -1,0 +1,3 @@
+from matricxon_b200.sampling.config import SamplingConfig
+
+__all__ = ["SamplingConfig"]

@@ -1,0 +1,292 @@
+"""Each part alone against the plain implementation, and a toy mixer with state of its own
+registered from the test, built and stepped without touching the framework's files."""
+
+from types import SimpleNamespace
+
+import pytest
+import torch
+
+from plain_reference import (
+    plain_apply_rope,
+    plain_attention,
+    plain_config,
+    plain_layer,
+    plain_layernorm,
+    plain_mlp,
+    plain_rope_tables,
+)
+from tiny_configs import TINY, random_ids, tiny_config, tiny_tensors
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def tol(dtype):
+    return dict(atol=2e-5, rtol=1e-5) if dtype == torch.float32 else dict(atol=3e-2, rtol=3e-2)
+
+
+def make_runtime(dtype, page_size=16):
+    from matricxon_b200.parts.base import Runtime
+
+    return Runtime(device=torch.device(DEV), dtype=dtype, page_size=page_size)
+
+
+def hand_made_context(seq_lens, page_size, pages, start=0):
+    """A StepContext for whole sequences starting at ``start``, pages handed out in reverse."""
+    from matricxon_b200.engine.step import GroupStep, HostStep, StepContext
+
+    runner = SimpleNamespace(
+        status=torch.zeros(1, dtype=torch.int32, device=DEV), sm_count=148,
+        hidden_buffer=lambda n, h: torch.empty(n, h, device=DEV),
+        scratch_buffer=lambda nbytes: torch.empty(nbytes // 4 + 1, device=DEV))
+    ctx = StepContext(runner)
+    positions, tok_seq, slots, tables = [], [], [], []
+    next_page = pages - 1
+    width = max((start + n + page_size - 1) // page_size for n in seq_lens)
+    for s, n in enumerate(seq_lens):
+        table = []
+        for _ in range((start + n + page_size - 1) // page_size):
+            table.append(next_page)
+            next_page -= 1
+        assert next_page >= -1
+        for i in range(start, start + n):
+            positions.append(i)
+            tok_seq.append(s)
+            slots.append(table[i // page_size] * page_size + i % page_size)
+        tables.append(table + [-1] * (width - len(table)))
+    as_int = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    ctx.n_tokens, ctx.n_seqs, ctx.max_kv_len = len(positions), len(seq_lens), start + max(seq_lens)
+    ctx.positions, ctx.tok_seq = as_int(positions), as_int(tok_seq)
+    ctx.groups = [GroupStep(slots=as_int(slots), block_tables=as_int(tables))]
+    ctx.host = HostStep(q_lens=list(seq_lens), context_lens=[start] * len(seq_lens),
+                        state_slots=list(range(len(seq_lens))), fresh=[True] * len(seq_lens))
+    ctx.state_slots = as_int(list(range(len(seq_lens))))
+    return ctx
+
+
+def fetcher(tensors, dtype):
+    def fetch(name):
+        t = tensors[name]
+        want = dtype if t.dim() == 2 else torch.float32
+        return t.to(DEV, want).contiguous()
+
+    return fetch
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_norm_mlp_attention_block_alone(name, dtype):
+    import matricxon_b200.parts  # noqa: F401  (registers the built-in kinds)
+    from matricxon_b200.parts.base import CacheBinding, build_part, part_class
+
+    raw = TINY[name][0]
+    cfg = plain_config(raw)
+    config = tiny_config(name)
+    spec = config.model_spec()
+    tensors = tiny_tensors(name, torch.bfloat16 if dtype == torch.bfloat16 else torch.float32)
+    plain_w = {k: v.double() for k, v in tensors.items()}
+    rt = make_runtime(dtype)
+    fetch = fetcher(tensors, dtype)
+    seq_lens = [50, 7]
+    n = sum(seq_lens)
+    torch.manual_seed(3)
+    x = torch.randn(n, cfg["hidden"], device=DEV)
+    x_cpu = x.double().cpu()
+    prefix = "model.layers.1."
+
+    # norm
+    norm = build_part("norm", spec.layers[1].mixer_norm, rt, prefix + "input_layernorm.")
+    norm.load(fetch)
+    h = norm.forward(x)
+    h_ref = plain_layernorm(x_cpu, plain_w[prefix + "input_layernorm.weight"],
+                            plain_w[prefix + "input_layernorm.bias"], cfg["eps"])
+    assert h.dtype == dtype and torch.allclose(h.double().cpu(), h_ref, **tol(dtype))
+
+    # feed-forward: residual + mlp(h)
+    mlp = build_part("feed_forward", spec.layers[1].feed_forward, rt, prefix + "mlp.")
+    mlp.load(fetch)
+    ctx = hand_made_context(seq_lens, 16, 16)
+    out = mlp.forward(h, x.clone(), ctx)
+    ref = x_cpu + plain_mlp(h.double().cpu(), plain_w, prefix + "mlp.", cfg)
+    assert out.dtype == torch.float32 and torch.allclose(out.double().cpu(), ref, **tol(dtype))
+
+    # mixer: residual + attention(h), two whole sequences in one batch
+    mixer = build_part("mixer", spec.layers[1].mixer, rt, prefix + "self_attn.")
+    mixer.load(fetch)
+    kv = torch.full((16, 2, cfg["kv_heads"], 16, cfg["head_dim"]), float("nan"), dtype=dtype, device=DEV)
+    binding = CacheBinding(group=0, kv=kv, writes=True)
+    out = mixer.forward(h, x.clone(), ctx, binding)
+    assert int(ctx.status.item()) == 0
+    refs, start = [], 0
+    for length in seq_lens:
+        piece = h.double().cpu()[start:start + length]
+        refs.append(x_cpu[start:start + length] +
+                    plain_attention(piece, plain_w, prefix + "self_attn.", cfg, torch.arange(length)))
+        start += length
+    assert torch.allclose(out.double().cpu(), torch.cat(refs), **tol(dtype))
+
+    # the whole block
+    block = part_class("block", spec.layers[1].block)(spec.layers[1], rt, prefix)
+    block.load(fetch)
+    kv.fill_(float("nan"))
+    ctx = hand_made_context(seq_lens, 16, 16)
+    out = block.forward(x.clone(), ctx, binding)
+    refs, start = [], 0
+    for length in seq_lens:
+        refs.append(plain_layer(x_cpu[start:start + length], plain_w, 1, cfg, torch.arange(length)))
+        start += length
+    assert torch.allclose(out.double().cpu(), torch.cat(refs), **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_rotary_part_alone(dtype):
+    import matricxon_b200.parts  # noqa: F401
+    from matricxon_b200.parts.base import CacheBinding, build_part
+    from matricxon_b200.parts.spec import RotarySpec
+
+    heads, kv_heads, dim = 3, 1, 32
+    rt = make_runtime(dtype, page_size=8)
+    rotary = build_part("position", RotarySpec(rotary_dim=dim, theta=100000.0), rt, "unused.")
+    ctx = hand_made_context([11], 8, 4, start=200)
+    qkv = torch.randn(11, (heads + 2 * kv_heads) * dim, device=DEV).to(dtype)
+    before = qkv.double().cpu()
+    kv = torch.zeros(4, 2, kv_heads, 8, dim, dtype=dtype, device=DEV)
+    rotary.rotate_and_store(qkv, ctx, CacheBinding(group=0, kv=kv, writes=True), heads, kv_heads, dim)
+    cos, sin = plain_rope_tables(torch.arange(200, 211), dim, 100000.0)
+    q_ref = plain_apply_rope(before[:, :heads * dim].view(11, heads, dim).transpose(0, 1), cos, sin)
+    got = qkv[:, :heads * dim].double().cpu().view(11, heads, dim).transpose(0, 1)
+    assert torch.allclose(got, q_ref, **tol(dtype))
+    # a reader of someone else's cache stores nothing
+    kv.zero_()
+    rotary.rotate_and_store(qkv, ctx, CacheBinding(group=0, kv=kv, writes=False), heads, kv_heads, dim)
+    assert torch.all(kv == 0)
+
+
+# --------------------------------------------------------------------------- a toy mixer
+def register_toy_parts():
+    """A mixer that keeps a running, decayed sum of its projected inputs per request:
+    s_t = decay * s_{t-1} + h_t W^T ; out_t = s_t. State of its own, no pages."""
+    from matricxon_b200.parts.base import Mixer, StateRequest, register_part
+    from matricxon_b200.weights.loader import WeightSpec
+
+    class ToyDecaySpec:
+        kind = "toy_decay"
+
+        def __init__(self, hidden_size, decay):
+            self.hidden_size, self.decay = hidden_size, decay
+
+    @register_part("mixer", "toy_decay")
+    class ToyDecayMixer(Mixer):
+        @classmethod
+        def weight_specs(cls, spec, prefix):
+            return [WeightSpec(prefix + "mix.weight", (spec.hidden_size, spec.hidden_size))]
+
+        @classmethod
+        def state_request(cls, spec):
+            return StateRequest(shape=(spec.hidden_size,), dtype=torch.float32)
+
+        def load(self, fetch):
+            self.weight = fetch(self.prefix + "mix.weight")
+
+        def forward(self, h, residual, ctx, binding):
+            projected = (h.float() @ self.weight.float().T)
+            out = torch.empty_like(projected)
+            start = 0
+            for q_len, slot in zip(ctx.host.q_lens, ctx.host.state_slots):
+                state = binding.state[slot]
+                for i in range(start, start + q_len):           # tokens of a sequence in order
+                    state.mul_(self.spec.decay).add_(projected[i])
+                    out[i] = state
+                start += q_len
+            return residual + out
+
+    return ToyDecaySpec
+
+
+def toy_reference(spec_layers, schedule, weights, cfg, ids, decay):
+    """The toy model on the CPU, whole sequence, in double."""
+    w = {k: v.double() for k, v in weights.items()}
+    x = w["model.embed_tokens.weight"][torch.tensor(ids)]
+    positions = torch.arange(len(ids))
+    for entry in schedule:
+        p = f"model.layers.{entry.layer}."
+        h = plain_layernorm(x, w[p + "input_layernorm.weight"], w[p + "input_layernorm.bias"], cfg["eps"])
+        if spec_layers[entry.layer].mixer.kind == "toy_decay":
+            projected = h @ w[p + "self_attn.mix.weight"].T
+            state = torch.zeros(cfg["hidden"], dtype=torch.float64)
+            rows = []
+            for row in projected:
+                state = decay * state + row
+                rows.append(state)
+            x = x + torch.stack(rows)
+        else:
+            x = x + plain_attention(h, w, p + "self_attn.", cfg, positions)
+        h = plain_layernorm(x, w[p + "post_attention_layernorm.weight"],
+                            w[p + "post_attention_layernorm.bias"], cfg["eps"])
+        x = x + plain_mlp(h, w, p + "mlp.", cfg)
+    x = plain_layernorm(x, w["model.norm.weight"], w["model.norm.bias"], cfg["eps"])
+    return x @ w["model.embed_tokens.weight"].T
+
+
+def test_toy_mixer_with_state_is_registered_built_and_stepped():
+    """Layers of different kinds in one model, a layer named twice in the schedule (weights
+    shared, caches and states apart), and per-request state carried across steps."""
+    import matricxon_b200.parts  # noqa: F401
+    from matricxon_b200.engine.core import EngineCore
+    from matricxon_b200.engine.step import StepEntry
+    from matricxon_b200.models.decoder import DecoderModel, model_weight_specs
+    from matricxon_b200.parts.spec import LayerSpec, ModelSpec, ScheduleEntry
+    from matricxon_b200.weights.loader import DictSource, make_fetcher
+    from matricxon_b200.weights.random_init import RandomInit, RandomSource
+
+    ToyDecaySpec = register_toy_parts()
+    base = tiny_config("A").model_spec()
+    attention_layer = base.layers[0]
+    toy_layer = LayerSpec(mixer=ToyDecaySpec(base.hidden_size, 0.5), feed_forward=attention_layer.feed_forward,
+                          mixer_norm=attention_layer.mixer_norm, ffn_norm=attention_layer.ffn_norm)
+    schedule = (ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(0), ScheduleEntry(1))
+    spec = ModelSpec(hidden_size=base.hidden_size, vocab_size=base.vocab_size,
+                     layers=(attention_layer, toy_layer), schedule=schedule, final_norm=base.final_norm,
+                     tie_word_embeddings=True, max_position_embeddings=128)
+    specs = model_weight_specs(spec)
+    assert any(s.name == "model.layers.1.self_attn.mix.weight" for s in specs)
+    source = RandomSource(specs, seed=11, init=RandomInit(0.05, 0.02, 0.02, 0.02))
+    weights = {name: source.read(name) for name in source.names()}
+
+    rt = make_runtime(torch.float32)
+    model = DecoderModel(spec, rt)
+    assert model.cache_plan.state_bytes_per_request == 2 * 64 * 4       # two executions of the toy layer
+    assert model.cache_plan.groups[0].entries == (0, 2)                 # two caches for attention layer 0
+    model.load(make_fetcher(specs, DictSource(weights), torch.float32, DEV))
+    core = EngineCore(model, max_cache_tokens=256, max_requests=4)
+
+    cfg = plain_config(TINY["A"][0])
+    prompts = {"x": random_ids(45, 512, 1), "y": random_ids(20, 512, 2)}
+    refs = {k: toy_reference(spec.layers, schedule, weights, cfg, ids, 0.5) for k, ids in prompts.items()}
+    for rid in prompts:
+        core.cache.add_request(rid)
+    got = {rid: [] for rid in prompts}
+    done = {rid: 0 for rid in prompts}
+    sizes = [5, 1, 9, 2, 1, 1, 13, 3]
+    turn = 0
+    while any(done[r] < len(prompts[r]) for r in prompts):
+        entries = []
+        for rid, ids in prompts.items():
+            if done[rid] < len(ids):
+                size = min(sizes[turn % len(sizes)], len(ids) - done[rid])
+                turn += 1
+                entries.append(StepEntry(rid, ids[done[rid]:done[rid] + size], list(range(size))))
+                done[rid] += size
+        logits = core.runner.run(entries).cpu()
+        core.runner.check_status()
+        row = 0
+        for entry in entries:
+            got[entry.request_id].append(logits[row:row + len(entry.tokens)])
+            row += len(entry.tokens)
+    for rid in prompts:
+        assert torch.allclose(torch.cat(got[rid]).double(), refs[rid], atol=5e-5), rid
+    # a slot given to a new request starts from zero again
+    core.cache.free_request("x")
+    core.cache.add_request("z")
+    logits = core.runner.run([StepEntry("z", prompts["x"], list(range(45)))]).cpu()
+    assert torch.allclose(logits.double(), refs["x"], atol=5e-5)

@@ -1,0 +1,220 @@
+"""The scheduler's decisions with a fake step function (no GPU), in the manner of the
+reference's scheduler tests with a fake decoder (tests/unit/test_batching_scheduler.py:14-23)."""
+
+import pytest
+
+from matricxon_b200.cache.manager import CacheManager, GroupRule
+from matricxon_b200.engine.scheduler import (
+    FINISHED,
+    RUNNING,
+    RequestRefused,
+    Scheduler,
+    SchedulerConfig,
+)
+from matricxon_b200.sampling.config import SamplingConfig
+from matricxon_b200.sampling.sampler import uniform_for
+
+
+def make(pages=64, page_size=4, window=None, eos=(), **config):
+    cache = CacheManager([GroupRule(window)], pages, page_size, num_state_slots=8)
+    defaults = dict(max_num_seqs=4, max_num_batched_tokens=16, prefill_chunk=8, max_model_len=256)
+    defaults.update(config)
+    return cache, Scheduler(cache, SchedulerConfig(**defaults), set(eos))
+
+
+def fake_token(sequence, upto):
+    """What a model would 'predict' after ``upto`` tokens: a function of the tokens alone."""
+    tokens = sequence.tokens[:upto]
+    return (sum((i + 1) * t for i, t in enumerate(tokens)) + len(tokens)) % 50 + 3
+
+
+def run_step(cache, scheduler, log=None):
+    plan = scheduler.schedule()
+    sampled = []
+    for entry in plan.entries:
+        cache.reserve(entry.sequence.request_id, entry.count)
+        cache.commit(entry.sequence.request_id, entry.count)
+        if entry.samples:
+            sampled.append(fake_token(entry.sequence, entry.start + entry.count))
+    if log is not None:
+        log.append([(e.sequence.request_id, e.start, e.count) for e in plan.entries])
+    cache.check_invariants()
+    return plan, scheduler.step_done(plan, sampled)
+
+
+def run_all(cache, scheduler, log=None, limit=2000):
+    for _ in range(limit):
+        if not scheduler.has_work():
+            return
+        run_step(cache, scheduler, log)
+    raise AssertionError("scheduler did not finish")
+
+
+def sampling(num_predict=6, num_ctx=256, **kw):
+    return SamplingConfig(temperature=0.0, num_predict=num_predict, num_ctx=num_ctx, **kw)
+
+
+def test_single_request_prefill_in_portions_then_decode():
+    cache, scheduler = make()
+    scheduler.add("a", list(range(1, 21)), sampling(num_predict=3))
+    log = []
+    run_all(cache, scheduler, log)
+    assert log[:3] == [[("a", 0, 8)], [("a", 8, 8)], [("a", 16, 4)]]      # chunk 8, then the rest
+    assert log[3:] == [[("a", 20, 1)], [("a", 21, 1)]]                     # two decode steps
+    done = scheduler.finished["a"]
+    assert len(done.outputs) == 3 and done.finish_reason == "length"
+    assert cache.free_pages() == [64]
+
+
+def test_budget_decodes_first_then_portions():
+    cache, scheduler = make(max_num_batched_tokens=10, prefill_chunk=8)
+    scheduler.add("a", [1, 2, 3], sampling(num_predict=20))
+    run_step(cache, scheduler)                                 # a: whole prompt, samples
+    scheduler.add("b", list(range(1, 31)), sampling(num_predict=2))
+    log = []
+    run_step(cache, scheduler, log)
+    assert log[0] == [("a", 3, 1), ("b", 0, 8)]                # decode first, then the portion
+    scheduler.add("c", list(range(1, 31)), sampling(num_predict=2))
+    run_step(cache, scheduler, log)
+    # budget 10: a's decode, 8 of b, and the one token left for c
+    assert log[1] == [("a", 4, 1), ("b", 8, 8), ("c", 0, 1)]
+    assert sum(count for _, _, count in log[1]) == 10
+
+
+def test_max_num_seqs_and_fifo_admission():
+    cache, scheduler = make(max_num_seqs=2, max_num_batched_tokens=64, prefill_chunk=64)
+    for name in "abc":
+        scheduler.add(name, [1, 2, 3, 4], sampling(num_predict=2))
+    log = []
+    run_step(cache, scheduler, log)
+    assert [e[0] for e in log[0]] == ["a", "b"] and len(scheduler.waiting) == 1
+    run_all(cache, scheduler, log)
+    assert [e[0] for e in log[2]] == ["c"]                     # admitted once a and b are done
+    assert all(scheduler.finished[n].finish_reason == "length" for n in "abc")
+
+
+def test_eos_is_emitted_then_stops():
+    cache, scheduler = make()
+    scheduler.add("probe", [5, 6, 7], sampling(num_predict=10))
+    run_all(cache, scheduler)
+    tokens = scheduler.finished["probe"].outputs
+    cache2, scheduler2 = make(eos=[tokens[2]])
+    scheduler2.add("a", [5, 6, 7], sampling(num_predict=10))
+    run_all(cache2, scheduler2)
+    done = scheduler2.finished["a"]
+    assert done.outputs == tokens[:3] and done.finish_reason == "stop"
+
+
+def test_num_ctx_bounds_generation_and_rejects_long_prompts():
+    cache, scheduler = make()
+    scheduler.add("a", [1] * 10, sampling(num_predict=-1, num_ctx=14))
+    run_all(cache, scheduler)
+    assert len(scheduler.finished["a"].outputs) == 4           # until num_ctx
+    with pytest.raises(RequestRefused):
+        scheduler.add("b", [1] * 15, sampling(num_ctx=14))
+    with pytest.raises(RequestRefused):
+        scheduler.add("c", [], sampling())
+    done = scheduler.add("d", [1] * 14, sampling(num_predict=5, num_ctx=14))
+    assert done.status == FINISHED and done.finish_reason == "length" and done.outputs == []
+    small_cache, small = make(pages=10)
+    with pytest.raises(RequestRefused):
+        small.add("e", [1] * 30, SamplingConfig(num_predict=100, num_ctx=1000))   # 130 tokens > pool
+
+
+def test_batched_tokens_equal_alone():
+    prompts = {"a": [3, 1, 4, 1, 5], "b": list(range(2, 25)), "c": [9, 9]}
+    alone = {}
+    for name, prompt in prompts.items():
+        cache, scheduler = make()
+        scheduler.add(name, prompt, sampling(num_predict=7))
+        run_all(cache, scheduler)
+        alone[name] = scheduler.finished[name].outputs
+    cache, scheduler = make()
+    for name, prompt in prompts.items():
+        scheduler.add(name, prompt, sampling(num_predict=7))
+    log = []
+    run_all(cache, scheduler, log)
+    assert max(len(step) for step in log) >= 3
+    for name in prompts:
+        assert scheduler.finished[name].outputs == alone[name]
+
+
+def test_pages_run_out_portions_wait_decodes_go_on():
+    cache, scheduler = make(pages=6, page_size=4, max_num_batched_tokens=64, prefill_chunk=64)
+    scheduler.add("a", [1] * 10, sampling(num_predict=2))      # 3 pages
+    run_step(cache, scheduler)
+    scheduler.add("b", [2] * 20, sampling(num_predict=2))      # 5 pages: only 3 free
+    log = []
+    run_step(cache, scheduler, log)
+    # b is cut to the portion that fits the free pages; a decodes beside it
+    assert log[0][0] == ("a", 10, 1)
+    assert log[0][1][0] == "b" and log[0][1][2] < 20
+    run_all(cache, scheduler, log)
+    assert scheduler.finished["b"].finish_reason == "length" and cache.free_pages() == [6]
+
+
+def test_preemption_keeps_tokens_and_requeues_in_front():
+    prompts = {"a": [1] * 6, "b": [2] * 6, "c": [3] * 6}
+    alone = {}
+    for name, prompt in prompts.items():
+        cache, scheduler = make()
+        scheduler.add(name, prompt, sampling(num_predict=12))
+        run_all(cache, scheduler)
+        alone[name] = scheduler.finished[name].outputs
+    # 18 tokens of prompt + 36 generated need 15 pages of 4; give 9: someone must be preempted
+    cache, scheduler = make(pages=9, page_size=4, max_num_batched_tokens=64, prefill_chunk=64)
+    for name, prompt in prompts.items():
+        scheduler.add(name, prompt, sampling(num_predict=12))
+    log = []
+    preempted = []
+    for _ in range(500):
+        if not scheduler.has_work():
+            break
+        plan, _ = run_step(cache, scheduler, log)
+        preempted.extend(s.request_id for s in plan.preempted)
+    assert not scheduler.has_work()
+    assert scheduler.num_preemptions >= 1 and preempted
+    assert preempted[0] == "c"                                  # the most recently admitted goes first
+    for name in prompts:
+        assert scheduler.finished[name].outputs == alone[name], name
+    # a recomputation runs prompt + kept tokens as one prompt
+    victim = preempted[0]
+    restarts = [step for step in log if any(e[0] == victim and e[1] == 0 for e in step)]
+    assert len(restarts) >= 2
+    assert cache.free_pages() == [9]
+
+
+def test_request_alone_that_exhausts_the_pool_finishes():
+    cache, scheduler = make(pages=3, page_size=4, window=None)
+    scheduler.add("a", [1] * 8, sampling(num_predict=4))       # fits exactly: 12 tokens = 3 pages
+    run_all(cache, scheduler)
+    assert len(scheduler.finished["a"].outputs) == 4
+    with pytest.raises(RequestRefused):
+        scheduler.add("b", [1] * 8, sampling(num_predict=8))   # 16 tokens never fit 3 pages
+
+
+def test_window_lets_a_long_request_run_in_few_pages():
+    cache, scheduler = make(pages=5, page_size=4, window=8, max_num_batched_tokens=4, prefill_chunk=4)
+    scheduler.add("a", [1] * 30, sampling(num_predict=20))
+    run_all(cache, scheduler)
+    assert len(scheduler.finished["a"].outputs) == 20
+    assert cache.pages_reused > 0 and cache.free_pages() == [5]
+
+
+def test_cancel_waiting_and_running():
+    cache, scheduler = make(max_num_seqs=1)
+    scheduler.add("a", [1, 2, 3], sampling(num_predict=50))
+    scheduler.add("b", [1, 2, 3], sampling(num_predict=50))
+    run_step(cache, scheduler)
+    assert scheduler.cancel("b") and scheduler.finished["b"].finish_reason == "cancelled"
+    assert scheduler.cancel("a") and cache.free_pages() == [64]
+    assert not scheduler.cancel("a") and not scheduler.has_work()
+    assert scheduler.schedule().entries == []
+
+
+def test_uniform_stream_is_a_function_of_seed_and_index():
+    a = [uniform_for(7, i) for i in range(50)]
+    assert a == [uniform_for(7, i) for i in range(50)]
+    assert a != [uniform_for(8, i) for i in range(50)]
+    assert all(0.0 <= u < 1.0 for u in a) and len(set(a)) == 50
+    assert abs(sum(uniform_for(1, i) for i in range(4000)) / 4000 - 0.5) < 0.02
