@@ -203,6 +203,7 @@ def test_eos_and_cancel():
     engine = ChatEngine(model, eos_token_ids={eos}, max_cache_tokens=256, max_active=2, max_model_len=128)
     stopped = engine.generate(GenerationRequest(prompt, sampling))
     assert stopped.finish_reason == "stop" and stopped.token_ids == free_run.token_ids[:first + 1]
+    engine = ChatEngine(model, max_cache_tokens=256, max_active=2, max_model_len=128)
     rid = engine.add_request(prompt, sampling)
     engine.step()
     assert engine.cancel(rid) and engine.result(rid).finish_reason == "cancelled"
