@@ -147,10 +147,10 @@ def test_rotary_part_alone(dtype):
     heads, kv_heads, dim = 3, 1, 32
     rt = make_runtime(dtype, page_size=8)
     rotary = build_part("position", RotarySpec(rotary_dim=dim, theta=100000.0), rt, "unused.")
-    ctx = hand_made_context([11], 8, 4, start=200)
+    ctx = hand_made_context([11], 8, 32, start=200)
     qkv = torch.randn(11, (heads + 2 * kv_heads) * dim, device=DEV).to(dtype)
     before = qkv.double().cpu()
-    kv = torch.zeros(4, 2, kv_heads, 8, dim, dtype=dtype, device=DEV)
+    kv = torch.zeros(32, 2, kv_heads, 8, dim, dtype=dtype, device=DEV)
     rotary.rotate_and_store(qkv, ctx, CacheBinding(group=0, kv=kv, writes=True), heads, kv_heads, dim)
     cos, sin = plain_rope_tables(torch.arange(200, 211), dim, 100000.0)
     q_ref = plain_apply_rope(before[:, :heads * dim].view(11, heads, dim).transpose(0, 1), cos, sin)
