@@ -349,3 +349,67 @@ extern "C" int mx_paged_attention(const void* q, int dtype, int q_stride, const 
     return two ? launch_attention<__nv_bfloat16, 2>(p, n_tokens, stream)
                : launch_attention<__nv_bfloat16, 1>(p, n_tokens, stream);
 }
+
+// ---------------------------------------------------------------------------------------------
+// The same attention for callers that cannot allocate: scratch lives in the library image.
+// See no_alloc.h for who needs this and for the rules of use.
+#include "no_alloc.h"
+
+namespace {
+
+constexpr int MX_MAX_DEVICES = 64;
+
+// Reserved on every device that loads this library, until the process exits.
+static __device__ __align__(256) float g_static_attention_scratch[MX_STATIC_ATTENTION_SCRATCH_BYTES / sizeof(float)];
+
+// In host code the array's name is only a handle for the runtime, not a device pointer; the
+// address a kernel can use comes from cudaGetSymbolAddress, once per device.
+float* g_static_scratch_address[MX_MAX_DEVICES] = {nullptr};
+
+int static_scratch_for_current_device(float** address) {
+    int device = -1;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) {
+        mx_set_error("static attention: cudaGetDevice failed: %s", cudaGetErrorString(e));
+        return (int)e;
+    }
+    if (device < 0 || device >= MX_MAX_DEVICES)
+        MX_REFUSE("static attention: device ordinal %d is beyond the %d this library tracks", device, MX_MAX_DEVICES);
+    if (g_static_scratch_address[device] == nullptr) {
+        void* found = nullptr;
+        e = cudaGetSymbolAddress(&found, g_static_attention_scratch);
+        if (e != cudaSuccess || found == nullptr) {
+            mx_set_error("static attention: cudaGetSymbolAddress failed on device %d: %s", device,
+                         cudaGetErrorString(e));
+            return e != cudaSuccess ? (int)e : MX_ERR_ARGUMENT;
+        }
+        g_static_scratch_address[device] = static_cast<float*>(found);
+    }
+    *address = g_static_scratch_address[device];
+    return MX_OK;
+}
+
+}  // namespace
+
+extern "C" long long mx_static_attention_scratch_bytes(void) { return MX_STATIC_ATTENTION_SCRATCH_BYTES; }
+
+extern "C" int mx_paged_attention_static(const void* q, int dtype, int q_stride, const void* cache,
+                                         long long n_pages, int page_size, const int* block_tables,
+                                         int bt_stride, const int* tok_seq, const int* positions,
+                                         int n_tokens, int n_heads, int n_kv_heads, int head_dim,
+                                         int window, float scale, void* out, int out_stride,
+                                         int n_splits, int* status, cudaStream_t stream) {
+    if (n_tokens <= 0) return MX_OK;
+    if (n_splits < 1) MX_REFUSE("static attention: n_splits %d", n_splits);
+    const long long need = mx_attention_scratch_bytes(n_tokens, n_heads, head_dim, n_splits);
+    if (need > MX_STATIC_ATTENTION_SCRATCH_BYTES)
+        MX_REFUSE("static attention: %d tokens x %d heads x %d splits x head_dim %d need %lld bytes "
+                  "of scratch, the built-in array holds %lld; use fewer splits or tokens per call",
+                  n_tokens, n_heads, n_splits, head_dim, need, (long long)MX_STATIC_ATTENTION_SCRATCH_BYTES);
+    float* scratch = nullptr;
+    const int rc = static_scratch_for_current_device(&scratch);
+    if (rc != MX_OK) return rc;
+    return mx_paged_attention(q, dtype, q_stride, cache, n_pages, page_size, block_tables, bt_stride,
+                              tok_seq, positions, n_tokens, n_heads, n_kv_heads, head_dim, window,
+                              scale, out, out_stride, n_splits, scratch, status, stream);
+}
