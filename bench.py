@@ -121,7 +121,7 @@ def reference_arm(args) -> int:
 
 
 def build_engine(config_dict: dict, n_layers: int, max_active: int, cache_tokens: int,
-                 max_batched_tokens: int):
+                 max_batched_tokens: int, use_graphs: bool = True):
     import torch
 
     from matricxon_b200 import ChatEngine
@@ -138,7 +138,7 @@ def build_engine(config_dict: dict, n_layers: int, max_active: int, cache_tokens
     model = build_model(config, source, "bfloat16", "cuda:0", PAGE_SIZE)
     engine = ChatEngine(model, max_cache_tokens=cache_tokens, max_active=max_active,
                         max_batched_tokens=max_batched_tokens, prefill_chunk=PREFILL_TOKENS,
-                        max_model_len=CONTEXT)
+                        max_model_len=CONTEXT, use_graphs=use_graphs)
     return config, model, engine
 
 
@@ -218,6 +218,10 @@ def main() -> int:
     parser.add_argument("--context", type=int, default=CONTEXT - 1024,
                         help="cached tokens per request when decode timing starts")
     parser.add_argument("--skip-points", action="store_true")
+    parser.add_argument("--skip-prefill", action="store_true")
+    parser.add_argument("--skip-e2e", action="store_true")
+    parser.add_argument("--no-graphs", action="store_true",
+                        help="launch every kernel of a decode step by itself (for profilers)")
     args = parser.parse_args()
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
@@ -242,7 +246,8 @@ def main() -> int:
     # ---- the headline: decode at batch 8
     batch = args.batch
     cache_tokens = 64 * CONTEXT
-    config, model, engine = build_engine(STARCODER2_3B, n_layers, 64, cache_tokens, 8192)
+    config, model, engine = build_engine(STARCODER2_3B, n_layers, 64, cache_tokens, 8192,
+                                         use_graphs=not args.no_graphs)
     vocab = config.vocab_size
     context = min(args.context, CONTEXT - args.steps - args.warmup - 1)
     ids = fill_cache(engine, batch, context, vocab)
@@ -274,7 +279,7 @@ def main() -> int:
     generator = torch.Generator().manual_seed(3)
     prompt = torch.randint(0, vocab, (PREFILL_TOKENS,), generator=generator).tolist()
     prefill_ms = []
-    for rep in range(5):
+    for rep in range(0 if args.skip_prefill else 5):
         engine.core.cache.add_request("prefill")
         torch.cuda.synchronize()
         begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -285,7 +290,7 @@ def main() -> int:
         engine.core.cache.free_request("prefill")
         if rep >= 2:
             prefill_ms.append(begin.elapsed_time(end))
-    pf_ms = sorted(prefill_ms)[len(prefill_ms) // 2]
+    pf_ms = sorted(prefill_ms)[len(prefill_ms) // 2] if prefill_ms else float("nan")
     pf_flops = prefill_flops(config, n_layers, PREFILL_TOKENS)
     pf_frac = pf_flops / (pf_ms * 1e-3) / (peaks["bf16_tflops"] * 1e12)
 
@@ -293,8 +298,8 @@ def main() -> int:
     sampling = SamplingConfig(temperature=0.0, num_predict=args.steps + args.warmup, num_ctx=CONTEXT)
     e2e_context = context
     prompts = [torch.randint(0, vocab, (e2e_context,), generator=generator).tolist() for _ in range(batch)]
-    rids = [engine.add_request(p, sampling) for p in prompts]
-    produced = 0
+    rids = [] if args.skip_e2e else [engine.add_request(p, sampling) for p in prompts]
+    produced = 0 if rids else batch * args.warmup
     while produced < batch * args.warmup:                       # prefill + warm-up decode steps
         produced += len(engine.step())
     torch.cuda.synchronize()

@@ -32,7 +32,7 @@ class ChatEngine:
                  device: str = "cuda:0", max_cache_tokens: int | None = None, max_active: int = 8,
                  max_batched_tokens: int = 2048, prefill_chunk: int = 256,
                  max_model_len: int | None = None, page_size: int = 16,
-                 gemm_backend: str = "auto") -> None:
+                 gemm_backend: str = "auto", use_graphs: bool = True) -> None:
         if isinstance(model, (str, Path)):
             _, model = load_model(model, dtype=dtype, device=device, page_size=page_size,
                                   gemm_backend=gemm_backend)
@@ -41,7 +41,8 @@ class ChatEngine:
         if max_cache_tokens is None:
             max_cache_tokens = max_active * limit
         self.core = EngineCore(model, max_cache_tokens=max_cache_tokens, max_requests=max_active,
-                               max_step_tokens=max(max_batched_tokens, 1))
+                               max_step_tokens=max(max_batched_tokens, 1), max_model_len=limit,
+                               use_graphs=use_graphs)
         self.scheduler = Scheduler(
             self.core.cache,
             SchedulerConfig(max_num_seqs=max_active, max_num_batched_tokens=max_batched_tokens,

@@ -73,7 +73,8 @@ class EngineCore:
     """A model with its cache: what the scheduler, the entry point and trace replay drive."""
 
     def __init__(self, model, max_cache_tokens: int, max_requests: int = 64,
-                 max_step_tokens: int = 8192, poison_cache: bool = False) -> None:
+                 max_step_tokens: int = 8192, poison_cache: bool = False,
+                 max_model_len: int | None = None, use_graphs: bool = True) -> None:
         runtime = model.runtime
         plan = model.cache_plan
         page_size = runtime.page_size
@@ -86,5 +87,6 @@ class EngineCore:
         self.storage = CacheStorage(plan, pages_per_group, page_size, runtime.dtype,
                                     runtime.device, max_requests, poison=poison_cache)
         self.runner = StepRunner(model, self.cache, self.storage, max_step_tokens=max_step_tokens,
-                                 max_step_seqs=max(max_requests, 1))
+                                 max_step_seqs=max(max_requests, 1), max_model_len=max_model_len,
+                                 use_graphs=use_graphs)
         self.bytes_per_token = bytes_per_token(plan, runtime.dtype)

@@ -19,9 +19,10 @@ from __future__ import annotations
 
 from dataclasses import dataclass, field
 
+import numpy as np
 import torch
 
-from matricxon_b200.cache.manager import CacheManager
+from matricxon_b200.cache.manager import CacheManager, OutOfPages
 from matricxon_b200.cache.storage import CacheStorage
 from matricxon_b200.ops import kernels
 
@@ -73,8 +74,12 @@ class StepContext:
         self.groups: list[GroupStep] = []
         self.status: torch.Tensor = runner.status
         self.host: HostStep = None
+        self.capturing = False        # inside a CUDA-graph capture: buffers must belong to the graph
 
     def hidden(self, hidden_size: int) -> torch.Tensor:
+        if self.capturing:
+            return torch.empty((self.n_tokens, hidden_size), dtype=torch.float32,
+                               device=self.token_ids.device)
         return self._runner.hidden_buffer(self.n_tokens, hidden_size)
 
     def attention_splits(self, n_heads: int, n_kv_heads: int, head_dim: int,
@@ -92,12 +97,17 @@ class StepContext:
         if n_splits == 1:
             return 1, None
         need = kernels.attention_scratch_bytes(self.n_tokens, n_heads, head_dim, n_splits)
+        if self.capturing:
+            return n_splits, torch.empty((need + 3) // 4, dtype=torch.float32,
+                                         device=self.token_ids.device)
         return n_splits, self._runner.scratch_buffer(need)
 
 
 class StepRunner:
     def __init__(self, model, cache: CacheManager, storage: CacheStorage,
-                 max_step_tokens: int = 8192, max_step_seqs: int = 256) -> None:
+                 max_step_tokens: int = 8192, max_step_seqs: int = 256,
+                 max_model_len: int | None = None, use_graphs: bool = True,
+                 max_graph_batch: int = 64) -> None:
         self.model = model
         self.cache = cache
         self.storage = storage
@@ -113,6 +123,12 @@ class StepRunner:
         self._upload_done: torch.cuda.Event | None = None
         self.steps_run = 0
         self.tokens_run = 0
+        limit = max_model_len or model.spec.max_position_embeddings
+        self.graph_table_width = (limit + cache.page_size - 1) // cache.page_size
+        self.use_graphs = use_graphs
+        self.max_graph_batch = max_graph_batch
+        self._graphs: dict[int, tuple] = {}
+        self._graph_pool = None
         self.last_upload_bytes = 0        # host-to-device bytes of the latest step's metadata
         self.launches_per_step = 0        # this library's kernel launches in the latest step
         model.bind_cache(storage.groups, storage.states)
@@ -159,9 +175,16 @@ class StepRunner:
         if len(entries) > self.max_step_seqs:
             raise StepError(f"step of {len(entries)} requests exceeds max_step_seqs={self.max_step_seqs}")
 
-    def build(self, entries: list[StepEntry]) -> StepContext:
+    def build(self, entries: list[StepEntry], pad_to: int | None = None,
+              table_widths: list[int] | None = None, buffers=None) -> StepContext:
         """Reserves pages for every entry and lays the step's metadata out on the device.
-        Raises OutOfPages (with every reservation of this step undone) if the pool is short."""
+        Raises OutOfPages (with every reservation of this step undone) if the pool is short.
+
+        ``pad_to`` (single-token entries only) pads the batch to a fixed number of rows with
+        padding rows (``tok_seq = -1``, ``slot = -1``) and ``table_widths`` fixes the block
+        tables' widths, so that the layout depends on nothing but those numbers: what a
+        captured CUDA graph needs. ``buffers`` is a (pinned host, device, event) triple to use
+        instead of the runner's growing ones."""
         self._validate(entries)
         cache = self.cache
         reserved: list[str] = []
@@ -178,105 +201,193 @@ class StepRunner:
 
         page_size = cache.page_size
         n_groups = len(cache.rules)
-        token_ids: list[int] = []
-        positions: list[int] = []
-        tok_seq: list[int] = []
-        cu_q = [0]
-        context_lens: list[int] = []
-        state_slots: list[int] = []
-        logit_rows: list[int] = []
-        fresh: list[bool] = []
-        slots: list[list[int]] = [[] for _ in range(n_groups)]
-        max_kv = 0
-        for s, entry in enumerate(entries):
-            record = cache.record(entry.request_id)
-            start = record.length
-            n = len(entry.tokens)
-            base = len(token_ids)
-            token_ids.extend(entry.tokens)
-            positions.extend(range(start, start + n))
-            tok_seq.extend([s] * n)
-            cu_q.append(base + n)
-            context_lens.append(start)
-            state_slots.append(record.state_slot)
-            fresh.append(record.fresh_state and start == 0)
-            logit_rows.extend(base + index for index in entry.want)
-            for g in range(n_groups):
-                slots[g].extend(cache.slot_ids(entry.request_id, g, start, n))
-            max_kv = max(max_kv, start + n)
-        n_tok, n_seq = len(token_ids), len(entries)
-        widths = []
-        tables: list[list[int]] = []
-        for g in range(n_groups):
-            width = max(1, max(len(cache.record(e.request_id).tables[g]) for e in entries))
-            widths.append(width)
-            flat: list[int] = []
-            for entry in entries:
-                table = cache.record(entry.request_id).tables[g]
-                flat.extend(table)
-                flat.extend([-1] * (width - len(table)))
-            tables.append(flat)
-        del page_size
+        n_seq_real = len(entries)
+        n_tok_real = sum(len(e.tokens) for e in entries)
+        n_seq = pad_to if pad_to is not None else n_seq_real
+        n_tok = pad_to if pad_to is not None else n_tok_real
+        records = [cache.record(e.request_id) for e in entries]
+        if table_widths is None:
+            table_widths = [max(1, max(len(r.tables[g]) for r in records)) for g in range(n_groups)]
+        n_out = n_tok if pad_to is not None else sum(len(e.want) for e in entries)
 
-        pieces = [token_ids, positions, tok_seq, cu_q, context_lens, state_slots, logit_rows]
+        lengths = [n_tok, n_tok, n_tok, n_seq + 1, n_seq, n_seq, n_out]
         for g in range(n_groups):
-            pieces.extend((slots[g], tables[g]))
+            lengths.extend((n_tok, n_seq * table_widths[g]))
         offsets = []
         total = 0
-        for piece in pieces:
+        for length in lengths:
             offsets.append(total)
-            total += (len(piece) + 3) & ~3          # keep every array 16-byte aligned
-        host, dev = self._int_buffers(max(total, 4))
-        flat_all = torch.zeros(total, dtype=torch.int32)
-        for piece, offset in zip(pieces, offsets):
-            if piece:
-                flat_all[offset:offset + len(piece)] = torch.tensor(piece, dtype=torch.int32)
-        if self._upload_done is not None:
-            self._upload_done.synchronize()      # the pinned buffer may still be in flight
-        host[:total].copy_(flat_all)
+            total += (length + 3) & ~3              # keep every array 16-byte aligned
+        flat = np.zeros(max(total, 4), dtype=np.int32)
+
+        def part(i: int) -> np.ndarray:
+            return flat[offsets[i]:offsets[i] + lengths[i]]
+
+        token_ids, positions, tok_seq, cu_q = part(0), part(1), part(2), part(3)
+        context_lens, state_slots, logit_rows = part(4), part(5), part(6)
+        tok_seq[:] = -1
+        context_list: list[int] = []
+        slot_list: list[int] = []
+        fresh: list[bool] = []
+        max_kv = 0
+        base = 0
+        out_row = 0
+        for s, (entry, record) in enumerate(zip(entries, records)):
+            start = record.length
+            n = len(entry.tokens)
+            token_ids[base:base + n] = entry.tokens
+            positions[base:base + n] = np.arange(start, start + n, dtype=np.int32)
+            tok_seq[base:base + n] = s
+            cu_q[s + 1] = base + n
+            context_lens[s] = start
+            state_slots[s] = record.state_slot
+            context_list.append(start)
+            slot_list.append(record.state_slot)
+            fresh.append(record.fresh_state and start == 0)
+            if pad_to is None:
+                for index in entry.want:
+                    logit_rows[out_row] = base + index
+                    out_row += 1
+            for g in range(n_groups):
+                table = record.tables[g]
+                width = table_widths[g]
+                if len(table) > width:
+                    raise StepError(f"request {entry.request_id!r} holds {len(table)} pages, "
+                                    f"the fixed table width is {width}")
+                row = part(8 + 2 * g)[s * width:(s + 1) * width]
+                row[:len(table)] = table
+                row[len(table):] = -1
+                slots_g = part(7 + 2 * g)
+                if n == 1:
+                    page = table[start // page_size]
+                    if page < 0:
+                        raise StepError(f"position {start} of {entry.request_id!r} has no page")
+                    slots_g[base] = page * page_size + start % page_size
+                else:
+                    slots_g[base:base + n] = cache.slot_ids(entry.request_id, g, start, n)
+            max_kv = max(max_kv, start + n)
+            base += n
+        if pad_to is not None:
+            cu_q[n_seq_real + 1:] = base
+            logit_rows[:] = np.arange(n_tok, dtype=np.int32)
+            for g in range(n_groups):
+                part(7 + 2 * g)[n_tok_real:] = -1
+                part(8 + 2 * g)[n_seq_real * table_widths[g]:] = -1
+
+        if buffers is None:
+            host, dev = self._int_buffers(max(total, 4))
+            if self._upload_done is None:
+                self._upload_done = torch.cuda.Event()
+            done = self._upload_done
+        else:
+            host, dev, done = buffers
+        done.synchronize()                           # the pinned buffer may still be in flight
+        host[:total].copy_(torch.from_numpy(flat[:total]))
         dev[:total].copy_(host[:total], non_blocking=True)
+        done.record()
         self.last_upload_bytes = total * 4
-        if self._upload_done is None:
-            self._upload_done = torch.cuda.Event()
-        self._upload_done.record()
 
         def view(i: int) -> torch.Tensor:
-            return dev[offsets[i]:offsets[i] + len(pieces[i])]
+            return dev[offsets[i]:offsets[i] + lengths[i]]
 
         ctx = StepContext(self)
         ctx.n_tokens, ctx.n_seqs, ctx.max_kv_len = n_tok, n_seq, max_kv
         ctx.token_ids, ctx.positions, ctx.tok_seq = view(0), view(1), view(2)
         ctx.cu_q, ctx.context_lens, ctx.state_slots, ctx.logit_rows = view(3), view(4), view(5), view(6)
         ctx.groups = [GroupStep(slots=view(7 + 2 * g),
-                                block_tables=view(8 + 2 * g).view(n_seq, widths[g]))
+                                block_tables=view(8 + 2 * g).view(n_seq, table_widths[g]))
                       for g in range(n_groups)]
-        ctx.host = HostStep(q_lens=[len(e.tokens) for e in entries], context_lens=context_lens,
-                            state_slots=state_slots, fresh=fresh)
-        for slot, is_fresh in zip(state_slots, fresh):
+        ctx.host = HostStep(q_lens=[len(e.tokens) for e in entries], context_lens=context_list,
+                            state_slots=slot_list, fresh=fresh)
+        for slot, is_fresh in zip(slot_list, fresh):
             if is_fresh:
                 self.storage.zero_state(slot)
         return ctx
 
     # ------------------------------------------------------------------ running a step
+    def _forward(self, ctx: StepContext) -> torch.Tensor | None:
+        hidden = self.model.forward(ctx)
+        if ctx.logit_rows.numel() == 0:
+            return None
+        return self.model.logits(hidden, ctx.logit_rows)
+
+    def _graph_bucket(self, entries: list[StepEntry]) -> int | None:
+        """The captured batch size a pure decode step can replay, or None for an eager step."""
+        if not self.use_graphs or self.model.cache_plan.state_bytes_per_request:
+            return None
+        if len(entries) > self.max_graph_batch:
+            return None
+        if any(len(e.tokens) != 1 or e.want != [0] for e in entries):
+            return None
+        page_size = self.cache.page_size
+        for entry in entries:
+            if not self.cache.has_request(entry.request_id):
+                return None
+            if self.cache.record(entry.request_id).length // page_size >= self.graph_table_width:
+                return None                      # longer than the captured block tables
+        bucket = 1
+        while bucket < len(entries):
+            bucket *= 2
+        return bucket
+
+    def _run_graph(self, entries: list[StepEntry], bucket: int) -> torch.Tensor:
+        record = self._graphs.get(bucket)
+        widths = [self.graph_table_width] * len(self.cache.rules)
+        if record is None:
+            layout_ints = 16 * bucket + 64 + sum(bucket * (w + 4) for w in widths)
+            buffers = (torch.empty(layout_ints, dtype=torch.int32, pin_memory=True),
+                       torch.zeros(layout_ints, dtype=torch.int32, device=self.device),
+                       torch.cuda.Event())
+            buffers[2].record()
+            ctx = self.build(entries, pad_to=bucket, table_widths=widths, buffers=buffers)
+            ctx.max_kv_len = self.graph_table_width * self.cache.page_size
+            launches_before = kernels.launch_count
+            self._forward(ctx)                                   # warm-up, outside the capture
+            self.launches_per_step = kernels.launch_count - launches_before
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            ctx.capturing = True
+            with torch.cuda.graph(graph, pool=self._graph_pool):
+                static_logits = self._forward(ctx)
+            ctx.capturing = False
+            if self._graph_pool is None:
+                self._graph_pool = graph.pool()
+            self._graphs[bucket] = (graph, static_logits, buffers, self.launches_per_step)
+            graph.replay()
+            return static_logits[:len(entries)]
+        graph, static_logits, buffers, launches = record
+        self.build(entries, pad_to=bucket, table_widths=widths, buffers=buffers)
+        graph.replay()
+        self.launches_per_step = launches
+        return static_logits[:len(entries)]
+
     def run(self, entries: list[StepEntry]) -> torch.Tensor | None:
         """Runs the entries as one batch and commits them. Returns float32 logits
-        [wanted, vocab] in the order of the entries and of each ``want``, or None."""
-        ctx = self.build(entries)
-        launches_before = kernels.launch_count
+        [wanted, vocab] in the order of the entries and of each ``want``, or None.
+
+        A step of single decode tokens replays a CUDA graph captured for its batch size
+        (rounded up to a power of two with padding rows); the logits it returns live in the
+        graph's memory and are overwritten by the next step of that size."""
+        bucket = self._graph_bucket(entries)
         try:
-            hidden = self.model.forward(ctx)
-            logits = None
-            if ctx.logit_rows.numel() > 0:
-                logits = self.model.logits(hidden, ctx.logit_rows)
+            if bucket is not None:
+                logits = self._run_graph(entries, bucket)
+            else:
+                ctx = self.build(entries)
+                launches_before = kernels.launch_count
+                logits = self._forward(ctx)
+                self.launches_per_step = kernels.launch_count - launches_before
+        except OutOfPages:
+            raise
         except Exception:
             for entry in entries:
-                self.cache.cancel_reservation(entry.request_id)
+                if self.cache.has_request(entry.request_id):
+                    self.cache.cancel_reservation(entry.request_id)
             raise
         for entry in entries:
             self.cache.commit(entry.request_id, len(entry.tokens))
         self.steps_run += 1
-        self.tokens_run += ctx.n_tokens
-        self.launches_per_step = kernels.launch_count - launches_before
+        self.tokens_run += len(entries) if bucket is not None else sum(len(e.tokens) for e in entries)
         return logits
 
     def check_status(self) -> None:
