@@ -1,8 +1,10 @@
 """Device tensors behind the cache manager's page numbers and state slots.
 
-One allocation per group: [entries, pages, 2 (k, v), kv heads, page_size, head_dim]
-in the runtime dtype, so that one page's keys for one KV head are a contiguous
-``page_size x head_dim`` tile. Fixed-size state: one tensor [slots, *shape] per
+One allocation per group: [entries, pages, 2 (k, v), kv heads, page_size * head_dim]
+in the runtime dtype (kept 6-D as [..., page_size, head_dim] for its element count). One
+page's keys for one KV head are a contiguous ``[slot][dim]`` tile; its values are stored
+transposed as ``[dim][slot]``, which lets a tensor-core kernel read the keys of one value
+dimension with one 16-byte load. ``keys_view`` / ``values_view`` give the two layouts names. Fixed-size state: one tensor [slots, *shape] per
 schedule entry that asks for it (the reference allocates conv/ssm state per
 recurrent layer the same way, app/runtime/mamba_cache.py:63-70).
 """
@@ -46,6 +48,17 @@ class CacheStorage:
         total = sum(t.numel() * t.element_size() for t in self.groups)
         total += sum(t.numel() * t.element_size() for t in self.states if t is not None)
         return total
+
+
+def keys_view(entry_cache: torch.Tensor) -> torch.Tensor:
+    """[pages, kv heads, page_size, head_dim] view of the keys of one schedule entry's cache."""
+    return entry_cache[:, 0]
+
+
+def values_view(entry_cache: torch.Tensor) -> torch.Tensor:
+    """[pages, kv heads, head_dim, page_size] view of the (transposed) values."""
+    pages, _, heads, page_size, dim = entry_cache.shape
+    return entry_cache[:, 1].reshape(pages, heads, page_size * dim).view(pages, heads, dim, page_size)
 
 
 def bytes_per_token(plan: CachePlan, dtype: torch.dtype) -> int:

@@ -11,8 +11,9 @@
 // chunks. With more than one split each block writes an unnormalised partial (max, sum, weighted
 // values) and mx_attention_merge combines them in a fixed order.
 //
-// Cache layout: [page][2 (k, v)][kv head][page_size][head_dim]; block_tables[seq][logical page]
-// gives the physical page, negative when the request holds none there.
+// Cache layout: [page][2 (k, v)][kv head][page_size x head_dim]: keys as [slot][dim], values
+// transposed as [dim][slot]; block_tables[seq][logical page] gives the physical page, negative
+// when the request holds none there. page_size must be a multiple of 8.
 #include <math.h>
 
 #include "common.cuh"
@@ -129,11 +130,11 @@ paged_attention_kernel(const AttnParams p) {
 
     for (int ci = c_begin; ci < c_end; ++ci) {
         const int c0 = ci * KEYS;
-        // ---- stage the chunk's K and V rows (zero for keys outside [lo, hi])
+        // ---- stage the chunk's K rows (zero for keys outside [lo, hi])
         for (int item = tid; item < KEYS * cpr; item += ATT_THREADS) {
             const int j = item / cpr, c = item - j * cpr;
             const int kpos = c0 + j;
-            uint4 kv = make_uint4(0, 0, 0, 0), vv = make_uint4(0, 0, 0, 0);
+            uint4 kv = make_uint4(0, 0, 0, 0);
             if (kpos >= lo && kpos <= hi) {
                 const int lp = kpos / p.page_size;
                 const long long page = (lp < p.bt_stride) ? bt[lp] : -1;
@@ -143,13 +144,37 @@ paged_attention_kernel(const AttnParams p) {
                     const int off = kpos - lp * p.page_size;
                     const T* kptr = cache + ((size_t)page * 2 * p.n_kv_heads + kh) * head_stride +
                                     (size_t)off * hd + (size_t)c * E;
-                    const T* vptr = kptr + (size_t)p.n_kv_heads * head_stride;
                     kv = *reinterpret_cast<const uint4*>(kptr);
-                    vv = *reinterpret_cast<const uint4*>(vptr);
                 }
             }
             k_s[j * cpr + (c ^ (j & swz_mask))] = kv;
-            v_s[j * cpr + c] = vv;
+        }
+        // ---- stage V: global holds [dim][slot]; shared memory wants [key][dim]
+        {
+            constexpr int GROUPS = KEYS / E;                  // runs of E keys, each inside one page
+            T* v_t = reinterpret_cast<T*>(v_s);
+            for (int item = tid; item < hd * GROUPS; item += ATT_THREADS) {
+                const int d = item / GROUPS, jg = item - d * GROUPS;
+                const int kpos0 = c0 + jg * E;
+                uint4 raw = make_uint4(0, 0, 0, 0);
+                if (kpos0 <= hi && kpos0 + E - 1 >= lo) {
+                    const int lp = kpos0 / p.page_size;
+                    const long long page = (lp < p.bt_stride) ? bt[lp] : -1;
+                    if (page >= 0 && page < p.n_pages) {
+                        const int off = kpos0 - lp * p.page_size;
+                        const T* vptr = cache + ((size_t)page * 2 * p.n_kv_heads + p.n_kv_heads + kh) * head_stride +
+                                        (size_t)d * p.page_size + off;
+                        raw = *reinterpret_cast<const uint4*>(vptr);
+                    }
+                }
+                const T* elems = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+                for (int e = 0; e < E; ++e) {
+                    const int kpos = kpos0 + e;
+                    v_t[(size_t)(jg * E + e) * hd + d] =
+                        (kpos >= lo && kpos <= hi) ? elems[e] : from_float<T>(0.f);
+                }
+            }
         }
         __syncthreads();
 
@@ -331,7 +356,8 @@ extern "C" int mx_paged_attention(const void* q, int dtype, int q_stride, const 
         MX_REFUSE("attention: %d heads are not a multiple of %d kv heads", n_heads, n_kv_heads);
     if (head_dim % 16 != 0 || head_dim < 16 || head_dim > 256)
         MX_REFUSE("attention: head_dim %d is not a multiple of 16 in [16, 256]", head_dim);
-    if (page_size <= 0) MX_REFUSE("attention: page size %d", page_size);
+    if (page_size <= 0 || page_size % 8 != 0)
+        MX_REFUSE("attention: page size %d is not a positive multiple of 8", page_size);
     if (n_splits < 1) MX_REFUSE("attention: n_splits %d", n_splits);
     if (n_splits > 1 && scratch == nullptr) MX_REFUSE("attention: split path without scratch memory");
     if (n_splits > 65535) MX_REFUSE("attention: %d splits exceed the grid's third dimension", n_splits);
@@ -348,6 +374,17 @@ extern "C" int mx_paged_attention(const void* q, int dtype, int q_stride, const 
         return two ? launch_attention<float, 2>(p, n_tokens, stream) : launch_attention<float, 1>(p, n_tokens, stream);
     return two ? launch_attention<__nv_bfloat16, 2>(p, n_tokens, stream)
                : launch_attention<__nv_bfloat16, 1>(p, n_tokens, stream);
+}
+
+// The merge step alone, for kernels in other files that write partials in this layout.
+extern "C" int mx_attention_merge_bf16(const float* part_o, const float* part_ml, void* out,
+                                       int out_stride, int n_tokens, int n_heads, int head_dim,
+                                       int n_splits, cudaStream_t stream) {
+    if (n_tokens <= 0) return MX_OK;
+    dim3 mgrid(n_tokens, n_heads);
+    attention_merge_kernel<__nv_bfloat16><<<mgrid, 128, 0, stream>>>(
+        part_o, part_ml, (__nv_bfloat16*)out, out_stride, n_heads, head_dim, n_splits);
+    return mx_launch_status();
 }
 
 // ---------------------------------------------------------------------------------------------

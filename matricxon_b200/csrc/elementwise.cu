@@ -106,7 +106,8 @@ extern "C" int mx_layernorm(const float* x, const int* rows, const float* weight
 // ---------------------------------------------------------------- rotary + cache write
 // qkv rows are [q heads | k heads | v heads], each head `head_dim` wide. q is rotated in
 // place; k is rotated and stored, v is stored, at `slot = page * page_size + offset` of a
-// cache laid out [page][2 (k,v)][kv head][page_size][head_dim]. Angles and the rotation
+// cache laid out [page][2 (k,v)][kv head][page_size x head_dim], keys as [slot][dim] and values
+// transposed as [dim][slot] (so a tensor-core B operand reads keys contiguously). Angles and the rotation
 // are float; one rounding to T at the end. With write_cache == 0 only q is rotated. A slot of
 // -1 marks a padding row (rotated, not stored); any other slot outside the pool sets the
 // status bit MX_STATUS_BAD_SLOT.
@@ -150,8 +151,9 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int row_stride,
     const long long page = slot / page_size;
     const int offset = (int)(slot - page * page_size);
     const size_t head_stride = (size_t)page_size * head_dim;
+    // keys: [page][0][kv head][slot][dim]; values transposed: [page][1][kv head][dim][slot]
     T* kbase = cache + ((size_t)page * 2 * n_kv_heads) * head_stride + (size_t)offset * head_dim;
-    T* vbase = kbase + (size_t)n_kv_heads * head_stride;
+    T* vbase = cache + ((size_t)page * 2 * n_kv_heads + n_kv_heads) * head_stride + offset;
     const T* krow = row + (size_t)n_heads * head_dim;
     const T* vrow = krow + (size_t)n_kv_heads * head_dim;
 
@@ -172,7 +174,7 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int row_stride,
     }
     for (int item = threadIdx.x; item < n_kv_heads * head_dim; item += blockDim.x) {
         const int h = item / head_dim, i = item - h * head_dim;
-        vbase[(size_t)h * head_stride + i] = vrow[(size_t)h * head_dim + i];
+        vbase[(size_t)h * head_stride + (size_t)i * page_size] = vrow[(size_t)h * head_dim + i];
     }
 }
 

@@ -75,12 +75,52 @@ class StepContext:
         self.status: torch.Tensor = runner.status
         self.host: HostStep = None
         self.capturing = False        # inside a CUDA-graph capture: buffers must belong to the graph
+        self.padded = False           # a fixed-size decode batch: every sequence has one row or none
+        self._tiles: dict[int, tuple[torch.Tensor, int]] = {}
 
     def hidden(self, hidden_size: int) -> torch.Tensor:
         if self.capturing:
             return torch.empty((self.n_tokens, hidden_size), dtype=torch.float32,
                                device=self.token_ids.device)
         return self._runner.hidden_buffer(self.n_tokens, hidden_size)
+
+    def attention_tiles(self, group: int) -> tuple[torch.Tensor, int]:
+        """(sequence, first row) of every 16-row tile of the step's (token, head-in-group)
+        rows, for query groups of ``group`` heads; built once per step and group size."""
+        cached = self._tiles.get(group)
+        if cached is not None:
+            return cached
+        if self.padded:
+            q_lens = [1] * self.n_seqs
+        else:
+            q_lens = self.host.q_lens
+        pairs: list[int] = []
+        for seq, q_len in enumerate(q_lens):
+            for row in range(0, q_len * group, 16):
+                pairs.extend((seq, row))
+        tiles = torch.tensor(pairs, dtype=torch.int32).to(self.token_ids.device, non_blocking=True)
+        self._tiles[group] = (tiles, len(pairs) // 2)
+        return self._tiles[group]
+
+    def tile_splits(self, n_tiles: int, n_heads: int, n_kv_heads: int, head_dim: int,
+                    window: int | None) -> tuple[int, torch.Tensor | None]:
+        """Key splits for the tensor-core attention, where one warp is one work item: enough
+        items to give every SM a dozen warps, never less than one 32-key chunk per split."""
+        items = max(n_tiles * n_kv_heads, 1)
+        span = self.max_kv_len if window is None else min(self.max_kv_len, window)
+        chunks = span // 32 + 1
+        target = self._runner.sm_count * 16
+        n_splits = max(1, min(target // items, chunks, 128))
+        while n_splits > 1 and kernels.attention_scratch_bytes(
+                self.n_tokens, n_heads, head_dim, n_splits) > (256 << 20):
+            n_splits //= 2
+        if n_splits == 1:
+            return 1, None
+        need = kernels.attention_scratch_bytes(self.n_tokens, n_heads, head_dim, n_splits)
+        if self.capturing:
+            return n_splits, torch.empty((need + 3) // 4, dtype=torch.float32,
+                                         device=self.token_ids.device)
+        return n_splits, self._runner.scratch_buffer(need)
 
     def attention_splits(self, n_heads: int, n_kv_heads: int, head_dim: int,
                          window: int | None) -> tuple[int, torch.Tensor | None]:
@@ -292,6 +332,7 @@ class StepRunner:
 
         ctx = StepContext(self)
         ctx.n_tokens, ctx.n_seqs, ctx.max_kv_len = n_tok, n_seq, max_kv
+        ctx.padded = pad_to is not None
         ctx.token_ids, ctx.positions, ctx.tok_seq = view(0), view(1), view(2)
         ctx.cu_q, ctx.context_lens, ctx.state_slots, ctx.logit_rows = view(3), view(4), view(5), view(6)
         ctx.groups = [GroupStep(slots=view(7 + 2 * g),

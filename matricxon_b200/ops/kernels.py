@@ -185,3 +185,39 @@ def paged_attention(q: torch.Tensor, q_stride: int, cache: torch.Tensor, block_t
         n_heads, n_kv_heads, head_dim, int(window or 0), float(scale), _ptr(out), out.stride(0),
         n_splits, _ptr(scratch), _ptr(status), _stream()), "paged_attention")
     _launched(2 if n_splits > 1 else 1)
+
+
+def paged_attention_mma(q: torch.Tensor, q_stride: int, cache: torch.Tensor,
+                        block_tables: torch.Tensor, cu_q: torch.Tensor, context_lens: torch.Tensor,
+                        tiles: torch.Tensor, n_tiles: int, n_tokens: int, n_heads: int,
+                        n_kv_heads: int, head_dim: int, window: int | None, scale: float,
+                        out: torch.Tensor, status: torch.Tensor, n_splits: int = 1,
+                        scratch: torch.Tensor | None = None) -> None:
+    """Tensor-core attention (bfloat16, head_dim 64 or 128). ``tiles`` is int32 [n_tiles, 2]:
+    (sequence, first row) of each 16-row tile of the (token, head-in-group) rows."""
+    _need(q, "q", torch.bfloat16, contiguous=False)
+    _need(cache, "cache", torch.bfloat16)
+    for name, tensor in (("block_tables", block_tables), ("cu_q", cu_q),
+                         ("context_lens", context_lens), ("tiles", tiles), ("status", status)):
+        _need(tensor, name, torch.int32)
+    _need(out, "out", torch.bfloat16)
+    page_size = cache.shape[3]
+    assert tuple(cache.shape[1:]) == (2, n_kv_heads, page_size, head_dim), cache.shape
+    assert out.shape[1] == n_heads * head_dim and out.shape[0] >= n_tokens
+    assert tiles.numel() >= 2 * n_tiles
+    if n_splits > 1:
+        need = attention_scratch_bytes(n_tokens, n_heads, head_dim, n_splits)
+        if scratch is None or scratch.numel() * scratch.element_size() < need:
+            raise KernelLibraryError(f"attention with {n_splits} splits needs {need} bytes of scratch")
+        _need(scratch, "scratch", torch.float32)
+    check(library().mx_paged_attention_mma(
+        _ptr(q), q_stride, _ptr(cache), cache.shape[0], page_size, _ptr(block_tables),
+        block_tables.stride(0), _ptr(cu_q), _ptr(context_lens), _ptr(tiles), n_tiles, n_tokens,
+        n_heads, n_kv_heads, head_dim, int(window or 0), float(scale), _ptr(out), out.stride(0),
+        n_splits, _ptr(scratch), _ptr(status), _stream()), "paged_attention_mma")
+    _launched(2 if n_splits > 1 else 1)
+
+
+def mma_attention_supported(dtype: torch.dtype, head_dim: int, page_size: int, q_stride: int) -> bool:
+    return (dtype == torch.bfloat16 and head_dim in (64, 128) and page_size % 8 == 0
+            and q_stride % 8 == 0)

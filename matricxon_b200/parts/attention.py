@@ -72,11 +72,21 @@ class PagedAttention(Mixer):
                                    spec.head_dim, rt.page_size)
         group = ctx.groups[binding.group]
         attn = torch.empty((ctx.n_tokens, self.q_size), dtype=rt.dtype, device=h.device)
-        n_splits, scratch = ctx.attention_splits(spec.num_heads, spec.num_kv_heads, spec.head_dim,
-                                                 spec.window)
-        kernels.paged_attention(qkv, qkv.stride(0), binding.kv, group.block_tables, ctx.tok_seq,
-                                ctx.positions, ctx.n_tokens, spec.num_heads, spec.num_kv_heads,
-                                spec.head_dim, spec.window, spec.scale, attn, ctx.status,
-                                n_splits=n_splits, scratch=scratch)
+        if kernels.mma_attention_supported(rt.dtype, spec.head_dim, rt.page_size, qkv.stride(0)):
+            tiles, n_tiles = ctx.attention_tiles(spec.num_heads // spec.num_kv_heads)
+            n_splits, scratch = ctx.tile_splits(n_tiles, spec.num_heads, spec.num_kv_heads,
+                                                spec.head_dim, spec.window)
+            kernels.paged_attention_mma(qkv, qkv.stride(0), binding.kv, group.block_tables,
+                                        ctx.cu_q, ctx.context_lens, tiles, n_tiles, ctx.n_tokens,
+                                        spec.num_heads, spec.num_kv_heads, spec.head_dim,
+                                        spec.window, spec.scale, attn, ctx.status,
+                                        n_splits=n_splits, scratch=scratch)
+        else:
+            n_splits, scratch = ctx.attention_splits(spec.num_heads, spec.num_kv_heads,
+                                                     spec.head_dim, spec.window)
+            kernels.paged_attention(qkv, qkv.stride(0), binding.kv, group.block_tables, ctx.tok_seq,
+                                    ctx.positions, ctx.n_tokens, spec.num_heads, spec.num_kv_heads,
+                                    spec.head_dim, spec.window, spec.scale, attn, ctx.status,
+                                    n_splits=n_splits, scratch=scratch)
         return linear(attn, self.o_weight, self.o_bias, EPILOGUE_RESIDUAL, residual=residual,
                       out=residual, backend=rt.gemm_backend)

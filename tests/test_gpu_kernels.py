@@ -153,14 +153,18 @@ def test_rope_kv_write(dtype, heads, kv_heads, dim, rot):
     assert torch.allclose(got_q, q_ref, **tol(dtype))
     # v part of the row is untouched, k part of the row is untouched (only the cache gets rotated k)
     assert torch.equal(qkv[:, heads * dim:], original[:, heads * dim:])
+    from matricxon_b200.cache.storage import keys_view, values_view
+
+    keys, values = keys_view(cache), values_view(cache)       # [p, h, slot, d] and [p, h, d, slot]
     for t in range(n):
         page, off = divmod(int(slots[t]), page_size)
-        assert torch.allclose(cache[page, 0, :, off].double().cpu(), k_ref[:, t], **tol(dtype))
-        assert torch.equal(cache[page, 1, :, off].double().cpu(), vv[:, t])
+        assert torch.allclose(keys[page, :, off].double().cpu(), k_ref[:, t], **tol(dtype))
+        assert torch.equal(values[page, :, :, off].double().cpu(), vv[:, t])
     written = torch.zeros(pages * page_size, dtype=torch.bool)
     written[slots.cpu().long()] = True
-    flat = cache.permute(0, 3, 1, 2, 4).reshape(pages * page_size, -1)
-    assert torch.isnan(flat[~written]).all() and not torch.isnan(flat[written]).any()
+    for flat in (keys.permute(0, 2, 1, 3).reshape(pages * page_size, -1),
+                 values.permute(0, 3, 1, 2).reshape(pages * page_size, -1)):
+        assert torch.isnan(flat[~written]).all() and not torch.isnan(flat[written]).any()
 
 
 def test_rope_bad_slot_sets_status_and_padding_slot_is_silent():
@@ -206,7 +210,8 @@ def paged_case(dtype, heads, kv_heads, dim, page_size, seq_lens, q_lens, seed, s
             tables[s, lp] = page
             lo, hi = lp * page_size, min(length, (lp + 1) * page_size)
             cache[page, 0, :, : hi - lo] = ks[:, lo:hi]
-            cache[page, 1, :, : hi - lo] = vs[:, lo:hi]
+            # values are stored transposed: [kv head][dim][slot]
+            cache[page, 1].view(kv_heads, dim, page_size)[:, :, : hi - lo] = vs[:, lo:hi].transpose(1, 2)
     q_rows, tok_seq, positions = [], [], []
     for s, (qs, _, _) in enumerate(dense):
         for i in range(q_lens[s]):
@@ -228,7 +233,8 @@ def reference_attention(dense, q_lens, seq_lens, scale, window):
     return torch.cat(rows)
 
 
-def run_attention(k, q, cache, tables, tok_seq, positions, heads, kv_heads, dim, window, scale, n_splits):
+def run_attention(k, q, cache, tables, tok_seq, positions, heads, kv_heads, dim, window, scale, n_splits,
+                  impl="simt"):
     n = q.shape[0]
     out = torch.full((n, heads * dim), float("nan"), dtype=q.dtype, device=DEV)
     st = status()
@@ -236,14 +242,32 @@ def run_attention(k, q, cache, tables, tok_seq, positions, heads, kv_heads, dim,
     if n_splits > 1:
         need = k.attention_scratch_bytes(n, heads, dim, n_splits)
         scratch = torch.full((need // 4,), float("nan"), device=DEV)
-    k.paged_attention(q, q.stride(0), cache, tables, tok_seq, positions, n, heads, kv_heads, dim,
-                      window, scale, out, st, n_splits=n_splits, scratch=scratch)
+    if impl == "simt":
+        k.paged_attention(q, q.stride(0), cache, tables, tok_seq, positions, n, heads, kv_heads, dim,
+                          window, scale, out, st, n_splits=n_splits, scratch=scratch)
+        return out, st.item()
+    # the tensor-core kernel takes per-sequence metadata and a list of 16-row tiles
+    seq_ids = tok_seq.cpu().tolist()
+    n_seq = max(seq_ids) + 1
+    q_lens = [seq_ids.count(s) for s in range(n_seq)]
+    cu_q = [0]
+    for length in q_lens:
+        cu_q.append(cu_q[-1] + length)
+    pos = positions.cpu().tolist()
+    context = [pos[cu_q[s]] for s in range(n_seq)]
+    group = heads // kv_heads
+    tiles = [v for s in range(n_seq) for row in range(0, q_lens[s] * group, 16) for v in (s, row)]
+    as_int = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    k.paged_attention_mma(q, q.stride(0), cache, tables, as_int(cu_q), as_int(context), as_int(tiles),
+                          len(tiles) // 2, n, heads, kv_heads, dim, window, scale, out, st,
+                          n_splits=n_splits, scratch=scratch)
     return out, st.item()
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("heads,kv_heads,dim,page_size", [
-    (4, 2, 16, 16), (3, 1, 32, 16), (24, 2, 128, 16), (5, 5, 48, 8), (40, 2, 64, 32), (2, 1, 256, 16)])
+    (4, 2, 16, 16), (3, 1, 32, 16), (24, 2, 128, 16), (5, 5, 48, 8), (40, 2, 64, 32), (2, 1, 256, 16),
+    (8, 8, 64, 16), (14, 2, 128, 64)])
 @pytest.mark.parametrize("window", [None, 24, 100])
 def test_paged_attention_mixed_batch(dtype, heads, kv_heads, dim, page_size, window):
     k = kernels()
@@ -259,14 +283,37 @@ def test_paged_attention_mixed_batch(dtype, heads, kv_heads, dim, page_size, win
         assert torch.allclose(out.double().cpu(), ref, **tol(dtype)), (n_splits, (out.double().cpu() - ref).abs().max())
 
 
+@pytest.mark.parametrize("heads,kv_heads,dim,page_size", [
+    (24, 2, 128, 16), (4, 4, 64, 16), (14, 2, 64, 8), (7, 1, 128, 32), (32, 2, 128, 16), (6, 3, 64, 64)])
+@pytest.mark.parametrize("window", [None, 24, 100])
+def test_tensor_core_attention_mixed_batch(heads, kv_heads, dim, page_size, window):
+    """The bfloat16 tensor-core kernel on decode rows, short portions and a long portion at
+    once, over a cache whose unwritten slots hold NaN."""
+    k = kernels()
+    seq_lens, q_lens = [1, 37, 130, 64, 301, 257], [1, 37, 1, 5, 2, 257]
+    scale = dim ** -0.5
+    q, cache, tables, tok_seq, positions, dense = paged_case(
+        torch.bfloat16, heads, kv_heads, dim, page_size, seq_lens, q_lens, seed=dim + heads)
+    ref = reference_attention(dense, q_lens, seq_lens, scale, window)
+    for n_splits in (1, 3, 16):
+        out, st = run_attention(k, q, cache, tables, tok_seq, positions, heads, kv_heads, dim,
+                                window, scale, n_splits, impl="mma")
+        assert st == 0
+        worst = (out.double().cpu() - ref).abs().max(dim=1).values
+        assert torch.allclose(out.double().cpu(), ref, **tol(torch.bfloat16)), (n_splits, worst.argmax(), worst.max())
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("edge", ["window_first_visible", "just_outside_window", "page_last_slot",
                                   "page_first_slot", "self", "far_key_full_attention"])
-def test_paged_attention_one_key_stands_out(dtype, edge):
+@pytest.mark.parametrize("impl", ["simt", "mma"])
+def test_paged_attention_one_key_stands_out(dtype, edge, impl):
     """One key gets a score far above the rest, so the output is (almost) that key's value if
     it is visible and unchanged by it if it is not: a wrong mask edge or page offset shows."""
+    if impl == "mma" and dtype != torch.bfloat16:
+        pytest.skip("the tensor-core kernel is bfloat16 only")
     k = kernels()
-    heads, kv_heads, dim, page_size = 4, 2, 32, 16
+    heads, kv_heads, dim, page_size = 4, 2, (64 if impl == "mma" else 32), 16
     length, window = 400, 96
     p = length - 1
     target = {"window_first_visible": p - window + 1, "just_outside_window": p - window,
@@ -284,7 +331,7 @@ def test_paged_attention_one_key_stands_out(dtype, edge):
     ref = reference_attention(dense, [1], [length], scale, use_window)
     for n_splits in (1, 4):
         out, st = run_attention(k, q, cache, tables, tok_seq, positions, heads, kv_heads, dim,
-                                use_window, scale, n_splits)
+                                use_window, scale, n_splits, impl=impl)
         assert st == 0
         assert torch.allclose(out.double().cpu(), ref, **tol(dtype))
     qs, ks, vs = dense[0]
