@@ -393,10 +393,12 @@ class StepRunner:
             ctx.capturing = False
             if self._graph_pool is None:
                 self._graph_pool = graph.pool()
-            self._graphs[bucket] = (graph, static_logits, buffers, self.launches_per_step)
+            # the captured kernels hold raw pointers into everything the context owns (the tile
+            # list among them), so the context lives as long as the graph
+            self._graphs[bucket] = (graph, static_logits, buffers, self.launches_per_step, ctx)
             graph.replay()
             return static_logits[:len(entries)]
-        graph, static_logits, buffers, launches = record
+        graph, static_logits, buffers, launches, _ctx = record
         self.build(entries, pad_to=bucket, table_widths=widths, buffers=buffers)
         graph.replay()
         self.launches_per_step = launches
