@@ -1,29 +1,31 @@
-// Tensor-core paged attention for bfloat16: prefill portions and decode tokens in one kernel.
+// Tensor-core paged attention for bfloat16: prompt portions and decode tokens.
 //
 // Same mathematics and visibility rule as attention.cu (query at p sees key j iff j <= p and
 // (window == 0 or j > p - window); scores q.k * scale; float softmax; query head h reads KV
 // head h / group), cf. app/native/src/mx_attention.c:16-68 and
 // app/architectures/qwen_layers.py:12-17,94-100.
 //
-// Rows. For one sequence and one KV head, the query rows are the pairs (token, head in
+// Rows. For one sequence and one KV head the query rows are the pairs (token, head in
 // group), token-major: row r = t * group + h. A warp owns 16 consecutive rows (an MMA M
 // tile); with grouped queries those rows sit on one or two tokens, so they share nearly the
-// same causal limit and every key they load is used by all of them. A decode token is the
-// case of `group` rows; a prompt portion of q tokens has q * group rows.
+// same causal limit and every key they load is used by all of them.
 //
-// Work. One warp = one work item (row tile, KV head, key split); warps never talk to each
-// other, there is no shared memory and no block barrier. Keys are walked in chunks of 32
-// absolute positions. Everything stays in registers, read from global memory with 16-byte
-// loads:
-//   * S = Q K^T: mma.sync.m16n8k16 (bf16 in, float out). The contraction runs over head
-//     dims in a permuted order chosen so that each thread's A and B fragments are 16
-//     contiguous bytes of a Q row and of a K row.
-//   * the 8 score columns of an MMA are assigned to keys so that, after the four MMAs of a
-//     chunk, thread t of a quad holds the scores of keys 8t..8t+7 of the chunk: exactly the
-//     A fragment the P V product needs, with values stored transposed ([dim][slot]) so that
-//     its B fragment is again 16 contiguous bytes.
-// With more than one split a work item writes unnormalised partials (max, sum, values) in
-// the layout of attention.cu, and that file's merge kernel combines them.
+// Work. A block of four warps owns a tile of rows of one (sequence, KV head) and a split of
+// the keys, walked in chunks of 32 absolute positions. Chunks travel from the pages to
+// shared memory through a cp.async pipeline (STAGES chunks in flight), keys as [key][dim]
+// with swizzled 16-byte pieces, values as stored, [dim][key].
+//   * "wide" tiles (64 rows, prompt portions): each warp has 16 rows of its own and every
+//     warp works on every chunk, so a chunk is fetched once for 64 rows;
+//   * "narrow" tiles (at most 16 rows, decode tokens): all four warps hold the same rows and
+//     take the chunks in turn; their partial results are combined in shared memory.
+// Per chunk and warp: S = Q K^T with mma.sync.m16n8k16 (bf16 in, float out), float online
+// softmax in registers, O += P V. Two orderings are chosen so that every fragment is 16
+// contiguous bytes: the contraction over head dims runs in a permuted order (thread t of a
+// quad takes dims 8t..8t+7 of each block of 32), and the 8 score columns of an MMA are
+// assigned to keys so that thread t ends up holding the scores of keys 8t..8t+7 of the
+// chunk, which is the A fragment of P V against values stored [dim][key].
+// With more than one split a block writes unnormalised partials (max, sum, values) in the
+// layout of attention.cu, and that file's merge kernel combines them.
 #include <math.h>
 
 #include "common.cuh"
@@ -33,6 +35,7 @@ namespace {
 constexpr int MMA_WARPS = 4;
 constexpr int MMA_THREADS = MMA_WARPS * 32;
 constexpr int CHUNK = 32;
+constexpr int STAGES = 3;
 
 struct MmaAttnParams {
     const __nv_bfloat16* q;      // [tokens][q_stride], head h at h * HD
@@ -43,7 +46,7 @@ struct MmaAttnParams {
     const int* block_tables;     // [seqs][bt_stride]
     const int* cu_q;             // [seqs + 1] first token row of each sequence
     const int* context_lens;     // [seqs] tokens cached before this step
-    const int* tiles;            // [n_tiles][2]: (sequence, first row of the 16-row tile)
+    const int* tiles;            // [n_tiles][2]: (sequence, first row of the tile)
     int* status;
     long long n_pages;
     int n_tiles, q_stride, out_stride, bt_stride;
@@ -65,50 +68,118 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
     return *reinterpret_cast<unsigned*>(&v);
 }
 
-template <int HD>
+// 16 bytes global -> shared, or 16 zero bytes when `valid` is false.
+__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gmem_src, bool valid) {
+    const unsigned dst = (unsigned)__cvta_generic_to_shared(smem_dst);
+    const int bytes = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(gmem_src), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+// Which 16-byte piece of a key row a logical piece lands in: rows that one MMA reads
+// together (keys 8a + 2b + c, a in 0..3, c in 0..1) get eight different values.
+__device__ __forceinline__ int key_swizzle(int row) { return ((row >> 3) << 1) | (row & 1); }
+
+template <int HD, bool NARROW>
 __global__ void __launch_bounds__(MMA_THREADS)
 attention_mma_kernel(const MmaAttnParams p) {
-    constexpr int KB = HD / 32;   // 32-wide blocks of the head dim (two MMA k-steps each)
-    constexpr int NB = HD / 8;    // 8-wide output column blocks
-    const int lane = threadIdx.x & 31;
-    const int g = lane >> 2, t = lane & 3;
-    const long long item = (long long)blockIdx.x * MMA_WARPS + (threadIdx.x >> 5);
-    const long long n_items = (long long)p.n_tiles * p.n_kv_heads * p.n_splits;
-    if (item >= n_items) return;
-    const int split = (int)(item % p.n_splits);
-    const int kh = (int)((item / p.n_splits) % p.n_kv_heads);
-    const int tile = (int)(item / ((long long)p.n_splits * p.n_kv_heads));
+    constexpr int KB = HD / 32;                 // 32-wide blocks of the head dim
+    constexpr int NB = HD / 8;                  // 8-wide output column blocks
+    constexpr int PIECES = HD / 8;              // 16-byte pieces per key row
+    constexpr int STAGE_ELEMS = 2 * CHUNK * HD; // keys then values
+    constexpr int TILE_ROWS = NARROW ? 16 : 16 * MMA_WARPS;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __nv_bfloat16* stages = reinterpret_cast<__nv_bfloat16*>(smem_raw);
 
-    const int seq = p.tiles[2 * tile], row0 = p.tiles[2 * tile + 1];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int tile = blockIdx.x, kh = blockIdx.y, split = blockIdx.z;
+    const int seq = p.tiles[2 * tile], tile_row0 = p.tiles[2 * tile + 1];
     const int group = p.n_heads / p.n_kv_heads;
     const int q_start = p.cu_q[seq];
     const int q_len = p.cu_q[seq + 1] - q_start;
     const int ctx = p.context_lens[seq];
     const int n_rows = q_len * group;
-    if (row0 >= n_rows) return;
+    if (tile_row0 >= n_rows) return;            // a padding sequence of a fixed-size batch
+
+    // rows of this block and of this warp
+    const int tile_last = min(tile_row0 + TILE_ROWS - 1, n_rows - 1);
+    const int row0 = NARROW ? tile_row0 : tile_row0 + 16 * warp;
+    const bool warp_has_rows = row0 < n_rows;
     const int last_row = min(row0 + 15, n_rows - 1);
 
-    // the two rows this thread owns: row0 + g and row0 + g + 8
     int r_tok[2], r_head[2], r_pos[2], r_lo[2];
     bool r_valid[2];
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
         const int r = row0 + g + 8 * i;
         r_valid[i] = r < n_rows;
-        const int rr = r_valid[i] ? r : last_row;
+        const int rr = r_valid[i] ? r : tile_last;
         r_tok[i] = rr / group;
         r_head[i] = rr - r_tok[i] * group;
         r_pos[i] = ctx + r_tok[i];
         r_lo[i] = p.window > 0 ? max(0, r_pos[i] - p.window + 1) : 0;
     }
-    const int first_tok = row0 / group, last_tok = last_row / group;
-    const int hi_tile = ctx + last_tok;
-    const int lo_tile = p.window > 0 ? max(0, ctx + first_tok - p.window + 1) : 0;
+    // key range of the block (what is fetched) and of the warp (what it computes)
+    const int hi_tile = ctx + tile_last / group;
+    const int lo_tile = p.window > 0 ? max(0, ctx + tile_row0 / group - p.window + 1) : 0;
+    const int hi_warp = warp_has_rows ? ctx + last_row / group : -1;
+    const int lo_warp = p.window > 0 ? max(0, ctx + row0 / group - p.window + 1) : 0;
     const int first_chunk = lo_tile / CHUNK, last_chunk = hi_tile / CHUNK;
     const int n_chunks = last_chunk - first_chunk + 1;
     const int per_split = (n_chunks + p.n_splits - 1) / p.n_splits;
     const int c_begin = first_chunk + split * per_split;
     const int c_end = min(last_chunk + 1, c_begin + per_split);
+
+    const int* bt = p.block_tables + (size_t)seq * p.bt_stride;
+    const size_t head_stride = (size_t)p.page_size * HD;
+    const size_t page_stride = 2 * (size_t)p.n_kv_heads * head_stride;
+    const __nv_bfloat16* kbase = p.cache + (size_t)kh * head_stride;
+    const __nv_bfloat16* vbase = p.cache + (size_t)(p.n_kv_heads + kh) * head_stride;
+
+    // ---- fetch one chunk into a stage (all threads); always followed by a commit
+    auto fetch = [&](int ci) {
+        if (ci < c_end) {
+            __nv_bfloat16* ks = stages + (size_t)((ci - c_begin) % STAGES) * STAGE_ELEMS;
+            __nv_bfloat16* vs = ks + CHUNK * HD;
+            const int c0 = ci * CHUNK;
+            for (int idx = tid; idx < CHUNK * PIECES; idx += MMA_THREADS) {
+                const int j = idx / PIECES, c = idx - j * PIECES;
+                const int key = c0 + j;
+                const __nv_bfloat16* src = p.cache;
+                bool valid = false;
+                if (key >= lo_tile && key <= hi_tile) {
+                    const int lp = key / p.page_size;
+                    const long long page = lp < p.bt_stride ? bt[lp] : -1;
+                    if (page >= 0 && page < p.n_pages) {
+                        valid = true;
+                        src = kbase + (size_t)page * page_stride + (size_t)(key - lp * p.page_size) * HD + 8 * c;
+                    } else if (c == 0) {
+                        atomicOr(p.status, MX_STATUS_BAD_PAGE);
+                    }
+                }
+                cp_async_16(ks + (size_t)j * HD + 8 * (c ^ key_swizzle(j)), src, valid);
+            }
+            for (int idx = tid; idx < HD * 4; idx += MMA_THREADS) {
+                const int d = idx >> 2, grp = idx & 3;
+                const int key0 = c0 + 8 * grp;
+                const __nv_bfloat16* src = p.cache;
+                bool valid = false;
+                if (key0 <= hi_tile && key0 + 7 >= lo_tile) {
+                    const int lp = key0 / p.page_size;
+                    const long long page = lp < p.bt_stride ? bt[lp] : -1;
+                    if (page >= 0 && page < p.n_pages) {
+                        valid = true;
+                        src = vbase + (size_t)page * page_stride + (size_t)d * p.page_size + (key0 - lp * p.page_size);
+                    }
+                }
+                cp_async_16(vs + (size_t)d * CHUNK + 8 * grp, src, valid);
+            }
+        }
+        cp_async_commit();
+    };
 
     // Q fragments: 16 bytes of each owned row per 32-wide block
     uint4 qf[2][KB];
@@ -127,34 +198,31 @@ attention_mma_kernel(const MmaAttnParams p) {
     for (int nb = 0; nb < NB; ++nb) o[nb][0] = o[nb][1] = o[nb][2] = o[nb][3] = 0.f;
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
 
-    const int* bt = p.block_tables + (size_t)seq * p.bt_stride;
-    const size_t head_stride = (size_t)p.page_size * HD;
-    const __nv_bfloat16* kbase = p.cache + (size_t)kh * head_stride;
-    const __nv_bfloat16* vbase = p.cache + (size_t)(p.n_kv_heads + kh) * head_stride;
-    const size_t page_stride = 2 * (size_t)p.n_kv_heads * head_stride;
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; ++s) fetch(c_begin + s);
 
     for (int ci = c_begin; ci < c_end; ++ci) {
+        cp_async_wait<STAGES - 2>();
+        __syncthreads();                         // chunk ci has landed; chunk ci - 1 is done with
+        fetch(ci + STAGES - 1);
         const int c0 = ci * CHUNK;
-        // ---- scores: block b of the chunk gives this thread keys 8t + 2b, 8t + 2b + 1
+        const bool mine = NARROW ? ((ci - c_begin) % MMA_WARPS == warp)
+                                 : (warp_has_rows && c0 <= hi_warp && c0 + CHUNK - 1 >= lo_warp);
+        if (!mine) continue;
+        const __nv_bfloat16* ks = stages + (size_t)((ci - c_begin) % STAGES) * STAGE_ELEMS;
+        const __nv_bfloat16* vs = ks + CHUNK * HD;
+
+        // ---- scores: block b gives this thread keys 8t + 2b, 8t + 2b + 1 of the chunk
         float s[4][4];
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
             s[b][0] = s[b][1] = s[b][2] = s[b][3] = 0.f;
-            // column g of block b is key 8 * (g / 2) + 2b + (g % 2): this thread supplies its K row
-            const int key = c0 + 8 * (g >> 1) + 2 * b + (g & 1);
-            const __nv_bfloat16* krow = nullptr;
-            if (key >= lo_tile && key <= hi_tile) {
-                const int lp = key / p.page_size;
-                const long long page = lp < p.bt_stride ? bt[lp] : -1;
-                if (page >= 0 && page < p.n_pages)
-                    krow = kbase + (size_t)page * page_stride + (size_t)(key - lp * p.page_size) * HD;
-                else if (t == 0)
-                    atomicOr(p.status, MX_STATUS_BAD_PAGE);
-            }
+            // column g of block b is key 8 (g / 2) + 2b + (g % 2); its swizzle value is g
+            const int j = 8 * (g >> 1) + 2 * b + (g & 1);
+            const __nv_bfloat16* krow = ks + (size_t)j * HD;
 #pragma unroll
             for (int kb = 0; kb < KB; ++kb) {
-                const uint4 kf = krow ? *reinterpret_cast<const uint4*>(krow + 32 * kb + 8 * t)
-                                      : make_uint4(0, 0, 0, 0);
+                const uint4 kf = *reinterpret_cast<const uint4*>(krow + 8 * ((4 * kb + t) ^ g));
                 mma_bf16(s[b], qf[0][kb].x, qf[1][kb].x, qf[0][kb].y, qf[1][kb].y, kf.x, kf.y);
                 mma_bf16(s[b], qf[0][kb].z, qf[1][kb].z, qf[0][kb].w, qf[1][kb].w, kf.z, kf.w);
             }
@@ -194,7 +262,6 @@ attention_mma_kernel(const MmaAttnParams p) {
             l_run[i] = l_run[i] * alpha[i] + sum[i];
             m_run[i] = m_new[i];
         }
-        // P as A fragments: step st uses blocks 2 st and 2 st + 1
         unsigned pa[2][4];
 #pragma unroll
         for (int st = 0; st < 2; ++st) {
@@ -203,16 +270,9 @@ attention_mma_kernel(const MmaAttnParams p) {
             pa[st][2] = pack_bf16(s[2 * st + 1][0], s[2 * st + 1][1]);
             pa[st][3] = pack_bf16(s[2 * st + 1][2], s[2 * st + 1][3]);
         }
-        // ---- values: this thread reads keys 8t..8t+7 of value dim 8 nb + g
+        // ---- values: this thread reads keys 8t..8t+7 of value dim 8 nb + g. Slots beyond the
+        // newest key hold no data yet: keep them out of the product.
         const int vkey0 = c0 + 8 * t;
-        const __nv_bfloat16* vrow = nullptr;
-        if (vkey0 <= hi_tile && vkey0 + 7 >= lo_tile) {
-            const int lp = vkey0 / p.page_size;
-            const long long page = lp < p.bt_stride ? bt[lp] : -1;
-            if (page >= 0 && page < p.n_pages)
-                vrow = vbase + (size_t)page * page_stride + (vkey0 - lp * p.page_size);
-        }
-        // slots beyond the newest key hold no data yet: keep them out of the product
         unsigned keep[4] = {0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu};
         if (vkey0 + 7 > hi_tile) {
 #pragma unroll
@@ -223,8 +283,7 @@ attention_mma_kernel(const MmaAttnParams p) {
         }
 #pragma unroll
         for (int nb = 0; nb < NB; ++nb) {
-            uint4 vf = make_uint4(0, 0, 0, 0);
-            if (vrow) vf = *reinterpret_cast<const uint4*>(vrow + (size_t)(8 * nb + g) * p.page_size);
+            uint4 vf = *reinterpret_cast<const uint4*>(vs + (size_t)(8 * nb + g) * CHUNK + 8 * t);
             vf.x &= keep[0]; vf.y &= keep[1]; vf.z &= keep[2]; vf.w &= keep[3];
             o[nb][0] *= alpha[0]; o[nb][1] *= alpha[0];
             o[nb][2] *= alpha[1]; o[nb][3] *= alpha[1];
@@ -232,8 +291,61 @@ attention_mma_kernel(const MmaAttnParams p) {
             mma_bf16(o[nb], pa[1][0], pa[1][1], pa[1][2], pa[1][3], vf.z, vf.w);
         }
     }
+    cp_async_wait<0>();
 
-    // ---- write out: this thread holds columns 8 nb + 2t, + 1 of rows g and g + 8
+    if (NARROW) {
+        // ---- combine the four warps' partial results through shared memory (stages are free)
+        __syncthreads();
+        float* red_o = reinterpret_cast<float*>(smem_raw);              // [warp][16][HD]
+        float* red_ml = red_o + MMA_WARPS * 16 * HD;                    // [warp][16][2]
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int r = g + 8 * i;
+            float* dst = red_o + ((size_t)warp * 16 + r) * HD;
+#pragma unroll
+            for (int nb = 0; nb < NB; ++nb) {
+                dst[8 * nb + 2 * t] = o[nb][2 * i];
+                dst[8 * nb + 2 * t + 1] = o[nb][2 * i + 1];
+            }
+            if (t == 0) {
+                red_ml[((size_t)warp * 16 + r) * 2] = m_run[i];
+                red_ml[((size_t)warp * 16 + r) * 2 + 1] = l_run[i];
+            }
+        }
+        __syncthreads();
+        const int rows_here = min(16, n_rows - tile_row0);
+        const float ln2 = 0.6931471805599453f;
+        for (int idx = tid; idx < rows_here * HD; idx += MMA_THREADS) {
+            const int r = idx / HD, d = idx - r * HD;
+            float m = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < MMA_WARPS; ++w) m = fmaxf(m, red_ml[((size_t)w * 16 + r) * 2]);
+            float l = 0.f, acc = 0.f;
+#pragma unroll
+            for (int w = 0; w < MMA_WARPS; ++w) {
+                const float mw = red_ml[((size_t)w * 16 + r) * 2];
+                const float wgt = (mw == -INFINITY) ? 0.f : exp2f(mw - m);
+                l += red_ml[((size_t)w * 16 + r) * 2 + 1] * wgt;
+                acc += red_o[((size_t)w * 16 + r) * HD + d] * wgt;
+            }
+            const int row = tile_row0 + r;
+            const int tok = row / group, head = kh * group + (row - tok * group);
+            if (p.n_splits == 1) {
+                p.out[(size_t)(q_start + tok) * p.out_stride + (size_t)head * HD + d] =
+                    __float2bfloat16_rn(acc / l);
+            } else {
+                const size_t base = ((size_t)(q_start + tok) * p.n_heads + head) * p.n_splits + split;
+                p.part_o[base * HD + d] = acc;
+                if (d == 0) {
+                    p.part_ml[base * 2] = m * ln2;     // the merge kernel works with natural logs
+                    p.part_ml[base * 2 + 1] = l;
+                }
+            }
+        }
+        return;
+    }
+
+    // ---- wide tiles: each warp writes its own rows; this thread holds columns 8 nb + 2t, + 1
     if (p.n_splits == 1) {
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
@@ -260,12 +372,28 @@ attention_mma_kernel(const MmaAttnParams p) {
                 po[8 * nb + 2 * t + 1] = o[nb][2 * i + 1];
             }
             if (t == 0) {
-                // the merge kernel works with natural-log maxima
                 p.part_ml[base * 2] = m_run[i] * ln2;
                 p.part_ml[base * 2 + 1] = l_run[i];
             }
         }
     }
+}
+
+template <int HD, bool NARROW>
+int launch_mma(const MmaAttnParams& p, cudaStream_t stream) {
+    size_t smem = (size_t)STAGES * 2 * CHUNK * HD * sizeof(__nv_bfloat16);
+    if (NARROW) {
+        const size_t reduce = (size_t)MMA_WARPS * 16 * (HD + 2) * sizeof(float);
+        if (reduce > smem) smem = reduce;
+    }
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(attention_mma_kernel<HD, NARROW>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) MX_REFUSE("attention: cannot reserve %zu bytes of shared memory", smem);
+    }
+    dim3 grid(p.n_tiles, p.n_kv_heads, p.n_splits);
+    attention_mma_kernel<HD, NARROW><<<grid, MMA_THREADS, smem, stream>>>(p);
+    return mx_launch_status();
 }
 
 }  // namespace
@@ -274,13 +402,15 @@ extern "C" int mx_attention_merge_bf16(const float* part_o, const float* part_ml
                                        int out_stride, int n_tokens, int n_heads, int head_dim,
                                        int n_splits, cudaStream_t stream);
 
+// `narrow` != 0: every tile has at most 16 rows (decode tokens); the four warps of a block
+// share them and take the key chunks in turn. Otherwise tiles are 64 rows, 16 per warp.
 extern "C" int mx_paged_attention_mma(const void* q, int q_stride, const void* cache,
                                       long long n_pages, int page_size, const int* block_tables,
                                       int bt_stride, const int* cu_q, const int* context_lens,
-                                      const int* tiles, int n_tiles, int n_tokens, int n_heads,
-                                      int n_kv_heads, int head_dim, int window, float scale,
-                                      void* out, int out_stride, int n_splits, float* scratch,
-                                      int* status, cudaStream_t stream) {
+                                      const int* tiles, int n_tiles, int narrow, int n_tokens,
+                                      int n_heads, int n_kv_heads, int head_dim, int window,
+                                      float scale, void* out, int out_stride, int n_splits,
+                                      float* scratch, int* status, cudaStream_t stream) {
     if (n_tiles <= 0 || n_tokens <= 0) return MX_OK;
     if (n_kv_heads <= 0 || n_heads % n_kv_heads != 0)
         MX_REFUSE("attention: %d heads are not a multiple of %d kv heads", n_heads, n_kv_heads);
@@ -291,6 +421,7 @@ extern "C" int mx_paged_attention_mma(const void* q, int q_stride, const void* c
     if (q_stride % 8 != 0 || out_stride % 2 != 0)
         MX_REFUSE("tensor-core attention needs 16-byte aligned query rows (stride %d)", q_stride);
     if (n_splits < 1 || n_splits > 65535) MX_REFUSE("attention: n_splits %d", n_splits);
+    if (n_kv_heads > 65535) MX_REFUSE("attention: %d kv heads exceed the grid", n_kv_heads);
     if (n_splits > 1 && scratch == nullptr) MX_REFUSE("attention: split path without scratch memory");
     MmaAttnParams p;
     p.q = (const __nv_bfloat16*)q; p.cache = (const __nv_bfloat16*)cache; p.out = (__nv_bfloat16*)out;
@@ -301,14 +432,9 @@ extern "C" int mx_paged_attention_mma(const void* q, int q_stride, const void* c
     p.out_stride = out_stride; p.bt_stride = bt_stride; p.n_heads = n_heads; p.n_kv_heads = n_kv_heads;
     p.page_size = page_size; p.window = window; p.n_splits = n_splits;
     p.scale_log2 = scale * 1.4426950408889634f;
-    const long long n_items = (long long)n_tiles * n_kv_heads * n_splits;
-    const long long blocks = (n_items + MMA_WARPS - 1) / MMA_WARPS;
-    if (blocks > 2147483647LL) MX_REFUSE("attention: too many work items");
-    if (head_dim == 64)
-        attention_mma_kernel<64><<<(unsigned)blocks, MMA_THREADS, 0, stream>>>(p);
-    else
-        attention_mma_kernel<128><<<(unsigned)blocks, MMA_THREADS, 0, stream>>>(p);
-    int rc = mx_launch_status();
+    int rc;
+    if (head_dim == 64) rc = narrow ? launch_mma<64, true>(p, stream) : launch_mma<64, false>(p, stream);
+    else rc = narrow ? launch_mma<128, true>(p, stream) : launch_mma<128, false>(p, stream);
     if (rc != MX_OK || n_splits == 1) return rc;
     return mx_attention_merge_bf16(p.part_o, p.part_ml, out, out_stride, n_tokens, n_heads, head_dim,
                                    n_splits, stream);

@@ -84,33 +84,32 @@ class StepContext:
                                device=self.token_ids.device)
         return self._runner.hidden_buffer(self.n_tokens, hidden_size)
 
-    def attention_tiles(self, group: int) -> tuple[torch.Tensor, int]:
-        """(sequence, first row) of every 16-row tile of the step's (token, head-in-group)
-        rows, for query groups of ``group`` heads; built once per step and group size."""
+    def attention_tiles(self, group: int):
+        """Tile lists of the tensor-core attention for query groups of ``group`` heads:
+        (narrow tiles, their count, wide tiles, their count); built once per step and group."""
         cached = self._tiles.get(group)
         if cached is not None:
             return cached
-        if self.padded:
-            q_lens = [1] * self.n_seqs
-        else:
-            q_lens = self.host.q_lens
-        pairs: list[int] = []
-        for seq, q_len in enumerate(q_lens):
-            for row in range(0, q_len * group, 16):
-                pairs.extend((seq, row))
-        tiles = torch.tensor(pairs, dtype=torch.int32).to(self.token_ids.device, non_blocking=True)
-        self._tiles[group] = (tiles, len(pairs) // 2)
+        q_lens = [1] * self.n_seqs if self.padded else self.host.q_lens
+        narrow, wide = kernels.attention_tile_lists(q_lens, group)
+        device = self.token_ids.device
+        both = torch.tensor(narrow + wide + [0, 0], dtype=torch.int32).to(device, non_blocking=True)
+        self._tiles[group] = (both[:len(narrow)], len(narrow) // 2,
+                              both[len(narrow):len(narrow) + len(wide)], len(wide) // 2)
         return self._tiles[group]
 
-    def tile_splits(self, n_tiles: int, n_heads: int, n_kv_heads: int, head_dim: int,
-                    window: int | None) -> tuple[int, torch.Tensor | None]:
-        """Key splits for the tensor-core attention, where one warp is one work item: enough
-        items to give every SM a dozen warps, never less than one 32-key chunk per split."""
+    def tile_splits(self, n_tiles: int, narrow: bool, alone: bool, n_heads: int, n_kv_heads: int,
+                    head_dim: int, window: int | None) -> tuple[int, torch.Tensor | None]:
+        """Key splits for one launch of the tensor-core attention (a block per tile, KV head
+        and split). Splits only pay when the tiles alone leave SMs idle, and only a launch
+        that covers every token of the step may use them (the merge runs over all tokens)."""
+        if not alone:
+            return 1, None
         items = max(n_tiles * n_kv_heads, 1)
         span = self.max_kv_len if window is None else min(self.max_kv_len, window)
         chunks = span // 32 + 1
-        target = self._runner.sm_count * 16
-        n_splits = max(1, min(target // items, chunks, 128))
+        target = self._runner.sm_count * (4 if narrow else 2)
+        n_splits = max(1, min(target // items, chunks // (4 if narrow else 8), 128))
         while n_splits > 1 and kernels.attention_scratch_bytes(
                 self.n_tokens, n_heads, head_dim, n_splits) > (256 << 20):
             n_splits //= 2

@@ -150,6 +150,34 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None,
     _launched()
 
 
+def skinny_gemm_supported(a: torch.Tensor, w: torch.Tensor) -> bool:
+    return (a.dtype == torch.bfloat16 and a.shape[0] <= 16 and a.shape[1] % 32 == 0
+            and a.stride(1) == 1 and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+            and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemm_skinny(a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None,
+                residual: torch.Tensor | None, out: torch.Tensor, mode: int) -> None:
+    """The decode product: at most 16 rows of bfloat16 ``a`` against all of ``w``, streamed once,
+    with the epilogue fused."""
+    _need(a, "a", torch.bfloat16, contiguous=False)
+    _need(w, "w", torch.bfloat16)
+    _need(out, "out")
+    m, k = a.shape
+    n = w.shape[0]
+    assert w.shape[1] == k and tuple(out.shape) == (m, n), (a.shape, w.shape, out.shape)
+    if bias is not None:
+        _need(bias, "bias", torch.float32)
+        assert bias.numel() == n
+    if residual is not None:
+        _need(residual, "residual", torch.float32)
+        assert tuple(residual.shape) == (m, n) and residual.stride(0) == out.stride(0)
+    check(library().mx_gemm_skinny(_ptr(a), _ptr(w), _ptr(bias), _ptr(residual), _ptr(out),
+                                   dtype_code(out.dtype), m, n, k, a.stride(0), w.stride(0),
+                                   out.stride(0), mode, _stream()), "gemm_skinny")
+    _launched()
+
+
 def attention_scratch_bytes(n_tokens: int, n_heads: int, head_dim: int, n_splits: int) -> int:
     return int(library().mx_attention_scratch_bytes(n_tokens, n_heads, head_dim, n_splits))
 
@@ -187,14 +215,34 @@ def paged_attention(q: torch.Tensor, q_stride: int, cache: torch.Tensor, block_t
     _launched(2 if n_splits > 1 else 1)
 
 
+def attention_tile_lists(q_lens: list[int], group: int) -> tuple[list[int], list[int]]:
+    """Row tiles of the tensor-core attention for sequences that bring ``q_lens`` tokens and
+    ``group`` query heads per KV head: flat (sequence, first row) pairs. Sequences with at most
+    16 rows (decode tokens) go to the narrow list, one tile each; the others are cut into
+    64-row tiles in the wide list."""
+    narrow: list[int] = []
+    wide: list[int] = []
+    for seq, q_len in enumerate(q_lens):
+        rows = q_len * group
+        if rows <= 0:
+            continue
+        if rows <= 16:
+            narrow.extend((seq, 0))
+        else:
+            for row in range(0, rows, 64):
+                wide.extend((seq, row))
+    return narrow, wide
+
+
 def paged_attention_mma(q: torch.Tensor, q_stride: int, cache: torch.Tensor,
                         block_tables: torch.Tensor, cu_q: torch.Tensor, context_lens: torch.Tensor,
-                        tiles: torch.Tensor, n_tiles: int, n_tokens: int, n_heads: int,
+                        tiles: torch.Tensor, n_tiles: int, narrow: bool, n_tokens: int, n_heads: int,
                         n_kv_heads: int, head_dim: int, window: int | None, scale: float,
                         out: torch.Tensor, status: torch.Tensor, n_splits: int = 1,
                         scratch: torch.Tensor | None = None) -> None:
     """Tensor-core attention (bfloat16, head_dim 64 or 128). ``tiles`` is int32 [n_tiles, 2]:
-    (sequence, first row) of each 16-row tile of the (token, head-in-group) rows."""
+    (sequence, first row) of each tile of the (token, head-in-group) rows; ``narrow`` tiles
+    hold at most 16 rows, the others 64 (see ``attention_tile_lists``)."""
     _need(q, "q", torch.bfloat16, contiguous=False)
     _need(cache, "cache", torch.bfloat16)
     for name, tensor in (("block_tables", block_tables), ("cu_q", cu_q),
@@ -212,9 +260,10 @@ def paged_attention_mma(q: torch.Tensor, q_stride: int, cache: torch.Tensor,
         _need(scratch, "scratch", torch.float32)
     check(library().mx_paged_attention_mma(
         _ptr(q), q_stride, _ptr(cache), cache.shape[0], page_size, _ptr(block_tables),
-        block_tables.stride(0), _ptr(cu_q), _ptr(context_lens), _ptr(tiles), n_tiles, n_tokens,
-        n_heads, n_kv_heads, head_dim, int(window or 0), float(scale), _ptr(out), out.stride(0),
-        n_splits, _ptr(scratch), _ptr(status), _stream()), "paged_attention_mma")
+        block_tables.stride(0), _ptr(cu_q), _ptr(context_lens), _ptr(tiles), n_tiles,
+        1 if narrow else 0, n_tokens, n_heads, n_kv_heads, head_dim, int(window or 0), float(scale),
+        _ptr(out), out.stride(0), n_splits, _ptr(scratch), _ptr(status), _stream()),
+        "paged_attention_mma")
     _launched(2 if n_splits > 1 else 1)
 
 

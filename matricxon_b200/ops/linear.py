@@ -2,10 +2,12 @@
 
 Backends, chosen by the runtime:
   "simt"    -- the engine's own FP32-core kernel; the only backend of the 32-bit path.
+  "skinny"  -- the engine's tensor-core kernel for at most 16 rows (decoding): the weight
+               matrix is streamed once and the epilogue is fused.
   "library" -- cuBLAS through ``torch.mm`` for bfloat16 (the reference runs its products
                through nn.Linear, i.e. the library: app/architectures/qwen_layers.py:50-53),
                followed by the engine's fused bias / GELU / residual epilogue kernel.
-  "auto"    -- "simt" for float32, "library" for bfloat16.
+  "auto"    -- "simt" for float32; for bfloat16 "skinny" when the shape allows it, else "library".
 """
 
 from __future__ import annotations
@@ -44,7 +46,9 @@ def resolve_backend(requested: str, dtype: torch.dtype) -> str:
             raise KernelLibraryError(
                 f"the float32 path runs on the FP32-core kernel only, not {requested!r}")
         return "simt"
-    return "library" if requested == "auto" else requested
+    if requested not in ("auto", "simt", "skinny", "library"):
+        raise KernelLibraryError(f"unknown GEMM backend {requested!r}")
+    return requested
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, mode: int,
@@ -58,6 +62,8 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, mod
     m, n = x.shape[0], weight.shape[0]
     out_dtype = torch.float32 if mode in (EPILOGUE_RESIDUAL, EPILOGUE_F32) else x.dtype
     backend = resolve_backend(backend, x.dtype)
+    if backend == "auto":
+        backend = "skinny" if kernels.skinny_gemm_supported(x, weight) else "library"
     if backend == "library" and out is None and mode == EPILOGUE_F32 and bias is None and m > 0:
         acc = _mm_f32(x, weight.t())
         if acc is not None:
@@ -69,18 +75,19 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, mod
     if backend == "simt":
         kernels.gemm_simt(x, weight, bias, residual, out, mode)
         return out
-    if backend == "library":
-        acc = None
-        if out_dtype == torch.float32:
-            acc = _mm_f32(x, weight.t())
-        if acc is None:
-            acc = torch.mm(x, weight.t())
-        if mode == EPILOGUE_F32 and bias is None and acc.dtype == torch.float32:
-            out.copy_(acc)
-            return out
-        kernels.epilogue(acc, bias, residual, out, mode)
+    if backend == "skinny":
+        kernels.gemm_skinny(x, weight, bias, residual, out, mode)
         return out
-    raise KernelLibraryError(f"unknown GEMM backend {backend!r}")
+    acc = None
+    if out_dtype == torch.float32:
+        acc = _mm_f32(x, weight.t())
+    if acc is None:
+        acc = torch.mm(x, weight.t())
+    if mode == EPILOGUE_F32 and bias is None and acc.dtype == torch.float32:
+        out.copy_(acc)
+        return out
+    kernels.epilogue(acc, bias, residual, out, mode)
+    return out
 
 
 __all__ = ["linear", "resolve_backend", "EPILOGUE_NONE", "EPILOGUE_GELU", "EPILOGUE_RESIDUAL",

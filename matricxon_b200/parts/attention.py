@@ -73,14 +73,18 @@ class PagedAttention(Mixer):
         group = ctx.groups[binding.group]
         attn = torch.empty((ctx.n_tokens, self.q_size), dtype=rt.dtype, device=h.device)
         if kernels.mma_attention_supported(rt.dtype, spec.head_dim, rt.page_size, qkv.stride(0)):
-            tiles, n_tiles = ctx.attention_tiles(spec.num_heads // spec.num_kv_heads)
-            n_splits, scratch = ctx.tile_splits(n_tiles, spec.num_heads, spec.num_kv_heads,
-                                                spec.head_dim, spec.window)
-            kernels.paged_attention_mma(qkv, qkv.stride(0), binding.kv, group.block_tables,
-                                        ctx.cu_q, ctx.context_lens, tiles, n_tiles, ctx.n_tokens,
-                                        spec.num_heads, spec.num_kv_heads, spec.head_dim,
-                                        spec.window, spec.scale, attn, ctx.status,
-                                        n_splits=n_splits, scratch=scratch)
+            narrow, n_narrow, wide, n_wide = ctx.attention_tiles(spec.num_heads // spec.num_kv_heads)
+            for tiles, n_tiles, is_narrow in ((narrow, n_narrow, True), (wide, n_wide, False)):
+                if n_tiles == 0:
+                    continue
+                alone = (n_wide == 0) if is_narrow else (n_narrow == 0)
+                n_splits, scratch = ctx.tile_splits(n_tiles, is_narrow, alone, spec.num_heads,
+                                                    spec.num_kv_heads, spec.head_dim, spec.window)
+                kernels.paged_attention_mma(qkv, qkv.stride(0), binding.kv, group.block_tables,
+                                            ctx.cu_q, ctx.context_lens, tiles, n_tiles, is_narrow,
+                                            ctx.n_tokens, spec.num_heads, spec.num_kv_heads,
+                                            spec.head_dim, spec.window, spec.scale, attn, ctx.status,
+                                            n_splits=n_splits, scratch=scratch)
         else:
             n_splits, scratch = ctx.attention_splits(spec.num_heads, spec.num_kv_heads,
                                                      spec.head_dim, spec.window)

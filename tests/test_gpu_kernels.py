@@ -103,6 +103,42 @@ def test_gemm_simt_row_result_does_not_depend_on_the_batch():
     assert torch.equal(one[0], whole[33])
 
 
+@pytest.mark.parametrize("m", [1, 3, 8, 9, 16])
+@pytest.mark.parametrize("n,k_dim", [(3584, 3072), (1000, 96), (50, 352), (17, 32)])
+def test_skinny_gemm_all_epilogues(m, n, k_dim):
+    """The decode product against float64, all epilogues, rows and columns that fill no tile."""
+    k = kernels()
+    torch.manual_seed(m * n + k_dim)
+    a = torch.randn(m, k_dim, device=DEV).bfloat16()
+    w = (torch.randn(n, k_dim, device=DEV) / math.sqrt(k_dim)).bfloat16()
+    bias = torch.randn(n, device=DEV)
+    residual = torch.randn(m, n, device=DEV)
+    assert k.skinny_gemm_supported(a, w)
+    acc = a.double().cpu() @ w.double().cpu().T + bias.double().cpu()
+    out = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=DEV)
+    k.gemm_skinny(a, w, bias, None, out, k.EPILOGUE_NONE)
+    assert torch.allclose(out.double().cpu(), acc, **tol(torch.bfloat16))
+    k.gemm_skinny(a, w, bias, None, out, k.EPILOGUE_GELU)
+    assert torch.allclose(out.double().cpu(), plain_gelu_tanh(acc), **tol(torch.bfloat16))
+    out32 = residual.clone()
+    k.gemm_skinny(a, w, bias, out32, out32, k.EPILOGUE_RESIDUAL)
+    assert torch.allclose(out32.double().cpu(), acc + residual.double().cpu(), atol=1e-4, rtol=1e-5)
+    k.gemm_skinny(a, w, None, None, out32, k.EPILOGUE_F32)
+    assert torch.allclose(out32.double().cpu(), acc - bias.double().cpu(), atol=1e-4, rtol=1e-5)
+    # a row's result does not depend on the rest of the batch
+    one = torch.empty(1, n, device=DEV)
+    k.gemm_skinny(a[m - 1:m], w, None, None, one, k.EPILOGUE_F32)
+    assert torch.equal(one[0], out32[m - 1])
+    # rows of a wider buffer (the q part of a fused qkv row, say)
+    wide = torch.randn(m, k_dim + 64, device=DEV).bfloat16()
+    view = wide[:, 32:32 + k_dim]
+    if k.skinny_gemm_supported(view, w):
+        k.gemm_skinny(view, w, None, None, out32, k.EPILOGUE_F32)
+        assert torch.allclose(out32.double().cpu(), view.double().cpu() @ w.double().cpu().T, atol=1e-4, rtol=1e-5)
+    assert not k.skinny_gemm_supported(torch.zeros(17, 64, device=DEV).bfloat16(), w[:, :64].contiguous()) \
+        or k_dim < 64
+
+
 @pytest.mark.parametrize("mode", [0, 1, 2, 3])
 def test_library_product_with_epilogue(mode):
     from matricxon_b200.ops.linear import linear
@@ -256,11 +292,15 @@ def run_attention(k, q, cache, tables, tok_seq, positions, heads, kv_heads, dim,
     pos = positions.cpu().tolist()
     context = [pos[cu_q[s]] for s in range(n_seq)]
     group = heads // kv_heads
-    tiles = [v for s in range(n_seq) for row in range(0, q_lens[s] * group, 16) for v in (s, row)]
+    narrow, wide = k.attention_tile_lists(q_lens, group)
     as_int = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
-    k.paged_attention_mma(q, q.stride(0), cache, tables, as_int(cu_q), as_int(context), as_int(tiles),
-                          len(tiles) // 2, n, heads, kv_heads, dim, window, scale, out, st,
-                          n_splits=n_splits, scratch=scratch)
+    for tiles, is_narrow, others in ((narrow, True, wide), (wide, False, narrow)):
+        if not tiles:
+            continue
+        splits = n_splits if not others else 1      # splits need a launch that covers every token
+        k.paged_attention_mma(q, q.stride(0), cache, tables, as_int(cu_q), as_int(context), as_int(tiles),
+                              len(tiles) // 2, is_narrow, n, heads, kv_heads, dim, window, scale, out, st,
+                              n_splits=splits, scratch=scratch)
     return out, st.item()
 
 
@@ -284,7 +324,8 @@ def test_paged_attention_mixed_batch(dtype, heads, kv_heads, dim, page_size, win
 
 
 @pytest.mark.parametrize("heads,kv_heads,dim,page_size", [
-    (24, 2, 128, 16), (4, 4, 64, 16), (14, 2, 64, 8), (7, 1, 128, 32), (32, 2, 128, 16), (6, 3, 64, 64)])
+    (24, 2, 128, 16), (4, 4, 64, 16), (14, 2, 64, 8), (7, 1, 128, 32), (32, 2, 128, 16), (6, 3, 64, 64),
+    (40, 2, 64, 16)])
 @pytest.mark.parametrize("window", [None, 24, 100])
 def test_tensor_core_attention_mixed_batch(heads, kv_heads, dim, page_size, window):
     """The bfloat16 tensor-core kernel on decode rows, short portions and a long portion at
@@ -295,12 +336,22 @@ def test_tensor_core_attention_mixed_batch(heads, kv_heads, dim, page_size, wind
     q, cache, tables, tok_seq, positions, dense = paged_case(
         torch.bfloat16, heads, kv_heads, dim, page_size, seq_lens, q_lens, seed=dim + heads)
     ref = reference_attention(dense, q_lens, seq_lens, scale, window)
-    for n_splits in (1, 3, 16):
-        out, st = run_attention(k, q, cache, tables, tok_seq, positions, heads, kv_heads, dim,
-                                window, scale, n_splits, impl="mma")
-        assert st == 0
-        worst = (out.double().cpu() - ref).abs().max(dim=1).values
-        assert torch.allclose(out.double().cpu(), ref, **tol(torch.bfloat16)), (n_splits, worst.argmax(), worst.max())
+    out, st = run_attention(k, q, cache, tables, tok_seq, positions, heads, kv_heads, dim,
+                            window, scale, 1, impl="mma")
+    assert st == 0
+    worst = (out.double().cpu() - ref).abs().max(dim=1).values
+    assert torch.allclose(out.double().cpu(), ref, **tol(torch.bfloat16)), (worst.argmax(), worst.max())
+    # decode tokens alone and prompt portions alone, with the keys split
+    for seq_lens, q_lens in (([1, 300, 33, 1000, 64], [1, 1, 1, 1, 1]), ([257, 90, 700], [257, 40, 100])):
+        q, cache, tables, tok_seq, positions, dense = paged_case(
+            torch.bfloat16, heads, kv_heads, dim, page_size, seq_lens, q_lens, seed=dim + heads + 1)
+        ref = reference_attention(dense, q_lens, seq_lens, scale, window)
+        for n_splits in (1, 3, 16):
+            out, st = run_attention(k, q, cache, tables, tok_seq, positions, heads, kv_heads, dim,
+                                    window, scale, n_splits, impl="mma")
+            assert st == 0
+            worst = (out.double().cpu() - ref).abs().max(dim=1).values
+            assert torch.allclose(out.double().cpu(), ref, **tol(torch.bfloat16)), (n_splits, worst.argmax(), worst.max())
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
