@@ -11,13 +11,17 @@
 // same causal limit and every key they load is used by all of them.
 //
 // Work. A block of four warps owns a tile of rows of one (sequence, KV head) and a split of
-// the keys, walked in chunks of 32 absolute positions. Chunks travel from the pages to
-// shared memory through a cp.async pipeline (STAGES chunks in flight), keys as [key][dim]
-// with swizzled 16-byte pieces, values as stored, [dim][key].
+// the keys, walked in chunks of 32 absolute positions. A page's keys for one KV head are one
+// contiguous piece of memory and so are its values, so a chunk reaches shared memory as a
+// few bulk asynchronous copies (cp.async.bulk, completion counted on an mbarrier) issued by
+// one thread, several chunks ahead of the arithmetic. Pages must hold 8, 16 or 32 slots.
 //   * "wide" tiles (64 rows, prompt portions): each warp has 16 rows of its own and every
-//     warp works on every chunk, so a chunk is fetched once for 64 rows;
-//   * "narrow" tiles (at most 16 rows, decode tokens): all four warps hold the same rows and
-//     take the chunks in turn; their partial results are combined in shared memory.
+//     warp works on every chunk, so a chunk is fetched once for 64 rows (3 stages a block);
+//   * "narrow" tiles (at most 16 rows, decode tokens): all four warps hold the same rows,
+//     each streams every fourth chunk through a two-stage pipeline of its own, and their
+//     partial results are combined in shared memory.
+// Every wait on an mbarrier is bounded: after SPIN_LIMIT polls the kernel sets
+// MX_STATUS_WAIT_TIMEOUT in the step's status word and goes on, so it always ends.
 // Per chunk and warp: S = Q K^T with mma.sync.m16n8k16 (bf16 in, float out), float online
 // softmax in registers, O += P V. Two orderings are chosen so that every fragment is 16
 // contiguous bytes: the contraction over head dims runs in a permuted order (thread t of a
@@ -35,7 +39,9 @@ namespace {
 constexpr int MMA_WARPS = 4;
 constexpr int MMA_THREADS = MMA_WARPS * 32;
 constexpr int CHUNK = 32;
-constexpr int STAGES = 3;
+constexpr int WIDE_STAGES = 3;      // chunks in flight per block, wide tiles
+constexpr int NARROW_STAGES = 2;    // chunks in flight per warp, narrow tiles
+constexpr int SPIN_LIMIT = 1 << 22;
 
 struct MmaAttnParams {
     const __nv_bfloat16* q;      // [tokens][q_stride], head h at h * HD
@@ -50,7 +56,7 @@ struct MmaAttnParams {
     int* status;
     long long n_pages;
     int n_tiles, q_stride, out_stride, bt_stride;
-    int n_heads, n_kv_heads, page_size, window, n_splits;
+    int n_heads, n_kv_heads, page_size, page_shift, window, n_splits;
     float scale_log2;            // scale * log2(e)
 };
 
@@ -68,30 +74,111 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
     return *reinterpret_cast<unsigned*>(&v);
 }
 
-// 16 bytes global -> shared, or 16 zero bytes when `valid` is false.
-__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gmem_src, bool valid) {
-    const unsigned dst = (unsigned)__cvta_generic_to_shared(smem_dst);
-    const int bytes = valid ? 16 : 0;
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(gmem_src), "r"(bytes));
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
 }
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
 
-// Which 16-byte piece of a key row a logical piece lands in: rows that one MMA reads
-// together (keys 8a + 2b + c, a in 0..3, c in 0..1) get eight different values.
-__device__ __forceinline__ int key_swizzle(int row) { return ((row >> 3) << 1) | (row & 1); }
+// ---- mbarrier + bulk copy (all waits bounded)
+__device__ __forceinline__ unsigned smem_addr(const void* ptr) {
+    return (unsigned)__cvta_generic_to_shared(ptr);
+}
+__device__ __forceinline__ void mbar_init(unsigned long long* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_addr(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_addr(bar)), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, unsigned parity) {
+    unsigned ok;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok)
+        : "r"(smem_addr(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ void mbar_wait(unsigned long long* bar, unsigned parity, int* status) {
+    for (int spin = 0; spin < SPIN_LIMIT; ++spin)
+        if (mbar_try_wait(bar, parity)) return;
+    atomicOr(status, MX_STATUS_WAIT_TIMEOUT);       // give up: the results are void, the kernel ends
+}
+__device__ __forceinline__ void bulk_copy(void* smem_dst, const void* gmem_src, unsigned bytes,
+                                          unsigned long long* bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(
+            smem_addr(smem_dst)),
+        "l"(gmem_src), "r"(bytes), "r"(smem_addr(bar))
+        : "memory");
+}
+
+// Brings the chunk starting at key c0 into a stage: keys as [key][HD], values page by page as
+// [HD][page_size]. `who` of `n_who` cooperating threads; thread 0 issues the copies. Pages the
+// request no longer holds (they lie wholly outside [lo, hi]) are filled with zeros instead.
+template <int HD>
+__device__ __forceinline__ void issue_chunk(const MmaAttnParams& p, __nv_bfloat16* ks,
+                                            __nv_bfloat16* vs, unsigned long long* bar, int c0, int lo,
+                                            int hi, const int* bt, const __nv_bfloat16* kbase,
+                                            const __nv_bfloat16* vbase, size_t page_stride, int who,
+                                            int n_who) {
+    const int ps = p.page_size;
+    const int pages = CHUNK >> p.page_shift;
+    const unsigned tile_bytes = (unsigned)(ps * HD * sizeof(__nv_bfloat16));
+    long long page_of[4];
+    unsigned total = 0;
+#pragma unroll
+    for (int pg = 0; pg < 4; ++pg) {
+        page_of[pg] = -1;
+        if (pg < pages) {
+            const int key0 = c0 + pg * ps;
+            if (key0 <= hi && key0 + ps - 1 >= lo) {
+                const int lp = key0 >> p.page_shift;
+                const long long page = lp < p.bt_stride ? bt[lp] : -1;
+                if (page >= 0 && page < p.n_pages) {
+                    page_of[pg] = page;
+                    total += 2 * tile_bytes;
+                } else if (who == 0) {
+                    atomicOr(p.status, MX_STATUS_BAD_PAGE);
+                }
+            }
+        }
+    }
+    if (who == 0) {
+        mbar_expect_tx(bar, total);
+#pragma unroll
+        for (int pg = 0; pg < 4; ++pg)
+            if (pg < pages && page_of[pg] >= 0) {
+                bulk_copy(ks + (size_t)pg * ps * HD, kbase + (size_t)page_of[pg] * page_stride, tile_bytes, bar);
+                bulk_copy(vs + (size_t)pg * ps * HD, vbase + (size_t)page_of[pg] * page_stride, tile_bytes, bar);
+            }
+    }
+#pragma unroll
+    for (int pg = 0; pg < 4; ++pg)
+        if (pg < pages && page_of[pg] < 0) {
+            uint4* kz = reinterpret_cast<uint4*>(ks + (size_t)pg * ps * HD);
+            uint4* vz = reinterpret_cast<uint4*>(vs + (size_t)pg * ps * HD);
+            for (int i = who; i < (int)(tile_bytes / 16); i += n_who) {
+                kz[i] = make_uint4(0, 0, 0, 0);
+                vz[i] = make_uint4(0, 0, 0, 0);
+            }
+        }
+}
 
 template <int HD, bool NARROW>
 __global__ void __launch_bounds__(MMA_THREADS)
 attention_mma_kernel(const MmaAttnParams p) {
     constexpr int KB = HD / 32;                 // 32-wide blocks of the head dim
     constexpr int NB = HD / 8;                  // 8-wide output column blocks
-    constexpr int PIECES = HD / 8;              // 16-byte pieces per key row
     constexpr int STAGE_ELEMS = 2 * CHUNK * HD; // keys then values
     constexpr int TILE_ROWS = NARROW ? 16 : 16 * MMA_WARPS;
-    extern __shared__ __align__(16) unsigned char smem_raw[];
+    constexpr int N_STAGES = NARROW ? NARROW_STAGES * MMA_WARPS : WIDE_STAGES;
+    extern __shared__ __align__(128) unsigned char smem_raw[];
     __nv_bfloat16* stages = reinterpret_cast<__nv_bfloat16*>(smem_raw);
+    __shared__ __align__(8) unsigned long long bars[N_STAGES];
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
@@ -103,6 +190,13 @@ attention_mma_kernel(const MmaAttnParams p) {
     const int ctx = p.context_lens[seq];
     const int n_rows = q_len * group;
     if (tile_row0 >= n_rows) return;            // a padding sequence of a fixed-size batch
+
+    if (tid == 0) {
+#pragma unroll
+        for (int s = 0; s < N_STAGES; ++s) mbar_init(&bars[s], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    __syncthreads();
 
     // rows of this block and of this warp
     const int tile_last = min(tile_row0 + TILE_ROWS - 1, n_rows - 1);
@@ -127,6 +221,10 @@ attention_mma_kernel(const MmaAttnParams p) {
     const int lo_tile = p.window > 0 ? max(0, ctx + tile_row0 / group - p.window + 1) : 0;
     const int hi_warp = warp_has_rows ? ctx + last_row / group : -1;
     const int lo_warp = p.window > 0 ? max(0, ctx + row0 / group - p.window + 1) : 0;
+    // rows of the warp see every key of a chunk that lies in [all_lo, all_hi]: no mask needed
+    const int all_hi = warp_has_rows ? ctx + row0 / group : -1;
+    const int all_lo = p.window > 0 ? max(0, hi_warp - p.window + 1) : 0;
+    const bool rows_full = row0 + 15 < n_rows;
     const int first_chunk = lo_tile / CHUNK, last_chunk = hi_tile / CHUNK;
     const int n_chunks = last_chunk - first_chunk + 1;
     const int per_split = (n_chunks + p.n_splits - 1) / p.n_splits;
@@ -138,48 +236,6 @@ attention_mma_kernel(const MmaAttnParams p) {
     const size_t page_stride = 2 * (size_t)p.n_kv_heads * head_stride;
     const __nv_bfloat16* kbase = p.cache + (size_t)kh * head_stride;
     const __nv_bfloat16* vbase = p.cache + (size_t)(p.n_kv_heads + kh) * head_stride;
-
-    // ---- fetch one chunk into a stage (all threads); always followed by a commit
-    auto fetch = [&](int ci) {
-        if (ci < c_end) {
-            __nv_bfloat16* ks = stages + (size_t)((ci - c_begin) % STAGES) * STAGE_ELEMS;
-            __nv_bfloat16* vs = ks + CHUNK * HD;
-            const int c0 = ci * CHUNK;
-            for (int idx = tid; idx < CHUNK * PIECES; idx += MMA_THREADS) {
-                const int j = idx / PIECES, c = idx - j * PIECES;
-                const int key = c0 + j;
-                const __nv_bfloat16* src = p.cache;
-                bool valid = false;
-                if (key >= lo_tile && key <= hi_tile) {
-                    const int lp = key / p.page_size;
-                    const long long page = lp < p.bt_stride ? bt[lp] : -1;
-                    if (page >= 0 && page < p.n_pages) {
-                        valid = true;
-                        src = kbase + (size_t)page * page_stride + (size_t)(key - lp * p.page_size) * HD + 8 * c;
-                    } else if (c == 0) {
-                        atomicOr(p.status, MX_STATUS_BAD_PAGE);
-                    }
-                }
-                cp_async_16(ks + (size_t)j * HD + 8 * (c ^ key_swizzle(j)), src, valid);
-            }
-            for (int idx = tid; idx < HD * 4; idx += MMA_THREADS) {
-                const int d = idx >> 2, grp = idx & 3;
-                const int key0 = c0 + 8 * grp;
-                const __nv_bfloat16* src = p.cache;
-                bool valid = false;
-                if (key0 <= hi_tile && key0 + 7 >= lo_tile) {
-                    const int lp = key0 / p.page_size;
-                    const long long page = lp < p.bt_stride ? bt[lp] : -1;
-                    if (page >= 0 && page < p.n_pages) {
-                        valid = true;
-                        src = vbase + (size_t)page * page_stride + (size_t)d * p.page_size + (key0 - lp * p.page_size);
-                    }
-                }
-                cp_async_16(vs + (size_t)d * CHUNK + 8 * grp, src, valid);
-            }
-        }
-        cp_async_commit();
-    };
 
     // Q fragments: 16 bytes of each owned row per 32-wide block
     uint4 qf[2][KB];
@@ -198,62 +254,61 @@ attention_mma_kernel(const MmaAttnParams p) {
     for (int nb = 0; nb < NB; ++nb) o[nb][0] = o[nb][1] = o[nb][2] = o[nb][3] = 0.f;
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
 
-#pragma unroll
-    for (int s = 0; s < STAGES - 1; ++s) fetch(c_begin + s);
-
-    for (int ci = c_begin; ci < c_end; ++ci) {
-        cp_async_wait<STAGES - 2>();
-        __syncthreads();                         // chunk ci has landed; chunk ci - 1 is done with
-        fetch(ci + STAGES - 1);
-        const int c0 = ci * CHUNK;
-        const bool mine = NARROW ? ((ci - c_begin) % MMA_WARPS == warp)
-                                 : (warp_has_rows && c0 <= hi_warp && c0 + CHUNK - 1 >= lo_warp);
-        if (!mine) continue;
-        const __nv_bfloat16* ks = stages + (size_t)((ci - c_begin) % STAGES) * STAGE_ELEMS;
-        const __nv_bfloat16* vs = ks + CHUNK * HD;
-
-        // ---- scores: block b gives this thread keys 8t + 2b, 8t + 2b + 1 of the chunk
+    // ---- one chunk of arithmetic on a stage
+    auto compute = [&](const __nv_bfloat16* ks, const __nv_bfloat16* vs, int c0) {
+        // scores: block b gives this thread keys 8t + 2b, 8t + 2b + 1 of the chunk
         float s[4][4];
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
             s[b][0] = s[b][1] = s[b][2] = s[b][3] = 0.f;
-            // column g of block b is key 8 (g / 2) + 2b + (g % 2); its swizzle value is g
-            const int j = 8 * (g >> 1) + 2 * b + (g & 1);
-            const __nv_bfloat16* krow = ks + (size_t)j * HD;
+            // column g of block b is key 8 (g / 2) + 2b + (g % 2)
+            const __nv_bfloat16* krow = ks + (size_t)(8 * (g >> 1) + 2 * b + (g & 1)) * HD + 8 * t;
 #pragma unroll
             for (int kb = 0; kb < KB; ++kb) {
-                const uint4 kf = *reinterpret_cast<const uint4*>(krow + 8 * ((4 * kb + t) ^ g));
+                const uint4 kf = *reinterpret_cast<const uint4*>(krow + 32 * kb);
                 mma_bf16(s[b], qf[0][kb].x, qf[1][kb].x, qf[0][kb].y, qf[1][kb].y, kf.x, kf.y);
                 mma_bf16(s[b], qf[0][kb].z, qf[1][kb].z, qf[0][kb].w, qf[1][kb].w, kf.z, kf.w);
             }
         }
-        // ---- mask, running max and sum (rows g and g + 8), probabilities in place
+        // mask (only where the chunk crosses an edge), running max and sum for rows g, g + 8
         float m_new[2] = {m_run[0], m_run[1]};
+        const bool plain = rows_full && c0 >= all_lo && c0 + CHUNK - 1 <= all_hi;
+        if (plain) {
 #pragma unroll
-        for (int b = 0; b < 4; ++b)
+            for (int b = 0; b < 4; ++b)
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int i = e >> 1;
-                const int key = c0 + 8 * t + 2 * b + (e & 1);
-                const bool visible = r_valid[i] && key <= r_pos[i] && key >= r_lo[i];
-                s[b][e] = visible ? s[b][e] * p.scale_log2 : -INFINITY;
-                m_new[i] = fmaxf(m_new[i], s[b][e]);
-            }
-        float alpha[2], sum[2] = {0.f, 0.f};
+                for (int e = 0; e < 4; ++e) {
+                    s[b][e] *= p.scale_log2;
+                    m_new[e >> 1] = fmaxf(m_new[e >> 1], s[b][e]);
+                }
+        } else {
+#pragma unroll
+            for (int b = 0; b < 4; ++b)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int i = e >> 1;
+                    const int key = c0 + 8 * t + 2 * b + (e & 1);
+                    const bool visible = r_valid[i] && key <= r_pos[i] && key >= r_lo[i];
+                    s[b][e] = visible ? s[b][e] * p.scale_log2 : -INFINITY;
+                    m_new[i] = fmaxf(m_new[i], s[b][e]);
+                }
+        }
+        float alpha[2], sum[2] = {0.f, 0.f}, m_use[2];
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
             m_new[i] = fmaxf(m_new[i], __shfl_xor_sync(0xffffffffu, m_new[i], 1));
             m_new[i] = fmaxf(m_new[i], __shfl_xor_sync(0xffffffffu, m_new[i], 2));
-            alpha[i] = (m_run[i] == -INFINITY) ? 0.f : exp2f(m_run[i] - m_new[i]);
+            // a row with nothing visible so far keeps max = -inf; subtract 0 then, exp2(-inf) = 0
+            m_use[i] = (m_new[i] == -INFINITY) ? 0.f : m_new[i];
+            alpha[i] = fast_exp2(m_run[i] - m_use[i]);
         }
 #pragma unroll
         for (int b = 0; b < 4; ++b)
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                const int i = e >> 1;
-                const float pv = (s[b][e] == -INFINITY) ? 0.f : exp2f(s[b][e] - m_new[i]);
+                const float pv = fast_exp2(s[b][e] - m_use[e >> 1]);
                 s[b][e] = pv;
-                sum[i] += pv;
+                sum[e >> 1] += pv;
             }
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
@@ -270,8 +325,8 @@ attention_mma_kernel(const MmaAttnParams p) {
             pa[st][2] = pack_bf16(s[2 * st + 1][0], s[2 * st + 1][1]);
             pa[st][3] = pack_bf16(s[2 * st + 1][2], s[2 * st + 1][3]);
         }
-        // ---- values: this thread reads keys 8t..8t+7 of value dim 8 nb + g. Slots beyond the
-        // newest key hold no data yet: keep them out of the product.
+        // values: this thread reads keys 8t..8t+7 of value dim 8 nb + g, from the page that
+        // holds them. Slots beyond the newest key hold no data yet: keep them out.
         const int vkey0 = c0 + 8 * t;
         unsigned keep[4] = {0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu};
         if (vkey0 + 7 > hi_tile) {
@@ -281,19 +336,43 @@ attention_mma_kernel(const MmaAttnParams p) {
                 keep[w] = (lo_ok ? 0x0000ffffu : 0u) | (hi_ok ? 0xffff0000u : 0u);
             }
         }
+        const int in_chunk = 8 * t;
+        const int pg = in_chunk >> p.page_shift, off = in_chunk & (p.page_size - 1);
+        const __nv_bfloat16* vcol = vs + (size_t)pg * p.page_size * HD + (size_t)g * p.page_size + off;
 #pragma unroll
         for (int nb = 0; nb < NB; ++nb) {
-            uint4 vf = *reinterpret_cast<const uint4*>(vs + (size_t)(8 * nb + g) * CHUNK + 8 * t);
+            uint4 vf = *reinterpret_cast<const uint4*>(vcol + (size_t)(8 * nb) * p.page_size);
             vf.x &= keep[0]; vf.y &= keep[1]; vf.z &= keep[2]; vf.w &= keep[3];
             o[nb][0] *= alpha[0]; o[nb][1] *= alpha[0];
             o[nb][2] *= alpha[1]; o[nb][3] *= alpha[1];
             mma_bf16(o[nb], pa[0][0], pa[0][1], pa[0][2], pa[0][3], vf.x, vf.y);
             mma_bf16(o[nb], pa[1][0], pa[1][1], pa[1][2], pa[1][3], vf.z, vf.w);
         }
-    }
-    cp_async_wait<0>();
+    };
 
     if (NARROW) {
+        // ---- each warp streams chunks c_begin + warp, + 4, ... through two stages of its own
+        __nv_bfloat16* my_stages = stages + (size_t)warp * NARROW_STAGES * STAGE_ELEMS;
+        unsigned long long* my_bars = bars + warp * NARROW_STAGES;
+        const int my_first = c_begin + warp;
+        const int my_count = my_first < c_end ? (c_end - my_first + MMA_WARPS - 1) / MMA_WARPS : 0;
+        if (my_count > 0)
+            issue_chunk<HD>(p, my_stages, my_stages + CHUNK * HD, &my_bars[0], my_first * CHUNK, lo_tile,
+                            hi_tile, bt, kbase, vbase, page_stride, lane, 32);
+        for (int i = 0; i < my_count; ++i) {
+            const int st = i % NARROW_STAGES;
+            if (i + 1 < my_count) {
+                const int nx = (i + 1) % NARROW_STAGES;
+                __nv_bfloat16* ks = my_stages + (size_t)nx * STAGE_ELEMS;
+                issue_chunk<HD>(p, ks, ks + CHUNK * HD, &my_bars[nx], (my_first + MMA_WARPS * (i + 1)) * CHUNK,
+                                lo_tile, hi_tile, bt, kbase, vbase, page_stride, lane, 32);
+            }
+            __syncwarp();
+            mbar_wait(&my_bars[st], (unsigned)((i / NARROW_STAGES) & 1), p.status);
+            const __nv_bfloat16* ks = my_stages + (size_t)st * STAGE_ELEMS;
+            compute(ks, ks + CHUNK * HD, (my_first + MMA_WARPS * i) * CHUNK);
+            __syncwarp();                         // the stage may be refilled from here on
+        }
         // ---- combine the four warps' partial results through shared memory (stages are free)
         __syncthreads();
         float* red_o = reinterpret_cast<float*>(smem_raw);              // [warp][16][HD]
@@ -345,7 +424,32 @@ attention_mma_kernel(const MmaAttnParams p) {
         return;
     }
 
-    // ---- wide tiles: each warp writes its own rows; this thread holds columns 8 nb + 2t, + 1
+    // ---- wide tiles: the block streams every chunk through WIDE_STAGES shared stages
+#pragma unroll
+    for (int s = 0; s < WIDE_STAGES - 1; ++s)
+        if (c_begin + s < c_end) {
+            __nv_bfloat16* ks = stages + (size_t)s * STAGE_ELEMS;
+            issue_chunk<HD>(p, ks, ks + CHUNK * HD, &bars[s], (c_begin + s) * CHUNK, lo_tile, hi_tile, bt,
+                            kbase, vbase, page_stride, tid, MMA_THREADS);
+        }
+    for (int ci = c_begin; ci < c_end; ++ci) {
+        const int i = ci - c_begin;
+        __syncthreads();                         // every warp is done with chunk ci - 1: its stage is free
+        if (ci + WIDE_STAGES - 1 < c_end) {
+            const int nx = (i + WIDE_STAGES - 1) % WIDE_STAGES;
+            __nv_bfloat16* ks = stages + (size_t)nx * STAGE_ELEMS;
+            issue_chunk<HD>(p, ks, ks + CHUNK * HD, &bars[nx], (ci + WIDE_STAGES - 1) * CHUNK, lo_tile,
+                            hi_tile, bt, kbase, vbase, page_stride, tid, MMA_THREADS);
+        }
+        const int c0 = ci * CHUNK;
+        if (!(warp_has_rows && c0 <= hi_warp && c0 + CHUNK - 1 >= lo_warp)) continue;
+        const int st = i % WIDE_STAGES;
+        mbar_wait(&bars[st], (unsigned)((i / WIDE_STAGES) & 1), p.status);
+        const __nv_bfloat16* ks = stages + (size_t)st * STAGE_ELEMS;
+        compute(ks, ks + CHUNK * HD, c0);
+    }
+
+    // each warp writes its own rows; this thread holds columns 8 nb + 2t, + 1 of rows g, g + 8
     if (p.n_splits == 1) {
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
@@ -381,12 +485,13 @@ attention_mma_kernel(const MmaAttnParams p) {
 
 template <int HD, bool NARROW>
 int launch_mma(const MmaAttnParams& p, cudaStream_t stream) {
-    size_t smem = (size_t)STAGES * 2 * CHUNK * HD * sizeof(__nv_bfloat16);
+    const size_t stage_bytes = 2 * (size_t)CHUNK * HD * sizeof(__nv_bfloat16);
+    size_t smem = stage_bytes * (NARROW ? NARROW_STAGES * MMA_WARPS : WIDE_STAGES);
     if (NARROW) {
         const size_t reduce = (size_t)MMA_WARPS * 16 * (HD + 2) * sizeof(float);
         if (reduce > smem) smem = reduce;
     }
-    if (smem > 48 * 1024) {
+    if (smem + 1024 > 48 * 1024) {   // the kernel also has a little static shared memory
         cudaError_t e = cudaFuncSetAttribute(attention_mma_kernel<HD, NARROW>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) MX_REFUSE("attention: cannot reserve %zu bytes of shared memory", smem);
@@ -416,8 +521,8 @@ extern "C" int mx_paged_attention_mma(const void* q, int q_stride, const void* c
         MX_REFUSE("attention: %d heads are not a multiple of %d kv heads", n_heads, n_kv_heads);
     if (head_dim != 64 && head_dim != 128)
         MX_REFUSE("tensor-core attention is built for head_dim 64 and 128, not %d", head_dim);
-    if (page_size <= 0 || page_size % 8 != 0)
-        MX_REFUSE("attention: page size %d is not a positive multiple of 8", page_size);
+    if (page_size != 8 && page_size != 16 && page_size != 32)
+        MX_REFUSE("tensor-core attention takes pages of 8, 16 or 32 slots, not %d", page_size);
     if (q_stride % 8 != 0 || out_stride % 2 != 0)
         MX_REFUSE("tensor-core attention needs 16-byte aligned query rows (stride %d)", q_stride);
     if (n_splits < 1 || n_splits > 65535) MX_REFUSE("attention: n_splits %d", n_splits);
@@ -430,7 +535,8 @@ extern "C" int mx_paged_attention_mma(const void* q, int q_stride, const void* c
     p.block_tables = block_tables; p.cu_q = cu_q; p.context_lens = context_lens; p.tiles = tiles;
     p.status = status; p.n_pages = n_pages; p.n_tiles = n_tiles; p.q_stride = q_stride;
     p.out_stride = out_stride; p.bt_stride = bt_stride; p.n_heads = n_heads; p.n_kv_heads = n_kv_heads;
-    p.page_size = page_size; p.window = window; p.n_splits = n_splits;
+    p.page_size = page_size; p.page_shift = page_size == 8 ? 3 : (page_size == 16 ? 4 : 5);
+    p.window = window; p.n_splits = n_splits;
     p.scale_log2 = scale * 1.4426950408889634f;
     int rc;
     if (head_dim == 64) rc = narrow ? launch_mma<64, true>(p, stream) : launch_mma<64, false>(p, stream);

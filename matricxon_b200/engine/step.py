@@ -108,7 +108,8 @@ class StepContext:
         items = max(n_tiles * n_kv_heads, 1)
         span = self.max_kv_len if window is None else min(self.max_kv_len, window)
         chunks = span // 32 + 1
-        target = self._runner.sm_count * (4 if narrow else 2)
+        # a narrow block fills an SM's shared memory with its four private pipelines: one per SM
+        target = self._runner.sm_count * (1 if narrow else 2)
         n_splits = max(1, min(target // items, chunks // (4 if narrow else 8), 128))
         while n_splits > 1 and kernels.attention_scratch_bytes(
                 self.n_tokens, n_heads, head_dim, n_splits) > (256 << 20):

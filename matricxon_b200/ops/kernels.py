@@ -268,5 +268,5 @@ def paged_attention_mma(q: torch.Tensor, q_stride: int, cache: torch.Tensor,
 
 
 def mma_attention_supported(dtype: torch.dtype, head_dim: int, page_size: int, q_stride: int) -> bool:
-    return (dtype == torch.bfloat16 and head_dim in (64, 128) and page_size % 8 == 0
+    return (dtype == torch.bfloat16 and head_dim in (64, 128) and page_size in (8, 16, 32)
             and q_stride % 8 == 0)

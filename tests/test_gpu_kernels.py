@@ -324,7 +324,7 @@ def test_paged_attention_mixed_batch(dtype, heads, kv_heads, dim, page_size, win
 
 
 @pytest.mark.parametrize("heads,kv_heads,dim,page_size", [
-    (24, 2, 128, 16), (4, 4, 64, 16), (14, 2, 64, 8), (7, 1, 128, 32), (32, 2, 128, 16), (6, 3, 64, 64),
+    (24, 2, 128, 16), (4, 4, 64, 16), (14, 2, 64, 8), (7, 1, 128, 32), (32, 2, 128, 16), (6, 3, 64, 32),
     (40, 2, 64, 16)])
 @pytest.mark.parametrize("window", [None, 24, 100])
 def test_tensor_core_attention_mixed_batch(heads, kv_heads, dim, page_size, window):
