@@ -1,0 +1,367 @@
+// out[M,N] = epilogue(A[M,K] . W[N,K]^T + bias[N]) on the 5th-generation tensor cores.
+//
+// bfloat16 operands, float accumulation in tensor memory, bias / GELU / residual applied to
+// the float accumulator before the one rounding: the product behind every Linear of the
+// reference (app/architectures/qwen_layers.py:50-53, app/architectures/starcoder2_layers.py:19-23)
+// for prompt-sized M, with no separate epilogue pass over the activations.
+//
+// One block computes one 128 x 256 tile of the output (128 x 128 when N is small) in six warps:
+//   warp 4, one lane: producer. For every 64-wide slice of K it waits for a free stage,
+//     announces the bytes on the stage's "full" mbarrier and issues two TMA tile loads
+//     (cp.async.bulk.tensor.2d, 128-byte swizzle) for A and W, both K-major.
+//   warp 5, one lane: MMA issuer. Waits for "full", issues four tcgen05.mma (K = 16 each) whose
+//     operands are shared-memory descriptors over the swizzled stage, and commits them to the
+//     stage's "empty" mbarrier; after the last slice it commits to the "accumulator ready"
+//     mbarrier. Warp 5 also allocates and frees the 256 columns of tensor memory.
+//   warps 0-3: epilogue. Each owns 32 of the 128 accumulator lanes (rows): tcgen05.ld brings
+//     32 columns at a time into registers, the epilogue is applied and the row piece stored.
+// Rows and columns beyond M, N and K are zero-filled by TMA on the way in and skipped on the
+// way out. Every mbarrier wait is bounded: a wait that runs out sets MX_STATUS_WAIT_TIMEOUT in
+// the status word and the role moves on, so the block always reaches the point where tensor
+// memory is freed.
+//
+// Epilogue modes as in gemm_simt.cu: 0 out(bf16) = v; 1 out(bf16) = gelu_tanh(v);
+// 2 out(f32) = residual + v; 3 out(f32) = v, with v = acc + bias.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int TC_BM = 128;
+constexpr int TC_BK = 64;              // 64 bf16 = 128 bytes = one swizzle row
+constexpr int TC_STAGES = 4;
+constexpr int TC_THREADS = 192;
+constexpr int TC_SPIN_LIMIT = 1 << 22;
+
+__device__ __forceinline__ unsigned smem_u32(const void* ptr) {
+    return (unsigned)__cvta_generic_to_shared(ptr);
+}
+__device__ __forceinline__ void tc_mbar_init(unsigned long long* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void tc_mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ bool tc_mbar_try_wait(unsigned long long* bar, unsigned parity) {
+    unsigned ok;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Returns false when the wait ran out (the status word is set; the caller carries on).
+__device__ __forceinline__ bool tc_mbar_wait(unsigned long long* bar, unsigned parity, int* status) {
+    for (int spin = 0; spin < TC_SPIN_LIMIT; ++spin)
+        if (tc_mbar_try_wait(bar, parity)) return true;
+    atomicOr(status, MX_STATUS_WAIT_TIMEOUT);
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y,
+                                            unsigned long long* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::"r"(
+            smem_u32(smem_dst)),
+        "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+        : "memory");
+}
+
+// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows of 128 bytes, groups of
+// eight rows 1024 bytes apart.
+__device__ __forceinline__ unsigned long long umma_desc(const void* smem_tile) {
+    unsigned long long desc = 0;
+    desc |= (unsigned long long)((smem_u32(smem_tile) & 0x3FFFF) >> 4);        // start address
+    desc |= (unsigned long long)1 << 16;                                       // leading offset (unused here)
+    desc |= (unsigned long long)(1024 >> 4) << 32;                             // stride between 8-row groups
+    desc |= (unsigned long long)1 << 46;                                       // descriptor version of sm_100
+    desc |= (unsigned long long)2 << 61;                                       // SWIZZLE_128B
+    return desc;
+}
+
+// Instruction descriptor of kind::f16: bf16 x bf16 -> f32, both operands K-major, M x N tile.
+__device__ __forceinline__ unsigned umma_idesc(int m, int n) {
+    unsigned d = 0;
+    d |= 1u << 4;                      // accumulator format: f32
+    d |= 1u << 7;                      // A format: bf16
+    d |= 1u << 10;                     // B format: bf16
+    d |= (unsigned)(n >> 3) << 17;
+    d |= (unsigned)(m >> 4) << 24;
+    return d;
+}
+
+__device__ __forceinline__ void umma_bf16(unsigned tmem_acc, unsigned long long adesc,
+                                          unsigned long long bdesc, unsigned idesc, bool accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_acc),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"((unsigned)accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(unsigned long long* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(
+                     smem_u32(bar))
+                 : "memory");
+}
+
+struct TcShared {
+    unsigned long long full[TC_STAGES];
+    unsigned long long empty[TC_STAGES];
+    unsigned long long acc_ready;
+    unsigned tmem_base;
+};
+
+template <int BN>
+__global__ void __launch_bounds__(TC_THREADS)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                    const float* __restrict__ bias, const float* residual, void* out, int ldo, int M,
+                    int N, int K, int mode, int* status) {
+    constexpr unsigned A_BYTES = TC_BM * TC_BK * 2, W_BYTES = BN * TC_BK * 2;
+    constexpr unsigned STAGE_BYTES = A_BYTES + W_BYTES;
+    extern __shared__ unsigned char tc_smem_raw[];
+    // stages must start on a 1024-byte boundary for the 128-byte swizzle
+    unsigned char* tiles = reinterpret_cast<unsigned char*>(
+        (reinterpret_cast<uintptr_t>(tc_smem_raw) + 1023) & ~(uintptr_t)1023);
+    __shared__ TcShared sh;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.y * TC_BM, n0 = blockIdx.x * BN;
+    const int k_slices = (K + TC_BK - 1) / TC_BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < TC_STAGES; ++s) {
+            tc_mbar_init(&sh.full[s], 1);
+            tc_mbar_init(&sh.empty[s], 1);
+        }
+        tc_mbar_init(&sh.acc_ready, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 5) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(
+                         smem_u32(&sh.tmem_base)),
+                     "r"(BN)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    const unsigned tmem_acc = sh.tmem_base;
+
+    if (warp == 4) {
+        // ---------------- producer
+        if (lane == 0) {
+            int issued = 0;
+            for (int ks = 0; ks < k_slices; ++ks) {
+                const int s = ks % TC_STAGES;
+                const unsigned use = (unsigned)(ks / TC_STAGES);
+                if (!tc_mbar_wait(&sh.empty[s], (use & 1) ^ 1, status)) break;
+                tc_mbar_expect_tx(&sh.full[s], STAGE_BYTES);
+                unsigned char* a_tile = tiles + (size_t)s * STAGE_BYTES;
+                tma_load_2d(a_tile, &map_a, ks * TC_BK, m0, &sh.full[s]);
+                tma_load_2d(a_tile + A_BYTES, &map_w, ks * TC_BK, n0, &sh.full[s]);
+                issued = ks + 1;
+            }
+            // no copy of this block may still be in flight when it ends: wait (bounded) for the
+            // loads of the last stages to land
+            for (int ks = max(0, issued - TC_STAGES); ks < issued; ++ks)
+                if (!tc_mbar_wait(&sh.full[ks % TC_STAGES], (unsigned)(ks / TC_STAGES) & 1, status)) break;
+        }
+    } else if (warp == 5) {
+        // ---------------- MMA issuer
+        if (lane == 0) {
+            const unsigned idesc = umma_idesc(TC_BM, BN);
+            bool alive = true;
+            for (int ks = 0; ks < k_slices && alive; ++ks) {
+                const int s = ks % TC_STAGES;
+                const unsigned use = (unsigned)(ks / TC_STAGES);
+                alive = tc_mbar_wait(&sh.full[s], use & 1, status);
+                if (!alive) break;
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                const unsigned char* a_tile = tiles + (size_t)s * STAGE_BYTES;
+                const unsigned long long adesc = umma_desc(a_tile);
+                const unsigned long long bdesc = umma_desc(a_tile + A_BYTES);
+#pragma unroll
+                for (int k = 0; k < TC_BK / 16; ++k)   // 16 elements = 32 bytes further along K
+                    umma_bf16(tmem_acc, adesc + 2 * k, bdesc + 2 * k, idesc, (ks | k) != 0);
+                umma_commit(&sh.empty[s]);
+            }
+            umma_commit(&sh.acc_ready);              // arrives when every MMA above has finished
+        }
+    } else {
+        // ---------------- epilogue: warp w owns accumulator lanes 32 w .. 32 w + 31
+        const bool ready = tc_mbar_wait(&sh.acc_ready, 0, status);
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        const int row = m0 + 32 * warp + lane;
+        if (ready) {
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                unsigned r[32];
+                const unsigned taddr = tmem_acc + ((unsigned)(32 * warp) << 16) + (unsigned)c0;
+                asm volatile(
+                    "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                    "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                    "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+                    : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+                      "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+                      "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
+                      "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),
+                      "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                    : "r"(taddr)
+                    : "memory");
+                asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+                if (row < M) {
+                    const int nbase = n0 + c0;
+                    const size_t obase = (size_t)row * ldo + nbase;
+                    if (mode >= 2) {
+                        float* o = reinterpret_cast<float*>(out) + obase;
+                        const float* res = (mode == 2) ? residual + obase : nullptr;
+                        const bool vec = nbase + 32 <= N && (obase % 4) == 0;
+                        if (vec) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 4) {
+                                float4 v;
+                                v.x = __uint_as_float(r[j]); v.y = __uint_as_float(r[j + 1]);
+                                v.z = __uint_as_float(r[j + 2]); v.w = __uint_as_float(r[j + 3]);
+                                if (bias) {
+                                    v.x += bias[nbase + j]; v.y += bias[nbase + j + 1];
+                                    v.z += bias[nbase + j + 2]; v.w += bias[nbase + j + 3];
+                                }
+                                if (res) {
+                                    const float4 q = *reinterpret_cast<const float4*>(res + j);
+                                    v.x += q.x; v.y += q.y; v.z += q.z; v.w += q.w;
+                                }
+                                *reinterpret_cast<float4*>(o + j) = v;
+                            }
+                        } else {
+                            for (int j = 0; j < 32; ++j) {
+                                if (nbase + j >= N) break;
+                                float v = __uint_as_float(r[j]);
+                                if (bias) v += bias[nbase + j];
+                                if (res) v += res[j];
+                                o[j] = v;
+                            }
+                        }
+                    } else {
+                        __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out) + obase;
+                        const bool vec = nbase + 32 <= N && (obase % 8) == 0;
+                        if (vec) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 8) {
+                                float v[8];
+#pragma unroll
+                                for (int e = 0; e < 8; ++e) {
+                                    v[e] = __uint_as_float(r[j + e]);
+                                    if (bias) v[e] += bias[nbase + j + e];
+                                    if (mode == 1) v[e] = gelu_tanh(v[e]);
+                                }
+                                uint4 pk;
+                                __nv_bfloat162 h0 = __floats2bfloat162_rn(v[0], v[1]);
+                                __nv_bfloat162 h1 = __floats2bfloat162_rn(v[2], v[3]);
+                                __nv_bfloat162 h2 = __floats2bfloat162_rn(v[4], v[5]);
+                                __nv_bfloat162 h3 = __floats2bfloat162_rn(v[6], v[7]);
+                                pk.x = *reinterpret_cast<unsigned*>(&h0); pk.y = *reinterpret_cast<unsigned*>(&h1);
+                                pk.z = *reinterpret_cast<unsigned*>(&h2); pk.w = *reinterpret_cast<unsigned*>(&h3);
+                                *reinterpret_cast<uint4*>(o + j) = pk;
+                            }
+                        } else {
+                            for (int j = 0; j < 32; ++j) {
+                                if (nbase + j >= N) break;
+                                float v = __uint_as_float(r[j]);
+                                if (bias) v += bias[nbase + j];
+                                if (mode == 1) v = gelu_tanh(v);
+                                o[j] = __float2bfloat16_rn(v);
+                            }
+                        }
+                    }
+                }
+            }
+        }
+    }
+    // ---------------- teardown: every role arrives here; then tensor memory is freed
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    if (warp == 5) {
+        __syncwarp();
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_acc), "r"(BN)
+                     : "memory");
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn == nullptr) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult query;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &query) == cudaSuccess &&
+            query == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+    return fn;
+}
+
+// A [rows, K] bfloat16 matrix with `ld` elements between rows, cut into boxes of box_rows x 64.
+int make_map(CUtensorMap* map, const void* base, long long rows, long long K, long long ld, int box_rows) {
+    EncodeTiledFn encode = encode_tiled_fn();
+    if (encode == nullptr) MX_REFUSE("tcgen05 gemm: the driver does not offer cuTensorMapEncodeTiled");
+    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult rc = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides,
+                               box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (rc != CUDA_SUCCESS) MX_REFUSE("tcgen05 gemm: cuTensorMapEncodeTiled failed with code %d", (int)rc);
+    return MX_OK;
+}
+
+template <int BN>
+int launch_tc(const CUtensorMap& map_a, const CUtensorMap& map_w, const float* bias, const float* residual,
+              void* out, int ldo, int M, int N, int K, int mode, int* status, cudaStream_t stream) {
+    const size_t smem = (size_t)TC_STAGES * (TC_BM + BN) * TC_BK * 2 + 1024;
+    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)smem);
+    if (e != cudaSuccess) MX_REFUSE("tcgen05 gemm: cannot reserve %zu bytes of shared memory", smem);
+    dim3 grid((N + BN - 1) / BN, (M + TC_BM - 1) / TC_BM);
+    gemm_tcgen05_kernel<BN><<<grid, TC_THREADS, smem, stream>>>(map_a, map_w, bias, residual, out, ldo, M, N,
+                                                                K, mode, status);
+    return mx_launch_status();
+}
+
+}  // namespace
+
+extern "C" int mx_gemm_tcgen05(const void* A, const void* W, const float* bias, const float* residual,
+                               void* out, int out_dtype, int M, int N, int K, int lda, int ldw, int ldo,
+                               int mode, int* status, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return MX_OK;
+    if (K <= 0 || K % 8 != 0) MX_REFUSE("tcgen05 gemm: K = %d is not a positive multiple of 8", K);
+    if (lda % 8 != 0 || ldw % 8 != 0)
+        MX_REFUSE("tcgen05 gemm: row strides %d, %d are not multiples of 8 elements (16 bytes)", lda, ldw);
+    if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(W)) % 16 != 0)
+        MX_REFUSE("tcgen05 gemm: operands must start on 16-byte boundaries");
+    if (mode < 0 || mode > 3) MX_REFUSE("tcgen05 gemm: unknown epilogue mode %d", mode);
+    if (mode == 2 && residual == nullptr) MX_REFUSE("tcgen05 gemm: residual mode without a residual");
+    if ((mode >= 2) != (out_dtype == MX_DTYPE_F32))
+        MX_REFUSE("tcgen05 gemm: epilogue mode %d does not write dtype %d", mode, out_dtype);
+    if (status == nullptr) MX_REFUSE("tcgen05 gemm: needs a status word for its bounded waits");
+    const int bn = N > 128 ? 256 : 128;
+    CUtensorMap map_a, map_w;
+    int rc = make_map(&map_a, A, M, K, lda, TC_BM);
+    if (rc != MX_OK) return rc;
+    rc = make_map(&map_w, W, N, K, ldw, bn);
+    if (rc != MX_OK) return rc;
+    if (bn == 256)
+        return launch_tc<256>(map_a, map_w, bias, residual, out, ldo, M, N, K, mode, status, stream);
+    return launch_tc<128>(map_a, map_w, bias, residual, out, ldo, M, N, K, mode, status, stream);
+}

@@ -156,6 +156,7 @@ class StepRunner:
         self.max_step_seqs = max_step_seqs
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        kernels.set_default_status(self.status)     # kernels with bounded waits report here too
         self._hidden: torch.Tensor | None = None
         self._scratch: torch.Tensor | None = None
         self._ints_host: torch.Tensor | None = None

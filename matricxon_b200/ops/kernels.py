@@ -150,6 +150,54 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None,
     _launched()
 
 
+_default_status: dict[int, torch.Tensor] = {}
+
+
+def default_status(device: torch.device) -> torch.Tensor:
+    """The status word kernels with bounded waits report to when the caller names none; a step
+    runner registers its own with ``set_default_status`` so that one read covers everything."""
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    if index not in _default_status:
+        _default_status[index] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _default_status[index]
+
+
+def set_default_status(status: torch.Tensor) -> None:
+    _default_status[status.device.index if status.device.index is not None
+                    else torch.cuda.current_device()] = status
+
+
+def tcgen05_gemm_supported(a: torch.Tensor, w: torch.Tensor) -> bool:
+    return (a.dtype == torch.bfloat16 and a.shape[1] % 8 == 0 and a.stride(1) == 1
+            and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+            and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None,
+                 residual: torch.Tensor | None, out: torch.Tensor, mode: int,
+                 status: torch.Tensor | None = None) -> None:
+    """The prompt-sized product on the tcgen05 tensor cores: TMA-fed, accumulator in tensor
+    memory, epilogue fused."""
+    _need(a, "a", torch.bfloat16, contiguous=False)
+    _need(w, "w", torch.bfloat16)
+    _need(out, "out")
+    m, k = a.shape
+    n = w.shape[0]
+    assert w.shape[1] == k and tuple(out.shape) == (m, n), (a.shape, w.shape, out.shape)
+    if bias is not None:
+        _need(bias, "bias", torch.float32)
+        assert bias.numel() == n
+    if residual is not None:
+        _need(residual, "residual", torch.float32)
+        assert tuple(residual.shape) == (m, n) and residual.stride(0) == out.stride(0)
+    if status is None:
+        status = default_status(a.device)
+    check(library().mx_gemm_tcgen05(_ptr(a), _ptr(w), _ptr(bias), _ptr(residual), _ptr(out),
+                                    dtype_code(out.dtype), m, n, k, a.stride(0), w.stride(0),
+                                    out.stride(0), mode, _ptr(status), _stream()), "gemm_tcgen05")
+    _launched()
+
+
 def skinny_gemm_supported(a: torch.Tensor, w: torch.Tensor) -> bool:
     return (a.dtype == torch.bfloat16 and a.shape[0] <= 16 and a.shape[1] % 32 == 0
             and a.stride(1) == 1 and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0

@@ -4,10 +4,13 @@ Backends, chosen by the runtime:
   "simt"    -- the engine's own FP32-core kernel; the only backend of the 32-bit path.
   "skinny"  -- the engine's tensor-core kernel for at most 16 rows (decoding): the weight
                matrix is streamed once and the epilogue is fused.
+  "tcgen05" -- the engine's TMA + tcgen05 kernel for prompt-sized products: operands staged by
+               TMA, accumulator in tensor memory, epilogue fused.
   "library" -- cuBLAS through ``torch.mm`` for bfloat16 (the reference runs its products
                through nn.Linear, i.e. the library: app/architectures/qwen_layers.py:50-53),
                followed by the engine's fused bias / GELU / residual epilogue kernel.
-  "auto"    -- "simt" for float32; for bfloat16 "skinny" when the shape allows it, else "library".
+  "auto"    -- "simt" for float32; for bfloat16 "skinny" up to 16 rows, "tcgen05" above, and
+               "library" for shapes neither takes (a K that is no multiple of 8).
 """
 
 from __future__ import annotations
@@ -46,7 +49,7 @@ def resolve_backend(requested: str, dtype: torch.dtype) -> str:
             raise KernelLibraryError(
                 f"the float32 path runs on the FP32-core kernel only, not {requested!r}")
         return "simt"
-    if requested not in ("auto", "simt", "skinny", "library"):
+    if requested not in ("auto", "simt", "skinny", "tcgen05", "library"):
         raise KernelLibraryError(f"unknown GEMM backend {requested!r}")
     return requested
 
@@ -63,7 +66,12 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, mod
     out_dtype = torch.float32 if mode in (EPILOGUE_RESIDUAL, EPILOGUE_F32) else x.dtype
     backend = resolve_backend(backend, x.dtype)
     if backend == "auto":
-        backend = "skinny" if kernels.skinny_gemm_supported(x, weight) else "library"
+        if kernels.skinny_gemm_supported(x, weight):
+            backend = "skinny"
+        elif kernels.tcgen05_gemm_supported(x, weight):
+            backend = "tcgen05"
+        else:
+            backend = "library"
     if backend == "library" and out is None and mode == EPILOGUE_F32 and bias is None and m > 0:
         acc = _mm_f32(x, weight.t())
         if acc is not None:
@@ -77,6 +85,9 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, mod
         return out
     if backend == "skinny":
         kernels.gemm_skinny(x, weight, bias, residual, out, mode)
+        return out
+    if backend == "tcgen05":
+        kernels.gemm_tcgen05(x, weight, bias, residual, out, mode)
         return out
     acc = None
     if out_dtype == torch.float32:
