@@ -5,14 +5,16 @@
 // reference (app/architectures/qwen_layers.py:50-53, app/architectures/starcoder2_layers.py:19-23)
 // for prompt-sized M, with no separate epilogue pass over the activations.
 //
-// One block computes one 128 x 256 tile of the output (128 x 128 when N is small) in six warps:
+// A block walks 128 x BN tiles of the output (BN a multiple of 16 up to 256, chosen per shape so
+// that the SMs get even shares) in six warps:
 //   warp 4, one lane: producer. For every 64-wide slice of K it waits for a free stage,
 //     announces the bytes on the stage's "full" mbarrier and issues two TMA tile loads
 //     (cp.async.bulk.tensor.2d, 128-byte swizzle) for A and W, both K-major.
 //   warp 5, one lane: MMA issuer. Waits for "full", issues four tcgen05.mma (K = 16 each) whose
 //     operands are shared-memory descriptors over the swizzled stage, and commits them to the
 //     stage's "empty" mbarrier; after the last slice it commits to the "accumulator ready"
-//     mbarrier. Warp 5 also allocates and frees the 256 columns of tensor memory.
+//     mbarrier of the accumulator buffer in use. Warp 5 also allocates and frees tensor memory
+//     (all 512 columns: two accumulator buffers, so one block per SM).
 //   warps 0-3: epilogue. Each owns 32 of the 128 accumulator lanes (rows): tcgen05.ld brings
 //     32 columns at a time into registers, the epilogue is applied and the row piece stored.
 // Rows and columns beyond M, N and K are zero-filled by TMA on the way in and skipped on the
@@ -113,17 +115,100 @@ __device__ __forceinline__ void umma_commit(unsigned long long* bar) {
 struct TcShared {
     unsigned long long full[TC_STAGES];
     unsigned long long empty[TC_STAGES];
-    unsigned long long acc_ready;
+    unsigned long long acc_full[2];
+    unsigned long long acc_empty[2];
     unsigned tmem_base;
 };
 
-template <int BN>
+__device__ __forceinline__ void tc_mbar_arrive(unsigned long long* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void tmem_load16(unsigned taddr, unsigned (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+}
+
+// Applies the epilogue to 16 accumulator values of one output row and stores them.
+__device__ __forceinline__ void store_piece(const unsigned (&r)[16], const float* __restrict__ bias,
+                                            const float* residual, void* out, size_t obase, int nbase, int N,
+                                            int mode) {
+    if (mode >= 2) {
+        float* o = reinterpret_cast<float*>(out) + obase;
+        const float* res = (mode == 2) ? residual + obase : nullptr;
+        if (nbase + 16 <= N && (obase % 4) == 0) {
+#pragma unroll
+            for (int j = 0; j < 16; j += 4) {
+                float4 v;
+                v.x = __uint_as_float(r[j]); v.y = __uint_as_float(r[j + 1]);
+                v.z = __uint_as_float(r[j + 2]); v.w = __uint_as_float(r[j + 3]);
+                if (bias) {
+                    v.x += bias[nbase + j]; v.y += bias[nbase + j + 1];
+                    v.z += bias[nbase + j + 2]; v.w += bias[nbase + j + 3];
+                }
+                if (res) {
+                    const float4 q = *reinterpret_cast<const float4*>(res + j);
+                    v.x += q.x; v.y += q.y; v.z += q.z; v.w += q.w;
+                }
+                *reinterpret_cast<float4*>(o + j) = v;
+            }
+        } else {
+            for (int j = 0; j < 16; ++j) {
+                if (nbase + j >= N) break;
+                float v = __uint_as_float(r[j]);
+                if (bias) v += bias[nbase + j];
+                if (res) v += res[j];
+                o[j] = v;
+            }
+        }
+        return;
+    }
+    __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out) + obase;
+    if (nbase + 16 <= N && (obase % 8) == 0) {
+#pragma unroll
+        for (int j = 0; j < 16; j += 8) {
+            float v[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                v[e] = __uint_as_float(r[j + e]);
+                if (bias) v[e] += bias[nbase + j + e];
+                if (mode == 1) v[e] = gelu_tanh(v[e]);
+            }
+            uint4 pk;
+            __nv_bfloat162 h0 = __floats2bfloat162_rn(v[0], v[1]);
+            __nv_bfloat162 h1 = __floats2bfloat162_rn(v[2], v[3]);
+            __nv_bfloat162 h2 = __floats2bfloat162_rn(v[4], v[5]);
+            __nv_bfloat162 h3 = __floats2bfloat162_rn(v[6], v[7]);
+            pk.x = *reinterpret_cast<unsigned*>(&h0); pk.y = *reinterpret_cast<unsigned*>(&h1);
+            pk.z = *reinterpret_cast<unsigned*>(&h2); pk.w = *reinterpret_cast<unsigned*>(&h3);
+            *reinterpret_cast<uint4*>(o + j) = pk;
+        }
+    } else {
+        for (int j = 0; j < 16; ++j) {
+            if (nbase + j >= N) break;
+            float v = __uint_as_float(r[j]);
+            if (bias) v += bias[nbase + j];
+            if (mode == 1) v = gelu_tanh(v);
+            o[j] = __float2bfloat16_rn(v);
+        }
+    }
+}
+
+// Persistent: a block walks the tiles blockIdx.x, blockIdx.x + gridDim.x, ... (rows fastest, so
+// blocks that run together share weight tiles through L2). The accumulator is double-buffered
+// in tensor memory (2 x 256 columns): the epilogue of one tile overlaps the products of the next.
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     const float* __restrict__ bias, const float* residual, void* out, int ldo, int M,
-                    int N, int K, int mode, int* status) {
-    constexpr unsigned A_BYTES = TC_BM * TC_BK * 2, W_BYTES = BN * TC_BK * 2;
-    constexpr unsigned STAGE_BYTES = A_BYTES + W_BYTES;
+                    int N, int K, int bn, int mode, int* status) {
+    const unsigned a_bytes = TC_BM * TC_BK * 2, w_bytes = (unsigned)bn * TC_BK * 2;
+    const unsigned stage_bytes = a_bytes + w_bytes;
     extern __shared__ unsigned char tc_smem_raw[];
     // stages must start on a 1024-byte boundary for the 128-byte swizzle
     unsigned char* tiles = reinterpret_cast<unsigned char*>(
@@ -131,156 +216,103 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     __shared__ TcShared sh;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.y * TC_BM, n0 = blockIdx.x * BN;
     const int k_slices = (K + TC_BK - 1) / TC_BK;
+    const int tiles_m = (M + TC_BM - 1) / TC_BM, tiles_n = (N + bn - 1) / bn;
+    const int n_tiles = tiles_m * tiles_n;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < TC_STAGES; ++s) {
             tc_mbar_init(&sh.full[s], 1);
             tc_mbar_init(&sh.empty[s], 1);
         }
-        tc_mbar_init(&sh.acc_ready, 1);
+        for (int b = 0; b < 2; ++b) {
+            tc_mbar_init(&sh.acc_full[b], 1);
+            tc_mbar_init(&sh.acc_empty[b], 4);          // one arrival per epilogue warp
+        }
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     if (warp == 5) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(
                          smem_u32(&sh.tmem_base)),
-                     "r"(BN)
+                     "r"(512)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-    const unsigned tmem_acc = sh.tmem_base;
+    const unsigned tmem_base = sh.tmem_base;
 
     if (warp == 4) {
         // ---------------- producer
         if (lane == 0) {
-            int issued = 0;
-            for (int ks = 0; ks < k_slices; ++ks) {
-                const int s = ks % TC_STAGES;
-                const unsigned use = (unsigned)(ks / TC_STAGES);
-                if (!tc_mbar_wait(&sh.empty[s], (use & 1) ^ 1, status)) break;
-                tc_mbar_expect_tx(&sh.full[s], STAGE_BYTES);
-                unsigned char* a_tile = tiles + (size_t)s * STAGE_BYTES;
-                tma_load_2d(a_tile, &map_a, ks * TC_BK, m0, &sh.full[s]);
-                tma_load_2d(a_tile + A_BYTES, &map_w, ks * TC_BK, n0, &sh.full[s]);
-                issued = ks + 1;
+            int it = 0;
+            bool alive = true;
+            for (int tile = blockIdx.x; tile < n_tiles && alive; tile += gridDim.x) {
+                const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * bn;
+                for (int ks = 0; ks < k_slices; ++ks, ++it) {
+                    const int s = it % TC_STAGES;
+                    alive = tc_mbar_wait(&sh.empty[s], ((unsigned)(it / TC_STAGES) & 1) ^ 1, status);
+                    if (!alive) break;
+                    tc_mbar_expect_tx(&sh.full[s], stage_bytes);
+                    unsigned char* a_tile = tiles + (size_t)s * stage_bytes;
+                    tma_load_2d(a_tile, &map_a, ks * TC_BK, m0, &sh.full[s]);
+                    tma_load_2d(a_tile + a_bytes, &map_w, ks * TC_BK, n0, &sh.full[s]);
+                }
             }
             // no copy of this block may still be in flight when it ends: wait (bounded) for the
             // loads of the last stages to land
-            for (int ks = max(0, issued - TC_STAGES); ks < issued; ++ks)
-                if (!tc_mbar_wait(&sh.full[ks % TC_STAGES], (unsigned)(ks / TC_STAGES) & 1, status)) break;
+            for (int j = max(0, it - TC_STAGES); j < it; ++j)
+                if (!tc_mbar_wait(&sh.full[j % TC_STAGES], (unsigned)(j / TC_STAGES) & 1, status)) break;
         }
     } else if (warp == 5) {
         // ---------------- MMA issuer
         if (lane == 0) {
-            const unsigned idesc = umma_idesc(TC_BM, BN);
+            const unsigned idesc = umma_idesc(TC_BM, bn);
+            int it = 0, local = 0;
             bool alive = true;
-            for (int ks = 0; ks < k_slices && alive; ++ks) {
-                const int s = ks % TC_STAGES;
-                const unsigned use = (unsigned)(ks / TC_STAGES);
-                alive = tc_mbar_wait(&sh.full[s], use & 1, status);
+            for (int tile = blockIdx.x; tile < n_tiles && alive; tile += gridDim.x, ++local) {
+                const int buf = local & 1;
+                alive = tc_mbar_wait(&sh.acc_empty[buf], ((unsigned)(local >> 1) & 1) ^ 1, status);
                 if (!alive) break;
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                const unsigned char* a_tile = tiles + (size_t)s * STAGE_BYTES;
-                const unsigned long long adesc = umma_desc(a_tile);
-                const unsigned long long bdesc = umma_desc(a_tile + A_BYTES);
+                const unsigned tmem_acc = tmem_base + (unsigned)buf * 256;
+                for (int ks = 0; ks < k_slices; ++ks, ++it) {
+                    const int s = it % TC_STAGES;
+                    alive = tc_mbar_wait(&sh.full[s], (unsigned)(it / TC_STAGES) & 1, status);
+                    if (!alive) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                    const unsigned char* a_tile = tiles + (size_t)s * stage_bytes;
+                    const unsigned long long adesc = umma_desc(a_tile);
+                    const unsigned long long bdesc = umma_desc(a_tile + a_bytes);
 #pragma unroll
-                for (int k = 0; k < TC_BK / 16; ++k)   // 16 elements = 32 bytes further along K
-                    umma_bf16(tmem_acc, adesc + 2 * k, bdesc + 2 * k, idesc, (ks | k) != 0);
-                umma_commit(&sh.empty[s]);
+                    for (int k = 0; k < TC_BK / 16; ++k)   // 16 elements = 32 bytes further along K
+                        umma_bf16(tmem_acc, adesc + 2 * k, bdesc + 2 * k, idesc, (ks | k) != 0);
+                    umma_commit(&sh.empty[s]);
+                }
+                if (alive) umma_commit(&sh.acc_full[buf]);   // arrives when the tile's MMAs are done
             }
-            umma_commit(&sh.acc_ready);              // arrives when every MMA above has finished
         }
     } else {
         // ---------------- epilogue: warp w owns accumulator lanes 32 w .. 32 w + 31
-        const bool ready = tc_mbar_wait(&sh.acc_ready, 0, status);
-        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-        const int row = m0 + 32 * warp + lane;
-        if (ready) {
-            for (int c0 = 0; c0 < BN; c0 += 32) {
-                unsigned r[32];
-                const unsigned taddr = tmem_acc + ((unsigned)(32 * warp) << 16) + (unsigned)c0;
-                asm volatile(
-                    "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                    "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-                    "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
-                    : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-                      "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
-                      "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
-                      "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),
-                      "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-                    : "r"(taddr)
-                    : "memory");
-                asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-                if (row < M) {
-                    const int nbase = n0 + c0;
-                    const size_t obase = (size_t)row * ldo + nbase;
-                    if (mode >= 2) {
-                        float* o = reinterpret_cast<float*>(out) + obase;
-                        const float* res = (mode == 2) ? residual + obase : nullptr;
-                        const bool vec = nbase + 32 <= N && (obase % 4) == 0;
-                        if (vec) {
-#pragma unroll
-                            for (int j = 0; j < 32; j += 4) {
-                                float4 v;
-                                v.x = __uint_as_float(r[j]); v.y = __uint_as_float(r[j + 1]);
-                                v.z = __uint_as_float(r[j + 2]); v.w = __uint_as_float(r[j + 3]);
-                                if (bias) {
-                                    v.x += bias[nbase + j]; v.y += bias[nbase + j + 1];
-                                    v.z += bias[nbase + j + 2]; v.w += bias[nbase + j + 3];
-                                }
-                                if (res) {
-                                    const float4 q = *reinterpret_cast<const float4*>(res + j);
-                                    v.x += q.x; v.y += q.y; v.z += q.z; v.w += q.w;
-                                }
-                                *reinterpret_cast<float4*>(o + j) = v;
-                            }
-                        } else {
-                            for (int j = 0; j < 32; ++j) {
-                                if (nbase + j >= N) break;
-                                float v = __uint_as_float(r[j]);
-                                if (bias) v += bias[nbase + j];
-                                if (res) v += res[j];
-                                o[j] = v;
-                            }
-                        }
-                    } else {
-                        __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out) + obase;
-                        const bool vec = nbase + 32 <= N && (obase % 8) == 0;
-                        if (vec) {
-#pragma unroll
-                            for (int j = 0; j < 32; j += 8) {
-                                float v[8];
-#pragma unroll
-                                for (int e = 0; e < 8; ++e) {
-                                    v[e] = __uint_as_float(r[j + e]);
-                                    if (bias) v[e] += bias[nbase + j + e];
-                                    if (mode == 1) v[e] = gelu_tanh(v[e]);
-                                }
-                                uint4 pk;
-                                __nv_bfloat162 h0 = __floats2bfloat162_rn(v[0], v[1]);
-                                __nv_bfloat162 h1 = __floats2bfloat162_rn(v[2], v[3]);
-                                __nv_bfloat162 h2 = __floats2bfloat162_rn(v[4], v[5]);
-                                __nv_bfloat162 h3 = __floats2bfloat162_rn(v[6], v[7]);
-                                pk.x = *reinterpret_cast<unsigned*>(&h0); pk.y = *reinterpret_cast<unsigned*>(&h1);
-                                pk.z = *reinterpret_cast<unsigned*>(&h2); pk.w = *reinterpret_cast<unsigned*>(&h3);
-                                *reinterpret_cast<uint4*>(o + j) = pk;
-                            }
-                        } else {
-                            for (int j = 0; j < 32; ++j) {
-                                if (nbase + j >= N) break;
-                                float v = __uint_as_float(r[j]);
-                                if (bias) v += bias[nbase + j];
-                                if (mode == 1) v = gelu_tanh(v);
-                                o[j] = __float2bfloat16_rn(v);
-                            }
-                        }
-                    }
-                }
+        int local = 0;
+        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++local) {
+            const int buf = local & 1;
+            if (!tc_mbar_wait(&sh.acc_full[buf], (unsigned)(local >> 1) & 1, status)) break;
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * bn;
+            const int row = m0 + 32 * warp + lane;
+            const unsigned tbase = tmem_base + (unsigned)buf * 256 + ((unsigned)(32 * warp) << 16);
+            for (int c0 = 0; c0 < bn; c0 += 16) {
+                unsigned r[16];
+                tmem_load16(tbase + (unsigned)c0, r);
+                if (row < M && n0 + c0 < N)
+                    store_piece(r, bias, residual, out, (size_t)row * ldo + n0 + c0, n0 + c0, N, mode);
             }
+            // the accumulator buffer may be overwritten from here on
+            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+            __syncwarp();
+            if (lane == 0) tc_mbar_arrive(&sh.acc_empty[buf]);
         }
     }
     // ---------------- teardown: every role arrives here; then tensor memory is freed
@@ -289,7 +321,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (warp == 5) {
         __syncwarp();
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_acc), "r"(BN)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(512)
                      : "memory");
     }
 }
@@ -326,17 +358,30 @@ int make_map(CUtensorMap* map, const void* base, long long rows, long long K, lo
     return MX_OK;
 }
 
-template <int BN>
-int launch_tc(const CUtensorMap& map_a, const CUtensorMap& map_w, const float* bias, const float* residual,
-              void* out, int ldo, int M, int N, int K, int mode, int* status, cudaStream_t stream) {
-    const size_t smem = (size_t)TC_STAGES * (TC_BM + BN) * TC_BK * 2 + 1024;
-    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)smem);
-    if (e != cudaSuccess) MX_REFUSE("tcgen05 gemm: cannot reserve %zu bytes of shared memory", smem);
-    dim3 grid((N + BN - 1) / BN, (M + TC_BM - 1) / TC_BM);
-    gemm_tcgen05_kernel<BN><<<grid, TC_THREADS, smem, stream>>>(map_a, map_w, bias, residual, out, ldo, M, N,
-                                                                K, mode, status);
-    return mx_launch_status();
+// The tile width that needs the fewest rounds of work per SM: the time of a product is about
+// (rounds of tiles per SM) x (tile width + a fixed cost per tile).
+int pick_tile_width(int M, int N, int n_sm) {
+    const long long tiles_m = (M + TC_BM - 1) / TC_BM;
+    int best = 256;
+    long long best_cost = -1;
+    for (int bn = 256; bn >= 32; bn -= 16) {
+        const long long tiles = tiles_m * ((N + bn - 1) / bn);
+        const long long rounds = (tiles + n_sm - 1) / n_sm;
+        const long long cost = rounds * (bn + 24);
+        if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = bn; }
+    }
+    return best;
+}
+
+int sm_count() {
+    static int count = 0;
+    if (count == 0) {
+        int device = 0;
+        cudaGetDevice(&device);
+        cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device);
+        if (count <= 0) count = 148;
+    }
+    return count;
 }
 
 }  // namespace
@@ -355,13 +400,25 @@ extern "C" int mx_gemm_tcgen05(const void* A, const void* W, const float* bias, 
     if ((mode >= 2) != (out_dtype == MX_DTYPE_F32))
         MX_REFUSE("tcgen05 gemm: epilogue mode %d does not write dtype %d", mode, out_dtype);
     if (status == nullptr) MX_REFUSE("tcgen05 gemm: needs a status word for its bounded waits");
-    const int bn = N > 128 ? 256 : 128;
+    const int n_sm = sm_count();
+    const int bn = pick_tile_width(M, N, n_sm);
     CUtensorMap map_a, map_w;
     int rc = make_map(&map_a, A, M, K, lda, TC_BM);
     if (rc != MX_OK) return rc;
     rc = make_map(&map_w, W, N, K, ldw, bn);
     if (rc != MX_OK) return rc;
-    if (bn == 256)
-        return launch_tc<256>(map_a, map_w, bias, residual, out, ldo, M, N, K, mode, status, stream);
-    return launch_tc<128>(map_a, map_w, bias, residual, out, ldo, M, N, K, mode, status, stream);
+    const size_t smem = (size_t)TC_STAGES * (TC_BM + bn) * TC_BK * 2 + 1024;
+    static bool attribute_set = false;
+    if (!attribute_set) {
+        const size_t most = (size_t)TC_STAGES * (TC_BM + 256) * TC_BK * 2 + 1024;
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)most);
+        if (e != cudaSuccess) MX_REFUSE("tcgen05 gemm: cannot reserve %zu bytes of shared memory", most);
+        attribute_set = true;
+    }
+    const long long tiles = (long long)((M + TC_BM - 1) / TC_BM) * ((N + bn - 1) / bn);
+    const int grid = (int)(tiles < n_sm ? tiles : n_sm);
+    gemm_tcgen05_kernel<<<grid, TC_THREADS, smem, stream>>>(map_a, map_w, bias, residual, out, ldo, M, N, K, bn,
+                                                           mode, status);
+    return mx_launch_status();
 }

@@ -9,8 +9,9 @@ Backends, chosen by the runtime:
   "library" -- cuBLAS through ``torch.mm`` for bfloat16 (the reference runs its products
                through nn.Linear, i.e. the library: app/architectures/qwen_layers.py:50-53),
                followed by the engine's fused bias / GELU / residual epilogue kernel.
-  "auto"    -- "simt" for float32; for bfloat16 "skinny" up to 16 rows, "tcgen05" above, and
-               "library" for shapes neither takes (a K that is no multiple of 8).
+  "auto"    -- "simt" for float32; for bfloat16 "skinny" up to 16 rows, "tcgen05" above 128 rows,
+               and "library" between (a weight stream that 128-row tiles would leave to a few
+               SMs) and for shapes neither takes (a K that is no multiple of 8).
 """
 
 from __future__ import annotations
@@ -68,7 +69,7 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, mod
     if backend == "auto":
         if kernels.skinny_gemm_supported(x, weight):
             backend = "skinny"
-        elif kernels.tcgen05_gemm_supported(x, weight):
+        elif m > 128 and kernels.tcgen05_gemm_supported(x, weight):
             backend = "tcgen05"
         else:
             backend = "library"
