@@ -292,6 +292,8 @@ template <typename T>
 __global__ void attention_merge_kernel(const float* __restrict__ part_o,
                                        const float* __restrict__ part_ml, T* __restrict__ out,
                                        int out_stride, int n_heads, int head_dim, int n_splits) {
+    pdl_trigger();
+    pdl_wait();
     const int t = blockIdx.x, h = blockIdx.y;
     const size_t base = ((size_t)t * n_heads + h) * n_splits;
     float m = -INFINITY;
@@ -382,8 +384,8 @@ extern "C" int mx_attention_merge_bf16(const float* part_o, const float* part_ml
                                        int n_splits, cudaStream_t stream) {
     if (n_tokens <= 0) return MX_OK;
     dim3 mgrid(n_tokens, n_heads);
-    attention_merge_kernel<__nv_bfloat16><<<mgrid, 128, 0, stream>>>(
-        part_o, part_ml, (__nv_bfloat16*)out, out_stride, n_heads, head_dim, n_splits);
+    mx_launch_chained(attention_merge_kernel<__nv_bfloat16>, mgrid, dim3(128), 0, stream, part_o, part_ml,
+                      (__nv_bfloat16*)out, out_stride, n_heads, head_dim, n_splits);
     return mx_launch_status();
 }
 

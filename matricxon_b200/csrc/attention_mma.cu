@@ -180,6 +180,7 @@ attention_mma_kernel(const MmaAttnParams p) {
     __nv_bfloat16* stages = reinterpret_cast<__nv_bfloat16*>(smem_raw);
     __shared__ __align__(8) unsigned long long bars[N_STAGES];
 
+    pdl_trigger();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
     const int tile = blockIdx.x, kh = blockIdx.y, split = blockIdx.z;
@@ -197,6 +198,9 @@ attention_mma_kernel(const MmaAttnParams p) {
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     __syncthreads();
+    // up to here only step metadata was read (uploaded before the step, written by no kernel);
+    // queries and the newest keys and values come from the kernels before this one
+    pdl_wait();
 
     // rows of this block and of this warp
     const int tile_last = min(tile_row0 + TILE_ROWS - 1, n_rows - 1);
@@ -497,7 +501,7 @@ int launch_mma(const MmaAttnParams& p, cudaStream_t stream) {
         if (e != cudaSuccess) MX_REFUSE("attention: cannot reserve %zu bytes of shared memory", smem);
     }
     dim3 grid(p.n_tiles, p.n_kv_heads, p.n_splits);
-    attention_mma_kernel<HD, NARROW><<<grid, MMA_THREADS, smem, stream>>>(p);
+    mx_launch_chained(attention_mma_kernel<HD, NARROW>, grid, dim3(MMA_THREADS), smem, stream, p);
     return mx_launch_status();
 }
 

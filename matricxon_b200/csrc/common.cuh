@@ -42,6 +42,35 @@ static inline int mx_launch_status() {
     return MX_OK;
 }
 
+// ---- programmatic dependent launch: a kernel launched with mx_launch_chained may start while the
+// kernel before it in the stream is still running. It must call pdl_wait() before it reads anything
+// an earlier kernel wrote and before it writes global memory at all; what it does before that
+// (reading weights, setting up shared memory) overlaps the predecessor's tail. pdl_trigger() lets
+// the NEXT kernel in the stream begin its own preamble.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;\n" ::); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void prefetch_l2(const void* p) {
+    asm volatile("prefetch.global.L2 [%0];\n" ::"l"(p));
+}
+
+bool mx_chained_launch_enabled();
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t mx_launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                            cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = mx_chained_launch_enabled() ? 1 : 0;
+    config.attrs = attribute;
+    config.numAttrs = 1;
+    return cudaLaunchKernelEx(&config, kernel, KArgs(args)...);
+}
+
 __device__ __forceinline__ float to_float(float v) { return v; }
 __device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
 

@@ -9,11 +9,24 @@
 // (app/architectures/starcoder2_layers.py:23).
 #include <stdarg.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 
 static thread_local char g_error[512] = "";
 extern "C" const char* mx_last_error_message() { return g_error; }
+// MATRICXON_CHAINED_LAUNCH=1 turns programmatic dependent launch on for the decode kernels; by
+// default every kernel waits for the one before it to finish, as an ordinary launch does (measured
+// on B200 inside CUDA graphs, chaining changed a decode step by less than 4% either way).
+bool mx_chained_launch_enabled() {
+    static int enabled = -1;
+    if (enabled < 0) {
+        const char* value = getenv("MATRICXON_CHAINED_LAUNCH");
+        enabled = (value != nullptr && value[0] == '1') ? 1 : 0;
+    }
+    return enabled == 1;
+}
+
 void mx_set_error(const char* fmt, ...) {
     va_list ap;
     va_start(ap, fmt);
@@ -25,9 +38,11 @@ void mx_set_error(const char* fmt, ...) {
 template <typename T>
 __global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ table,
                              float* __restrict__ out, int hidden, int vocab, int* status) {
+    pdl_trigger();
     const int row = blockIdx.x;
-    const int id = ids[row];
+    const int id = ids[row];                 // step metadata: uploaded before the step, by no kernel
     float* o = out + (size_t)row * hidden;
+    pdl_wait();
     if (id < 0 || id >= vocab) {
         if (threadIdx.x == 0) atomicOr(status, MX_STATUS_BAD_TOKEN_ID);
         for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = 0.f;
@@ -42,11 +57,11 @@ extern "C" int mx_embed(const int* ids, const void* table, int dtype, float* out
     if (n_tokens <= 0) return MX_OK;
     const int threads = hidden >= 1024 ? 256 : 128;
     if (dtype == MX_DTYPE_F32)
-        embed_kernel<float><<<n_tokens, threads, 0, stream>>>(ids, (const float*)table, out, hidden,
-                                                              vocab, status);
+        mx_launch_chained(embed_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, ids,
+                          (const float*)table, out, hidden, vocab, status);
     else
-        embed_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>(
-            ids, (const __nv_bfloat16*)table, out, hidden, vocab, status);
+        mx_launch_chained(embed_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, stream, ids,
+                          (const __nv_bfloat16*)table, out, hidden, vocab, status);
     return mx_launch_status();
 }
 
@@ -59,8 +74,10 @@ __global__ void layernorm_kernel(const float* __restrict__ x, const int* __restr
                                  TOut* __restrict__ out, int hidden, float eps) {
     extern __shared__ float row_cache[];
     __shared__ float scratch[32];
+    pdl_trigger();
     const int r = blockIdx.x;
     const int src_row = rows ? rows[r] : r;
+    pdl_wait();
     const float* xr = x + (size_t)src_row * hidden;
     float s = 0.f;
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
@@ -94,11 +111,13 @@ extern "C" int mx_layernorm(const float* x, const int* rows, const float* weight
     if (out_dtype == MX_DTYPE_F32) {
         if (smem > 48 * 1024)
             cudaFuncSetAttribute(layernorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        layernorm_kernel<float><<<n_rows, threads, smem, stream>>>(x, rows, weight, bias, (float*)out, hidden, eps);
+        mx_launch_chained(layernorm_kernel<float>, dim3(n_rows), dim3(threads), smem, stream, x, rows, weight,
+                          bias, (float*)out, hidden, eps);
     } else {
         if (smem > 48 * 1024)
             cudaFuncSetAttribute(layernorm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        layernorm_kernel<__nv_bfloat16><<<n_rows, threads, smem, stream>>>(x, rows, weight, bias, (__nv_bfloat16*)out, hidden, eps);
+        mx_launch_chained(layernorm_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), smem, stream, x, rows,
+                          weight, bias, (__nv_bfloat16*)out, hidden, eps);
     }
     return mx_launch_status();
 }
@@ -120,15 +139,17 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int row_stride,
                                      int page_size, long long n_slots, int write_cache,
                                      int* status) {
     extern __shared__ float cs[];  // cos[half], sin[half]
+    pdl_trigger();
     const int t = blockIdx.x;
     const int half = rotary_dim >> 1;
-    const float pos = (float)positions[t];
+    const float pos = (float)positions[t];   // step metadata and constants: no kernel writes them
     for (int i = threadIdx.x; i < half; i += blockDim.x) {
         const float angle = pos * inv_freq[i];
         cs[i] = cosf(angle);
         cs[half + i] = sinf(angle);
     }
     __syncthreads();
+    pdl_wait();
     T* row = qkv + (size_t)t * row_stride;
 
     // q heads: rotate in place
@@ -192,13 +213,14 @@ extern "C" int mx_rope_kv_write(void* qkv, int dtype, int row_stride, const int*
     const int threads = work >= 1024 ? 256 : 128;
     const long long n_slots = n_pages * page_size;
     if (dtype == MX_DTYPE_F32)
-        rope_kv_write_kernel<float><<<n_tokens, threads, smem, stream>>>(
-            (float*)qkv, row_stride, positions, inv_freq, slots, (float*)cache, n_heads, n_kv_heads,
-            head_dim, rotary_dim, page_size, n_slots, write_cache, status);
+        mx_launch_chained(rope_kv_write_kernel<float>, dim3(n_tokens), dim3(threads), smem, stream,
+                          (float*)qkv, row_stride, positions, inv_freq, slots, (float*)cache, n_heads,
+                          n_kv_heads, head_dim, rotary_dim, page_size, n_slots, write_cache, status);
     else
-        rope_kv_write_kernel<__nv_bfloat16><<<n_tokens, threads, smem, stream>>>(
-            (__nv_bfloat16*)qkv, row_stride, positions, inv_freq, slots, (__nv_bfloat16*)cache,
-            n_heads, n_kv_heads, head_dim, rotary_dim, page_size, n_slots, write_cache, status);
+        mx_launch_chained(rope_kv_write_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), smem, stream,
+                          (__nv_bfloat16*)qkv, row_stride, positions, inv_freq, slots,
+                          (__nv_bfloat16*)cache, n_heads, n_kv_heads, head_dim, rotary_dim, page_size,
+                          n_slots, write_cache, status);
     return mx_launch_status();
 }
 

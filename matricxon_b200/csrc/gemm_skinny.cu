@@ -66,6 +66,18 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bflo
     for (int mb = 0; mb < MB; ++mb) acc[mb][0] = acc[mb][1] = acc[mb][2] = acc[mb][3] = 0.f;
 
     const int n_blocks = K / 32;
+    // The weights are nobody's output: start pulling this thread's first pieces towards L2 while
+    // the kernel before this one is still finishing, then wait for it before touching activations.
+    pdl_trigger();
+#pragma unroll
+    for (int u = 0; u < 2 * SK_UNROLL; ++u) {
+        const int kb = warp + u * SK_WARPS;
+        if (kb < n_blocks) {
+            if (row_ok[0]) prefetch_l2(wrow[0] + 32 * kb);
+            if (row_ok[1]) prefetch_l2(wrow[1] + 32 * kb);
+        }
+    }
+    pdl_wait();
     for (int kb0 = warp; kb0 < n_blocks; kb0 += SK_WARPS * SK_UNROLL) {
         uint4 wf[SK_UNROLL][2], xf[SK_UNROLL][MB];
 #pragma unroll
@@ -131,10 +143,12 @@ extern "C" int mx_gemm_skinny(const void* x, const void* W, const float* bias, c
         MX_REFUSE("skinny gemm: epilogue mode %d does not write dtype %d", mode, out_dtype);
     const int grid = (N + 15) / 16;
     if (M <= 8)
-        gemm_skinny_kernel<1><<<grid, SK_THREADS, 0, stream>>>(
-            (const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)W, ldw, bias, residual, out, ldo, M, N, K, mode);
+        mx_launch_chained(gemm_skinny_kernel<1>, dim3(grid), dim3(SK_THREADS), 0, stream,
+                          (const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)W, ldw, bias, residual, out, ldo,
+                          M, N, K, mode);
     else
-        gemm_skinny_kernel<2><<<grid, SK_THREADS, 0, stream>>>(
-            (const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)W, ldw, bias, residual, out, ldo, M, N, K, mode);
+        mx_launch_chained(gemm_skinny_kernel<2>, dim3(grid), dim3(SK_THREADS), 0, stream,
+                          (const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)W, ldw, bias, residual, out, ldo,
+                          M, N, K, mode);
     return mx_launch_status();
 }
