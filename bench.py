@@ -107,16 +107,13 @@ class ClockSampler:
 
 
 def reference_arm(args) -> int:
-    """The unmodified reference through its own API, if it is installed under baseline/_ref."""
-    ref_dir = os.path.join(ROOT, "baseline", "_ref")
-    if not os.path.isdir(os.path.join(ref_dir, "app")):
-        print(json.dumps({"impl": "reference",
-                          "unavailable": "nesmind/matricxon is not installed under baseline/_ref "
-                                         "(pip install --no-index of /root/reference: see DESIGN.md)"}))
-        return 0
-    from baseline.reference_arm import run_reference     # imported only when the install exists
-
-    print(json.dumps(run_reference(args, STARCODER2_3B, CONTEXT)))
+    """The reference arm. nesmind/matricxon cannot be installed offline: it has no package
+    metadata (pip stops at "metadata-generation-failed": flat layout with several top-level
+    packages, no [project] table), so there is nothing under baseline/_ref to run."""
+    print(json.dumps({"impl": "reference",
+                      "unavailable": "pip install --no-index --target baseline/_ref of nesmind/matricxon "
+                                     "fails at metadata generation (the tree is not an installable "
+                                     "package: flat layout, no [project] table)"}))
     return 0
 
 
@@ -299,9 +296,10 @@ def main() -> int:
     e2e_context = context
     prompts = [torch.randint(0, vocab, (e2e_context,), generator=generator).tolist() for _ in range(batch)]
     rids = [] if args.skip_e2e else [engine.add_request(p, sampling) for p in prompts]
-    produced = 0 if rids else batch * args.warmup
-    while produced < batch * args.warmup:                       # prefill + warm-up decode steps
-        produced += len(engine.step())
+    produced = {rid: 0 for rid in rids}
+    while rids and min(produced.values()) < args.warmup:        # prefill + warm-up decode steps
+        for rid, _, _ in engine.step():
+            produced[rid] += 1
     torch.cuda.synchronize()
     t0 = time.perf_counter()
     tokens_out = 0
