@@ -292,8 +292,9 @@ def main() -> int:
     pf_frac = pf_flops / (pf_ms * 1e-3) / (peaks["bf16_tflops"] * 1e12)
 
     # ---- end to end through the entry point: host ids in, sampled ids out, every step
-    sampling = SamplingConfig(temperature=0.0, num_predict=args.steps + args.warmup, num_ctx=CONTEXT)
-    e2e_context = context
+    # every request decodes through the whole timed region: K steps of the full batch, then cancel
+    sampling = SamplingConfig(temperature=0.0, num_predict=args.steps + args.warmup + 64, num_ctx=CONTEXT)
+    e2e_context = min(context, CONTEXT - (args.steps + args.warmup + 64) - 8)
     prompts = [torch.randint(0, vocab, (e2e_context,), generator=generator).tolist() for _ in range(batch)]
     rids = [] if args.skip_e2e else [engine.add_request(p, sampling) for p in prompts]
     produced = {rid: 0 for rid in rids}
@@ -304,15 +305,16 @@ def main() -> int:
     t0 = time.perf_counter()
     tokens_out = 0
     e2e_steps = 0
-    while engine.has_unfinished():
+    for _ in range(args.steps if rids else 0):
         tokens_out += len(engine.step())
         e2e_steps += 1
     torch.cuda.synchronize()
     e2e_seconds = time.perf_counter() - t0
     for rid in rids:
+        engine.cancel(rid)
         engine.result(rid)
     e2e_value = tokens_out / e2e_seconds if e2e_seconds > 0 else 0.0
-    h2d_bytes = engine.core.runner.last_upload_bytes
+    h2d_bytes = engine.core.runner.last_upload_bytes + engine.sampler.last_upload_bytes
     d2h_bytes = batch * 4 + 4
 
     clocks.stop()

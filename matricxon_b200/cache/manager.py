@@ -25,6 +25,8 @@ from __future__ import annotations
 
 from dataclasses import dataclass, field
 
+import numpy as np
+
 
 class OutOfPages(RuntimeError):
     """A reservation that the pool cannot satisfy now. Nothing was taken."""
@@ -112,6 +114,22 @@ class RequestRecord:
     reserved: int = 0                   # tokens reserved beyond ``length``, not yet committed
     tables: list[list[int]] = field(default_factory=list)   # per group: logical -> physical / -1
     fresh_state: bool = True            # the state slot has not been zeroed for this request yet
+    # the same tables as int32 arrays (-1 beyond the end), kept in step so that a step can copy a
+    # whole row without converting a list
+    table_arrays: list = field(default_factory=list)
+
+    def mirror(self, group: int, first: int = 0) -> None:
+        """Copies ``tables[group][first:]`` into the array mirror, growing it when needed."""
+        table = self.tables[group]
+        array = self.table_arrays[group]
+        if len(table) > array.shape[0]:
+            grown = np.full(max(2 * array.shape[0], len(table), 16), -1, dtype=np.int32)
+            grown[:array.shape[0]] = array
+            self.table_arrays[group] = array = grown
+            first = min(first, len(table))
+        if first < len(table):
+            array[first:len(table)] = table[first:]
+        array[len(table):] = -1
 
 
 class CacheManager:
@@ -136,7 +154,8 @@ class CacheManager:
         if request_id in self.requests:
             raise CacheError(f"request {request_id!r} is already live")
         record = RequestRecord(request_id=request_id, state_slot=self.slots.allocate(),
-                               tables=[[] for _ in self.rules])
+                               tables=[[] for _ in self.rules],
+                               table_arrays=[np.full(16, -1, dtype=np.int32) for _ in self.rules])
         self.requests[request_id] = record
         return record
 
@@ -193,7 +212,10 @@ class CacheManager:
                 if page in self._ever_held[group]:
                     self.pages_reused += 1
                 self._ever_held[group].add(page)
-            record.tables[group].extend(pages)
+            if pages:
+                first = len(record.tables[group])
+                record.tables[group].extend(pages)
+                record.mirror(group, first)
         record.reserved += new_tokens
 
     def commit(self, request_id: str, new_tokens: int) -> None:
@@ -215,6 +237,7 @@ class CacheManager:
                     table[logical] = -1
             if expired:
                 self.pools[group].release(expired)
+                record.mirror(group, 0)
 
     def cancel_reservation(self, request_id: str) -> None:
         """Drops an uncommitted reservation (a step that did not run)."""
@@ -226,7 +249,18 @@ class CacheManager:
             extra = [page for page in table[keep:] if page >= 0]
             del table[keep:]
             self.pools[group].release(extra)
+            record.mirror(group, min(keep, len(table)))
         record.reserved = 0
+
+    def table_row(self, request_id: str, group: int, width: int) -> "np.ndarray":
+        """The request's block table of ``group`` as int32[width], -1 where it holds no page."""
+        record = self.record(request_id)
+        array = record.table_arrays[group]
+        if array.shape[0] < width:
+            grown = np.full(width, -1, dtype=np.int32)
+            grown[:array.shape[0]] = array
+            record.table_arrays[group] = array = grown
+        return array[:width]
 
     def slot_ids(self, request_id: str, group: int, start: int, count: int) -> list[int]:
         """Physical slots (page * page_size + offset) of positions [start, start + count)."""
@@ -267,6 +301,11 @@ class CacheManager:
                 raise CacheError(f"group {group}: pages both free and held: {sorted(free & seen.keys())}")
             if len(free) + len(seen) != pool.num_pages:
                 raise CacheError(f"group {group}: {pool.num_pages - len(free) - len(seen)} pages lost")
+            for record in self.requests.values():
+                table = record.tables[group]
+                array = record.table_arrays[group]
+                if list(array[:len(table)]) != table or (array[len(table):] != -1).any():
+                    raise CacheError(f"group {group}: the array mirror of {record.request_id!r} is stale")
         slots = [r.state_slot for r in self.requests.values()]
         if len(set(slots)) != len(slots):
             raise CacheError("a state slot is held by two requests")

@@ -295,9 +295,7 @@ class StepRunner:
                 if len(table) > width:
                     raise StepError(f"request {entry.request_id!r} holds {len(table)} pages, "
                                     f"the fixed table width is {width}")
-                row = part(8 + 2 * g)[s * width:(s + 1) * width]
-                row[:len(table)] = table
-                row[len(table):] = -1
+                part(8 + 2 * g)[s * width:(s + 1) * width] = cache.table_row(entry.request_id, g, width)
                 slots_g = part(7 + 2 * g)
                 if n == 1:
                     page = table[start // page_size]
