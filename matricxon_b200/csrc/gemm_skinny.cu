@@ -117,7 +117,7 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bflo
 #pragma unroll
         for (int w = 0; w < SK_WARPS; ++w) v += red[w][f][m];
         if (bias) v += bias[n];
-        if (mode == 1) v = gelu_tanh(v);
+        if (mode == 1) v = gelu_tanh_fast(v);
         const size_t o = (size_t)m * ldo + n;
         if (mode >= 2) {
             if (mode == 2) v += residual[o];

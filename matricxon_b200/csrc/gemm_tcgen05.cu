@@ -178,7 +178,7 @@ __device__ __forceinline__ void store_piece(const unsigned (&r)[16], const float
             for (int e = 0; e < 8; ++e) {
                 v[e] = __uint_as_float(r[j + e]);
                 if (bias) v[e] += bias[nbase + j + e];
-                if (mode == 1) v[e] = gelu_tanh(v[e]);
+                if (mode == 1) v[e] = gelu_tanh_fast(v[e]);
             }
             uint4 pk;
             __nv_bfloat162 h0 = __floats2bfloat162_rn(v[0], v[1]);
@@ -194,7 +194,7 @@ __device__ __forceinline__ void store_piece(const unsigned (&r)[16], const float
             if (nbase + j >= N) break;
             float v = __uint_as_float(r[j]);
             if (bias) v += bias[nbase + j];
-            if (mode == 1) v = gelu_tanh(v);
+            if (mode == 1) v = gelu_tanh_fast(v);
             o[j] = __float2bfloat16_rn(v);
         }
     }
@@ -326,6 +326,174 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// The same product with 256-row tiles: two 128 x BN accumulators share every weight tile, so a
+// block takes in (256 + BN) x 128 bytes per 64-wide slice of K for twice the arithmetic. What a
+// block can keep in flight (its shared memory) divided by the latency of a TMA load is its
+// bandwidth; with 128-row tiles that bandwidth feeds the tensor pipe for about 40 % of the
+// time, with 256-row tiles for most of it. The two accumulators fill tensor memory (2 x 256
+// columns), so the epilogue of a tile does not overlap the next tile's products; eight
+// epilogue warps (two per lane quarter, one per accumulator) keep it short, and the producer
+// goes on loading the next tile's stages meanwhile.
+constexpr int TCW_BM = 256;
+constexpr int TCW_STAGES = 3;
+constexpr int TCW_THREADS = 320;      // warps 0-7 epilogue, warp 8 producer, warp 9 MMA issuer
+
+struct TcWideShared {
+    unsigned long long full[TCW_STAGES];
+    unsigned long long empty[TCW_STAGES];
+    unsigned long long acc_full;
+    unsigned long long acc_empty;
+    unsigned tmem_base;
+};
+
+__global__ void __launch_bounds__(TCW_THREADS)
+gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                         const float* __restrict__ bias, const float* residual, void* out, int ldo, int M,
+                         int N, int K, int bn, int mode, int* status) {
+    const unsigned a_bytes = TCW_BM * TC_BK * 2, w_bytes = (unsigned)bn * TC_BK * 2;
+    const unsigned stage_bytes = a_bytes + w_bytes;
+    extern __shared__ unsigned char tc_smem_raw[];
+    unsigned char* tiles = reinterpret_cast<unsigned char*>(
+        (reinterpret_cast<uintptr_t>(tc_smem_raw) + 1023) & ~(uintptr_t)1023);
+    __shared__ TcWideShared sh;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int k_slices = (K + TC_BK - 1) / TC_BK;
+    const int tiles_m = (M + TCW_BM - 1) / TCW_BM, tiles_n = (N + bn - 1) / bn;
+    const int n_tiles = tiles_m * tiles_n;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < TCW_STAGES; ++s) {
+            tc_mbar_init(&sh.full[s], 1);
+            tc_mbar_init(&sh.empty[s], 1);
+        }
+        tc_mbar_init(&sh.acc_full, 1);
+        tc_mbar_init(&sh.acc_empty, 8);                 // one arrival per epilogue warp
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 9) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(
+                         smem_u32(&sh.tmem_base)),
+                     "r"(512)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    const unsigned tmem_base = sh.tmem_base;
+
+    if (warp == 8) {
+        // ---------------- producer
+        if (lane == 0) {
+            int it = 0;
+            bool alive = true;
+            for (int tile = blockIdx.x; tile < n_tiles && alive; tile += gridDim.x) {
+                const int m0 = (tile % tiles_m) * TCW_BM, n0 = (tile / tiles_m) * bn;
+                for (int ks = 0; ks < k_slices; ++ks, ++it) {
+                    const int s = it % TCW_STAGES;
+                    alive = tc_mbar_wait(&sh.empty[s], ((unsigned)(it / TCW_STAGES) & 1) ^ 1, status);
+                    if (!alive) break;
+                    tc_mbar_expect_tx(&sh.full[s], stage_bytes);
+                    unsigned char* a_tile = tiles + (size_t)s * stage_bytes;
+                    tma_load_2d(a_tile, &map_a, ks * TC_BK, m0, &sh.full[s]);
+                    tma_load_2d(a_tile + a_bytes, &map_w, ks * TC_BK, n0, &sh.full[s]);
+                }
+            }
+            for (int j = max(0, it - TCW_STAGES); j < it; ++j)     // nothing of ours stays in flight
+                if (!tc_mbar_wait(&sh.full[j % TCW_STAGES], (unsigned)(j / TCW_STAGES) & 1, status)) break;
+        }
+    } else if (warp == 9) {
+        // ---------------- MMA issuer: rows 0-127 into columns [0, bn), rows 128-255 into [256, 256 + bn)
+        if (lane == 0) {
+            const unsigned idesc = umma_idesc(128, bn);
+            int it = 0, local = 0;
+            bool alive = true;
+            for (int tile = blockIdx.x; tile < n_tiles && alive; tile += gridDim.x, ++local) {
+                alive = tc_mbar_wait(&sh.acc_empty, ((unsigned)local & 1) ^ 1, status);
+                if (!alive) break;
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                for (int ks = 0; ks < k_slices; ++ks, ++it) {
+                    const int s = it % TCW_STAGES;
+                    alive = tc_mbar_wait(&sh.full[s], (unsigned)(it / TCW_STAGES) & 1, status);
+                    if (!alive) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                    const unsigned char* a_tile = tiles + (size_t)s * stage_bytes;
+                    const unsigned long long adesc_lo = umma_desc(a_tile);
+                    const unsigned long long adesc_hi = umma_desc(a_tile + 128 * TC_BK * 2);
+                    const unsigned long long bdesc = umma_desc(a_tile + a_bytes);
+#pragma unroll
+                    for (int k = 0; k < TC_BK / 16; ++k) {
+                        umma_bf16(tmem_base, adesc_lo + 2 * k, bdesc + 2 * k, idesc, (ks | k) != 0);
+                        umma_bf16(tmem_base + 256, adesc_hi + 2 * k, bdesc + 2 * k, idesc, (ks | k) != 0);
+                    }
+                    umma_commit(&sh.empty[s]);
+                }
+                if (alive) umma_commit(&sh.acc_full);
+            }
+        }
+    } else {
+        // ---------------- epilogue: warp w -> accumulator w / 4, lane quarter w % 4
+        const int half = warp >> 2, quarter = warp & 3;
+        int local = 0;
+        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++local) {
+            if (!tc_mbar_wait(&sh.acc_full, (unsigned)local & 1, status)) break;
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            const int m0 = (tile % tiles_m) * TCW_BM, n0 = (tile / tiles_m) * bn;
+            const int row = m0 + 128 * half + 32 * quarter + lane;
+            const unsigned tbase = tmem_base + (unsigned)half * 256 + ((unsigned)(32 * quarter) << 16);
+            const size_t row_base = (size_t)row * ldo;
+            for (int c0 = 0; c0 < bn; c0 += 64) {
+                // the residual of up to four pieces first, so that the loads are in flight together
+                const bool fast = mode == 2 && row < M && n0 + c0 + 64 <= N && c0 + 64 <= bn &&
+                                  ((row_base + n0 + c0) % 4) == 0;
+                float4 res[16];
+                if (fast) {
+                    const float4* src = reinterpret_cast<const float4*>(residual + row_base + n0 + c0);
+#pragma unroll
+                    for (int q = 0; q < 16; ++q) res[q] = src[q];
+                }
+#pragma unroll
+                for (int piece = 0; piece < 4; ++piece) {
+                    const int c = c0 + 16 * piece;
+                    if (c >= bn) break;
+                    unsigned r[16];
+                    tmem_load16(tbase + (unsigned)c, r);
+                    if (row >= M || n0 + c >= N) continue;
+                    if (fast) {
+                        float* o = reinterpret_cast<float*>(out) + row_base + n0 + c;
+#pragma unroll
+                        for (int j = 0; j < 16; j += 4) {
+                            float4 v = res[4 * piece + j / 4];
+                            v.x += __uint_as_float(r[j]); v.y += __uint_as_float(r[j + 1]);
+                            v.z += __uint_as_float(r[j + 2]); v.w += __uint_as_float(r[j + 3]);
+                            if (bias) {
+                                v.x += bias[n0 + c + j]; v.y += bias[n0 + c + j + 1];
+                                v.z += bias[n0 + c + j + 2]; v.w += bias[n0 + c + j + 3];
+                            }
+                            *reinterpret_cast<float4*>(o + j) = v;
+                        }
+                    } else {
+                        store_piece(r, bias, residual, out, row_base + n0 + c, n0 + c, N, mode);
+                    }
+                }
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+            __syncwarp();
+            if (lane == 0) tc_mbar_arrive(&sh.acc_empty);
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    if (warp == 9) {
+        __syncwarp();
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(512)
+                     : "memory");
+    }
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
                                   CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
@@ -360,14 +528,14 @@ int make_map(CUtensorMap* map, const void* base, long long rows, long long K, lo
 
 // The tile width that needs the fewest rounds of work per SM: the time of a product is about
 // (rounds of tiles per SM) x (tile width + a fixed cost per tile).
-int pick_tile_width(int M, int N, int n_sm) {
-    const long long tiles_m = (M + TC_BM - 1) / TC_BM;
+int pick_tile_width(int M, int N, int n_sm, int tile_rows) {
+    const long long tiles_m = (M + tile_rows - 1) / tile_rows;
     int best = 256;
     long long best_cost = -1;
     for (int bn = 256; bn >= 32; bn -= 16) {
         const long long tiles = tiles_m * ((N + bn - 1) / bn);
         const long long rounds = (tiles + n_sm - 1) / n_sm;
-        const long long cost = rounds * (bn + 24);
+        const long long cost = rounds * (bn + (tile_rows == 128 ? 24 : 48));   // + a tile's fixed cost
         if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = bn; }
     }
     return best;
@@ -401,24 +569,35 @@ extern "C" int mx_gemm_tcgen05(const void* A, const void* W, const float* bias, 
         MX_REFUSE("tcgen05 gemm: epilogue mode %d does not write dtype %d", mode, out_dtype);
     if (status == nullptr) MX_REFUSE("tcgen05 gemm: needs a status word for its bounded waits");
     const int n_sm = sm_count();
-    const int bn = pick_tile_width(M, N, n_sm);
+    const bool wide = M > 256;                     // 256-row tiles once there are rows to fill them
+    const int tile_rows = wide ? TCW_BM : TC_BM;
+    const int stages = wide ? TCW_STAGES : TC_STAGES;
+    const int bn = pick_tile_width(M, N, n_sm, tile_rows);
     CUtensorMap map_a, map_w;
-    int rc = make_map(&map_a, A, M, K, lda, TC_BM);
+    int rc = make_map(&map_a, A, M, K, lda, tile_rows);
     if (rc != MX_OK) return rc;
     rc = make_map(&map_w, W, N, K, ldw, bn);
     if (rc != MX_OK) return rc;
-    const size_t smem = (size_t)TC_STAGES * (TC_BM + bn) * TC_BK * 2 + 1024;
+    const size_t smem = (size_t)stages * (tile_rows + bn) * TC_BK * 2 + 1024;
     static bool attribute_set = false;
     if (!attribute_set) {
         const size_t most = (size_t)TC_STAGES * (TC_BM + 256) * TC_BK * 2 + 1024;
+        const size_t most_wide = (size_t)TCW_STAGES * (TCW_BM + 256) * TC_BK * 2 + 1024;
         cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              (int)most);
-        if (e != cudaSuccess) MX_REFUSE("tcgen05 gemm: cannot reserve %zu bytes of shared memory", most);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(gemm_tcgen05_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)most_wide);
+        if (e != cudaSuccess) MX_REFUSE("tcgen05 gemm: cannot reserve %zu bytes of shared memory", most_wide);
         attribute_set = true;
     }
-    const long long tiles = (long long)((M + TC_BM - 1) / TC_BM) * ((N + bn - 1) / bn);
+    const long long tiles = (long long)((M + tile_rows - 1) / tile_rows) * ((N + bn - 1) / bn);
     const int grid = (int)(tiles < n_sm ? tiles : n_sm);
-    gemm_tcgen05_kernel<<<grid, TC_THREADS, smem, stream>>>(map_a, map_w, bias, residual, out, ldo, M, N, K, bn,
-                                                           mode, status);
+    if (wide)
+        gemm_tcgen05_wide_kernel<<<grid, TCW_THREADS, smem, stream>>>(map_a, map_w, bias, residual, out, ldo, M,
+                                                                      N, K, bn, mode, status);
+    else
+        gemm_tcgen05_kernel<<<grid, TC_THREADS, smem, stream>>>(map_a, map_w, bias, residual, out, ldo, M, N, K,
+                                                                bn, mode, status);
     return mx_launch_status();
 }
