@@ -16,7 +16,8 @@
 // few bulk asynchronous copies (cp.async.bulk, completion counted on an mbarrier) issued by
 // one thread, several chunks ahead of the arithmetic. Pages must hold 8, 16 or 32 slots.
 //   * "wide" tiles (64 rows, prompt portions): each warp has 16 rows of its own and every
-//     warp works on every chunk, so a chunk is fetched once for 64 rows (3 stages a block);
+//     warp works on every chunk, two chunks per softmax update, so a chunk is fetched once
+//     for 64 rows (four stages a block);
 //   * "narrow" tiles (at most 16 rows, decode tokens): all four warps hold the same rows,
 //     each streams every fourth chunk through a two-stage pipeline of its own, and their
 //     partial results are combined in shared memory.
@@ -39,7 +40,7 @@ namespace {
 constexpr int MMA_WARPS = 4;
 constexpr int MMA_THREADS = MMA_WARPS * 32;
 constexpr int CHUNK = 32;
-constexpr int WIDE_STAGES = 3;      // chunks in flight per block, wide tiles
+constexpr int WIDE_STAGES = 4;      // chunks in flight per block (two pairs), wide tiles
 constexpr int NARROW_STAGES = 2;    // chunks in flight per warp, narrow tiles
 constexpr int SPIN_LIMIT = 1 << 22;
 
@@ -168,8 +169,11 @@ __device__ __forceinline__ void issue_chunk(const MmaAttnParams& p, __nv_bfloat1
         }
 }
 
+struct One { static constexpr int value = 1; };
+struct Two { static constexpr int value = 2; };
+
 template <int HD, bool NARROW>
-__global__ void __launch_bounds__(MMA_THREADS)
+__global__ void __launch_bounds__(MMA_THREADS, NARROW ? 1 : 3)
 attention_mma_kernel(const MmaAttnParams p) {
     constexpr int KB = HD / 32;                 // 32-wide blocks of the head dim
     constexpr int NB = HD / 8;                  // 8-wide output column blocks
@@ -258,45 +262,61 @@ attention_mma_kernel(const MmaAttnParams p) {
     for (int nb = 0; nb < NB; ++nb) o[nb][0] = o[nb][1] = o[nb][2] = o[nb][3] = 0.f;
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
 
-    // ---- one chunk of arithmetic on a stage
-    auto compute = [&](const __nv_bfloat16* ks, const __nv_bfloat16* vs, int c0) {
-        // scores: block b gives this thread keys 8t + 2b, 8t + 2b + 1 of the chunk
-        float s[4][4];
+    // ---- arithmetic on one chunk, or on two consecutive chunks with one softmax update for both
+    auto compute = [&](auto n_chunks_tag, const __nv_bfloat16* ks0, const __nv_bfloat16* vs0,
+                       const __nv_bfloat16* ks1, const __nv_bfloat16* vs1, int c0) {
+        constexpr int NCH = decltype(n_chunks_tag)::value;
+        const __nv_bfloat16* ksv[2] = {ks0, ks1};
+        const __nv_bfloat16* vsv[2] = {vs0, vs1};
+        // scores: block b of a chunk gives this thread that chunk's keys 8t + 2b, 8t + 2b + 1.
+        // Column g of block b is key 8 (g / 2) + 2b + (g % 2). The 32-wide blocks of the head dim
+        // are the outer loop, so consecutive MMAs go to different accumulators.
+        float s[NCH][4][4];
 #pragma unroll
-        for (int b = 0; b < 4; ++b) {
-            s[b][0] = s[b][1] = s[b][2] = s[b][3] = 0.f;
-            // column g of block b is key 8 (g / 2) + 2b + (g % 2)
-            const __nv_bfloat16* krow = ks + (size_t)(8 * (g >> 1) + 2 * b + (g & 1)) * HD + 8 * t;
+        for (int ch = 0; ch < NCH; ++ch)
 #pragma unroll
-            for (int kb = 0; kb < KB; ++kb) {
-                const uint4 kf = *reinterpret_cast<const uint4*>(krow + 32 * kb);
-                mma_bf16(s[b], qf[0][kb].x, qf[1][kb].x, qf[0][kb].y, qf[1][kb].y, kf.x, kf.y);
-                mma_bf16(s[b], qf[0][kb].z, qf[1][kb].z, qf[0][kb].w, qf[1][kb].w, kf.z, kf.w);
+            for (int b = 0; b < 4; ++b) s[ch][b][0] = s[ch][b][1] = s[ch][b][2] = s[ch][b][3] = 0.f;
+#pragma unroll
+        for (int kb = 0; kb < KB; ++kb)
+#pragma unroll
+            for (int ch = 0; ch < NCH; ++ch) {
+                const __nv_bfloat16* kcol = ksv[ch] + (size_t)(8 * (g >> 1) + (g & 1)) * HD + 8 * t + 32 * kb;
+#pragma unroll
+                for (int b = 0; b < 4; ++b) {
+                    const uint4 kf = *reinterpret_cast<const uint4*>(kcol + 2 * b * HD);
+                    mma_bf16(s[ch][b], qf[0][kb].x, qf[1][kb].x, qf[0][kb].y, qf[1][kb].y, kf.x, kf.y);
+                    mma_bf16(s[ch][b], qf[0][kb].z, qf[1][kb].z, qf[0][kb].w, qf[1][kb].w, kf.z, kf.w);
+                }
             }
-        }
-        // mask (only where the chunk crosses an edge), running max and sum for rows g, g + 8
+        // mask (only where the chunks cross an edge), running max and sum for rows g, g + 8
         float m_new[2] = {m_run[0], m_run[1]};
-        const bool plain = rows_full && c0 >= all_lo && c0 + CHUNK - 1 <= all_hi;
+        const bool plain = rows_full && c0 >= all_lo && c0 + NCH * CHUNK - 1 <= all_hi;
+        // scores stay unscaled until the exponential: exp2(s * c - m * c) is one FMA and one ex2
+        // (c > 0, so the maximum of s * c is c times the maximum of s)
+        float raw_max[2] = {-INFINITY, -INFINITY};
         if (plain) {
 #pragma unroll
-            for (int b = 0; b < 4; ++b)
+            for (int ch = 0; ch < NCH; ++ch)
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    s[b][e] *= p.scale_log2;
-                    m_new[e >> 1] = fmaxf(m_new[e >> 1], s[b][e]);
-                }
+                for (int b = 0; b < 4; ++b)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) raw_max[e >> 1] = fmaxf(raw_max[e >> 1], s[ch][b][e]);
         } else {
 #pragma unroll
-            for (int b = 0; b < 4; ++b)
+            for (int ch = 0; ch < NCH; ++ch)
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int i = e >> 1;
-                    const int key = c0 + 8 * t + 2 * b + (e & 1);
-                    const bool visible = r_valid[i] && key <= r_pos[i] && key >= r_lo[i];
-                    s[b][e] = visible ? s[b][e] * p.scale_log2 : -INFINITY;
-                    m_new[i] = fmaxf(m_new[i], s[b][e]);
-                }
+                for (int b = 0; b < 4; ++b)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int i = e >> 1;
+                        const int key = c0 + CHUNK * ch + 8 * t + 2 * b + (e & 1);
+                        const bool visible = r_valid[i] && key <= r_pos[i] && key >= r_lo[i];
+                        s[ch][b][e] = visible ? s[ch][b][e] : -INFINITY;
+                        raw_max[i] = fmaxf(raw_max[i], s[ch][b][e]);
+                    }
         }
+        m_new[0] = fmaxf(m_new[0], raw_max[0] * p.scale_log2);
+        m_new[1] = fmaxf(m_new[1], raw_max[1] * p.scale_log2);
         float alpha[2], sum[2] = {0.f, 0.f}, m_use[2];
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
@@ -307,13 +327,15 @@ attention_mma_kernel(const MmaAttnParams p) {
             alpha[i] = fast_exp2(m_run[i] - m_use[i]);
         }
 #pragma unroll
-        for (int b = 0; b < 4; ++b)
+        for (int ch = 0; ch < NCH; ++ch)
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const float pv = fast_exp2(s[b][e] - m_use[e >> 1]);
-                s[b][e] = pv;
-                sum[e >> 1] += pv;
-            }
+            for (int b = 0; b < 4; ++b)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float pv = fast_exp2(fmaf(s[ch][b][e], p.scale_log2, -m_use[e >> 1]));
+                    s[ch][b][e] = pv;
+                    sum[e >> 1] += pv;
+                }
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
             sum[i] += __shfl_xor_sync(0xffffffffu, sum[i], 1);
@@ -321,39 +343,62 @@ attention_mma_kernel(const MmaAttnParams p) {
             l_run[i] = l_run[i] * alpha[i] + sum[i];
             m_run[i] = m_new[i];
         }
-        unsigned pa[2][4];
+        unsigned pa[NCH][2][4];
 #pragma unroll
-        for (int st = 0; st < 2; ++st) {
-            pa[st][0] = pack_bf16(s[2 * st][0], s[2 * st][1]);
-            pa[st][1] = pack_bf16(s[2 * st][2], s[2 * st][3]);
-            pa[st][2] = pack_bf16(s[2 * st + 1][0], s[2 * st + 1][1]);
-            pa[st][3] = pack_bf16(s[2 * st + 1][2], s[2 * st + 1][3]);
-        }
-        // values: this thread reads keys 8t..8t+7 of value dim 8 nb + g, from the page that
-        // holds them. Slots beyond the newest key hold no data yet: keep them out.
-        const int vkey0 = c0 + 8 * t;
-        unsigned keep[4] = {0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu};
-        if (vkey0 + 7 > hi_tile) {
+        for (int ch = 0; ch < NCH; ++ch)
 #pragma unroll
-            for (int w = 0; w < 4; ++w) {
-                const bool lo_ok = vkey0 + 2 * w <= hi_tile, hi_ok = vkey0 + 2 * w + 1 <= hi_tile;
-                keep[w] = (lo_ok ? 0x0000ffffu : 0u) | (hi_ok ? 0xffff0000u : 0u);
+            for (int st = 0; st < 2; ++st) {
+                pa[ch][st][0] = pack_bf16(s[ch][2 * st][0], s[ch][2 * st][1]);
+                pa[ch][st][1] = pack_bf16(s[ch][2 * st][2], s[ch][2 * st][3]);
+                pa[ch][st][2] = pack_bf16(s[ch][2 * st + 1][0], s[ch][2 * st + 1][1]);
+                pa[ch][st][3] = pack_bf16(s[ch][2 * st + 1][2], s[ch][2 * st + 1][3]);
             }
-        }
+        // values: this thread reads keys 8t..8t+7 (of each chunk) of value dim 8 nb + g, from the
+        // page that holds them. Slots beyond the newest key hold no data yet: keep them out.
         const int in_chunk = 8 * t;
         const int pg = in_chunk >> p.page_shift, off = in_chunk & (p.page_size - 1);
-        const __nv_bfloat16* vcol = vs + (size_t)pg * p.page_size * HD + (size_t)g * p.page_size + off;
+        const size_t voff = (size_t)pg * p.page_size * HD + (size_t)g * p.page_size + off;
+        // the running maximum moved for no row of the warp: the accumulators need no rescaling
+        const bool same_max = __all_sync(0xffffffffu, alpha[0] == 1.f && alpha[1] == 1.f);
+        if (!same_max) {
 #pragma unroll
-        for (int nb = 0; nb < NB; ++nb) {
-            uint4 vf = *reinterpret_cast<const uint4*>(vcol + (size_t)(8 * nb) * p.page_size);
-            vf.x &= keep[0]; vf.y &= keep[1]; vf.z &= keep[2]; vf.w &= keep[3];
-            o[nb][0] *= alpha[0]; o[nb][1] *= alpha[0];
-            o[nb][2] *= alpha[1]; o[nb][3] *= alpha[1];
-            mma_bf16(o[nb], pa[0][0], pa[0][1], pa[0][2], pa[0][3], vf.x, vf.y);
-            mma_bf16(o[nb], pa[1][0], pa[1][1], pa[1][2], pa[1][3], vf.z, vf.w);
+            for (int nb = 0; nb < NB; ++nb) {
+                o[nb][0] *= alpha[0]; o[nb][1] *= alpha[0];
+                o[nb][2] *= alpha[1]; o[nb][3] *= alpha[1];
+            }
+        }
+        if (c0 + NCH * CHUNK - 1 <= hi_tile) {
+#pragma unroll
+            for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+                for (int ch = 0; ch < NCH; ++ch) {
+                    const uint4 vf = *reinterpret_cast<const uint4*>(vsv[ch] + voff + (size_t)(8 * nb) * p.page_size);
+                    mma_bf16(o[nb], pa[ch][0][0], pa[ch][0][1], pa[ch][0][2], pa[ch][0][3], vf.x, vf.y);
+                    mma_bf16(o[nb], pa[ch][1][0], pa[ch][1][1], pa[ch][1][2], pa[ch][1][3], vf.z, vf.w);
+                }
+        } else {
+            // slots beyond the newest key hold no data yet: keep them out of the product
+            unsigned keep[NCH][4];
+#pragma unroll
+            for (int ch = 0; ch < NCH; ++ch) {
+                const int vkey0 = c0 + CHUNK * ch + 8 * t;
+#pragma unroll
+                for (int w = 0; w < 4; ++w) {
+                    const bool lo_ok = vkey0 + 2 * w <= hi_tile, hi_ok = vkey0 + 2 * w + 1 <= hi_tile;
+                    keep[ch][w] = (lo_ok ? 0x0000ffffu : 0u) | (hi_ok ? 0xffff0000u : 0u);
+                }
+            }
+#pragma unroll
+            for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+                for (int ch = 0; ch < NCH; ++ch) {
+                    uint4 vf = *reinterpret_cast<const uint4*>(vsv[ch] + voff + (size_t)(8 * nb) * p.page_size);
+                    vf.x &= keep[ch][0]; vf.y &= keep[ch][1]; vf.z &= keep[ch][2]; vf.w &= keep[ch][3];
+                    mma_bf16(o[nb], pa[ch][0][0], pa[ch][0][1], pa[ch][0][2], pa[ch][0][3], vf.x, vf.y);
+                    mma_bf16(o[nb], pa[ch][1][0], pa[ch][1][1], pa[ch][1][2], pa[ch][1][3], vf.z, vf.w);
+                }
         }
     };
-
     if (NARROW) {
         // ---- each warp streams chunks c_begin + warp, + 4, ... through two stages of its own
         __nv_bfloat16* my_stages = stages + (size_t)warp * NARROW_STAGES * STAGE_ELEMS;
@@ -374,7 +419,7 @@ attention_mma_kernel(const MmaAttnParams p) {
             __syncwarp();
             mbar_wait(&my_bars[st], (unsigned)((i / NARROW_STAGES) & 1), p.status);
             const __nv_bfloat16* ks = my_stages + (size_t)st * STAGE_ELEMS;
-            compute(ks, ks + CHUNK * HD, (my_first + MMA_WARPS * i) * CHUNK);
+            compute(One{}, ks, ks + CHUNK * HD, ks, ks + CHUNK * HD, (my_first + MMA_WARPS * i) * CHUNK);
             __syncwarp();                         // the stage may be refilled from here on
         }
         // ---- combine the four warps' partial results through shared memory (stages are free)
@@ -428,29 +473,35 @@ attention_mma_kernel(const MmaAttnParams p) {
         return;
     }
 
-    // ---- wide tiles: the block streams every chunk through WIDE_STAGES shared stages
-#pragma unroll
-    for (int s = 0; s < WIDE_STAGES - 1; ++s)
-        if (c_begin + s < c_end) {
-            __nv_bfloat16* ks = stages + (size_t)s * STAGE_ELEMS;
-            issue_chunk<HD>(p, ks, ks + CHUNK * HD, &bars[s], (c_begin + s) * CHUNK, lo_tile, hi_tile, bt,
-                            kbase, vbase, page_stride, tid, MMA_THREADS);
-        }
-    for (int ci = c_begin; ci < c_end; ++ci) {
-        const int i = ci - c_begin;
-        __syncthreads();                         // every warp is done with chunk ci - 1: its stage is free
-        if (ci + WIDE_STAGES - 1 < c_end) {
-            const int nx = (i + WIDE_STAGES - 1) % WIDE_STAGES;
-            __nv_bfloat16* ks = stages + (size_t)nx * STAGE_ELEMS;
-            issue_chunk<HD>(p, ks, ks + CHUNK * HD, &bars[nx], (ci + WIDE_STAGES - 1) * CHUNK, lo_tile,
+    // ---- wide tiles: the block streams the chunks two at a time through four shared stages
+    auto issue_wide = [&](int ci) {
+        if (ci < c_end) {
+            __nv_bfloat16* ks = stages + (size_t)((ci - c_begin) % WIDE_STAGES) * STAGE_ELEMS;
+            issue_chunk<HD>(p, ks, ks + CHUNK * HD, &bars[(ci - c_begin) % WIDE_STAGES], ci * CHUNK, lo_tile,
                             hi_tile, bt, kbase, vbase, page_stride, tid, MMA_THREADS);
         }
+    };
+    issue_wide(c_begin);
+    issue_wide(c_begin + 1);
+    for (int ci = c_begin; ci < c_end; ci += 2) {
+        const int i = ci - c_begin;
+        __syncthreads();                         // every warp is done with the pair before: its stages are free
+        issue_wide(ci + 2);
+        issue_wide(ci + 3);
         const int c0 = ci * CHUNK;
-        if (!(warp_has_rows && c0 <= hi_warp && c0 + CHUNK - 1 >= lo_warp)) continue;
-        const int st = i % WIDE_STAGES;
-        mbar_wait(&bars[st], (unsigned)((i / WIDE_STAGES) & 1), p.status);
-        const __nv_bfloat16* ks = stages + (size_t)st * STAGE_ELEMS;
-        compute(ks, ks + CHUNK * HD, c0);
+        const bool two = ci + 1 < c_end;
+        const int span = two ? 2 * CHUNK : CHUNK;
+        if (!(warp_has_rows && c0 <= hi_warp && c0 + span - 1 >= lo_warp)) continue;
+        const int st0 = i % WIDE_STAGES, st1 = (i + 1) % WIDE_STAGES;
+        const __nv_bfloat16* ks0 = stages + (size_t)st0 * STAGE_ELEMS;
+        const __nv_bfloat16* ks1 = stages + (size_t)st1 * STAGE_ELEMS;
+        mbar_wait(&bars[st0], (unsigned)((i / WIDE_STAGES) & 1), p.status);
+        if (two) {
+            mbar_wait(&bars[st1], (unsigned)(((i + 1) / WIDE_STAGES) & 1), p.status);
+            compute(Two{}, ks0, ks0 + CHUNK * HD, ks1, ks1 + CHUNK * HD, c0);
+        } else {
+            compute(One{}, ks0, ks0 + CHUNK * HD, ks0, ks0 + CHUNK * HD, c0);
+        }
     }
 
     // each warp writes its own rows; this thread holds columns 8 nb + 2t, + 1 of rows g, g + 8
