@@ -101,10 +101,84 @@ __global__ void layernorm_kernel(const float* __restrict__ x, const int* __restr
     }
 }
 
+// The same for rows whose length is a multiple of 4 and at most 256 x 4 x LN_VPT: the row lives in
+// registers as float4 vectors, read and written with 16-byte (8-byte for bfloat16) accesses.
+constexpr int LN_THREADS = 256;
+constexpr int LN_VPT = 8;
+
+template <typename TOut>
+__global__ void __launch_bounds__(LN_THREADS)
+layernorm_vec_kernel(const float* __restrict__ x, const int* __restrict__ rows,
+                     const float* __restrict__ weight, const float* __restrict__ bias,
+                     TOut* __restrict__ out, int hidden, float eps) {
+    __shared__ float scratch[32];
+    pdl_trigger();
+    const int r = blockIdx.x;
+    const int src_row = rows ? rows[r] : r;
+    pdl_wait();
+    const int n_vec = hidden >> 2;
+    const float4* xr = reinterpret_cast<const float4*>(x + (size_t)src_row * hidden);
+    float4 v[LN_VPT];
+    float s = 0.f;
+#pragma unroll
+    for (int k = 0; k < LN_VPT; ++k) {
+        const int i = threadIdx.x + k * LN_THREADS;
+        v[k] = i < n_vec ? xr[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+        s += (v[k].x + v[k].y) + (v[k].z + v[k].w);
+    }
+    const float mean = block_sum(s, scratch) / (float)hidden;
+    float q = 0.f;
+#pragma unroll
+    for (int k = 0; k < LN_VPT; ++k) {
+        const int i = threadIdx.x + k * LN_THREADS;
+        if (i < n_vec) {
+            const float a = v[k].x - mean, b = v[k].y - mean, c = v[k].z - mean, d = v[k].w - mean;
+            q += (a * a + b * b) + (c * c + d * d);
+        }
+    }
+    const float var = block_sum(q, scratch) / (float)hidden;
+    const float rstd = 1.0f / sqrtf(var + eps);
+    const float4* w4 = reinterpret_cast<const float4*>(weight);
+    const float4* b4 = reinterpret_cast<const float4*>(bias);
+#pragma unroll
+    for (int k = 0; k < LN_VPT; ++k) {
+        const int i = threadIdx.x + k * LN_THREADS;
+        if (i >= n_vec) continue;
+        const float4 w = w4[i];
+        float4 y;
+        y.x = (v[k].x - mean) * rstd * w.x; y.y = (v[k].y - mean) * rstd * w.y;
+        y.z = (v[k].z - mean) * rstd * w.z; y.w = (v[k].w - mean) * rstd * w.w;
+        if (bias) {
+            const float4 b = b4[i];
+            y.x += b.x; y.y += b.y; y.z += b.z; y.w += b.w;
+        }
+        if (sizeof(TOut) == 4) {
+            reinterpret_cast<float4*>(out + (size_t)r * hidden)[i] = y;
+        } else {
+            __nv_bfloat162 lo = __floats2bfloat162_rn(y.x, y.y), hi = __floats2bfloat162_rn(y.z, y.w);
+            uint2 packed;
+            packed.x = *reinterpret_cast<unsigned*>(&lo);
+            packed.y = *reinterpret_cast<unsigned*>(&hi);
+            reinterpret_cast<uint2*>(out + (size_t)r * hidden)[i] = packed;
+        }
+    }
+}
+
 extern "C" int mx_layernorm(const float* x, const int* rows, const float* weight, const float* bias,
                             void* out, int out_dtype, int n_rows, int hidden, float eps,
                             cudaStream_t stream) {
     if (n_rows <= 0) return MX_OK;
+    const bool aligned = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(weight) |
+                           reinterpret_cast<uintptr_t>(bias) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+    if (hidden % 4 == 0 && hidden <= 4 * LN_THREADS * LN_VPT && aligned) {
+        if (out_dtype == MX_DTYPE_F32)
+            mx_launch_chained(layernorm_vec_kernel<float>, dim3(n_rows), dim3(LN_THREADS), 0, stream, x, rows,
+                              weight, bias, (float*)out, hidden, eps);
+        else
+            mx_launch_chained(layernorm_vec_kernel<__nv_bfloat16>, dim3(n_rows), dim3(LN_THREADS), 0, stream, x,
+                              rows, weight, bias, (__nv_bfloat16*)out, hidden, eps);
+        return mx_launch_status();
+    }
     const size_t smem = (size_t)hidden * sizeof(float);
     if (smem > 200 * 1024) MX_REFUSE("layernorm: hidden size %d exceeds the 51200 this kernel stages", hidden);
     const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
@@ -199,6 +273,81 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int row_stride,
     }
 }
 
+// The same with 16-byte accesses: each thread rotates E consecutive pairs (E = 8 for bfloat16,
+// 4 for float). Needs rotary_dim / 2, head_dim and the row stride to be multiples of E.
+template <typename T>
+__global__ void rope_kv_write_vec_kernel(T* __restrict__ qkv, int row_stride,
+                                         const int* __restrict__ positions,
+                                         const float* __restrict__ inv_freq,
+                                         const int* __restrict__ slots, T* __restrict__ cache,
+                                         int n_heads, int n_kv_heads, int head_dim, int rotary_dim,
+                                         int page_size, long long n_slots, int write_cache,
+                                         int* status) {
+    constexpr int E = 16 / sizeof(T);
+    extern __shared__ float cs[];  // cos[half], sin[half]
+    pdl_trigger();
+    const int t = blockIdx.x;
+    const int half = rotary_dim >> 1;
+    const float pos = (float)positions[t];
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        const float angle = pos * inv_freq[i];
+        cs[i] = cosf(angle);
+        cs[half + i] = sinf(angle);
+    }
+    __syncthreads();
+    pdl_wait();
+    T* row = qkv + (size_t)t * row_stride;
+    const int per_head = half / E;
+
+    long long slot = -1;
+    if (write_cache) {
+        slot = slots[t];
+        if (slot != -1 && (slot < 0 || slot >= n_slots)) {
+            if (threadIdx.x == 0) atomicOr(status, MX_STATUS_BAD_SLOT);
+            slot = -1;
+        }
+    }
+    const long long page = slot >= 0 ? slot / page_size : 0;
+    const int offset = slot >= 0 ? (int)(slot - page * page_size) : 0;
+    const size_t head_stride = (size_t)page_size * head_dim;
+    T* kbase = cache + ((size_t)page * 2 * n_kv_heads) * head_stride + (size_t)offset * head_dim;
+    T* vbase = cache + ((size_t)page * 2 * n_kv_heads + n_kv_heads) * head_stride + offset;
+
+    // q heads (in place) and k heads (into the cache), E pairs per thread
+    const int rot_heads = n_heads + (slot >= 0 ? n_kv_heads : 0);
+    for (int item = threadIdx.x; item < rot_heads * per_head; item += blockDim.x) {
+        const int h = item / per_head, i = (item - h * per_head) * E;
+        const T* src = row + (size_t)h * head_dim;
+        uint4 lo_raw = *reinterpret_cast<const uint4*>(src + i);
+        uint4 hi_raw = *reinterpret_cast<const uint4*>(src + i + half);
+        T* lo = reinterpret_cast<T*>(&lo_raw);
+        T* hi = reinterpret_cast<T*>(&hi_raw);
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+            const float x1 = to_float(lo[e]), x2 = to_float(hi[e]);
+            const float c = cs[i + e], sn = cs[half + i + e];
+            lo[e] = from_float<T>(x1 * c - x2 * sn);
+            hi[e] = from_float<T>(x2 * c + x1 * sn);
+        }
+        T* dst = h < n_heads ? row + (size_t)h * head_dim
+                             : kbase + (size_t)(h - n_heads) * head_stride;
+        *reinterpret_cast<uint4*>(dst + i) = lo_raw;
+        *reinterpret_cast<uint4*>(dst + i + half) = hi_raw;
+    }
+    if (slot < 0) return;
+    const T* krow = row + (size_t)n_heads * head_dim;
+    const T* vrow = krow + (size_t)n_kv_heads * head_dim;
+    const int tail = head_dim - rotary_dim;          // dims beyond the rotary width pass through
+    for (int item = threadIdx.x; item < n_kv_heads * tail; item += blockDim.x) {
+        const int h = item / tail, i = rotary_dim + (item - h * tail);
+        kbase[(size_t)h * head_stride + i] = krow[(size_t)h * head_dim + i];
+    }
+    for (int item = threadIdx.x; item < n_kv_heads * head_dim; item += blockDim.x) {
+        const int h = item / head_dim, i = item - h * head_dim;
+        vbase[(size_t)h * head_stride + (size_t)i * page_size] = vrow[(size_t)h * head_dim + i];
+    }
+}
+
 extern "C" int mx_rope_kv_write(void* qkv, int dtype, int row_stride, const int* positions,
                                 const float* inv_freq, const int* slots, void* cache, int n_tokens,
                                 int n_heads, int n_kv_heads, int head_dim, int rotary_dim,
@@ -212,6 +361,22 @@ extern "C" int mx_rope_kv_write(void* qkv, int dtype, int row_stride, const int*
     const int work = n_heads * (rotary_dim / 2);
     const int threads = work >= 1024 ? 256 : 128;
     const long long n_slots = n_pages * page_size;
+    const int lanes = dtype == MX_DTYPE_F32 ? 4 : 8;
+    const bool vec = rotary_dim > 0 && (rotary_dim / 2) % lanes == 0 && head_dim % lanes == 0 &&
+                     row_stride % lanes == 0 && (reinterpret_cast<uintptr_t>(qkv) & 15) == 0 &&
+                     (reinterpret_cast<uintptr_t>(cache) & 15) == 0;
+    if (vec) {
+        if (dtype == MX_DTYPE_F32)
+            mx_launch_chained(rope_kv_write_vec_kernel<float>, dim3(n_tokens), dim3(threads), smem, stream,
+                              (float*)qkv, row_stride, positions, inv_freq, slots, (float*)cache, n_heads,
+                              n_kv_heads, head_dim, rotary_dim, page_size, n_slots, write_cache, status);
+        else
+            mx_launch_chained(rope_kv_write_vec_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), smem,
+                              stream, (__nv_bfloat16*)qkv, row_stride, positions, inv_freq, slots,
+                              (__nv_bfloat16*)cache, n_heads, n_kv_heads, head_dim, rotary_dim, page_size,
+                              n_slots, write_cache, status);
+        return mx_launch_status();
+    }
     if (dtype == MX_DTYPE_F32)
         mx_launch_chained(rope_kv_write_kernel<float>, dim3(n_tokens), dim3(threads), smem, stream,
                           (float*)qkv, row_stride, positions, inv_freq, slots, (float*)cache, n_heads,
