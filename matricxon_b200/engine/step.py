@@ -17,6 +17,7 @@ two-phase write of the reference's cache (app/runtime/kv_cache.py:53-72).
 
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass, field
 
 import numpy as np
@@ -24,6 +25,7 @@ import torch
 
 from matricxon_b200.cache.manager import CacheManager, OutOfPages
 from matricxon_b200.cache.storage import CacheStorage
+from matricxon_b200.engine.fused_decode import FusedDecode
 from matricxon_b200.ops import kernels
 
 
@@ -147,7 +149,7 @@ class StepRunner:
     def __init__(self, model, cache: CacheManager, storage: CacheStorage,
                  max_step_tokens: int = 8192, max_step_seqs: int = 256,
                  max_model_len: int | None = None, use_graphs: bool = True,
-                 max_graph_batch: int = 64) -> None:
+                 max_graph_batch: int = 64, fused_decode: bool | None = None) -> None:
         self.model = model
         self.cache = cache
         self.storage = storage
@@ -173,6 +175,15 @@ class StepRunner:
         self.last_upload_bytes = 0        # host-to-device bytes of the latest step's metadata
         self.launches_per_step = 0        # this library's kernel launches in the latest step
         model.bind_cache(storage.groups, storage.states)
+        # decode steps of up to 16 rows can run as one persistent kernel when the model fits it.
+        # Off unless asked for (the argument, or MATRICXON_FUSED_DECODE=1): measured on a B200 at
+        # StarCoder2-3B sizes it takes about 1.8 times as long as the captured graph of separate
+        # kernels, because its consumer warps, not HBM, set the pace.
+        if fused_decode is None:
+            fused_decode = os.environ.get("MATRICXON_FUSED_DECODE", "0") == "1"
+        self.fused = None
+        if use_graphs and fused_decode and model.runtime.dtype == torch.bfloat16:
+            self.fused = FusedDecode.try_build(model, cache.page_size)
 
     # ------------------------------------------------------------------ buffers
     def hidden_buffer(self, n_tokens: int, hidden_size: int) -> torch.Tensor:
@@ -345,7 +356,10 @@ class StepRunner:
         return ctx
 
     # ------------------------------------------------------------------ running a step
-    def _forward(self, ctx: StepContext) -> torch.Tensor | None:
+    def _forward(self, ctx: StepContext, decode_rows: bool = False) -> torch.Tensor | None:
+        """``decode_rows``: every row is one new token of its own sequence and wants logits."""
+        if decode_rows and self.fused is not None and self.fused.supports(ctx.n_tokens):
+            return self.fused.forward(ctx)
         hidden = self.model.forward(ctx)
         if ctx.logit_rows.numel() == 0:
             return None
@@ -382,13 +396,13 @@ class StepRunner:
             ctx = self.build(entries, pad_to=bucket, table_widths=widths, buffers=buffers)
             ctx.max_kv_len = self.graph_table_width * self.cache.page_size
             launches_before = kernels.launch_count
-            self._forward(ctx)                                   # warm-up, outside the capture
+            self._forward(ctx, decode_rows=True)                 # warm-up, outside the capture
             self.launches_per_step = kernels.launch_count - launches_before
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
             ctx.capturing = True
             with torch.cuda.graph(graph, pool=self._graph_pool):
-                static_logits = self._forward(ctx)
+                static_logits = self._forward(ctx, decode_rows=True)
             ctx.capturing = False
             if self._graph_pool is None:
                 self._graph_pool = graph.pool()

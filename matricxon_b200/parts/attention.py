@@ -59,6 +59,14 @@ class PagedAttention(Mixer):
         else:
             self.qkv_bias = self.o_bias = None
 
+    def describe(self):
+        spec = self.spec
+        return {"kind": "paged_attention", "qkv_weight": self.qkv_weight, "qkv_bias": self.qkv_bias,
+                "o_weight": self.o_weight, "o_bias": self.o_bias, "num_heads": spec.num_heads,
+                "num_kv_heads": spec.num_kv_heads, "head_dim": spec.head_dim, "window": spec.window,
+                "scale": float(spec.scale),
+                "position": self.position.describe() if self.position is not None else None}
+
     def forward(self, h, residual, ctx, binding):
         spec, rt = self.spec, self.runtime
         if binding.kv is None:

@@ -29,6 +29,9 @@ class RotaryNeox(PositionEncoding):
         super().__init__(spec, runtime, prefix)
         self.inv_freq = inverse_frequencies(spec.rotary_dim, spec.theta).to(runtime.device)
 
+    def describe(self):
+        return {"kind": "rotary_neox", "inv_freq": self.inv_freq, "rotary_dim": int(self.spec.rotary_dim)}
+
     def rotate_and_store(self, qkv, ctx, binding, n_heads, n_kv_heads, head_dim):
         group = ctx.groups[binding.group] if binding.group is not None else None
         writes = binding.writes and binding.kv is not None
