@@ -42,18 +42,50 @@ __device__ __forceinline__ uint4 load_stream(const __nv_bfloat16* p) {
     return v;
 }
 
-template <int MB>
+// Rotation and cache write in the epilogue of the QKV product (ROPE kernels): tile u of a rotated
+// head (a query or key head) holds dims 8j..8j+7 as its rows 0-7 and their partners at
+// + head_dim / 2 as rows 8-15, so the pair of every rotation is in one block; value heads keep 16
+// consecutive dims. Queries go to `out` (the qkv buffer, row stride ldo), rotated keys and the
+// values to their slot of the paged cache: what mx_rope_kv_write does after a plain product
+// (app/architectures/rope.py:152-169, app/architectures/qwen_layers.py:80-86).
+struct SkinnyRope {
+    const int* positions;
+    const float* inv_freq;          // [head_dim / 2]
+    const int* slots;               // may be null: nothing is stored
+    __nv_bfloat16* cache;           // [page][2][kv head][page_size * head_dim], keys [slot][dim], values [dim][slot]
+    int* status;
+    long long n_slots;
+    int n_heads, n_kv_heads, head_dim, page_size;
+};
+
+template <int MB, bool ROPE>
 __global__ void __launch_bounds__(SK_THREADS)
 gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bfloat16* __restrict__ W,
                    int ldw, const float* __restrict__ bias, const float* residual, void* out,
-                   int ldo, int M, int N, int K, int mode) {
-    __shared__ float red[SK_WARPS][16][8 * MB];
+                   int ldo, int M, int N, int K, int mode, const SkinnyRope rope) {
+    constexpr int UNROLL = SK_UNROLL;   // eight weight loads in flight per thread; sixteen measured slower
+    constexpr int ROWS = 16, NR = 2;                   // a block owns 16 output features: rows g and g + 8 per thread
+    __shared__ float red[SK_WARPS][ROWS][8 * MB];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
-    const int n0 = blockIdx.x * 16;
-    const bool row_ok[2] = {n0 + g < N, n0 + g + 8 < N};
-    const __nv_bfloat16* wrow[2] = {W + (size_t)min(n0 + g, N - 1) * ldw + 8 * t,
-                                    W + (size_t)min(n0 + g + 8, N - 1) * ldw + 8 * t};
+    int n_row[2];
+    if (ROPE) {
+        const int per_head = rope.head_dim >> 4;
+        const int head = blockIdx.x / per_head, j = blockIdx.x - head * per_head;
+        const bool rotated = head < rope.n_heads + rope.n_kv_heads;
+        n_row[0] = head * rope.head_dim + (rotated ? 8 * j : 16 * j) + g;
+        n_row[1] = n_row[0] + (rotated ? rope.head_dim / 2 : 8);
+    } else {
+        n_row[0] = blockIdx.x * ROWS + g;
+        n_row[1] = n_row[0] + 8;
+    }
+    bool row_ok[NR];
+    const __nv_bfloat16* wrow[NR];
+#pragma unroll
+    for (int i = 0; i < NR; ++i) {
+        row_ok[i] = n_row[i] < N;
+        wrow[i] = W + (size_t)min(n_row[i], N - 1) * ldw + 8 * t;
+    }
     const __nv_bfloat16* xrow[MB];
     bool tok_ok[MB];
 #pragma unroll
@@ -70,22 +102,24 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bflo
     // the kernel before this one is still finishing, then wait for it before touching activations.
     pdl_trigger();
 #pragma unroll
-    for (int u = 0; u < 2 * SK_UNROLL; ++u) {
+    for (int u = 0; u < 2 * UNROLL; ++u) {
         const int kb = warp + u * SK_WARPS;
         if (kb < n_blocks) {
-            if (row_ok[0]) prefetch_l2(wrow[0] + 32 * kb);
-            if (row_ok[1]) prefetch_l2(wrow[1] + 32 * kb);
+#pragma unroll
+            for (int i = 0; i < NR; ++i)
+                if (row_ok[i]) prefetch_l2(wrow[i] + 32 * kb);
         }
     }
     pdl_wait();
-    for (int kb0 = warp; kb0 < n_blocks; kb0 += SK_WARPS * SK_UNROLL) {
-        uint4 wf[SK_UNROLL][2], xf[SK_UNROLL][MB];
+    for (int kb0 = warp; kb0 < n_blocks; kb0 += SK_WARPS * UNROLL) {
+        uint4 wf[UNROLL][2], xf[UNROLL][MB];
 #pragma unroll
-        for (int u = 0; u < SK_UNROLL; ++u) {
+        for (int u = 0; u < UNROLL; ++u) {
             const int kb = kb0 + u * SK_WARPS;
             const bool in = kb < n_blocks;
+            wf[u][1] = make_uint4(0, 0, 0, 0);
 #pragma unroll
-            for (int i = 0; i < 2; ++i)
+            for (int i = 0; i < NR; ++i)
                 wf[u][i] = (in && row_ok[i]) ? load_stream(wrow[i] + 32 * kb) : make_uint4(0, 0, 0, 0);
 #pragma unroll
             for (int mb = 0; mb < MB; ++mb)
@@ -93,29 +127,84 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bflo
                                                : make_uint4(0, 0, 0, 0);
         }
 #pragma unroll
-        for (int u = 0; u < SK_UNROLL; ++u)
+        for (int u = 0; u < UNROLL; ++u)
 #pragma unroll
             for (int mb = 0; mb < MB; ++mb) {
                 mma_bf16_16816(acc[mb], wf[u][0].x, wf[u][1].x, wf[u][0].y, wf[u][1].y, xf[u][mb].x, xf[u][mb].y);
                 mma_bf16_16816(acc[mb], wf[u][0].z, wf[u][1].z, wf[u][0].w, wf[u][1].w, xf[u][mb].z, xf[u][mb].w);
             }
     }
-    // this thread holds features g, g + 8 for tokens 8 mb + 2t, + 1
+    // this thread holds features g (and g + 8) for tokens 8 mb + 2t, + 1
 #pragma unroll
     for (int mb = 0; mb < MB; ++mb) {
         red[warp][g][8 * mb + 2 * t] = acc[mb][0];
         red[warp][g][8 * mb + 2 * t + 1] = acc[mb][1];
-        red[warp][g + 8][8 * mb + 2 * t] = acc[mb][2];
-        red[warp][g + 8][8 * mb + 2 * t + 1] = acc[mb][3];
+        if (ROWS == 16) {
+            red[warp][(g + 8) % ROWS][8 * mb + 2 * t] = acc[mb][2];
+            red[warp][(g + 8) % ROWS][8 * mb + 2 * t + 1] = acc[mb][3];
+        }
     }
     __syncthreads();
-    for (int idx = tid; idx < 16 * 8 * MB; idx += SK_THREADS) {
-        const int f = idx & 15, m = idx >> 4;
-        const int n = n0 + f;
-        if (n >= N || m >= M) continue;
+    auto total = [&](int f, int m) {
         float v = 0.f;
 #pragma unroll
         for (int w = 0; w < SK_WARPS; ++w) v += red[w][f][m];
+        return v;
+    };
+    if constexpr (ROPE) {
+        const int HD = rope.head_dim;
+        const int per_head = HD >> 4;
+        const int head = blockIdx.x / per_head, j = blockIdx.x - head * per_head;
+        const bool rotated = head < rope.n_heads + rope.n_kv_heads;
+        const int m = rotated ? tid >> 3 : tid >> 4;
+        if (tid >= (rotated ? 8 : 16) * 8 * MB || m >= M) return;
+        long long page = 0;
+        int offset = 0;
+        if (head >= rope.n_heads) {          // a key or value head: the slot of this row's token
+            if (rope.slots == nullptr) return;
+            const long long slot = rope.slots[m];
+            if (slot == -1) return;          // a padding row of a fixed-size batch
+            if (slot < 0 || slot >= rope.n_slots) {
+                atomicOr(rope.status, MX_STATUS_BAD_SLOT);
+                return;
+            }
+            page = slot / rope.page_size;
+            offset = (int)(slot - page * rope.page_size);
+        }
+        const size_t head_stride = (size_t)rope.page_size * HD;
+        if (rotated) {
+            const int i = tid & 7;
+            const int d_lo = 8 * j + i, d_hi = d_lo + HD / 2;
+            float lo = total(i, m), hi = total(i + 8, m);
+            if (bias) {
+                lo += bias[head * HD + d_lo];
+                hi += bias[head * HD + d_hi];
+            }
+            // a plain product would round to bfloat16 before the rotation reads it: the same here
+            lo = __bfloat162float(__float2bfloat16_rn(lo));
+            hi = __bfloat162float(__float2bfloat16_rn(hi));
+            const float angle = (float)rope.positions[m] * rope.inv_freq[d_lo];
+            const float c = cosf(angle), sn = sinf(angle);
+            __nv_bfloat16* dst = head < rope.n_heads
+                                     ? reinterpret_cast<__nv_bfloat16*>(out) + (size_t)m * ldo + (size_t)head * HD
+                                     : rope.cache + ((size_t)page * 2 * rope.n_kv_heads + (head - rope.n_heads)) * head_stride +
+                                           (size_t)offset * HD;
+            dst[d_lo] = __float2bfloat16_rn(lo * c - hi * sn);
+            dst[d_hi] = __float2bfloat16_rn(hi * c + lo * sn);
+        } else {
+            const int r = tid & 15;
+            const int dim = 16 * j + r;
+            float v = total(r, m);
+            if (bias) v += bias[head * HD + dim];
+            rope.cache[((size_t)page * 2 * rope.n_kv_heads + rope.n_kv_heads + (head - rope.n_heads - rope.n_kv_heads)) *
+                           head_stride + (size_t)dim * rope.page_size + offset] = __float2bfloat16_rn(v);
+        }
+    } else {
+    for (int idx = tid; idx < ROWS * 8 * MB; idx += SK_THREADS) {
+        const int f = idx % ROWS, m = idx / ROWS;
+        const int n = blockIdx.x * ROWS + f;
+        if (n >= N || m >= M) continue;
+        float v = total(f, m);
         if (bias) v += bias[n];
         if (mode == 1) v = gelu_tanh_fast(v);
         const size_t o = (size_t)m * ldo + n;
@@ -126,6 +215,14 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bflo
             reinterpret_cast<__nv_bfloat16*>(out)[o] = __float2bfloat16_rn(v);
         }
     }
+    }
+}
+
+int check_skinny(int M, int K, int ldx, int ldw) {
+    if (M > 16) MX_REFUSE("skinny gemm: %d rows, this kernel takes at most 16", M);
+    if (K <= 0 || K % 32 != 0) MX_REFUSE("skinny gemm: K = %d is not a positive multiple of 32", K);
+    if (ldx % 8 != 0 || ldw % 8 != 0) MX_REFUSE("skinny gemm: row strides %d, %d are not multiples of 8", ldx, ldw);
+    return MX_OK;
 }
 
 }  // namespace
@@ -134,21 +231,42 @@ extern "C" int mx_gemm_skinny(const void* x, const void* W, const float* bias, c
                               void* out, int out_dtype, int M, int N, int K, int ldx, int ldw, int ldo,
                               int mode, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return MX_OK;
-    if (M > 16) MX_REFUSE("skinny gemm: %d rows, this kernel takes at most 16", M);
-    if (K <= 0 || K % 32 != 0) MX_REFUSE("skinny gemm: K = %d is not a positive multiple of 32", K);
-    if (ldx % 8 != 0 || ldw % 8 != 0) MX_REFUSE("skinny gemm: row strides %d, %d are not multiples of 8", ldx, ldw);
+    const int rc = check_skinny(M, K, ldx, ldw);
+    if (rc != MX_OK) return rc;
     if (mode < 0 || mode > 3) MX_REFUSE("skinny gemm: unknown epilogue mode %d", mode);
     if (mode == 2 && residual == nullptr) MX_REFUSE("skinny gemm: residual mode without a residual");
     if ((mode >= 2) != (out_dtype == MX_DTYPE_F32))
         MX_REFUSE("skinny gemm: epilogue mode %d does not write dtype %d", mode, out_dtype);
+    const SkinnyRope none = {};
     const int grid = (N + 15) / 16;
-    if (M <= 8)
-        mx_launch_chained(gemm_skinny_kernel<1>, dim3(grid), dim3(SK_THREADS), 0, stream,
-                          (const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)W, ldw, bias, residual, out, ldo,
-                          M, N, K, mode);
-    else
-        mx_launch_chained(gemm_skinny_kernel<2>, dim3(grid), dim3(SK_THREADS), 0, stream,
-                          (const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)W, ldw, bias, residual, out, ldo,
-                          M, N, K, mode);
+    auto kernel = M <= 8 ? gemm_skinny_kernel<1, false> : gemm_skinny_kernel<2, false>;
+    mx_launch_chained(kernel, dim3(grid), dim3(SK_THREADS), 0, stream, (const __nv_bfloat16*)x, ldx,
+                      (const __nv_bfloat16*)W, ldw, bias, residual, out, ldo, M, N, K, mode, none);
+    return mx_launch_status();
+}
+
+// The QKV product with the rotation and the cache write in its epilogue. W is
+// [(heads + 2 kv heads) * head_dim][K]; rotated queries go to `qkv` (bfloat16, row stride ldo; its
+// key and value columns are left untouched), keys and values to the cache slots `slots[m]`
+// (null: not stored). The rotation spans the whole head (rotary_dim == head_dim).
+extern "C" int mx_gemm_skinny_rope(const void* x, const void* W, const float* bias, void* qkv, int M, int K,
+                                   int ldx, int ldw, int ldo, const int* positions, const float* inv_freq,
+                                   const int* slots, void* cache, long long n_pages, int n_heads,
+                                   int n_kv_heads, int head_dim, int page_size, int* status,
+                                   cudaStream_t stream) {
+    if (M <= 0) return MX_OK;
+    const int rc = check_skinny(M, K, ldx, ldw);
+    if (rc != MX_OK) return rc;
+    if (head_dim <= 0 || head_dim % 16 != 0) MX_REFUSE("skinny gemm with rotation: head_dim %d is no multiple of 16", head_dim);
+    if (n_heads <= 0 || n_kv_heads <= 0) MX_REFUSE("skinny gemm with rotation: %d heads, %d kv heads", n_heads, n_kv_heads);
+    if (slots != nullptr && cache == nullptr) MX_REFUSE("skinny gemm with rotation: slots without a cache");
+    SkinnyRope rope;
+    rope.positions = positions; rope.inv_freq = inv_freq; rope.slots = slots;
+    rope.cache = (__nv_bfloat16*)cache; rope.status = status; rope.n_slots = n_pages * page_size;
+    rope.n_heads = n_heads; rope.n_kv_heads = n_kv_heads; rope.head_dim = head_dim; rope.page_size = page_size;
+    const int N = (n_heads + 2 * n_kv_heads) * head_dim;
+    auto kernel = M <= 8 ? gemm_skinny_kernel<1, true> : gemm_skinny_kernel<2, true>;
+    mx_launch_chained(kernel, dim3(N / 16), dim3(SK_THREADS), 0, stream, (const __nv_bfloat16*)x, ldx,
+                      (const __nv_bfloat16*)W, ldw, bias, (const float*)nullptr, qkv, ldo, M, N, K, 0, rope);
     return mx_launch_status();
 }

@@ -226,6 +226,40 @@ def gemm_skinny(a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None,
     _launched()
 
 
+def gemm_skinny_rope(a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, qkv: torch.Tensor,
+                     positions: torch.Tensor, inv_freq: torch.Tensor, slots: torch.Tensor | None,
+                     cache: torch.Tensor | None, n_heads: int, n_kv_heads: int, head_dim: int,
+                     page_size: int, status: torch.Tensor) -> None:
+    """The decode QKV product with the rotation and the cache write in its epilogue: rotated
+    queries go to the query columns of ``qkv``, rotated keys and the values to ``slots`` of
+    ``cache`` (both None: nothing stored). The rotation spans the whole head."""
+    _need(a, "a", torch.bfloat16, contiguous=False)
+    _need(w, "w", torch.bfloat16)
+    _need(qkv, "qkv", torch.bfloat16)
+    _need(positions, "positions", torch.int32)
+    _need(inv_freq, "inv_freq", torch.float32)
+    _need(status, "status", torch.int32)
+    m, k = a.shape
+    n = (n_heads + 2 * n_kv_heads) * head_dim
+    assert tuple(w.shape) == (n, k) and tuple(qkv.shape) == (m, n), (a.shape, w.shape, qkv.shape)
+    assert inv_freq.numel() == head_dim // 2 and positions.numel() >= m
+    if bias is not None:
+        _need(bias, "bias", torch.float32)
+        assert bias.numel() == n
+    n_pages = 0
+    if cache is not None:
+        _need(cache, "cache", torch.bfloat16)
+        _need(slots, "slots", torch.int32)
+        assert tuple(cache.shape[1:]) == (2, n_kv_heads, page_size, head_dim), cache.shape
+        n_pages = cache.shape[0]
+    check(library().mx_gemm_skinny_rope(_ptr(a), _ptr(w), _ptr(bias), _ptr(qkv), m, k, a.stride(0),
+                                        w.stride(0), qkv.stride(0), _ptr(positions), _ptr(inv_freq),
+                                        _ptr(slots) if cache is not None else None, _ptr(cache), n_pages,
+                                        n_heads, n_kv_heads, head_dim, page_size, _ptr(status), _stream()),
+          "gemm_skinny_rope")
+    _launched()
+
+
 def attention_scratch_bytes(n_tokens: int, n_heads: int, head_dim: int, n_splits: int) -> int:
     return int(library().mx_attention_scratch_bytes(n_tokens, n_heads, head_dim, n_splits))
 

@@ -48,6 +48,7 @@ def main() -> None:
         'layernorm': lambda: k.layernorm(x, g, b, 1e-5, h),
         'qkv skinny': lambda: k.gemm_skinny(h, wqkv, bq, None, qkv, 0),
         'rope_kv_write': lambda: k.rope_kv_write(qkv, positions, inv_freq, slots, cache, NH, NKV, HD, HD, ps, status),
+        'qkv skinny + rotation + cache write (one kernel; not in the total)': lambda: k.gemm_skinny_rope(h, wqkv, bq, qkv, positions, inv_freq, slots, cache, NH, NKV, HD, ps, status),
         f'attention narrow (+merge) splits={n_splits}': lambda: k.paged_attention_mma(qkv, QKV, cache, tables, cu_q, ctx_lens, tiles, M, True, M, NH, NKV, HD, 4096, HD ** -0.5, attn, status, n_splits=n_splits, scratch=scratch),
         'o skinny residual': lambda: k.gemm_skinny(attn, wo, bo, x, x, 2),
         'c_fc skinny gelu': lambda: k.gemm_skinny(h, wfc, bfc, None, mid, 1),
@@ -72,7 +73,8 @@ def main() -> None:
         for _ in range(5): graph.replay()
         e1.record(); torch.cuda.synchronize()
         us = e0.elapsed_time(e1) * 1000 / (5 * REP)
-        total += us * (2 if name == 'layernorm' else 1)
+        if 'not in the total' not in name:
+            total += us * (2 if name == 'layernorm' else 1)
         print(f"{name:45s} {us:8.2f} us")
     print(f"layer total (2 LN) {total:.1f} us  -> x30 = {total*30/1000:.2f} ms")
 

@@ -71,11 +71,18 @@ class PagedAttention(Mixer):
         spec, rt = self.spec, self.runtime
         if binding.kv is None:
             raise RuntimeError("attention needs cache pages bound to it")
-        qkv = linear(h, self.qkv_weight, self.qkv_bias, EPILOGUE_NONE, backend=rt.gemm_backend)
+        qkv = None
         if self.position is not None:
+            qkv = self.position.project_rotate_store(h, self.qkv_weight, self.qkv_bias, ctx, binding,
+                                                     spec.num_heads, spec.num_kv_heads, spec.head_dim)
+        if qkv is not None:
+            pass                                        # product, rotation and cache write were one kernel
+        elif self.position is not None:
+            qkv = linear(h, self.qkv_weight, self.qkv_bias, EPILOGUE_NONE, backend=rt.gemm_backend)
             self.position.rotate_and_store(qkv, ctx, binding, spec.num_heads, spec.num_kv_heads,
                                            spec.head_dim)
         else:
+            qkv = linear(h, self.qkv_weight, self.qkv_bias, EPILOGUE_NONE, backend=rt.gemm_backend)
             store_without_rotation(qkv, ctx, binding, spec.num_heads, spec.num_kv_heads,
                                    spec.head_dim, rt.page_size)
         group = ctx.groups[binding.group]

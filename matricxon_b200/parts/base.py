@@ -137,6 +137,13 @@ class PositionEncoding(Part):
     def rotate_and_store(self, qkv, ctx, binding, n_heads, n_kv_heads, head_dim):
         raise NotImplementedError
 
+    def project_rotate_store(self, h, weight, bias, ctx, binding, n_heads, n_kv_heads, head_dim):
+        """Optional shortcut: the QKV product of ``h`` with ``weight`` / ``bias``, rotated and
+        stored in one go. Returns the qkv tensor (its query columns rotated; keys and values
+        are in the cache and need not be in it), or None when the encoding has no such kernel
+        for this step; the mixer then runs the product and ``rotate_and_store``."""
+        return None
+
 
 class Mixer(Part):
     @classmethod

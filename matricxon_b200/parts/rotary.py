@@ -32,6 +32,19 @@ class RotaryNeox(PositionEncoding):
     def describe(self):
         return {"kind": "rotary_neox", "inv_freq": self.inv_freq, "rotary_dim": int(self.spec.rotary_dim)}
 
+    def project_rotate_store(self, h, weight, bias, ctx, binding, n_heads, n_kv_heads, head_dim):
+        rt = self.runtime
+        if (rt.dtype != torch.bfloat16 or rt.gemm_backend != "auto" or self.spec.rotary_dim != head_dim
+                or head_dim % 16 != 0 or not kernels.skinny_gemm_supported(h, weight)):
+            return None
+        writes = binding.writes and binding.kv is not None
+        qkv = torch.empty((h.shape[0], weight.shape[0]), dtype=rt.dtype, device=h.device)
+        kernels.gemm_skinny_rope(h, weight, bias, qkv, ctx.positions, self.inv_freq,
+                                 ctx.groups[binding.group].slots if writes else None,
+                                 binding.kv if writes else None, n_heads, n_kv_heads, head_dim,
+                                 rt.page_size, ctx.status)
+        return qkv
+
     def rotate_and_store(self, qkv, ctx, binding, n_heads, n_kv_heads, head_dim):
         group = ctx.groups[binding.group] if binding.group is not None else None
         writes = binding.writes and binding.kv is not None

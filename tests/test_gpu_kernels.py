@@ -203,6 +203,50 @@ def test_rope_kv_write(dtype, heads, kv_heads, dim, rot):
         assert torch.isnan(flat[~written]).all() and not torch.isnan(flat[written]).any()
 
 
+@pytest.mark.parametrize("m", [1, 5, 8, 13, 16])
+@pytest.mark.parametrize("heads,kv_heads,dim,k_dim,with_bias", [(6, 2, 64, 192, True), (3, 1, 16, 96, False),
+                                                               (4, 4, 128, 256, True), (5, 1, 48, 160, True)])
+def test_skinny_gemm_with_rotation_equals_product_then_rope(m, heads, kv_heads, dim, k_dim, with_bias):
+    """The QKV product with rotation and cache write in its epilogue against the plain product
+    followed by the rotary kernel (each checked against float64 above): same queries, same cache."""
+    k = kernels()
+    torch.manual_seed(m * 131 + dim)
+    n = (heads + 2 * kv_heads) * dim
+    page_size, pages = 4, 9
+    a = torch.randn(m, k_dim, device=DEV).bfloat16()
+    w = (torch.randn(n, k_dim, device=DEV) / math.sqrt(k_dim)).bfloat16()
+    bias = torch.randn(n, device=DEV) if with_bias else None
+    positions = torch.tensor([0, 1, 2, 3, 500, 4095, 16000, 7, 8, 9, 33, 34, 35, 36, 37, 38][:m], dtype=torch.int32, device=DEV)
+    slot_list = [5, 6, 7, 0, 27, 13, 12, 1, 2, -1, 20, 21, 22, 23, 30, 31][:m]
+    slots = torch.tensor(slot_list, dtype=torch.int32, device=DEV)
+    inv_freq = (1.0 / (100000.0 ** (torch.arange(0, dim, 2, dtype=torch.float32) / dim))).to(DEV)
+    st = status()
+    # the two kernels one after the other
+    qkv_ref = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
+    k.gemm_skinny(a, w, bias, None, qkv_ref, k.EPILOGUE_NONE)
+    cache_ref = torch.full((pages, 2, kv_heads, page_size, dim), float("nan"), dtype=torch.bfloat16, device=DEV)
+    k.rope_kv_write(qkv_ref, positions, inv_freq, slots, cache_ref, heads, kv_heads, dim, dim, page_size, st)
+    # the one kernel
+    qkv = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=DEV)
+    cache = torch.full((pages, 2, kv_heads, page_size, dim), float("nan"), dtype=torch.bfloat16, device=DEV)
+    k.gemm_skinny_rope(a, w, bias, qkv, positions, inv_freq, slots, cache, heads, kv_heads, dim, page_size, st)
+    assert st.item() == 0
+    q_cols = heads * dim
+    assert torch.equal(qkv[:, :q_cols], qkv_ref[:, :q_cols])
+    assert torch.isnan(qkv[:, q_cols:]).all()                        # key and value columns are not written
+    assert torch.equal(torch.isnan(cache), torch.isnan(cache_ref))   # the same slots, nothing else
+    assert torch.equal(torch.nan_to_num(cache), torch.nan_to_num(cache_ref))
+    # without a cache only the queries are produced
+    qkv2 = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=DEV)
+    k.gemm_skinny_rope(a, w, bias, qkv2, positions, inv_freq, None, None, heads, kv_heads, dim, page_size, st)
+    assert torch.equal(qkv2[:, :q_cols], qkv_ref[:, :q_cols])
+    # a slot outside the pool is reported, not written
+    bad = slots.clone()
+    bad[0] = pages * page_size
+    k.gemm_skinny_rope(a, w, bias, qkv2, positions, inv_freq, bad, cache, heads, kv_heads, dim, page_size, st)
+    assert st.item() == 2
+
+
 def test_rope_bad_slot_sets_status_and_padding_slot_is_silent():
     k = kernels()
     qkv = torch.randn(3, 4 * 16, device=DEV)
