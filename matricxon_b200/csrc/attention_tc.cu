@@ -1,0 +1,551 @@
+// Paged attention for prompt portions on the fifth-generation tensor cores (tcgen05), bfloat16,
+// head_dim 128, pages of 16 or 32 slots.
+//
+// Same mathematics and visibility rule as attention.cu / attention_mma.cu (query at p sees key j
+// iff j <= p and (window == 0 or j > p - window); scores q.k * scale; float softmax; query head h
+// reads KV head h / group), cf. app/native/src/mx_attention.c:16-68 and
+// app/architectures/qwen_layers.py:12-17,94-100.
+//
+// A block owns, for one sequence and one KV head, T = 128 / group consecutive query tokens: the
+// 128 rows of an MMA tile are the pairs (token, head in group), token-major, so all rows share
+// every key. It walks the keys in chunks of 128 positions:
+//   warp 4 (one lane)  producer: the query tile once (one 4-D TMA box per half of the head dim),
+//                      then per chunk the keys and values of its pages (TMA boxes straight out of
+//                      the paged cache, page numbers from the block table) into two stages;
+//   warp 5 (one lane)  issues S = Q K^T (tcgen05.mma, operands in swizzled shared memory,
+//                      accumulator in tensor memory, two S buffers) and O += P V (P from shared
+//                      memory, V^T pages as the K-major B operand, O in tensor memory);
+//   warps 0-3          softmax: thread r owns row r. It reads its 128 scores from tensor memory
+//                      (tcgen05.ld), masks the chunks that cross an edge, keeps a running
+//                      reference maximum that only moves when the new maximum exceeds it by 2^8
+//                      (then O is rescaled in tensor memory), writes P as bfloat16 into the
+//                      swizzled tile the next MMA reads, and at the end normalises O and stores it.
+// Keys beyond the newest one of the tile are not data yet: their scores are masked by selection and
+// their value columns are zeroed in shared memory before the last P V (0 x NaN must not happen).
+// Every mbarrier wait is bounded: a wait that runs out sets MX_STATUS_WAIT_TIMEOUT and the role
+// leaves its loop, so the block always reaches the point where tensor memory is freed.
+#include <cuda.h>
+#include <math.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int AT_ROWS = 128;
+constexpr int AT_KEYS = 128;
+constexpr int AT_HD = 128;
+constexpr int AT_STAGES = 2;
+constexpr int AT_THREADS = 192;
+constexpr unsigned AT_SPIN = 1u << 22;
+constexpr int AT_TILE = AT_ROWS * 64 * 2;            // bytes of a [128][64] bfloat16 half tile
+constexpr float AT_JUMP = 8.f;                        // log2 of the growth the reference maximum tolerates
+
+struct AtShared {
+    unsigned long long q_full;
+    unsigned long long k_full[AT_STAGES], v_full[AT_STAGES], kv_empty[AT_STAGES];
+    unsigned long long s_full[2], s_empty[2];
+    unsigned long long p_full, pv_done;
+    unsigned tmem_base;
+};
+
+struct AtParams {
+    const int* block_tables;     // [seqs][bt_stride]
+    const int* cu_q;             // [seqs + 1]
+    const int* context_lens;     // [seqs]
+    const int* tiles;            // [n_tiles][2]: (sequence, first token of the tile within the sequence)
+    __nv_bfloat16* out;          // [tokens][out_stride]
+    int* status;
+    long long n_pages;
+    int out_stride, bt_stride, n_heads, n_kv_heads, group, tokens_per_tile, page_size, page_shift, window;
+    float scale_log2;
+};
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void at_mbar_init(unsigned long long* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void at_expect_tx(unsigned long long* bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void at_arrive(unsigned long long* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool at_try_wait(unsigned long long* bar, unsigned parity) {
+    unsigned ok;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// false: the wait ran out (status set); the caller leaves its loop
+__device__ __forceinline__ bool at_wait(unsigned long long* bar, unsigned parity, int* status) {
+    for (unsigned spin = 0; spin < AT_SPIN; ++spin)
+        if (at_try_wait(bar, parity)) return true;
+    atomicOr(status, MX_STATUS_WAIT_TIMEOUT);
+    return false;
+}
+__device__ __forceinline__ void tma_3d(void* dst, const CUtensorMap* map, int x, int y, int z, unsigned long long* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];\n" ::"r"(
+            smem_u32(dst)),
+        "l"(map), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar))
+        : "memory");
+}
+__device__ __forceinline__ void tma_4d(void* dst, const CUtensorMap* map, int x, int y, int z, int w,
+                                       unsigned long long* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];\n" ::"r"(
+            smem_u32(dst)),
+        "l"(map), "r"(x), "r"(y), "r"(z), "r"(w), "r"(smem_u32(bar))
+        : "memory");
+}
+// Shared-memory operand descriptor, K-major: rows of `swizzle bytes`, groups of 8 rows `sbo` bytes apart.
+__device__ __forceinline__ unsigned long long at_desc(const void* tile, unsigned sbo, unsigned layout) {
+    unsigned long long desc = 0;
+    desc |= (unsigned long long)((smem_u32(tile) & 0x3FFFF) >> 4);
+    desc |= (unsigned long long)1 << 16;
+    desc |= (unsigned long long)(sbo >> 4) << 32;
+    desc |= (unsigned long long)1 << 46;                 // descriptor version of sm_100
+    desc |= (unsigned long long)layout << 61;            // 2: 128-byte swizzle, 4: 64-byte, 6: 32-byte
+    return desc;
+}
+__device__ __forceinline__ unsigned at_idesc(int m, int n) {
+    unsigned d = 0;
+    d |= 1u << 4;                      // accumulator format: f32
+    d |= 1u << 7;                      // A format: bf16
+    d |= 1u << 10;                     // B format: bf16
+    d |= (unsigned)(n >> 3) << 17;
+    d |= (unsigned)(m >> 4) << 24;
+    return d;
+}
+__device__ __forceinline__ void at_mma(unsigned tmem_acc, unsigned long long adesc, unsigned long long bdesc,
+                                       unsigned idesc, bool accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_acc),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"((unsigned)accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void at_commit(unsigned long long* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_load32(unsigned taddr, float* v) {
+    unsigned r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_store32(unsigned taddr, const float* v) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};\n" ::"r"(taddr),
+        "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
+        "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
+        "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+        "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])),
+        "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
+        "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
+        "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])),
+        "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+        : "memory");
+}
+__device__ __forceinline__ float at_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ unsigned at_pack(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<unsigned*>(&v);
+}
+
+__global__ void __launch_bounds__(AT_THREADS, 1)
+attention_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
+                    const __grid_constant__ CUtensorMap v_map, const AtParams p) {
+    extern __shared__ __align__(1024) unsigned char at_smem_raw[];
+    __shared__ AtShared sh;
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(at_smem_raw) + 1023) &
+                                                           ~(uintptr_t)1023);
+    unsigned char* q_tile = smem;                                   // 2 halves of [128][64]
+    unsigned char* k_stage = q_tile + 2 * AT_TILE;                  // per stage: 2 halves of [128 keys][64]
+    unsigned char* v_stage = k_stage + AT_STAGES * 2 * AT_TILE;     // per stage: pages of [128 dims][page_size]
+    unsigned char* p_tile = v_stage + AT_STAGES * 2 * AT_TILE;      // 2 halves of [128][64 keys]
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int seq = p.tiles[2 * blockIdx.x], tok0 = p.tiles[2 * blockIdx.x + 1];
+    const int kh = blockIdx.y;
+    const int q_start = p.cu_q[seq];
+    const int q_len = p.cu_q[seq + 1] - q_start;
+    const int ctx = p.context_lens[seq];
+    const int n_tok = min(p.tokens_per_tile, q_len - tok0);
+    if (n_tok <= 0) return;                                         // nothing was allocated yet
+    const int hi_tile = ctx + tok0 + n_tok - 1;
+    const int lo_tile = p.window > 0 ? max(0, ctx + tok0 - p.window + 1) : 0;
+    const int c_begin = lo_tile / AT_KEYS;
+    const int n_chunks = hi_tile / AT_KEYS + 1 - c_begin;
+    const int pages_per_chunk = AT_KEYS >> p.page_shift;
+    const unsigned page_bytes = (unsigned)(p.page_size * AT_HD * 2);
+
+    if (tid == 0) {
+        at_mbar_init(&sh.q_full, 1);
+        for (int s = 0; s < AT_STAGES; ++s) {
+            at_mbar_init(&sh.k_full[s], 1);
+            at_mbar_init(&sh.v_full[s], 1);
+            at_mbar_init(&sh.kv_empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            at_mbar_init(&sh.s_full[b], 1);
+            at_mbar_init(&sh.s_empty[b], 4);
+        }
+        at_mbar_init(&sh.p_full, 4);
+        at_mbar_init(&sh.pv_done, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    // value stages start as zeros: a page that is never fetched must not hold NaN bit patterns
+    for (int i = tid; i < AT_STAGES * 2 * AT_TILE / 16; i += AT_THREADS)
+        reinterpret_cast<uint4*>(v_stage)[i] = make_uint4(0u, 0u, 0u, 0u);
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    if (warp == 5) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&sh.tmem_base)),
+                     "r"(512)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    const unsigned tmem_base = sh.tmem_base;
+    const unsigned tmem_o = tmem_base + 256;
+
+    if (warp == 4) {
+        // ---------------- producer
+        if (lane == 0) {
+            const unsigned q_bytes = (unsigned)(2 * 64 * p.group * p.tokens_per_tile * 2);   // boxes count in full
+            at_expect_tx(&sh.q_full, q_bytes);
+            tma_4d(q_tile, &q_map, 0, 0, kh, q_start + tok0, &sh.q_full);
+            tma_4d(q_tile + AT_TILE, &q_map, 64, 0, kh, q_start + tok0, &sh.q_full);
+            const int* bt = p.block_tables + (size_t)seq * p.bt_stride;
+            for (int j = 0; j < n_chunks; ++j) {
+                const int s = j % AT_STAGES;
+                if (!at_wait(&sh.kv_empty[s], ((unsigned)(j / AT_STAGES) & 1) ^ 1, p.status)) break;
+                const int c0 = (c_begin + j) * AT_KEYS;
+                long long page_of[16];
+                int n_valid = 0;
+#pragma unroll
+                for (int pg = 0; pg < 16; ++pg) {
+                    page_of[pg] = -1;
+                    if (pg < pages_per_chunk) {
+                        const int key0 = c0 + pg * p.page_size;
+                        if (key0 <= hi_tile && key0 + p.page_size - 1 >= lo_tile) {
+                            const int lp = key0 >> p.page_shift;
+                            const long long page = lp < p.bt_stride ? bt[lp] : -1;
+                            if (page >= 0 && page < p.n_pages) {
+                                page_of[pg] = page;
+                                ++n_valid;
+                            } else {
+                                atomicOr(p.status, MX_STATUS_BAD_PAGE);
+                            }
+                        }
+                    }
+                }
+                at_expect_tx(&sh.k_full[s], (unsigned)n_valid * page_bytes);
+                at_expect_tx(&sh.v_full[s], (unsigned)n_valid * page_bytes);
+                unsigned char* ks = k_stage + (size_t)s * 2 * AT_TILE;
+                unsigned char* vs = v_stage + (size_t)s * 2 * AT_TILE;
+#pragma unroll
+                for (int pg = 0; pg < 16; ++pg)
+                    if (pg < pages_per_chunk && page_of[pg] >= 0) {
+                        const int block = (int)(page_of[pg] * 2 * p.n_kv_heads) + kh;
+                        tma_3d(ks + (size_t)pg * p.page_size * 128, &k_map, 0, 0, block, &sh.k_full[s]);
+                        tma_3d(ks + AT_TILE + (size_t)pg * p.page_size * 128, &k_map, 64, 0, block, &sh.k_full[s]);
+                    }
+#pragma unroll
+                for (int pg = 0; pg < 16; ++pg)
+                    if (pg < pages_per_chunk && page_of[pg] >= 0)
+                        tma_3d(vs + (size_t)pg * page_bytes, &v_map, 0, 0,
+                               (int)(page_of[pg] * 2 * p.n_kv_heads) + p.n_kv_heads + kh, &sh.v_full[s]);
+            }
+        }
+    } else if (warp == 5) {
+        // ---------------- MMA issuer
+        if (lane == 0) {
+            const unsigned idesc = at_idesc(AT_ROWS, AT_KEYS);
+            const unsigned v_layout = p.page_size == 16 ? 6u : 4u;       // 32- or 64-byte swizzle
+            const unsigned v_sbo = (unsigned)(8 * p.page_size * 2);       // eight rows of one page tile
+            const int steps_per_page = p.page_size / 16;
+            bool alive = at_wait(&sh.q_full, 0, p.status);
+            auto issue_qk = [&](int j) -> bool {
+                const int s = j % AT_STAGES, b = j & 1;
+                if (!at_wait(&sh.k_full[s], (unsigned)(j / AT_STAGES) & 1, p.status)) return false;
+                if (!at_wait(&sh.s_empty[b], ((unsigned)(j >> 1) & 1) ^ 1, p.status)) return false;
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                const unsigned char* ks = k_stage + (size_t)s * 2 * AT_TILE;
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    const unsigned long long adesc = at_desc(q_tile + half * AT_TILE, 1024, 2);
+                    const unsigned long long bdesc = at_desc(ks + half * AT_TILE, 1024, 2);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        at_mma(tmem_base + (unsigned)b * 128, adesc + 2 * k, bdesc + 2 * k, idesc, (half | k) != 0);
+                }
+                at_commit(&sh.s_full[b]);
+                return true;
+            };
+            if (alive) alive = issue_qk(0);
+            for (int j = 0; j < n_chunks && alive; ++j) {
+                if (j + 1 < n_chunks) {
+                    alive = issue_qk(j + 1);
+                    if (!alive) break;
+                }
+                const int s = j % AT_STAGES;
+                if (!at_wait(&sh.p_full, (unsigned)j & 1, p.status)) break;
+                if (!at_wait(&sh.v_full[s], (unsigned)(j / AT_STAGES) & 1, p.status)) break;
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                const unsigned char* vs = v_stage + (size_t)s * 2 * AT_TILE;
+#pragma unroll
+                for (int kk = 0; kk < AT_KEYS / 16; ++kk) {          // 16 keys per MMA
+                    const unsigned long long adesc = at_desc(p_tile + (kk >> 2) * AT_TILE, 1024, 2) + 2 * (kk & 3);
+                    const int pg = kk / steps_per_page, within = kk - pg * steps_per_page;
+                    const unsigned long long bdesc = at_desc(vs + (size_t)pg * page_bytes, v_sbo, v_layout) + 2 * within;
+                    at_mma(tmem_o, adesc, bdesc, idesc, (j | kk) != 0);
+                }
+                at_commit(&sh.kv_empty[s]);
+                at_commit(&sh.pv_done);
+            }
+        }
+    } else {
+        // ---------------- softmax and epilogue: thread `row` owns tile row `row`
+        const int row = tid;
+        const int t_in = row / p.group, h_in = row - t_in * p.group;
+        const bool valid = row < p.tokens_per_tile * p.group && t_in < n_tok;
+        const int pos = valid ? ctx + tok0 + t_in : -1;                 // -1: every key is masked
+        const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+        const unsigned lane_base = (unsigned)(32 * warp) << 16;
+        float m_ref = -INFINITY, l_run = 0.f;
+        bool alive = true;
+        for (int j = 0; j < n_chunks && alive; ++j) {
+            const int b = j & 1, s = j % AT_STAGES;
+            alive = at_wait(&sh.s_full[b], (unsigned)(j >> 1) & 1, p.status);
+            if (!alive) break;
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            float sc[AT_KEYS];
+#pragma unroll
+            for (int piece = 0; piece < 4; ++piece)
+                tmem_load32(tmem_base + (unsigned)b * 128 + lane_base + 32 * piece, sc + 32 * piece);
+            asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+            __syncwarp();
+            if (lane == 0) at_arrive(&sh.s_empty[b]);                   // the MMA warp may overwrite this S buffer
+            const int c0 = (c_begin + j) * AT_KEYS;
+            const bool edge = c0 + AT_KEYS - 1 > pos || c0 < lo;
+            if (__any_sync(0xffffffffu, edge)) {
+#pragma unroll
+                for (int c = 0; c < AT_KEYS; ++c) {
+                    const int key = c0 + c;
+                    sc[c] = (key <= pos && key >= lo) ? sc[c] : -INFINITY;
+                }
+            }
+            float mx = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < AT_KEYS; ++c) mx = fmaxf(mx, sc[c]);
+            mx *= p.scale_log2;
+            const bool jump = mx > m_ref + AT_JUMP || (m_ref == -INFINITY && mx > -INFINITY);
+            const float m_new = jump ? mx : m_ref;
+            // the P tile is free and O is at rest once the previous P V has completed
+            if (j > 0) {
+                alive = at_wait(&sh.pv_done, (unsigned)(j - 1) & 1, p.status);
+                if (!alive) break;
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                if (__any_sync(0xffffffffu, jump)) {
+                    const float alpha = jump ? at_exp2(m_ref - m_new) : 1.f;     // exp2(-inf) = 0: O was 0 anyway
+                    l_run *= alpha;
+#pragma unroll
+                    for (int piece = 0; piece < 4; ++piece) {
+                        float o[32];
+                        tmem_load32(tmem_o + lane_base + 32 * piece, o);
+                        asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+                        for (int c = 0; c < 32; ++c) o[c] *= alpha;
+                        tmem_store32(tmem_o + lane_base + 32 * piece, o);
+                    }
+                    asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+                }
+            }
+            m_ref = m_new;
+            const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
+            float sum = 0.f;
+#pragma unroll
+            for (int c8 = 0; c8 < AT_KEYS / 8; ++c8) {
+                float e[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    e[i] = at_exp2(fmaf(sc[8 * c8 + i], p.scale_log2, -m_use));
+                    sum += e[i];
+                }
+                // 16 bytes of row `row`: chunk c8 % 8 of half c8 / 8, moved by the 128-byte swizzle
+                unsigned char* dst = p_tile + (c8 >> 3) * AT_TILE + row * 128 + (((c8 & 7) ^ (row & 7)) << 4);
+                *reinterpret_cast<uint4*>(dst) = make_uint4(at_pack(e[0], e[1]), at_pack(e[2], e[3]),
+                                                            at_pack(e[4], e[5]), at_pack(e[6], e[7]));
+            }
+            l_run += sum;
+            if (j == n_chunks - 1 && c0 + AT_KEYS - 1 > hi_tile) {
+                // value slots beyond the newest key hold no data yet: zero them in the stage
+                alive = at_wait(&sh.v_full[s], (unsigned)(j / AT_STAGES) & 1, p.status);
+                unsigned char* vs = v_stage + (size_t)s * 2 * AT_TILE;
+                const int first_bad = hi_tile + 1 - c0;                     // first key column without data
+                const int row_bytes = p.page_size * 2;
+                for (int item = tid; alive && item < AT_HD * (AT_KEYS - first_bad); item += 128) {
+                    const int d = item / (AT_KEYS - first_bad), col = first_bad + item % (AT_KEYS - first_bad);
+                    const int pg = col >> p.page_shift, kcol = col & (p.page_size - 1);
+                    // 16-byte chunk kcol / 8 of row d, moved by the 32- or 64-byte swizzle of the tile
+                    const int moved = p.page_size == 16 ? ((kcol >> 3) ^ ((d >> 2) & 1)) : ((kcol >> 3) ^ ((d >> 1) & 3));
+                    *reinterpret_cast<__nv_bfloat16*>(vs + (size_t)pg * page_bytes + d * row_bytes + moved * 16 +
+                                                      (kcol & 7) * 2) = __float2bfloat16_rn(0.f);
+                }
+                asm volatile("bar.sync 2, 128;\n" ::: "memory");            // all four softmax warps zeroed their part
+                if (!alive) break;
+            }
+            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // P (and V) were written by ordinary stores
+            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+            __syncwarp();
+            if (lane == 0) at_arrive(&sh.p_full);
+        }
+        if (alive) alive = at_wait(&sh.pv_done, (unsigned)(n_chunks - 1) & 1, p.status);
+        if (alive) {
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+            __nv_bfloat16* dst = p.out + (size_t)(q_start + tok0 + t_in) * p.out_stride +
+                                 (size_t)(kh * p.group + h_in) * AT_HD;
+#pragma unroll
+            for (int piece = 0; piece < 4; ++piece) {
+                float o[32];
+                tmem_load32(tmem_o + lane_base + 32 * piece, o);
+                asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+                if (valid) {
+#pragma unroll
+                    for (int c = 0; c < 32; c += 8)
+                        *reinterpret_cast<uint4*>(dst + 32 * piece + c) =
+                            make_uint4(at_pack(o[c] * inv, o[c + 1] * inv), at_pack(o[c + 2] * inv, o[c + 3] * inv),
+                                       at_pack(o[c + 4] * inv, o[c + 5] * inv), at_pack(o[c + 6] * inv, o[c + 7] * inv));
+                }
+            }
+        }
+    }
+    // ---------------- teardown: every role arrives here; then tensor memory is freed
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    if (warp == 5) {
+        __syncwarp();
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(512) : "memory");
+    }
+}
+
+typedef CUresult (*AtEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                               const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                               CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+AtEncodeFn at_encode_fn() {
+    static AtEncodeFn fn = nullptr;
+    if (fn == nullptr) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult query;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &query) == cudaSuccess &&
+            query == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<AtEncodeFn>(ptr);
+    }
+    return fn;
+}
+int at_make_map(CUtensorMap* map, const void* base, int rank, const cuuint64_t* dims, const cuuint64_t* strides,
+                const cuuint32_t* box, CUtensorMapSwizzle swizzle) {
+    AtEncodeFn encode = at_encode_fn();
+    if (encode == nullptr) MX_REFUSE("tcgen05 attention: the driver does not offer cuTensorMapEncodeTiled");
+    const cuuint32_t elem[4] = {1, 1, 1, 1};
+    const CUresult rc = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank, const_cast<void*>(base), dims,
+                               strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
+                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (rc != CUDA_SUCCESS) MX_REFUSE("tcgen05 attention: cuTensorMapEncodeTiled failed with code %d", (int)rc);
+    return MX_OK;
+}
+
+}  // namespace
+
+// tiles: [n_tiles][2] (sequence, first token within the sequence); a tile covers
+// tokens_per_tile = 128 / group tokens of that sequence. q: [n_tokens][q_stride] with query head h
+// at column h * 128. cache: [n_pages][2][kv heads][page_size * 128], keys [slot][dim], values
+// [dim][slot]. Every token of every listed sequence must be covered by tiles.
+extern "C" int mx_paged_attention_tc(const void* q, int q_stride, const void* cache, long long n_pages,
+                                     int page_size, const int* block_tables, int bt_stride, const int* cu_q,
+                                     const int* context_lens, const int* tiles, int n_tiles, int n_tokens,
+                                     int n_heads, int n_kv_heads, int head_dim, int window, float scale,
+                                     void* out, int out_stride, int* status, cudaStream_t stream) {
+    if (n_tiles <= 0 || n_tokens <= 0) return MX_OK;
+    if (head_dim != AT_HD) MX_REFUSE("tcgen05 attention is built for head_dim 128, not %d", head_dim);
+    if (page_size != 16 && page_size != 32) MX_REFUSE("tcgen05 attention takes pages of 16 or 32 slots, not %d", page_size);
+    if (n_kv_heads <= 0 || n_heads % n_kv_heads != 0)
+        MX_REFUSE("attention: %d heads are not a multiple of %d kv heads", n_heads, n_kv_heads);
+    const int group = n_heads / n_kv_heads;
+    if (group > AT_ROWS) MX_REFUSE("tcgen05 attention: a query group of %d heads exceeds a tile", group);
+    if (q_stride % 8 != 0 || out_stride % 8 != 0 || reinterpret_cast<uintptr_t>(q) % 16 != 0 ||
+        reinterpret_cast<uintptr_t>(out) % 16 != 0 || reinterpret_cast<uintptr_t>(cache) % 16 != 0)
+        MX_REFUSE("tcgen05 attention needs 16-byte aligned rows (strides %d, %d)", q_stride, out_stride);
+    if (n_kv_heads > 65535) MX_REFUSE("attention: %d kv heads exceed the grid", n_kv_heads);
+    if (status == nullptr) MX_REFUSE("tcgen05 attention needs a status word for its bounded waits");
+    if (n_pages * 2 * n_kv_heads > 0x7fffffffLL) MX_REFUSE("tcgen05 attention: the cache has too many pages for a TMA coordinate");
+    const int tokens_per_tile = AT_ROWS / group;
+
+    CUtensorMap q_map, k_map, v_map;
+    {
+        const cuuint64_t dims[4] = {(cuuint64_t)AT_HD, (cuuint64_t)group, (cuuint64_t)n_kv_heads, (cuuint64_t)n_tokens};
+        const cuuint64_t strides[3] = {(cuuint64_t)AT_HD * 2, (cuuint64_t)group * AT_HD * 2, (cuuint64_t)q_stride * 2};
+        const cuuint32_t box[4] = {64, (cuuint32_t)group, 1, (cuuint32_t)tokens_per_tile};
+        const int rc = at_make_map(&q_map, q, 4, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (rc != MX_OK) return rc;
+    }
+    const cuuint64_t blocks = (cuuint64_t)n_pages * 2 * n_kv_heads;
+    {
+        const cuuint64_t dims[3] = {(cuuint64_t)AT_HD, (cuuint64_t)page_size, blocks};
+        const cuuint64_t strides[2] = {(cuuint64_t)AT_HD * 2, (cuuint64_t)page_size * AT_HD * 2};
+        const cuuint32_t box[3] = {64, (cuuint32_t)page_size, 1};
+        const int rc = at_make_map(&k_map, cache, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (rc != MX_OK) return rc;
+    }
+    {
+        const cuuint64_t dims[3] = {(cuuint64_t)page_size, (cuuint64_t)AT_HD, blocks};
+        const cuuint64_t strides[2] = {(cuuint64_t)page_size * 2, (cuuint64_t)page_size * AT_HD * 2};
+        const cuuint32_t box[3] = {(cuuint32_t)page_size, (cuuint32_t)AT_HD, 1};
+        const int rc = at_make_map(&v_map, cache, 3, dims, strides, box,
+                                   page_size == 16 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_64B);
+        if (rc != MX_OK) return rc;
+    }
+    AtParams p;
+    p.block_tables = block_tables; p.cu_q = cu_q; p.context_lens = context_lens; p.tiles = tiles;
+    p.out = (__nv_bfloat16*)out; p.status = status; p.n_pages = n_pages; p.out_stride = out_stride;
+    p.bt_stride = bt_stride; p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.group = group;
+    p.tokens_per_tile = tokens_per_tile; p.page_size = page_size; p.page_shift = page_size == 16 ? 4 : 5;
+    p.window = window; p.scale_log2 = scale * 1.4426950408889634f;
+    const size_t smem = (size_t)(2 + 2 * AT_STAGES * 2 + 2) * AT_TILE + 1024;
+    static bool attribute_set = false;
+    if (!attribute_set) {
+        cudaError_t e = cudaFuncSetAttribute(attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) MX_REFUSE("tcgen05 attention: cannot reserve %zu bytes of shared memory", smem);
+        attribute_set = true;
+    }
+    attention_tc_kernel<<<dim3(n_tiles, n_kv_heads), AT_THREADS, smem, stream>>>(q_map, k_map, v_map, p);
+    return mx_launch_status();
+}

@@ -78,7 +78,7 @@ class StepContext:
         self.host: HostStep = None
         self.capturing = False        # inside a CUDA-graph capture: buffers must belong to the graph
         self.padded = False           # a fixed-size decode batch: every sequence has one row or none
-        self._tiles: dict[int, tuple[torch.Tensor, int]] = {}
+        self._tiles: dict[tuple, tuple] = {}
 
     def hidden(self, hidden_size: int) -> torch.Tensor:
         if self.capturing:
@@ -86,19 +86,21 @@ class StepContext:
                                device=self.token_ids.device)
         return self._runner.hidden_buffer(self.n_tokens, hidden_size)
 
-    def attention_tiles(self, group: int):
+    def attention_tiles(self, group: int, token_tiles: bool = False):
         """Tile lists of the tensor-core attention for query groups of ``group`` heads:
-        (narrow tiles, their count, wide tiles, their count); built once per step and group."""
-        cached = self._tiles.get(group)
+        (narrow tiles, their count, wide tiles, their count); built once per step, group and
+        kind of wide tile (64 rows, or ``token_tiles``: 128 // group tokens for the tcgen05 kernel)."""
+        key = (group, token_tiles)
+        cached = self._tiles.get(key)
         if cached is not None:
             return cached
         q_lens = [1] * self.n_seqs if self.padded else self.host.q_lens
-        narrow, wide = kernels.attention_tile_lists(q_lens, group)
+        narrow, wide = kernels.attention_tile_lists(q_lens, group, token_tiles)
         device = self.token_ids.device
         both = torch.tensor(narrow + wide + [0, 0], dtype=torch.int32).to(device, non_blocking=True)
-        self._tiles[group] = (both[:len(narrow)], len(narrow) // 2,
-                              both[len(narrow):len(narrow) + len(wide)], len(wide) // 2)
-        return self._tiles[group]
+        self._tiles[key] = (both[:len(narrow)], len(narrow) // 2,
+                            both[len(narrow):len(narrow) + len(wide)], len(wide) // 2)
+        return self._tiles[key]
 
     def tile_splits(self, n_tiles: int, narrow: bool, alone: bool, n_heads: int, n_kv_heads: int,
                     head_dim: int, window: int | None) -> tuple[int, torch.Tensor | None]:

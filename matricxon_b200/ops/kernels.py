@@ -297,23 +297,63 @@ def paged_attention(q: torch.Tensor, q_stride: int, cache: torch.Tensor, block_t
     _launched(2 if n_splits > 1 else 1)
 
 
-def attention_tile_lists(q_lens: list[int], group: int) -> tuple[list[int], list[int]]:
+def attention_tile_lists(q_lens: list[int], group: int,
+                         token_tiles: bool = False) -> tuple[list[int], list[int]]:
     """Row tiles of the tensor-core attention for sequences that bring ``q_lens`` tokens and
-    ``group`` query heads per KV head: flat (sequence, first row) pairs. Sequences with at most
-    16 rows (decode tokens) go to the narrow list, one tile each; the others are cut into
-    64-row tiles in the wide list."""
+    ``group`` query heads per KV head. Sequences with at most 16 rows (decode tokens) go to the
+    narrow list, one (sequence, 0) tile each. The others go to the wide list: cut into 64-row
+    tiles as (sequence, first row) pairs, or, with ``token_tiles`` (the tcgen05 kernel), into
+    tiles of 128 // group tokens as (sequence, first token) pairs, the latest tokens first
+    because they have the most keys to walk."""
     narrow: list[int] = []
     wide: list[int] = []
+    per_tile = max(1, 128 // group)
     for seq, q_len in enumerate(q_lens):
         rows = q_len * group
         if rows <= 0:
             continue
         if rows <= 16:
             narrow.extend((seq, 0))
+        elif token_tiles:
+            for token in range((q_len - 1) // per_tile * per_tile, -1, -per_tile):
+                wide.extend((seq, token))
         else:
             for row in range(0, rows, 64):
                 wide.extend((seq, row))
     return narrow, wide
+
+
+def tc_attention_supported(dtype: torch.dtype, head_dim: int, page_size: int, q_stride: int,
+                           group: int) -> bool:
+    """Whether prompt portions can run on the tcgen05 attention kernel."""
+    return (dtype == torch.bfloat16 and head_dim == 128 and page_size in (16, 32)
+            and q_stride % 8 == 0 and 1 <= group <= 128)
+
+
+def paged_attention_tc(q: torch.Tensor, q_stride: int, cache: torch.Tensor, block_tables: torch.Tensor,
+                       cu_q: torch.Tensor, context_lens: torch.Tensor, tiles: torch.Tensor, n_tiles: int,
+                       n_tokens: int, n_heads: int, n_kv_heads: int, head_dim: int, window: int | None,
+                       scale: float, out: torch.Tensor, status: torch.Tensor) -> None:
+    """Attention of prompt portions on tcgen05 (bfloat16, head_dim 128, pages of 16 or 32).
+    ``tiles`` is int32 [n_tiles, 2]: (sequence, first token) of tiles of 128 // group tokens
+    (``attention_tile_lists(..., token_tiles=True)``); ``q`` holds the step's rows, query head h
+    at column h * head_dim."""
+    _need(q, "q", torch.bfloat16, contiguous=False)
+    _need(cache, "cache", torch.bfloat16)
+    for name, tensor in (("block_tables", block_tables), ("cu_q", cu_q),
+                         ("context_lens", context_lens), ("tiles", tiles), ("status", status)):
+        _need(tensor, name, torch.int32)
+    _need(out, "out", torch.bfloat16)
+    page_size = cache.shape[3]
+    assert tuple(cache.shape[1:]) == (2, n_kv_heads, page_size, head_dim), cache.shape
+    assert out.shape[1] == n_heads * head_dim and out.shape[0] >= n_tokens and q.shape[0] >= n_tokens
+    assert tiles.numel() >= 2 * n_tiles
+    check(library().mx_paged_attention_tc(
+        _ptr(q), q_stride, _ptr(cache), cache.shape[0], page_size, _ptr(block_tables),
+        block_tables.stride(0), _ptr(cu_q), _ptr(context_lens), _ptr(tiles), n_tiles, n_tokens,
+        n_heads, n_kv_heads, head_dim, int(window or 0), float(scale), _ptr(out), out.stride(0),
+        _ptr(status), _stream()), "paged_attention_tc")
+    _launched()
 
 
 def paged_attention_mma(q: torch.Tensor, q_stride: int, cache: torch.Tensor,

@@ -12,6 +12,8 @@ query head h uses KV head ``h // (heads / kv heads)`` (qwen_layers.py:90-100); t
 
 from __future__ import annotations
 
+import os
+
 import torch
 
 from matricxon_b200.ops import kernels
@@ -19,6 +21,10 @@ from matricxon_b200.ops.linear import EPILOGUE_NONE, EPILOGUE_RESIDUAL, linear
 from matricxon_b200.parts.base import KVCacheRequest, Mixer, build_part, register_part
 from matricxon_b200.parts.rotary import store_without_rotation
 from matricxon_b200.weights.loader import WeightSpec
+
+
+# MATRICXON_TC_ATTENTION=0 keeps prompt portions on the mma.sync kernel (for comparisons)
+_TC_ATTENTION = os.environ.get("MATRICXON_TC_ATTENTION", "1") != "0"
 
 
 @register_part("mixer", "attention")
@@ -88,9 +94,19 @@ class PagedAttention(Mixer):
         group = ctx.groups[binding.group]
         attn = torch.empty((ctx.n_tokens, self.q_size), dtype=rt.dtype, device=h.device)
         if kernels.mma_attention_supported(rt.dtype, spec.head_dim, rt.page_size, qkv.stride(0)):
-            narrow, n_narrow, wide, n_wide = ctx.attention_tiles(spec.num_heads // spec.num_kv_heads)
+            group_size = spec.num_heads // spec.num_kv_heads
+            # prompt portions on tcgen05 when the kernel takes the geometry, else on mma.sync
+            on_tc = _TC_ATTENTION and kernels.tc_attention_supported(rt.dtype, spec.head_dim, rt.page_size,
+                                                                     qkv.stride(0), group_size)
+            narrow, n_narrow, wide, n_wide = ctx.attention_tiles(group_size, token_tiles=on_tc)
             for tiles, n_tiles, is_narrow in ((narrow, n_narrow, True), (wide, n_wide, False)):
                 if n_tiles == 0:
+                    continue
+                if on_tc and not is_narrow:
+                    kernels.paged_attention_tc(qkv, qkv.stride(0), binding.kv, group.block_tables, ctx.cu_q,
+                                               ctx.context_lens, tiles, n_tiles, ctx.n_tokens,
+                                               spec.num_heads, spec.num_kv_heads, spec.head_dim,
+                                               spec.window, spec.scale, attn, ctx.status)
                     continue
                 alone = (n_wide == 0) if is_narrow else (n_narrow == 0)
                 n_splits, scratch = ctx.tile_splits(n_tiles, is_narrow, alone, spec.num_heads,

@@ -336,10 +336,14 @@ def run_attention(k, q, cache, tables, tok_seq, positions, heads, kv_heads, dim,
     pos = positions.cpu().tolist()
     context = [pos[cu_q[s]] for s in range(n_seq)]
     group = heads // kv_heads
-    narrow, wide = k.attention_tile_lists(q_lens, group)
+    narrow, wide = k.attention_tile_lists(q_lens, group, token_tiles=(impl == "tc"))
     as_int = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
     for tiles, is_narrow, others in ((narrow, True, wide), (wide, False, narrow)):
         if not tiles:
+            continue
+        if impl == "tc" and not is_narrow:          # prompt portions on the tcgen05 kernel
+            k.paged_attention_tc(q, q.stride(0), cache, tables, as_int(cu_q), as_int(context), as_int(tiles),
+                                 len(tiles) // 2, n, heads, kv_heads, dim, window, scale, out, st)
             continue
         splits = n_splits if not others else 1      # splits need a launch that covers every token
         k.paged_attention_mma(q, q.stride(0), cache, tables, as_int(cu_q), as_int(context), as_int(tiles),
@@ -396,6 +400,65 @@ def test_tensor_core_attention_mixed_batch(heads, kv_heads, dim, page_size, wind
             assert st == 0
             worst = (out.double().cpu() - ref).abs().max(dim=1).values
             assert torch.allclose(out.double().cpu(), ref, **tol(torch.bfloat16)), (n_splits, worst.argmax(), worst.max())
+
+
+@pytest.mark.parametrize("heads,kv_heads,page_size", [(24, 2, 16), (7, 1, 32), (32, 2, 16), (6, 6, 16), (16, 1, 32),
+                                                      (9, 3, 16)])
+@pytest.mark.parametrize("window", [None, 24, 100, 300])
+def test_tcgen05_attention_prompt_portions(heads, kv_heads, page_size, window):
+    """The tcgen05 kernel on prompt portions (with decode rows beside them on the narrow kernel),
+    over a cache whose unwritten slots hold NaN: whole prompts, portions deep in a sequence,
+    lengths on both sides of the 128-key chunks and of the token tiles."""
+    k = kernels()
+    dim, scale = 128, 128 ** -0.5
+    cases = [([1, 37, 130, 64, 301, 257], [1, 37, 1, 5, 2, 257]),
+             ([257, 90, 700, 128], [257, 40, 100, 128]),
+             ([1300, 129], [1300, 2])]
+    for index, (seq_lens, q_lens) in enumerate(cases):
+        q, cache, tables, tok_seq, positions, dense = paged_case(
+            torch.bfloat16, heads, kv_heads, dim, page_size, seq_lens, q_lens, seed=heads + index)
+        ref = reference_attention(dense, q_lens, seq_lens, scale, window)
+        out, st = run_attention(k, q, cache, tables, tok_seq, positions, heads, kv_heads, dim,
+                                window, scale, 1, impl="tc")
+        assert st == 0
+        got = out.double().cpu()
+        assert torch.isfinite(got).all(), f"case {index}: non-finite output at rows {torch.nonzero(~torch.isfinite(got).all(dim=1)).flatten()[:8].tolist()}"
+        worst = (got - ref).abs().max(dim=1).values
+        assert torch.allclose(got, ref, **tol(torch.bfloat16)), (index, int(worst.argmax()), float(worst.max()))
+
+
+@pytest.mark.parametrize("edge", ["window_first_visible", "just_outside_window", "page_last_slot",
+                                  "page_first_slot", "self", "far_key_full_attention", "chunk_last_key",
+                                  "chunk_first_key"])
+def test_tcgen05_attention_one_key_stands_out(edge):
+    """As the stand-out test below, for the last query of a 40-token portion on the tcgen05 kernel."""
+    k = kernels()
+    heads, kv_heads, dim, page_size = 4, 2, 128, 16
+    length, q_len, window = 400, 40, 96
+    p = length - 1
+    target = {"window_first_visible": p - window + 1, "just_outside_window": p - window,
+              "page_last_slot": 367, "page_first_slot": 368, "self": p, "far_key_full_attention": 3,
+              "chunk_last_key": 383, "chunk_first_key": 384}[edge]
+    use_window = None if edge == "far_key_full_attention" else window
+
+    def scale_up(s, qs, ks, vs):
+        ks[:, target] = qs[0::2, -1] * 4.0          # aligned with the last query of heads 0 and 2
+        qs[:, -1] *= 3.0
+
+    scale = dim ** -0.5
+    q, cache, tables, tok_seq, positions, dense = paged_case(
+        torch.bfloat16, heads, kv_heads, dim, page_size, [length], [q_len], seed=11, scale_up=scale_up)
+    ref = reference_attention(dense, [q_len], [length], scale, use_window)
+    out, st = run_attention(k, q, cache, tables, tok_seq, positions, heads, kv_heads, dim, use_window, scale, 1,
+                            impl="tc")
+    assert st == 0
+    assert torch.allclose(out.double().cpu(), ref, **tol(torch.bfloat16))
+    qs, ks, vs = dense[0]
+    head0 = ref[q_len - 1, :dim]
+    if edge == "just_outside_window":
+        assert (head0 - vs[0, target].double()).abs().max() > 0.3
+    else:
+        assert (head0 - vs[0, target].double()).abs().max() < 0.05
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
