@@ -9,17 +9,21 @@
 // A block owns, for one sequence and one KV head, T = 128 / group consecutive query tokens: the
 // 128 rows of an MMA tile are the pairs (token, head in group), token-major, so all rows share
 // every key. It walks the keys in chunks of 128 positions:
-//   warp 4 (one lane)  producer: the query tile once (one 4-D TMA box per half of the head dim),
-//                      then per chunk the keys and values of its pages (TMA boxes straight out of
-//                      the paged cache, page numbers from the block table) into two stages;
+//   warps 4 and 6      producers: warp 4 brings the query tile once (one 4-D TMA box per half of the
+//                      head dim) and per chunk the keys, warp 6 the values: TMA boxes straight out
+//                      of the paged cache, one page per lane, page numbers from the block table
+//                      (read once per tile into shared memory), two stages each. A key stage is
+//                      free as soon as its Q K^T has run, a value stage when its P V has;
 //   warp 5 (one lane)  issues S = Q K^T (tcgen05.mma, operands in swizzled shared memory,
-//                      accumulator in tensor memory, two S buffers) and O += P V (P from shared
-//                      memory, V^T pages as the K-major B operand, O in tensor memory);
+//                      accumulator in tensor memory, three S buffers so that the scores of the
+//                      next chunk exist before the softmax of this one ends) and O += P V (P read
+//                      from tensor memory, V^T pages as the K-major B operand, O in tensor memory);
 //   warps 0-3          softmax: thread r owns row r. It reads its 128 scores from tensor memory
 //                      (tcgen05.ld), masks the chunks that cross an edge, keeps a running
 //                      reference maximum that only moves when the new maximum exceeds it by 2^8
-//                      (then O is rescaled in tensor memory), writes P as bfloat16 into the
-//                      swizzled tile the next MMA reads, and at the end normalises O and stores it.
+//                      (then O is rescaled in tensor memory), writes P as bfloat16 over the first
+//                      64 columns of the same score buffer (tcgen05.st), and at the end
+//                      normalises O and stores it.
 // Keys beyond the newest one of the tile are not data yet: their scores are masked by selection and
 // their value columns are zeroed in shared memory before the last P V (0 x NaN must not happen).
 // Every mbarrier wait is bounded: a wait that runs out sets MX_STATUS_WAIT_TIMEOUT and the role
@@ -31,20 +35,55 @@
 
 namespace {
 
+// Tuning aid (compile with -DAT_PROFILE): thread 0 of every block adds the cycles between successive
+// marks of its softmax loop to g_at_marks[mark]; read with mx_attention_tc_marks.
+#ifdef AT_PROFILE
+#ifndef AT_MARK_TID
+#define AT_MARK_TID 0
+#endif
+__device__ unsigned long long g_at_marks[16];
+#define AT_MARK(i)                                                                        \
+    do {                                                                                  \
+        if (tid == AT_MARK_TID) {                                                         \
+            long long now_;                                                               \
+            asm volatile("mov.u64 %0, %%clock64;\n" : "=l"(now_));                        \
+            atomicAdd(&g_at_marks[i], (unsigned long long)(now_ - at_last_));             \
+            at_last_ = now_;                                                              \
+        }                                                                                 \
+    } while (0)
+// the same for the MMA-issuing thread (marks 8-15)
+#define AT_MARK_M(i)                                                                      \
+    do {                                                                                  \
+        long long now_;                                                                   \
+        asm volatile("mov.u64 %0, %%clock64;\n" : "=l"(now_));                            \
+        atomicAdd(&g_at_marks[i], (unsigned long long)(now_ - at_last_m_));               \
+        at_last_m_ = now_;                                                                \
+    } while (0)
+#else
+#define AT_MARK(i)
+#define AT_MARK_M(i)
+#endif
+
 constexpr int AT_ROWS = 128;
 constexpr int AT_KEYS = 128;
 constexpr int AT_HD = 128;
 constexpr int AT_STAGES = 2;
-constexpr int AT_THREADS = 192;
-constexpr unsigned AT_SPIN = 1u << 22;
+constexpr int AT_THREADS = 224;                       // warps 0-3 softmax, 4 keys, 5 MMA, 6 values
+constexpr unsigned AT_SPIN = 1u << 18;
 constexpr int AT_TILE = AT_ROWS * 64 * 2;            // bytes of a [128][64] bfloat16 half tile
+constexpr int AT_SBUF = 3;                            // score buffers in tensor memory: 3 x 128 columns, then O
+constexpr int AT_TABLE = 1024;                        // block-table entries of a tile kept in shared memory
 constexpr float AT_JUMP = 8.f;                        // log2 of the growth the reference maximum tolerates
 
 struct AtShared {
     unsigned long long q_full;
-    unsigned long long k_full[AT_STAGES], v_full[AT_STAGES], kv_empty[AT_STAGES];
-    unsigned long long s_full[2], s_empty[2];
-    unsigned long long p_full, pv_done;
+    unsigned long long k_full[AT_STAGES], v_full[AT_STAGES];
+    // three S buffers (P of a chunk overwrites its S): Q K^T runs two chunks ahead of P V, and a softmax
+    // warp may be up to two chunks ahead of another, so every barrier of a chunk is per buffer
+    unsigned long long s_full[AT_SBUF], p_full[AT_SBUF];
+    // completion of the P V of even and of odd chunks: the value producer, about to refill the stage of
+    // chunk j - 2, and the softmax threads wait on it; with two barriers neither can fall two phases behind
+    unsigned long long pv_done[2];
     unsigned tmem_base;
 };
 
@@ -131,6 +170,27 @@ __device__ __forceinline__ void at_mma(unsigned tmem_acc, unsigned long long ade
         "l"(adesc), "l"(bdesc), "r"(idesc), "r"((unsigned)accumulate)
         : "memory");
 }
+// The same with the A operand in tensor memory (16-bit elements, two per 32-bit column, row = lane).
+__device__ __forceinline__ void at_mma_ts(unsigned tmem_acc, unsigned tmem_a, unsigned long long bdesc, unsigned idesc,
+                                          bool accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n" ::"r"(tmem_acc),
+        "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"((unsigned)accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_store32_bits(unsigned taddr, const unsigned* v) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};\n" ::"r"(taddr),
+        "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]),
+        "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]), "r"(v[18]),
+        "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]),
+        "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+        : "memory");
+}
 __device__ __forceinline__ void at_commit(unsigned long long* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_u32(bar))
                  : "memory");
@@ -180,12 +240,12 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
                     const __grid_constant__ CUtensorMap v_map, const AtParams p) {
     extern __shared__ __align__(1024) unsigned char at_smem_raw[];
     __shared__ AtShared sh;
+    __shared__ int table_k[AT_TABLE], table_v[AT_TABLE];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(at_smem_raw) + 1023) &
                                                            ~(uintptr_t)1023);
     unsigned char* q_tile = smem;                                   // 2 halves of [128][64]
     unsigned char* k_stage = q_tile + 2 * AT_TILE;                  // per stage: 2 halves of [128 keys][64]
     unsigned char* v_stage = k_stage + AT_STAGES * 2 * AT_TILE;     // per stage: pages of [128 dims][page_size]
-    unsigned char* p_tile = v_stage + AT_STAGES * 2 * AT_TILE;      // 2 halves of [128][64 keys]
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int seq = p.tiles[2 * blockIdx.x], tok0 = p.tiles[2 * blockIdx.x + 1];
@@ -207,14 +267,13 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
         for (int s = 0; s < AT_STAGES; ++s) {
             at_mbar_init(&sh.k_full[s], 1);
             at_mbar_init(&sh.v_full[s], 1);
-            at_mbar_init(&sh.kv_empty[s], 1);
         }
-        for (int b = 0; b < 2; ++b) {
+        for (int b = 0; b < AT_SBUF; ++b) {
             at_mbar_init(&sh.s_full[b], 1);
-            at_mbar_init(&sh.s_empty[b], 4);
+            at_mbar_init(&sh.p_full[b], 4);
         }
-        at_mbar_init(&sh.p_full, 4);
-        at_mbar_init(&sh.pv_done, 1);
+        at_mbar_init(&sh.pv_done[0], 1);
+        at_mbar_init(&sh.pv_done[1], 1);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     // value stages start as zeros: a page that is never fetched must not hold NaN bit patterns
@@ -231,102 +290,150 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
     const unsigned tmem_base = sh.tmem_base;
-    const unsigned tmem_o = tmem_base + 256;
+    const unsigned tmem_o = tmem_base + AT_SBUF * 128;
 
-    if (warp == 4) {
-        // ---------------- producer
-        if (lane == 0) {
+    if (warp == 4 || warp == 6) {
+        // ---------------- producers: warp 4 brings the query tile and the keys, warp 6 the values, each
+        // at its own pace (a key stage is free once its Q K^T is done, a value stage once its P V is);
+        // lane pg owns page pg of every chunk
+        const bool keys = warp == 4;
+        int* table = keys ? table_k : table_v;
+        const int* bt = p.block_tables + (size_t)seq * p.bt_stride;
+        if (keys && lane == 0) {
             const unsigned q_bytes = (unsigned)(2 * 64 * p.group * p.tokens_per_tile * 2);   // boxes count in full
             at_expect_tx(&sh.q_full, q_bytes);
             tma_4d(q_tile, &q_map, 0, 0, kh, q_start + tok0, &sh.q_full);
             tma_4d(q_tile + AT_TILE, &q_map, 64, 0, kh, q_start + tok0, &sh.q_full);
-            const int* bt = p.block_tables + (size_t)seq * p.bt_stride;
-            for (int j = 0; j < n_chunks; ++j) {
-                const int s = j % AT_STAGES;
-                if (!at_wait(&sh.kv_empty[s], ((unsigned)(j / AT_STAGES) & 1) ^ 1, p.status)) break;
-                const int c0 = (c_begin + j) * AT_KEYS;
-                long long page_of[16];
-                int n_valid = 0;
-#pragma unroll
-                for (int pg = 0; pg < 16; ++pg) {
-                    page_of[pg] = -1;
-                    if (pg < pages_per_chunk) {
-                        const int key0 = c0 + pg * p.page_size;
-                        if (key0 <= hi_tile && key0 + p.page_size - 1 >= lo_tile) {
-                            const int lp = key0 >> p.page_shift;
-                            const long long page = lp < p.bt_stride ? bt[lp] : -1;
-                            if (page >= 0 && page < p.n_pages) {
-                                page_of[pg] = page;
-                                ++n_valid;
-                            } else {
-                                atomicOr(p.status, MX_STATUS_BAD_PAGE);
-                            }
-                        }
+        }
+        // this tile's part of the block table, read once (entries beyond AT_TABLE stay in global memory)
+        const int first_page = (c_begin * AT_KEYS) >> p.page_shift;
+        const int n_table = min(n_chunks * pages_per_chunk, AT_TABLE);
+        for (int i = lane; i < n_table; i += 32) {
+            const int lp = first_page + i;
+            table[i] = lp < p.bt_stride ? bt[lp] : -1;
+        }
+        __syncwarp();
+        for (int j = 0; j < n_chunks; ++j) {
+            const int s = j % AT_STAGES;
+            unsigned long long* full = keys ? &sh.k_full[s] : &sh.v_full[s];
+            bool free_now = true;
+            if (lane == 0 && j >= AT_STAGES) {
+                // the stage held chunk j - 2: its keys are free once that chunk's scores exist, its values
+                // once that chunk's P V has run
+                const int before = j - AT_STAGES;
+                free_now = keys ? at_wait(&sh.s_full[before % AT_SBUF], (unsigned)(before / AT_SBUF) & 1, p.status)
+                                : at_wait(&sh.pv_done[before & 1], (unsigned)(before >> 1) & 1, p.status);
+            }
+            if (!__shfl_sync(0xffffffffu, free_now, 0)) break;
+            const int c0 = (c_begin + j) * AT_KEYS;
+            long long page = -1;
+            if (lane < pages_per_chunk) {
+                const int key0 = c0 + lane * p.page_size;
+                if (key0 <= hi_tile && key0 + p.page_size - 1 >= lo_tile) {
+                    const int i = j * pages_per_chunk + lane;
+                    const int lp = first_page + i;
+                    page = i < AT_TABLE ? table[i] : (lp < p.bt_stride ? bt[lp] : -1);
+                    if (page < 0 || page >= p.n_pages) {
+                        page = -1;
+                        if (keys) atomicOr(p.status, MX_STATUS_BAD_PAGE);
                     }
                 }
-                at_expect_tx(&sh.k_full[s], (unsigned)n_valid * page_bytes);
-                at_expect_tx(&sh.v_full[s], (unsigned)n_valid * page_bytes);
-                unsigned char* ks = k_stage + (size_t)s * 2 * AT_TILE;
-                unsigned char* vs = v_stage + (size_t)s * 2 * AT_TILE;
-#pragma unroll
-                for (int pg = 0; pg < 16; ++pg)
-                    if (pg < pages_per_chunk && page_of[pg] >= 0) {
-                        const int block = (int)(page_of[pg] * 2 * p.n_kv_heads) + kh;
-                        tma_3d(ks + (size_t)pg * p.page_size * 128, &k_map, 0, 0, block, &sh.k_full[s]);
-                        tma_3d(ks + AT_TILE + (size_t)pg * p.page_size * 128, &k_map, 64, 0, block, &sh.k_full[s]);
-                    }
-#pragma unroll
-                for (int pg = 0; pg < 16; ++pg)
-                    if (pg < pages_per_chunk && page_of[pg] >= 0)
-                        tma_3d(vs + (size_t)pg * page_bytes, &v_map, 0, 0,
-                               (int)(page_of[pg] * 2 * p.n_kv_heads) + p.n_kv_heads + kh, &sh.v_full[s]);
+            }
+            const unsigned n_valid = __popc(__ballot_sync(0xffffffffu, page >= 0));
+            if (lane == 0) at_expect_tx(full, n_valid * page_bytes);
+            __syncwarp();
+            if (page >= 0) {
+                const int block = (int)(page * 2 * p.n_kv_heads) + kh;
+                if (keys) {
+                    unsigned char* ks = k_stage + (size_t)s * 2 * AT_TILE + (size_t)lane * p.page_size * 128;
+                    tma_3d(ks, &k_map, 0, 0, block, full);
+                    tma_3d(ks + AT_TILE, &k_map, 64, 0, block, full);
+                } else {
+                    tma_3d(v_stage + (size_t)s * 2 * AT_TILE + (size_t)lane * page_bytes, &v_map, 0, 0,
+                           block + p.n_kv_heads, full);
+                }
             }
         }
     } else if (warp == 5) {
-        // ---------------- MMA issuer
+        // ---------------- MMA issuer. One thread; everything it can know before the loop is computed
+        // there, and a chunk costs it two commits: tcgen05.mma of one thread run in issue order, so the
+        // Q K^T that overwrites a score buffer needs no barrier against the P V that read P from it.
         if (lane == 0) {
             const unsigned idesc = at_idesc(AT_ROWS, AT_KEYS);
             const unsigned v_layout = p.page_size == 16 ? 6u : 4u;       // 32- or 64-byte swizzle
             const unsigned v_sbo = (unsigned)(8 * p.page_size * 2);       // eight rows of one page tile
             const int steps_per_page = p.page_size / 16;
-            bool alive = at_wait(&sh.q_full, 0, p.status);
-            auto issue_qk = [&](int j) -> bool {
-                const int s = j % AT_STAGES, b = j & 1;
-                if (!at_wait(&sh.k_full[s], (unsigned)(j / AT_STAGES) & 1, p.status)) return false;
-                if (!at_wait(&sh.s_empty[b], ((unsigned)(j >> 1) & 1) ^ 1, p.status)) return false;
-                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                const unsigned char* ks = k_stage + (size_t)s * 2 * AT_TILE;
+            unsigned long long q_desc[2], k_desc[AT_STAGES][2], v_desc[AT_STAGES];
+            unsigned v_step[AT_KEYS / 16];                                 // where the 16 keys of step kk start
 #pragma unroll
-                for (int half = 0; half < 2; ++half) {
-                    const unsigned long long adesc = at_desc(q_tile + half * AT_TILE, 1024, 2);
-                    const unsigned long long bdesc = at_desc(ks + half * AT_TILE, 1024, 2);
+            for (int half = 0; half < 2; ++half) {
+                q_desc[half] = at_desc(q_tile + half * AT_TILE, 1024, 2);
+#pragma unroll
+                for (int st = 0; st < AT_STAGES; ++st)
+                    k_desc[st][half] = at_desc(k_stage + (size_t)st * 2 * AT_TILE + half * AT_TILE, 1024, 2);
+            }
+#pragma unroll
+            for (int st = 0; st < AT_STAGES; ++st) v_desc[st] = at_desc(v_stage + (size_t)st * 2 * AT_TILE, v_sbo, v_layout);
+#pragma unroll
+            for (int kk = 0; kk < AT_KEYS / 16; ++kk) {
+                const int pg = kk / steps_per_page, within = kk - pg * steps_per_page;
+                v_step[kk] = (unsigned)((pg * page_bytes) >> 4) + 2u * within;
+            }
+            bool alive = at_wait(&sh.q_full, 0, p.status);
+#ifdef AT_PROFILE
+            long long at_last_m_;
+            asm volatile("mov.u64 %0, %%clock64;\n" : "=l"(at_last_m_));
+#endif
+            // state of the chunk whose scores are issued next (qk_*) and of the chunk whose P V is next (pv_*)
+            int qk_stage = 0, qk_buf = 0;
+            unsigned qk_stage_parity = 0;
+            auto issue_qk = [&]() -> bool {
+                AT_MARK_M(8);
+                if (!at_wait(&sh.k_full[qk_stage], qk_stage_parity, p.status)) return false;
+                AT_MARK_M(9);
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                const unsigned acc = tmem_base + (unsigned)qk_buf * 128;
+#pragma unroll
+                for (int half = 0; half < 2; ++half)
 #pragma unroll
                     for (int k = 0; k < 4; ++k)
-                        at_mma(tmem_base + (unsigned)b * 128, adesc + 2 * k, bdesc + 2 * k, idesc, (half | k) != 0);
+                        at_mma(acc, q_desc[half] + 2 * k, k_desc[qk_stage][half] + 2 * k, idesc, (half | k) != 0);
+                at_commit(&sh.s_full[qk_buf]);
+                AT_MARK_M(10);
+                if (++qk_stage == AT_STAGES) {
+                    qk_stage = 0;
+                    qk_stage_parity ^= 1u;
                 }
-                at_commit(&sh.s_full[b]);
+                if (++qk_buf == AT_SBUF) qk_buf = 0;
                 return true;
             };
-            if (alive) alive = issue_qk(0);
+            if (alive) alive = issue_qk();
+            int pv_stage = 0, pv_buf = 0;
+            unsigned pv_stage_parity = 0, pv_buf_parity = 0;
             for (int j = 0; j < n_chunks && alive; ++j) {
-                if (j + 1 < n_chunks) {
-                    alive = issue_qk(j + 1);
+                if (j + 1 < n_chunks) {           // the scores of the next chunk, before this chunk's P V
+                    alive = issue_qk();
                     if (!alive) break;
                 }
-                const int s = j % AT_STAGES;
-                if (!at_wait(&sh.p_full, (unsigned)j & 1, p.status)) break;
-                if (!at_wait(&sh.v_full[s], (unsigned)(j / AT_STAGES) & 1, p.status)) break;
+                AT_MARK_M(11);
+                if (!at_wait(&sh.p_full[pv_buf], pv_buf_parity, p.status)) break;
+                AT_MARK_M(12);
+                if (!at_wait(&sh.v_full[pv_stage], pv_stage_parity, p.status)) break;
+                AT_MARK_M(13);
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                const unsigned char* vs = v_stage + (size_t)s * 2 * AT_TILE;
+                const unsigned p_addr = tmem_base + (unsigned)pv_buf * 128;
 #pragma unroll
-                for (int kk = 0; kk < AT_KEYS / 16; ++kk) {          // 16 keys per MMA
-                    const unsigned long long adesc = at_desc(p_tile + (kk >> 2) * AT_TILE, 1024, 2) + 2 * (kk & 3);
-                    const int pg = kk / steps_per_page, within = kk - pg * steps_per_page;
-                    const unsigned long long bdesc = at_desc(vs + (size_t)pg * page_bytes, v_sbo, v_layout) + 2 * within;
-                    at_mma(tmem_o, adesc, bdesc, idesc, (j | kk) != 0);
+                for (int kk = 0; kk < AT_KEYS / 16; ++kk)             // 16 keys per MMA: 8 columns of P
+                    at_mma_ts(tmem_o, p_addr + 8 * kk, v_desc[pv_stage] + v_step[kk], idesc, (j | kk) != 0);
+                at_commit(&sh.pv_done[j & 1]);
+                if (++pv_stage == AT_STAGES) {
+                    pv_stage = 0;
+                    pv_stage_parity ^= 1u;
                 }
-                at_commit(&sh.kv_empty[s]);
-                at_commit(&sh.pv_done);
+                if (++pv_buf == AT_SBUF) {
+                    pv_buf = 0;
+                    pv_buf_parity ^= 1u;
+                }
             }
         }
     } else {
@@ -339,22 +446,40 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
         const unsigned lane_base = (unsigned)(32 * warp) << 16;
         float m_ref = -INFINITY, l_run = 0.f;
         bool alive = true;
+        // Phases of the "P V done" barrier are consumed strictly in order (phase j completes when the
+        // P V of chunk j has run); the barrier can never be more than one phase ahead of a warp that
+        // has consumed every phase below j - 1 when it starts chunk j, so a parity is never ambiguous.
+        int consumed = 0;
+        auto pv_consumed_through = [&](int phases) {
+            while (alive && consumed < phases) {
+                alive = at_wait(&sh.pv_done[consumed & 1], (unsigned)(consumed >> 1) & 1, p.status);
+                ++consumed;
+            }
+        };
+#ifdef AT_PROFILE
+        long long at_last_;
+        asm volatile("mov.u64 %0, %%clock64;\n" : "=l"(at_last_));
+#endif
         for (int j = 0; j < n_chunks && alive; ++j) {
-            const int b = j & 1, s = j % AT_STAGES;
-            alive = at_wait(&sh.s_full[b], (unsigned)(j >> 1) & 1, p.status);
+            const int b = j % AT_SBUF, s = j % AT_STAGES;
+            AT_MARK(0);
+            alive = at_wait(&sh.s_full[b], (unsigned)(j / AT_SBUF) & 1, p.status);
             if (!alive) break;
+            AT_MARK(1);
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            pv_consumed_through(j - 1);               // long completed: this only keeps the count in step
+            if (!alive) break;
+            const int c0 = (c_begin + j) * AT_KEYS;
+            // rows that belong to no token of the tile need no mask: whatever they compute is never stored,
+            // and a row's output depends on that row alone
+            const bool edge = __any_sync(0xffffffffu, valid && (c0 + AT_KEYS - 1 > pos || c0 < lo));
+            const unsigned s_addr = tmem_base + (unsigned)b * 128 + lane_base;
             float sc[AT_KEYS];
 #pragma unroll
-            for (int piece = 0; piece < 4; ++piece)
-                tmem_load32(tmem_base + (unsigned)b * 128 + lane_base + 32 * piece, sc + 32 * piece);
+            for (int piece = 0; piece < 4; ++piece) tmem_load32(s_addr + 32 * piece, sc + 32 * piece);
             asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
-            __syncwarp();
-            if (lane == 0) at_arrive(&sh.s_empty[b]);                   // the MMA warp may overwrite this S buffer
-            const int c0 = (c_begin + j) * AT_KEYS;
-            const bool edge = c0 + AT_KEYS - 1 > pos || c0 < lo;
-            if (__any_sync(0xffffffffu, edge)) {
+            AT_MARK(2);
+            if (edge) {
 #pragma unroll
                 for (int c = 0; c < AT_KEYS; ++c) {
                     const int key = c0 + c;
@@ -365,14 +490,15 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
 #pragma unroll
             for (int c = 0; c < AT_KEYS; ++c) mx = fmaxf(mx, sc[c]);
             mx *= p.scale_log2;
+            AT_MARK(3);
             const bool jump = mx > m_ref + AT_JUMP || (m_ref == -INFINITY && mx > -INFINITY);
             const float m_new = jump ? mx : m_ref;
-            // the P tile is free and O is at rest once the previous P V has completed
-            if (j > 0) {
-                alive = at_wait(&sh.pv_done, (unsigned)(j - 1) & 1, p.status);
+            // O may only be touched while no P V is running: the rare rescaling waits for the previous one
+            if (j > 0 && __any_sync(0xffffffffu, jump)) {
+                pv_consumed_through(j);
                 if (!alive) break;
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                if (__any_sync(0xffffffffu, jump)) {
+                {
                     const float alpha = jump ? at_exp2(m_ref - m_new) : 1.f;     // exp2(-inf) = 0: O was 0 anyway
                     l_run *= alpha;
 #pragma unroll
@@ -390,19 +516,21 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
             m_ref = m_new;
             const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
             float sum = 0.f;
+            // P as bfloat16 pairs over the first 64 columns of this chunk's S buffer (its scores are in registers)
 #pragma unroll
-            for (int c8 = 0; c8 < AT_KEYS / 8; ++c8) {
-                float e[8];
+            for (int half = 0; half < 2; ++half) {
+                unsigned packed[32];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    e[i] = at_exp2(fmaf(sc[8 * c8 + i], p.scale_log2, -m_use));
-                    sum += e[i];
+                for (int c = 0; c < 32; ++c) {
+                    const float e0 = at_exp2(fmaf(sc[64 * half + 2 * c], p.scale_log2, -m_use));
+                    const float e1 = at_exp2(fmaf(sc[64 * half + 2 * c + 1], p.scale_log2, -m_use));
+                    sum += e0 + e1;
+                    packed[c] = at_pack(e0, e1);
                 }
-                // 16 bytes of row `row`: chunk c8 % 8 of half c8 / 8, moved by the 128-byte swizzle
-                unsigned char* dst = p_tile + (c8 >> 3) * AT_TILE + row * 128 + (((c8 & 7) ^ (row & 7)) << 4);
-                *reinterpret_cast<uint4*>(dst) = make_uint4(at_pack(e[0], e[1]), at_pack(e[2], e[3]),
-                                                            at_pack(e[4], e[5]), at_pack(e[6], e[7]));
+                tmem_store32_bits(s_addr + 32 * half, packed);
             }
+            asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+            AT_MARK(4);
             l_run += sum;
             if (j == n_chunks - 1 && c0 + AT_KEYS - 1 > hi_tile) {
                 // value slots beyond the newest key hold no data yet: zero them in the stage
@@ -418,15 +546,18 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
                     *reinterpret_cast<__nv_bfloat16*>(vs + (size_t)pg * page_bytes + d * row_bytes + moved * 16 +
                                                       (kcol & 7) * 2) = __float2bfloat16_rn(0.f);
                 }
+                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // ordinary stores, read by the MMA
                 asm volatile("bar.sync 2, 128;\n" ::: "memory");            // all four softmax warps zeroed their part
                 if (!alive) break;
             }
-            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // P (and V) were written by ordinary stores
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
             __syncwarp();
-            if (lane == 0) at_arrive(&sh.p_full);
+            if (lane == 0) at_arrive(&sh.p_full[b]);
+            AT_MARK(5);
         }
-        if (alive) alive = at_wait(&sh.pv_done, (unsigned)(n_chunks - 1) & 1, p.status);
+        AT_MARK(6);
+        pv_consumed_through(n_chunks);
+        AT_MARK(7);
         if (alive) {
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
             const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
@@ -485,6 +616,18 @@ int at_make_map(CUtensorMap* map, const void* base, int rank, const cuuint64_t* 
 
 }  // namespace
 
+#ifdef AT_PROFILE
+extern "C" int mx_attention_tc_marks(unsigned long long* out, int reset) {
+    cudaDeviceSynchronize();
+    if (out) cudaMemcpyFromSymbol(out, g_at_marks, sizeof(unsigned long long) * 16);
+    if (reset) {
+        static unsigned long long zeros[16];
+        cudaMemcpyToSymbol(g_at_marks, zeros, sizeof(zeros));
+    }
+    return MX_OK;
+}
+#endif
+
 // tiles: [n_tiles][2] (sequence, first token within the sequence); a tile covers
 // tokens_per_tile = 128 / group tokens of that sequence. q: [n_tokens][q_stride] with query head h
 // at column h * 128. cache: [n_pages][2][kv heads][page_size * 128], keys [slot][dim], values
@@ -539,7 +682,7 @@ extern "C" int mx_paged_attention_tc(const void* q, int q_stride, const void* ca
     p.bt_stride = bt_stride; p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.group = group;
     p.tokens_per_tile = tokens_per_tile; p.page_size = page_size; p.page_shift = page_size == 16 ? 4 : 5;
     p.window = window; p.scale_log2 = scale * 1.4426950408889634f;
-    const size_t smem = (size_t)(2 + 2 * AT_STAGES * 2 + 2) * AT_TILE + 1024;
+    const size_t smem = (size_t)(2 + 2 * AT_STAGES * 2) * AT_TILE + 1024;
     static bool attribute_set = false;
     if (!attribute_set) {
         cudaError_t e = cudaFuncSetAttribute(attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
