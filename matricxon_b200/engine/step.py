@@ -170,7 +170,7 @@ class StepRunner:
         self.tokens_run = 0
         limit = max_model_len or model.spec.max_position_embeddings
         self.graph_table_width = (limit + cache.page_size - 1) // cache.page_size
-        self.use_graphs = use_graphs
+        self.use_graphs = use_graphs and getattr(model, "capturable", False)
         self.max_graph_batch = max_graph_batch
         self._graphs: dict[int, tuple] = {}
         self._graph_pool = None

@@ -118,6 +118,8 @@ class DecoderModel:
         self.layers = [part_class("block", layer.block)(layer, runtime, f"{spec.layer_prefix}.{index}.")
                        for index, layer in enumerate(spec.layers)]
         self.final_norm = build_part("norm", spec.final_norm, runtime, f"{spec.final_norm_name}.")
+        # decode steps may be captured as CUDA graphs only if every part is stream-ordered
+        self.capturable = self.final_norm.capturable and all(layer.capturable for layer in self.layers)
         self.cache_plan = plan_cache(spec)
         self.embedding: torch.Tensor | None = None
         self.head: torch.Tensor | None = None

@@ -37,6 +37,8 @@ class PagedAttention(Mixer):
         self.kv_size = spec.num_kv_heads * spec.head_dim
         self.position = (build_part("position", spec.position, runtime, prefix)
                          if spec.position is not None else None)
+        # the kernels here are stream-ordered; a position encoding from elsewhere decides for itself
+        self.capturable = self.position is None or self.position.capturable
 
     @classmethod
     def weight_specs(cls, spec, prefix):

@@ -108,6 +108,12 @@ class CacheBinding:
 
 
 class Part:
+    # True when ``forward`` only enqueues work on the current CUDA stream (no host synchronisation,
+    # no memory from outside the step's allocator): such a part can run inside a captured CUDA graph.
+    # A model takes the graph path for decode steps only if every one of its parts says so; the
+    # default is the safe answer for parts written elsewhere.
+    capturable = False
+
     def __init__(self, spec: Any, runtime: Runtime, prefix: str) -> None:
         self.spec = spec
         self.runtime = runtime

@@ -19,6 +19,7 @@ class PreNormSequentialBlock(Block):
         self.ffn_norm = build_part("norm", spec.ffn_norm, runtime, f"{prefix}{spec.ffn_norm_name}.")
         self.feed_forward = build_part("feed_forward", spec.feed_forward, runtime,
                                        f"{prefix}{spec.feed_forward_name}.")
+        self.capturable = all(part.capturable for part in self.parts())
 
     @classmethod
     def weight_specs(cls, spec, prefix):

@@ -16,6 +16,8 @@ _ACTIVATION_MODES = {"gelu_tanh": EPILOGUE_GELU}
 
 @register_part("feed_forward", "mlp")
 class Mlp(FeedForward):
+    capturable = True
+
     def __init__(self, spec, runtime, prefix):
         super().__init__(spec, runtime, prefix)
         if spec.activation not in _ACTIVATION_MODES:

@@ -17,6 +17,8 @@ from matricxon_b200.weights.loader import WeightSpec
 
 @register_part("norm", "layernorm")
 class LayerNorm(Norm):
+    capturable = True
+
     @classmethod
     def weight_specs(cls, spec, prefix):
         specs = [WeightSpec(prefix + "weight", (spec.size,), role="vector", init="norm_weight")]

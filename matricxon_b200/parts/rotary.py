@@ -25,6 +25,8 @@ def inverse_frequencies(rotary_dim: int, theta: float) -> torch.Tensor:
 
 @register_part("position", "rotary_neox")
 class RotaryNeox(PositionEncoding):
+    capturable = True
+
     def __init__(self, spec, runtime, prefix):
         super().__init__(spec, runtime, prefix)
         self.inv_freq = inverse_frequencies(spec.rotary_dim, spec.theta).to(runtime.device)

@@ -12,6 +12,7 @@ from plain_reference import (
     plain_config,
     plain_layer,
     plain_layernorm,
+    plain_gelu_tanh,
     plain_mlp,
     plain_rope_tables,
 )
@@ -290,3 +291,166 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped():
     core.cache.add_request("z")
     logits = core.runner.run([StepEntry("z", prompts["x"], list(range(45)))]).cpu()
     assert torch.allclose(logits.double(), refs["x"], atol=5e-5)
+
+
+# ------------------------------------------- a toy position encoding and a toy routed feed-forward
+def register_toy_position_and_router():
+    """Two more kinds registered from the test file alone.
+
+    ``toy_distance_decay`` (a position encoding): q is scaled by a^p and k by a^-p at position p,
+    so the score of (p, j) carries the factor a^(p - j); then k and v are stored as they are.
+    ``toy_top1_experts`` (a feed-forward): router logits and their softmax in float; the token goes
+    through the one expert with the largest probability (an ungated tanh-GELU MLP) and the
+    result is scaled by that probability."""
+    from matricxon_b200.parts.base import FeedForward, PositionEncoding, register_part
+    from matricxon_b200.parts.rotary import store_without_rotation
+    from matricxon_b200.weights.loader import WeightSpec
+
+    class ToyDecaySpec:
+        kind = "toy_distance_decay"
+
+        def __init__(self, base):
+            self.base = base
+
+    class ToyExpertsSpec:
+        kind = "toy_top1_experts"
+
+        def __init__(self, hidden_size, intermediate_size, experts):
+            self.hidden_size, self.intermediate_size, self.experts = hidden_size, intermediate_size, experts
+
+    @register_part("position", "toy_distance_decay")
+    class ToyDistanceDecay(PositionEncoding):
+        def rotate_and_store(self, qkv, ctx, binding, n_heads, n_kv_heads, head_dim):
+            factor = (self.spec.base ** ctx.positions.double()).float()[:, None]
+            q_cols, k_cols = n_heads * head_dim, n_kv_heads * head_dim
+            qkv[:, :q_cols] = (qkv[:, :q_cols].float() * factor).to(qkv.dtype)
+            qkv[:, q_cols:q_cols + k_cols] = (qkv[:, q_cols:q_cols + k_cols].float() / factor).to(qkv.dtype)
+            store_without_rotation(qkv, ctx, binding, n_heads, n_kv_heads, head_dim, self.runtime.page_size)
+
+    @register_part("feed_forward", "toy_top1_experts")
+    class ToyTop1Experts(FeedForward):
+        @classmethod
+        def weight_specs(cls, spec, prefix):
+            specs = [WeightSpec(prefix + "router.weight", (spec.experts, spec.hidden_size))]
+            for e in range(spec.experts):
+                specs.append(WeightSpec(f"{prefix}experts.{e}.up.weight", (spec.intermediate_size, spec.hidden_size)))
+                specs.append(WeightSpec(f"{prefix}experts.{e}.down.weight", (spec.hidden_size, spec.intermediate_size)))
+            return specs
+
+        def load(self, fetch):
+            self.router = fetch(self.prefix + "router.weight")
+            self.up = [fetch(f"{self.prefix}experts.{e}.up.weight") for e in range(self.spec.experts)]
+            self.down = [fetch(f"{self.prefix}experts.{e}.down.weight") for e in range(self.spec.experts)]
+
+        def forward(self, h, residual, ctx):
+            probs = torch.softmax(h.float() @ self.router.float().T, dim=-1)
+            weight, choice = probs.max(dim=-1)
+            out = torch.zeros_like(residual)
+            for e in range(self.spec.experts):
+                rows = torch.nonzero(choice == e).flatten()
+                if rows.numel():
+                    mid = torch.nn.functional.gelu(h[rows].float() @ self.up[e].float().T, approximate="tanh")
+                    out[rows] = (mid @ self.down[e].float().T) * weight[rows, None]
+            return residual + out
+
+    return ToyDecaySpec, ToyExpertsSpec
+
+
+def test_toy_position_encoding_and_routed_feed_forward_beside_the_stock_parts():
+    """A layer whose attention uses a position encoding defined here and whose feed-forward routes
+    tokens between experts, beside a stock StarCoder2 layer, built from specs and stepped in
+    portions for two requests: nothing in the package names these kinds."""
+    import dataclasses
+
+    import matricxon_b200.parts  # noqa: F401
+    from matricxon_b200.engine.core import EngineCore
+    from matricxon_b200.engine.step import StepEntry
+    from matricxon_b200.models.decoder import DecoderModel, model_weight_specs
+    from matricxon_b200.parts.spec import LayerSpec, ModelSpec, ScheduleEntry
+    from matricxon_b200.weights.loader import DictSource, make_fetcher
+    from matricxon_b200.weights.random_init import RandomInit, RandomSource
+    from plain_reference import plain_attention_core, plain_linear
+
+    ToyDecaySpec, ToyExpertsSpec = register_toy_position_and_router()
+    base = tiny_config("A").model_spec()
+    stock = base.layers[0]
+    decay_base, experts, inter = 1.01, 3, 80
+    toy_attention = dataclasses.replace(stock.mixer, position=ToyDecaySpec(decay_base))
+    toy_layer = LayerSpec(mixer=toy_attention, feed_forward=ToyExpertsSpec(base.hidden_size, inter, experts),
+                          mixer_norm=stock.mixer_norm, ffn_norm=stock.ffn_norm)
+    schedule = (ScheduleEntry(0), ScheduleEntry(1))
+    spec = ModelSpec(hidden_size=base.hidden_size, vocab_size=base.vocab_size, layers=(toy_layer, stock),
+                     schedule=schedule, final_norm=base.final_norm, tie_word_embeddings=True,
+                     max_position_embeddings=128)
+    specs = model_weight_specs(spec)
+    assert any(s.name == "model.layers.0.mlp.experts.2.down.weight" for s in specs)
+    source = RandomSource(specs, seed=5, init=RandomInit(0.08, 0.02, 0.02, 0.02))
+    weights = {name: source.read(name) for name in source.names()}
+    model = DecoderModel(spec, make_runtime(torch.float32))
+    assert len(model.cache_plan.groups) == 1            # same geometry and window: one group of pages
+    model.load(make_fetcher(specs, DictSource(weights), torch.float32, DEV))
+    core = EngineCore(model, max_cache_tokens=256, max_requests=4)
+    cfg = plain_config(TINY["A"][0])
+
+    def reference(ids):
+        w = {k: v.double() for k, v in weights.items()}
+        t = len(ids)
+        heads, kv_heads, d = cfg["heads"], cfg["kv_heads"], cfg["head_dim"]
+        positions = torch.arange(t)
+        x = w["model.embed_tokens.weight"][torch.tensor(ids)]
+        # layer 0: toy position encoding, toy experts
+        p = "model.layers.0."
+        h = plain_layernorm(x, w[p + "input_layernorm.weight"], w[p + "input_layernorm.bias"], cfg["eps"])
+        q = plain_linear(h, w[p + "self_attn.q_proj.weight"], w[p + "self_attn.q_proj.bias"]).view(t, heads, d)
+        k = plain_linear(h, w[p + "self_attn.k_proj.weight"], w[p + "self_attn.k_proj.bias"]).view(t, kv_heads, d)
+        v = plain_linear(h, w[p + "self_attn.v_proj.weight"], w[p + "self_attn.v_proj.bias"]).view(t, kv_heads, d)
+        factor = (decay_base ** positions.double())[:, None, None]
+        o = plain_attention_core((q * factor).transpose(0, 1), (k / factor).transpose(0, 1), v.transpose(0, 1),
+                                 d ** -0.5, cfg["window"])
+        x = x + plain_linear(o.transpose(0, 1).reshape(t, heads * d), w[p + "self_attn.o_proj.weight"],
+                             w[p + "self_attn.o_proj.bias"])
+        h = plain_layernorm(x, w[p + "post_attention_layernorm.weight"], w[p + "post_attention_layernorm.bias"],
+                            cfg["eps"])
+        probs = torch.softmax(h @ w[p + "mlp.router.weight"].T, dim=-1)
+        gate, choice = probs.max(dim=-1)
+        rows = []
+        for i in range(t):
+            e = int(choice[i])
+            mid = plain_gelu_tanh(h[i] @ w[f"{p}mlp.experts.{e}.up.weight"].T)
+            rows.append((mid @ w[f"{p}mlp.experts.{e}.down.weight"].T) * gate[i])
+        x = x + torch.stack(rows)
+        # layer 1: the stock layer
+        p = "model.layers.1."
+        h = plain_layernorm(x, w[p + "input_layernorm.weight"], w[p + "input_layernorm.bias"], cfg["eps"])
+        x = x + plain_attention(h, w, p + "self_attn.", cfg, positions)
+        h = plain_layernorm(x, w[p + "post_attention_layernorm.weight"], w[p + "post_attention_layernorm.bias"],
+                            cfg["eps"])
+        x = x + plain_mlp(h, w, p + "mlp.", cfg)
+        x = plain_layernorm(x, w["model.norm.weight"], w["model.norm.bias"], cfg["eps"])
+        return x @ w["model.embed_tokens.weight"].T
+
+    prompts = {"x": random_ids(50, 512, 3), "y": random_ids(23, 512, 4)}
+    refs = {rid: reference(ids) for rid, ids in prompts.items()}
+    for rid in prompts:
+        core.cache.add_request(rid)
+    got = {rid: [] for rid in prompts}
+    done = {rid: 0 for rid in prompts}
+    sizes = [7, 1, 2, 11, 1, 1, 5, 3]
+    turn = 0
+    while any(done[r] < len(prompts[r]) for r in prompts):
+        entries = []
+        for rid, ids in prompts.items():
+            if done[rid] < len(ids):
+                size = min(sizes[turn % len(sizes)], len(ids) - done[rid])
+                turn += 1
+                entries.append(StepEntry(rid, ids[done[rid]:done[rid] + size], list(range(size))))
+                done[rid] += size
+        logits = core.runner.run(entries).cpu()
+        core.runner.check_status()
+        row = 0
+        for entry in entries:
+            got[entry.request_id].append(logits[row:row + len(entry.tokens)])
+            row += len(entry.tokens)
+    for rid in prompts:
+        worst = (torch.cat(got[rid]).double() - refs[rid]).abs().max()
+        assert torch.allclose(torch.cat(got[rid]).double(), refs[rid], atol=1e-4), (rid, float(worst))
