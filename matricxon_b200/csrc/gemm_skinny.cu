@@ -16,6 +16,8 @@
 //
 // Epilogue modes as in gemm_simt.cu: 0 out(bf16) = v; 1 out(bf16) = gelu_tanh(v);
 // 2 out(f32) = residual + v; 3 out(f32) = v, with v = acc + bias.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 
 namespace {
@@ -58,7 +60,11 @@ struct SkinnyRope {
     int n_heads, n_kv_heads, head_dim, page_size;
 };
 
-template <int MB, bool ROPE>
+// SPLIT: two blocks (a cluster of two, rank = blockIdx.x & 1) share a tile and take half of K each;
+// the second hands its sums to the first through distributed shared memory, which adds them after its
+// own (a fixed order) and runs the epilogue. For matrices with so few output features that one block
+// per tile leaves most of the GPU's warp slots, and so most of the loads it could have in flight, unused.
+template <int MB, bool ROPE, bool SPLIT>
 __global__ void __launch_bounds__(SK_THREADS)
 gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bfloat16* __restrict__ W,
                    int ldw, const float* __restrict__ bias, const float* residual, void* out,
@@ -66,8 +72,11 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bflo
     constexpr int UNROLL = SK_UNROLL;   // eight weight loads in flight per thread; sixteen measured slower
     constexpr int ROWS = 16, NR = 2;                   // a block owns 16 output features: rows g and g + 8 per thread
     __shared__ float red[SK_WARPS][ROWS][8 * MB];
+    __shared__ float peer[SPLIT ? ROWS : 1][8 * MB];   // SPLIT: the other block's sums, written by it
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
+    const int tile = SPLIT ? blockIdx.x >> 1 : blockIdx.x;
+    const int half = SPLIT ? blockIdx.x & 1 : 0;
     int n_row[2];
     if (ROPE) {
         const int per_head = rope.head_dim >> 4;
@@ -76,7 +85,7 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bflo
         n_row[0] = head * rope.head_dim + (rotated ? 8 * j : 16 * j) + g;
         n_row[1] = n_row[0] + (rotated ? rope.head_dim / 2 : 8);
     } else {
-        n_row[0] = blockIdx.x * ROWS + g;
+        n_row[0] = tile * ROWS + g;
         n_row[1] = n_row[0] + 8;
     }
     bool row_ok[NR];
@@ -97,13 +106,14 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bflo
 #pragma unroll
     for (int mb = 0; mb < MB; ++mb) acc[mb][0] = acc[mb][1] = acc[mb][2] = acc[mb][3] = 0.f;
 
-    const int n_blocks = K / 32;
+    const int kb_first = SPLIT ? half * (K / 64) : 0;          // SPLIT needs K to be a multiple of 64
+    const int n_blocks = SPLIT ? kb_first + K / 64 : K / 32;
     // The weights are nobody's output: start pulling this thread's first pieces towards L2 while
     // the kernel before this one is still finishing, then wait for it before touching activations.
     pdl_trigger();
 #pragma unroll
     for (int u = 0; u < 2 * UNROLL; ++u) {
-        const int kb = warp + u * SK_WARPS;
+        const int kb = kb_first + warp + u * SK_WARPS;
         if (kb < n_blocks) {
 #pragma unroll
             for (int i = 0; i < NR; ++i)
@@ -111,7 +121,7 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bflo
         }
     }
     pdl_wait();
-    for (int kb0 = warp; kb0 < n_blocks; kb0 += SK_WARPS * UNROLL) {
+    for (int kb0 = kb_first + warp; kb0 < n_blocks; kb0 += SK_WARPS * UNROLL) {
         uint4 wf[UNROLL][2], xf[UNROLL][MB];
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
@@ -149,8 +159,25 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bflo
         float v = 0.f;
 #pragma unroll
         for (int w = 0; w < SK_WARPS; ++w) v += red[w][f][m];
+        if (SPLIT) v += peer[SPLIT ? f : 0][m];
         return v;
     };
+    if constexpr (SPLIT) {
+        namespace cg = cooperative_groups;
+        cg::cluster_group cluster = cg::this_cluster();
+        if (half == 1) {
+            float* remote = cluster.map_shared_rank(&peer[0][0], 0);
+            for (int idx = tid; idx < ROWS * 8 * MB; idx += SK_THREADS) {
+                const int f = idx % ROWS, m = idx / ROWS;
+                float v = 0.f;
+#pragma unroll
+                for (int w = 0; w < SK_WARPS; ++w) v += red[w][f][m];
+                remote[f * 8 * MB + m] = v;
+            }
+        }
+        cluster.sync();
+        if (half == 1) return;
+    }
     if constexpr (ROPE) {
         const int HD = rope.head_dim;
         const int per_head = HD >> 4;
@@ -202,7 +229,7 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bflo
     } else {
     for (int idx = tid; idx < ROWS * 8 * MB; idx += SK_THREADS) {
         const int f = idx % ROWS, m = idx / ROWS;
-        const int n = blockIdx.x * ROWS + f;
+        const int n = tile * ROWS + f;
         if (n >= N || m >= M) continue;
         float v = total(f, m);
         if (bias) v += bias[n];
@@ -216,6 +243,17 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bflo
         }
     }
     }
+}
+
+int skinny_sm_count() {
+    static int count = 0;
+    if (count == 0) {
+        int device = 0;
+        cudaGetDevice(&device);
+        cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device);
+        if (count <= 0) count = 148;
+    }
+    return count;
 }
 
 int check_skinny(int M, int K, int ldx, int ldw) {
@@ -239,7 +277,30 @@ extern "C" int mx_gemm_skinny(const void* x, const void* W, const float* bias, c
         MX_REFUSE("skinny gemm: epilogue mode %d does not write dtype %d", mode, out_dtype);
     const SkinnyRope none = {};
     const int grid = (N + 15) / 16;
-    auto kernel = M <= 8 ? gemm_skinny_kernel<1, false> : gemm_skinny_kernel<2, false>;
+    if (2 * grid <= 3 * skinny_sm_count() && K % 64 == 0 && K >= 6144) {
+        // few tiles and a long K: two blocks a tile, as a cluster of two (c_proj 3072 x 12288: 14.8 us
+        // against 16.9; at K = 3072 the halves are too short to pay for the exchange: 6.7 against 6.6)
+        auto kernel = M <= 8 ? gemm_skinny_kernel<1, false, true> : gemm_skinny_kernel<2, false, true>;
+        cudaLaunchConfig_t config = {};
+        config.gridDim = dim3(2 * grid);
+        config.blockDim = dim3(SK_THREADS);
+        config.stream = stream;
+        cudaLaunchAttribute attribute[1];
+        attribute[0].id = cudaLaunchAttributeClusterDimension;
+        attribute[0].val.clusterDim.x = 2;
+        attribute[0].val.clusterDim.y = 1;
+        attribute[0].val.clusterDim.z = 1;
+        config.attrs = attribute;
+        config.numAttrs = 1;
+        const cudaError_t e = cudaLaunchKernelEx(&config, kernel, (const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)W,
+                                                 ldw, bias, residual, out, ldo, M, N, K, mode, none);
+        if (e != cudaSuccess) {
+            mx_set_error("skinny gemm: cluster launch failed: %s", cudaGetErrorString(e));
+            return (int)e;
+        }
+        return MX_OK;
+    }
+    auto kernel = M <= 8 ? gemm_skinny_kernel<1, false, false> : gemm_skinny_kernel<2, false, false>;
     mx_launch_chained(kernel, dim3(grid), dim3(SK_THREADS), 0, stream, (const __nv_bfloat16*)x, ldx,
                       (const __nv_bfloat16*)W, ldw, bias, residual, out, ldo, M, N, K, mode, none);
     return mx_launch_status();
@@ -265,7 +326,7 @@ extern "C" int mx_gemm_skinny_rope(const void* x, const void* W, const float* bi
     rope.cache = (__nv_bfloat16*)cache; rope.status = status; rope.n_slots = n_pages * page_size;
     rope.n_heads = n_heads; rope.n_kv_heads = n_kv_heads; rope.head_dim = head_dim; rope.page_size = page_size;
     const int N = (n_heads + 2 * n_kv_heads) * head_dim;
-    auto kernel = M <= 8 ? gemm_skinny_kernel<1, true> : gemm_skinny_kernel<2, true>;
+    auto kernel = M <= 8 ? gemm_skinny_kernel<1, true, false> : gemm_skinny_kernel<2, true, false>;
     mx_launch_chained(kernel, dim3(N / 16), dim3(SK_THREADS), 0, stream, (const __nv_bfloat16*)x, ldx,
                       (const __nv_bfloat16*)W, ldw, bias, (const float*)nullptr, qkv, ldo, M, N, K, 0, rope);
     return mx_launch_status();
