@@ -10,7 +10,7 @@
 // tile); with grouped queries those rows sit on one or two tokens, so they share nearly the
 // same causal limit and every key they load is used by all of them.
 //
-// Work. A block of four warps owns a tile of rows of one (sequence, KV head) and a split of
+// Work. A block (four warps for wide tiles, eight for narrow ones) owns a tile of rows of one (sequence, KV head) and a split of
 // the keys, walked in chunks of 32 absolute positions. A page's keys for one KV head are one
 // contiguous piece of memory and so are its values, so a chunk reaches shared memory as a
 // few bulk asynchronous copies (cp.async.bulk, completion counted on an mbarrier) issued by
@@ -18,8 +18,9 @@
 //   * "wide" tiles (64 rows, prompt portions): each warp has 16 rows of its own and every
 //     warp works on every chunk, two chunks per softmax update, so a chunk is fetched once
 //     for 64 rows (four stages a block);
-//   * "narrow" tiles (at most 16 rows, decode tokens): all four warps hold the same rows,
-//     each streams every fourth chunk through a two-stage pipeline of its own, and their
+//   * "narrow" tiles (at most 16 rows, decode tokens): all eight warps hold the same rows,
+//     each streams every eighth chunk through a stage of its own (its block-table entries read
+//     ahead into shared memory), and their
 //     partial results are combined in shared memory.
 // Every wait on an mbarrier is bounded: after SPIN_LIMIT polls the kernel sets
 // MX_STATUS_WAIT_TIMEOUT in the step's status word and goes on, so it always ends.
@@ -37,11 +38,14 @@
 
 namespace {
 
-constexpr int MMA_WARPS = 4;
+constexpr int MMA_WARPS = 4;        // wide tiles: 16 rows each
 constexpr int MMA_THREADS = MMA_WARPS * 32;
+constexpr int NARROW_WARPS = 8;     // narrow tiles: all warps hold the same rows and share the chunks
+constexpr int NARROW_THREADS = NARROW_WARPS * 32;
 constexpr int CHUNK = 32;
 constexpr int WIDE_STAGES = 4;      // chunks in flight per block (two pairs), wide tiles
-constexpr int NARROW_STAGES = 2;    // chunks in flight per warp, narrow tiles
+constexpr int NARROW_STAGES = 1;    // chunks in flight per warp, narrow tiles
+constexpr int NARROW_TABLE = 256;   // block-table entries a warp of a narrow tile reads ahead
 constexpr int SPIN_LIMIT = 1 << 22;
 
 struct MmaAttnParams {
@@ -125,7 +129,7 @@ __device__ __forceinline__ void issue_chunk(const MmaAttnParams& p, __nv_bfloat1
                                             __nv_bfloat16* vs, unsigned long long* bar, int c0, int lo,
                                             int hi, const int* bt, const __nv_bfloat16* kbase,
                                             const __nv_bfloat16* vbase, size_t page_stride, int who,
-                                            int n_who) {
+                                            int n_who, const int* cached = nullptr) {
     const int ps = p.page_size;
     const int pages = CHUNK >> p.page_shift;
     const unsigned tile_bytes = (unsigned)(ps * HD * sizeof(__nv_bfloat16));
@@ -138,7 +142,8 @@ __device__ __forceinline__ void issue_chunk(const MmaAttnParams& p, __nv_bfloat1
             const int key0 = c0 + pg * ps;
             if (key0 <= hi && key0 + ps - 1 >= lo) {
                 const int lp = key0 >> p.page_shift;
-                const long long page = lp < p.bt_stride ? bt[lp] : -1;
+                // `cached`: this chunk's block-table entries, read ahead into shared memory
+                const long long page = cached != nullptr ? cached[pg] : (lp < p.bt_stride ? bt[lp] : -1);
                 if (page >= 0 && page < p.n_pages) {
                     page_of[pg] = page;
                     total += 2 * tile_bytes;
@@ -173,16 +178,17 @@ struct One { static constexpr int value = 1; };
 struct Two { static constexpr int value = 2; };
 
 template <int HD, bool NARROW>
-__global__ void __launch_bounds__(MMA_THREADS, NARROW ? 1 : 3)
+__global__ void __launch_bounds__(NARROW ? NARROW_THREADS : MMA_THREADS, NARROW ? 1 : 3)
 attention_mma_kernel(const MmaAttnParams p) {
     constexpr int KB = HD / 32;                 // 32-wide blocks of the head dim
     constexpr int NB = HD / 8;                  // 8-wide output column blocks
     constexpr int STAGE_ELEMS = 2 * CHUNK * HD; // keys then values
     constexpr int TILE_ROWS = NARROW ? 16 : 16 * MMA_WARPS;
-    constexpr int N_STAGES = NARROW ? NARROW_STAGES * MMA_WARPS : WIDE_STAGES;
+    constexpr int N_STAGES = NARROW ? NARROW_STAGES * NARROW_WARPS : WIDE_STAGES;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     __nv_bfloat16* stages = reinterpret_cast<__nv_bfloat16*>(smem_raw);
     __shared__ __align__(8) unsigned long long bars[N_STAGES];
+    __shared__ int narrow_table[NARROW ? NARROW_WARPS : 1][NARROW ? NARROW_TABLE : 1];
 
     pdl_trigger();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -400,32 +406,49 @@ attention_mma_kernel(const MmaAttnParams p) {
         }
     };
     if (NARROW) {
-        // ---- each warp streams chunks c_begin + warp, + 4, ... through two stages of its own
+        // ---- each warp streams chunks c_begin + warp, + 8, ... through a stage of its own: with eight
+        // warps a block has eight chunks in flight, and a warp fetches its next chunk when it is done with
+        // the one before (more warps hide the copies' latency better than deeper per-warp pipelines did)
         __nv_bfloat16* my_stages = stages + (size_t)warp * NARROW_STAGES * STAGE_ELEMS;
         unsigned long long* my_bars = bars + warp * NARROW_STAGES;
         const int my_first = c_begin + warp;
-        const int my_count = my_first < c_end ? (c_end - my_first + MMA_WARPS - 1) / MMA_WARPS : 0;
+        const int my_count = my_first < c_end ? (c_end - my_first + NARROW_WARPS - 1) / NARROW_WARPS : 0;
+        // The block-table entries of this warp's chunks, read once and together: a lookup in front of
+        // every chunk's copies would put a round trip to L2 into each turn of the loop.
+        const int pages = CHUNK >> p.page_shift;
+        int* my_table = narrow_table[warp];
+        const int n_cached = min(my_count * pages, NARROW_TABLE);
+        for (int e = lane; e < n_cached; e += 32) {
+            const int lp = (my_first + NARROW_WARPS * (e / pages)) * pages + e % pages;
+            my_table[e] = lp < p.bt_stride ? bt[lp] : -1;
+        }
+        __syncwarp();
+        auto cached_for = [&](int i) -> const int* { return (i + 1) * pages <= n_cached ? my_table + i * pages : nullptr; };
         if (my_count > 0)
             issue_chunk<HD>(p, my_stages, my_stages + CHUNK * HD, &my_bars[0], my_first * CHUNK, lo_tile,
-                            hi_tile, bt, kbase, vbase, page_stride, lane, 32);
+                            hi_tile, bt, kbase, vbase, page_stride, lane, 32, cached_for(0));
         for (int i = 0; i < my_count; ++i) {
             const int st = i % NARROW_STAGES;
-            if (i + 1 < my_count) {
+            if (NARROW_STAGES > 1 && i + 1 < my_count) {
                 const int nx = (i + 1) % NARROW_STAGES;
                 __nv_bfloat16* ks = my_stages + (size_t)nx * STAGE_ELEMS;
-                issue_chunk<HD>(p, ks, ks + CHUNK * HD, &my_bars[nx], (my_first + MMA_WARPS * (i + 1)) * CHUNK,
-                                lo_tile, hi_tile, bt, kbase, vbase, page_stride, lane, 32);
+                issue_chunk<HD>(p, ks, ks + CHUNK * HD, &my_bars[nx], (my_first + NARROW_WARPS * (i + 1)) * CHUNK,
+                                lo_tile, hi_tile, bt, kbase, vbase, page_stride, lane, 32, cached_for(i + 1));
             }
             __syncwarp();
             mbar_wait(&my_bars[st], (unsigned)((i / NARROW_STAGES) & 1), p.status);
             const __nv_bfloat16* ks = my_stages + (size_t)st * STAGE_ELEMS;
-            compute(One{}, ks, ks + CHUNK * HD, ks, ks + CHUNK * HD, (my_first + MMA_WARPS * i) * CHUNK);
+            compute(One{}, ks, ks + CHUNK * HD, ks, ks + CHUNK * HD, (my_first + NARROW_WARPS * i) * CHUNK);
             __syncwarp();                         // the stage may be refilled from here on
+            if (NARROW_STAGES == 1 && i + 1 < my_count)
+                issue_chunk<HD>(p, my_stages, my_stages + CHUNK * HD, &my_bars[0],
+                                (my_first + NARROW_WARPS * (i + 1)) * CHUNK, lo_tile, hi_tile, bt, kbase, vbase,
+                                page_stride, lane, 32, cached_for(i + 1));
         }
-        // ---- combine the four warps' partial results through shared memory (stages are free)
+        // ---- combine the warps' partial results through shared memory (stages are free)
         __syncthreads();
         float* red_o = reinterpret_cast<float*>(smem_raw);              // [warp][16][HD]
-        float* red_ml = red_o + MMA_WARPS * 16 * HD;                    // [warp][16][2]
+        float* red_ml = red_o + NARROW_WARPS * 16 * HD;                    // [warp][16][2]
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
             const int r = g + 8 * i;
@@ -443,14 +466,14 @@ attention_mma_kernel(const MmaAttnParams p) {
         __syncthreads();
         const int rows_here = min(16, n_rows - tile_row0);
         const float ln2 = 0.6931471805599453f;
-        for (int idx = tid; idx < rows_here * HD; idx += MMA_THREADS) {
+        for (int idx = tid; idx < rows_here * HD; idx += NARROW_THREADS) {
             const int r = idx / HD, d = idx - r * HD;
             float m = -INFINITY;
 #pragma unroll
-            for (int w = 0; w < MMA_WARPS; ++w) m = fmaxf(m, red_ml[((size_t)w * 16 + r) * 2]);
+            for (int w = 0; w < NARROW_WARPS; ++w) m = fmaxf(m, red_ml[((size_t)w * 16 + r) * 2]);
             float l = 0.f, acc = 0.f;
 #pragma unroll
-            for (int w = 0; w < MMA_WARPS; ++w) {
+            for (int w = 0; w < NARROW_WARPS; ++w) {
                 const float mw = red_ml[((size_t)w * 16 + r) * 2];
                 const float wgt = (mw == -INFINITY) ? 0.f : exp2f(mw - m);
                 l += red_ml[((size_t)w * 16 + r) * 2 + 1] * wgt;
@@ -541,9 +564,9 @@ attention_mma_kernel(const MmaAttnParams p) {
 template <int HD, bool NARROW>
 int launch_mma(const MmaAttnParams& p, cudaStream_t stream) {
     const size_t stage_bytes = 2 * (size_t)CHUNK * HD * sizeof(__nv_bfloat16);
-    size_t smem = stage_bytes * (NARROW ? NARROW_STAGES * MMA_WARPS : WIDE_STAGES);
+    size_t smem = stage_bytes * (NARROW ? NARROW_STAGES * NARROW_WARPS : WIDE_STAGES);
     if (NARROW) {
-        const size_t reduce = (size_t)MMA_WARPS * 16 * (HD + 2) * sizeof(float);
+        const size_t reduce = (size_t)NARROW_WARPS * 16 * (HD + 2) * sizeof(float);
         if (reduce > smem) smem = reduce;
     }
     if (smem + 1024 > 48 * 1024) {   // the kernel also has a little static shared memory
@@ -552,7 +575,7 @@ int launch_mma(const MmaAttnParams& p, cudaStream_t stream) {
         if (e != cudaSuccess) MX_REFUSE("attention: cannot reserve %zu bytes of shared memory", smem);
     }
     dim3 grid(p.n_tiles, p.n_kv_heads, p.n_splits);
-    mx_launch_chained(attention_mma_kernel<HD, NARROW>, grid, dim3(MMA_THREADS), smem, stream, p);
+    mx_launch_chained(attention_mma_kernel<HD, NARROW>, grid, dim3(NARROW ? NARROW_THREADS : MMA_THREADS), smem, stream, p);
     return mx_launch_status();
 }
 
@@ -562,7 +585,7 @@ extern "C" int mx_attention_merge_bf16(const float* part_o, const float* part_ml
                                        int out_stride, int n_tokens, int n_heads, int head_dim,
                                        int n_splits, cudaStream_t stream);
 
-// `narrow` != 0: every tile has at most 16 rows (decode tokens); the four warps of a block
+// `narrow` != 0: every tile has at most 16 rows (decode tokens); the eight warps of a block
 // share them and take the key chunks in turn. Otherwise tiles are 64 rows, 16 per warp.
 extern "C" int mx_paged_attention_mma(const void* q, int q_stride, const void* cache,
                                       long long n_pages, int page_size, const int* block_tables,

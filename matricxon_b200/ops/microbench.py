@@ -55,6 +55,7 @@ def main() -> None:
         'c_proj skinny residual': lambda: k.gemm_skinny(mid, wpr, bo, x, x, 2),
     }
     if M > 16:
+        del ops['qkv skinny + rotation + cache write (one kernel; not in the total)']
         ops['qkv skinny'] = lambda: linear(h, wqkv, bq, 0, out=qkv)
         ops['o skinny residual'] = lambda: linear(attn, wo, bo, 2, residual=x, out=x)
         ops['c_fc skinny gelu'] = lambda: linear(h, wfc, bfc, 1, out=mid)
