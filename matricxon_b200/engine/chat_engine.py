@@ -81,8 +81,14 @@ class ChatEngine:
             if samples:
                 samplers.append(planned.sequence.sampler)
         logits = self.core.runner.run(entries)
-        sampled = self.sampler.sample(logits, samplers) if samplers else []
-        self.core.runner.check_status()
+        if samplers:
+            # the status word travels with the step; reading the sampled ids synchronises for both
+            self.core.runner.enqueue_status_read()
+            sampled = self.sampler.sample(logits, samplers)
+            self.core.runner.check_status(synchronised=True)
+        else:
+            sampled = []
+            self.core.runner.check_status()
         produced = self.scheduler.step_done(plan, sampled)
         self.steps += 1
         return [(seq.request_id, token, seq.status == FINISHED) for seq, token in produced]

@@ -173,6 +173,9 @@ class StepRunner:
         self.use_graphs = use_graphs and getattr(model, "capturable", False)
         self.max_graph_batch = max_graph_batch
         self._graphs: dict[int, tuple] = {}
+        self._status_host: torch.Tensor | None = None
+        self._graph_host_arrays: dict[int, tuple] = {}       # bucket -> (pinned tensor, its numpy view)
+        self._arange = np.arange(max_graph_batch + 2, dtype=np.int32)
         self._graph_pool = None
         self.last_upload_bytes = 0        # host-to-device bytes of the latest step's metadata
         self.launches_per_step = 0        # this library's kernel launches in the latest step
@@ -414,10 +417,86 @@ class StepRunner:
             graph.replay()
             return static_logits[:len(entries)]
         graph, static_logits, buffers, launches, _ctx = record
-        self.build(entries, pad_to=bucket, table_widths=widths, buffers=buffers)
+        self._refill_decode(entries, bucket, widths, buffers)
         graph.replay()
         self.launches_per_step = launches
         return static_logits[:len(entries)]
+
+    def _refill_decode(self, entries: list[StepEntry], bucket: int, widths: list[int], buffers) -> None:
+        """The metadata of a captured decode step, written straight into the graph's pinned buffer
+        and copied once: what ``build(entries, pad_to=bucket, ...)`` lays out, without the
+        intermediate arrays and the context object a replay does not need."""
+        self._validate(entries)
+        cache = self.cache
+        reserved: list[str] = []
+        try:
+            for entry in entries:
+                if not cache.has_request(entry.request_id):
+                    raise StepError(f"request {entry.request_id!r} is not live in the cache")
+                cache.reserve(entry.request_id, 1)
+                reserved.append(entry.request_id)
+        except Exception:
+            for request_id in reserved:
+                cache.cancel_reservation(request_id)
+            raise
+        host, dev, done = buffers
+        n, page_size, n_groups = len(entries), cache.page_size, len(cache.rules)
+        lengths = [bucket, bucket, bucket, bucket + 1, bucket, bucket, bucket]
+        for g in range(n_groups):
+            lengths.extend((bucket, bucket * widths[g]))
+        offsets, total = [], 0
+        for length in lengths:
+            offsets.append(total)
+            total += (length + 3) & ~3
+        arrays = self._graph_host_arrays.get(bucket)
+        if arrays is None or arrays[0] is not host:
+            arrays = (host, host.numpy())
+            self._graph_host_arrays[bucket] = arrays
+        flat = arrays[1]
+        records = [cache.requests[entry.request_id] for entry in entries]
+        lens = [record.length for record in records]
+        done.synchronize()                           # the pinned buffer may still be in flight
+        try:
+            def part(i: int) -> np.ndarray:
+                return flat[offsets[i]:offsets[i] + lengths[i]]
+
+            token_ids, positions, tok_seq, cu_q = part(0), part(1), part(2), part(3)
+            token_ids[:n] = [entry.tokens[0] for entry in entries]
+            token_ids[n:] = 0
+            positions[:n] = lens
+            positions[n:] = 0
+            tok_seq[:n] = self._arange[:n]
+            tok_seq[n:] = -1
+            cu_q[:n + 1] = self._arange[:n + 1]
+            cu_q[n + 1:] = n
+            context_lens, state_slots, logit_rows = part(4), part(5), part(6)
+            context_lens[:n] = lens
+            context_lens[n:] = 0
+            state_slots[:n] = [record.state_slot for record in records]
+            state_slots[n:] = 0
+            logit_rows[:] = self._arange[:bucket]
+            for g in range(n_groups):
+                width = widths[g]
+                slots_g, tables_g = part(7 + 2 * g), part(8 + 2 * g).reshape(bucket, width)
+                for s, (entry, record, start) in enumerate(zip(entries, records, lens)):
+                    table = record.tables[g]
+                    if len(table) > width:
+                        raise StepError(f"request {entry.request_id!r} holds {len(table)} pages, "
+                                        f"the fixed table width is {width}")
+                    page = table[start // page_size]
+                    if page < 0:
+                        raise StepError(f"position {start} of {entry.request_id!r} has no page")
+                    slots_g[s] = page * page_size + start % page_size
+                    tables_g[s] = cache.table_row(entry.request_id, g, width)
+                slots_g[n:] = -1
+                tables_g[n:] = -1
+        except Exception:
+            for request_id in reserved:
+                cache.cancel_reservation(request_id)
+            raise
+        dev[:total].copy_(host[:total], non_blocking=True)
+        done.record()
+        self.last_upload_bytes = total * 4
 
     def run(self, entries: list[StepEntry]) -> torch.Tensor | None:
         """Runs the entries as one batch and commits them. Returns float32 logits
@@ -448,10 +527,21 @@ class StepRunner:
         self.tokens_run += len(entries) if bucket is not None else sum(len(e.tokens) for e in entries)
         return logits
 
-    def check_status(self) -> None:
-        """Reads the device status word (a synchronisation) and raises if a kernel met a
-        bad index during the steps since the last check."""
-        word = int(self.status.item())
+    def enqueue_status_read(self) -> None:
+        """Queues a copy of the status word to pinned host memory on the current stream; after the
+        next synchronisation of that stream ``check_status(synchronised=True)`` reads it for free."""
+        if self._status_host is None:
+            self._status_host = torch.zeros(1, dtype=torch.int32, pin_memory=True)
+        self._status_host.copy_(self.status, non_blocking=True)
+
+    def check_status(self, synchronised: bool = False) -> None:
+        """Raises if a kernel met a bad index during the steps since the last check. Reads the
+        device status word (a synchronisation), or, with ``synchronised``, the copy that
+        ``enqueue_status_read`` queued before the caller's last synchronisation."""
+        if synchronised and self._status_host is not None:
+            word = int(self._status_host[0])
+        else:
+            word = int(self.status.item())
         if word != 0:
             self.status.zero_()
             raise StepError(f"a kernel reported: {kernels.describe_status(word)}")
