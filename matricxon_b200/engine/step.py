@@ -174,6 +174,7 @@ class StepRunner:
         self.max_graph_batch = max_graph_batch
         self._graphs: dict[int, tuple] = {}
         self._status_host: torch.Tensor | None = None
+        self.chained_launch_rows = int(os.environ.get("MATRICXON_CHAINED_ROWS", "2"))
         self._graph_host_arrays: dict[int, tuple] = {}       # bucket -> (pinned tensor, its numpy view)
         self._arange = np.arange(max_graph_batch + 2, dtype=np.int32)
         self._graph_pool = None
@@ -401,14 +402,19 @@ class StepRunner:
             ctx = self.build(entries, pad_to=bucket, table_widths=widths, buffers=buffers)
             ctx.max_kv_len = self.graph_table_width * self.cache.page_size
             launches_before = kernels.launch_count
-            self._forward(ctx, decode_rows=True)                 # warm-up, outside the capture
-            self.launches_per_step = kernels.launch_count - launches_before
-            torch.cuda.synchronize()
-            graph = torch.cuda.CUDAGraph()
-            ctx.capturing = True
-            with torch.cuda.graph(graph, pool=self._graph_pool):
-                static_logits = self._forward(ctx, decode_rows=True)
-            ctx.capturing = False
+            # steps of very few rows gain from kernels that start while their predecessor drains
+            kernels.set_chained_launch(bucket <= self.chained_launch_rows)
+            try:
+                self._forward(ctx, decode_rows=True)             # warm-up, outside the capture
+                self.launches_per_step = kernels.launch_count - launches_before
+                torch.cuda.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                ctx.capturing = True
+                with torch.cuda.graph(graph, pool=self._graph_pool):
+                    static_logits = self._forward(ctx, decode_rows=True)
+                ctx.capturing = False
+            finally:
+                kernels.set_chained_launch(False)
             if self._graph_pool is None:
                 self._graph_pool = graph.pool()
             # the captured kernels hold raw pointers into everything the context owns (the tile

@@ -51,6 +51,12 @@ def _need(t: torch.Tensor, name: str, dtype: torch.dtype | None = None, contiguo
         raise KernelLibraryError(f"{name} must be contiguous")
 
 
+def set_chained_launch(on: bool) -> None:
+    """Programmatic dependent launch for the kernels launched from here on (decode kernels only
+    take part): what a graph captures stays with the graph."""
+    library().mx_set_chained_launch(1 if on else 0)
+
+
 def describe_status(word: int) -> str:
     return "; ".join(text for bit, text in STATUS_BITS.items() if word & bit) or "no error"
 
