@@ -48,7 +48,9 @@ def gguf_name(name: str) -> str:
 
 
 def main() -> None:
-    reference = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py <path to a checkout of nesmind/matricxon>")
+    reference = sys.argv[1]
     sys.path.insert(0, reference)
     from app.architectures.starcoder2 import Starcoder2Architecture
     from app.gguf.constants import GGMLQuantizationType
