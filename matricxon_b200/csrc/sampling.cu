@@ -113,8 +113,8 @@ sample_kernel(const float* __restrict__ logits, long long row_stride, int vocab,
               const float* __restrict__ temperature, const int* __restrict__ top_k,
               const float* __restrict__ top_p, const float* __restrict__ repeat_penalty,
               const float* __restrict__ uniform, const int* __restrict__ penalty_offsets,
-              const int* __restrict__ penalty_ids, float* __restrict__ work_all,
-              int* __restrict__ out_tokens) {
+              const int* __restrict__ penalty_ids, const int* __restrict__ pending_ids,
+              float* __restrict__ work_all, int* __restrict__ out_tokens) {
     __shared__ ArgMax arg_scratch[SAMPLE_THREADS / 32];
     __shared__ unsigned long long sum_scratch[SAMPLE_THREADS / 32];
     __shared__ unsigned long long hist[256];
@@ -134,6 +134,19 @@ sample_kernel(const float* __restrict__ logits, long long row_stride, int vocab,
         for (int j = penalty_offsets[row] + tid; j < penalty_offsets[row + 1]; j += SAMPLE_THREADS) {
             const int id = penalty_ids[j];                   // ids are distinct within a row
             if (id >= 0 && id < vocab) {
+                const float x = work[id];
+                work[id] = x > 0.f ? x / penalty : x * penalty;
+            }
+        }
+        if (pending_ids != nullptr) {
+            // One more generated id that the host does not know yet (the token the step before this one
+            // chose, still on the device): penalised like the others unless it is one of them already.
+            const int id = pending_ids[row];
+            int listed = 0;
+            for (int j = penalty_offsets[row] + tid; j < penalty_offsets[row + 1]; j += SAMPLE_THREADS)
+                listed |= penalty_ids[j] == id;
+            listed = __syncthreads_or(listed);      // also orders the penalties above before the one below
+            if (!listed && tid == 0 && id >= 0 && id < vocab) {
                 const float x = work[id];
                 work[id] = x > 0.f ? x / penalty : x * penalty;
             }
@@ -227,14 +240,14 @@ extern "C" long long mx_sample_scratch_bytes(int n_rows, int vocab) {
 extern "C" int mx_sample(const float* logits, long long row_stride, int n_rows, int vocab,
                          const float* temperature, const int* top_k, const float* top_p,
                          const float* repeat_penalty, const float* uniform,
-                         const int* penalty_offsets, const int* penalty_ids, float* work,
-                         int* out_tokens, cudaStream_t stream) {
+                         const int* penalty_offsets, const int* penalty_ids, const int* pending_ids,
+                         float* work, int* out_tokens, cudaStream_t stream) {
     if (n_rows <= 0) return MX_OK;
     if (vocab <= 0) MX_REFUSE("sample: vocabulary of %d", vocab);
     if (work == nullptr) MX_REFUSE("sample: needs a work buffer of rows x vocab floats");
     sample_kernel<<<n_rows, SAMPLE_THREADS, 0, stream>>>(logits, row_stride, vocab, temperature,
                                                          top_k, top_p, repeat_penalty, uniform,
-                                                         penalty_offsets, penalty_ids, work,
-                                                         out_tokens);
+                                                         penalty_offsets, penalty_ids, pending_ids,
+                                                         work, out_tokens);
     return mx_launch_status();
 }

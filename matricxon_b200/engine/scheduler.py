@@ -81,12 +81,13 @@ class PlannedEntry:
     sequence: Sequence
     start: int
     count: int
+    ahead: bool = False        # planned before the token of the step before it was known (``plan_ahead``)
 
     @property
     def samples(self) -> bool:
         """The portion reaches the request's last token: its logits choose the next one."""
         seq = self.sequence
-        return self.start + self.count == len(seq.prompt) + len(seq.outputs)
+        return self.ahead or self.start + self.count == len(seq.prompt) + len(seq.outputs)
 
 
 @dataclass
@@ -239,6 +240,28 @@ class Scheduler:
             self._plan(plan, sequence, count, planned)
             budget -= count
         return plan
+
+    def plan_ahead(self, plan: StepPlan) -> StepPlan | None:
+        """The step after ``plan``, planned while ``plan`` still runs and its tokens are unknown: the
+        same requests, one token further. Only when that is certainly what ``schedule`` would
+        decide once the tokens are known, up to requests that stop at a token of ``plan`` (their
+        rows of the step ahead are wasted and dropped by ``step_done``): every running request
+        decodes in ``plan``, nobody waits, nobody reaches its length limit with the token of
+        ``plan``, and every request can have one more slot of cache. Otherwise None."""
+        if self.waiting or plan.preempted or not plan.entries or len(plan.entries) != len(self.running):
+            return None
+        ahead = StepPlan()
+        planned = [0] * len(self.cache.pools)
+        for entry in plan.entries:
+            sequence = entry.sequence
+            if (entry.count != 1 or not entry.samples or sequence.status != RUNNING
+                    or len(sequence.outputs) + 2 > sequence.max_new_tokens
+                    or not self._fits(sequence, 1, planned)):
+                return None
+            for group, n in enumerate(self.cache.pages_needed(sequence.request_id, 1)):
+                planned[group] += n
+            ahead.entries.append(PlannedEntry(sequence, entry.start + 1, 1, ahead=True))
+        return ahead
 
     # ------------------------------------------------------------------ after a step
     def _finish(self, sequence: Sequence, reason: str) -> None:

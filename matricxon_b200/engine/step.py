@@ -390,8 +390,10 @@ class StepRunner:
             bucket *= 2
         return bucket
 
-    def _run_graph(self, entries: list[StepEntry], bucket: int) -> torch.Tensor:
+    def _run_graph(self, entries: list[StepEntry], bucket: int, token_feed: torch.Tensor | None = None) -> torch.Tensor:
         record = self._graphs.get(bucket)
+        if token_feed is not None and record is None:
+            raise StepError("a step fed from the device needs the graph of its batch size to exist already")
         widths = [self.graph_table_width] * len(self.cache.rules)
         if record is None:
             layout_ints = 16 * bucket + 64 + sum(bucket * (w + 4) for w in widths)
@@ -424,6 +426,10 @@ class StepRunner:
             return static_logits[:len(entries)]
         graph, static_logits, buffers, launches, _ctx = record
         self._refill_decode(entries, bucket, widths, buffers)
+        if token_feed is not None:
+            # the rows' token ids are still on the device (the step before has not been read yet): they
+            # go over the placeholders that the metadata copy just wrote (ids are the buffer's first array)
+            buffers[1][:len(entries)].copy_(token_feed[:len(entries)], non_blocking=True)
         graph.replay()
         self.launches_per_step = launches
         return static_logits[:len(entries)]
@@ -504,17 +510,28 @@ class StepRunner:
         done.record()
         self.last_upload_bytes = total * 4
 
-    def run(self, entries: list[StepEntry]) -> torch.Tensor | None:
+    def can_feed_from_device(self, entries: list[StepEntry]) -> bool:
+        """Whether ``run(entries, token_feed=...)`` is possible: a pure decode step whose graph exists."""
+        bucket = self._graph_bucket(entries)
+        return bucket is not None and bucket in self._graphs
+
+    def run(self, entries: list[StepEntry], token_feed: torch.Tensor | None = None) -> torch.Tensor | None:
         """Runs the entries as one batch and commits them. Returns float32 logits
         [wanted, vocab] in the order of the entries and of each ``want``, or None.
+
+        ``token_feed`` (int32 on the device, one id per entry, in entry order) replaces the
+        entries' single tokens: for a decode step launched before the ids that the step before
+        it chose have reached the host. Only steps that replay an existing graph take it.
 
         A step of single decode tokens replays a CUDA graph captured for its batch size
         (rounded up to a power of two with padding rows); the logits it returns live in the
         graph's memory and are overwritten by the next step of that size."""
         bucket = self._graph_bucket(entries)
         try:
+            if token_feed is not None and bucket is None:
+                raise StepError("only a captured decode step can take its token ids from the device")
             if bucket is not None:
-                logits = self._run_graph(entries, bucket)
+                logits = self._run_graph(entries, bucket, token_feed)
             else:
                 ctx = self.build(entries)
                 launches_before = kernels.launch_count

@@ -21,7 +21,7 @@ from ctypes import c_int, c_longlong, c_void_p
 
 register_signature("mx_sample_scratch_bytes", [c_int, c_int], c_longlong)
 register_signature("mx_sample", [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p,
-                                 c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                 c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                  c_void_p], c_int)
 
 _MASK = (1 << 64) - 1
@@ -46,8 +46,9 @@ class RequestSampler:
         self._distinct: set[int] = set()
         self._distinct_list: list[int] = []
 
-    def next_uniform(self) -> float:
-        return uniform_for(self.seed, len(self.generated))
+    def next_uniform(self, ahead: int = 0) -> float:
+        """The uniform of the next token, or of the one ``ahead`` tokens after it."""
+        return uniform_for(self.seed, len(self.generated) + ahead)
 
     def accept(self, token: int) -> None:
         self.generated.append(token)
@@ -72,10 +73,30 @@ class BatchSampler:
         self._params_dev: torch.Tensor | None = None
         self._params_done: torch.cuda.Event | None = None
         self.last_upload_bytes = 0
+        self._results: list = [None, None]
+        self._device_ids: list = [None, None]
+        self._turn = 0
 
     def sample(self, logits: torch.Tensor, samplers: list[RequestSampler]) -> list[int]:
         """``logits`` float32 [rows, vocab] on the device; returns the chosen ids (a device
         synchronisation) without recording them: callers ``accept`` what they keep."""
+        return self.read(self.launch(logits, samplers))
+
+    def read(self, handle) -> list[int]:
+        """Waits for the ids of ``launch`` (only for the work queued up to that launch)."""
+        host, done, n = handle
+        done.synchronize()
+        return host[:n].tolist()
+
+    def launch(self, logits: torch.Tensor, samplers: list[RequestSampler],
+               pending: torch.Tensor | None = None):
+        """Queues the sampling kernel and the copy of its ids to pinned host memory; returns a
+        handle for ``read``. The ids also stay on the device in ``handle_ids(handle)``.
+
+        ``pending`` (int32 [rows], on the device) holds, per row, a token that the request has
+        generated but the host has not seen yet (the step before is still in flight): the
+        kernel counts it among the request's generated ids for the repeat penalty, and the
+        uniforms are the ones that follow it."""
         n = len(samplers)
         if logits.shape[0] != n or logits.shape[1] != self.vocab_size:
             raise ValueError(f"logits {tuple(logits.shape)} for {n} requests, vocab {self.vocab_size}")
@@ -94,7 +115,8 @@ class BatchSampler:
         as_float[0:n] = [s.config.temperature for s in samplers]
         as_float[n:2 * n] = [s.config.top_p for s in samplers]
         as_float[2 * n:3 * n] = [s.config.repeat_penalty for s in samplers]
-        as_float[3 * n:4 * n] = [s.next_uniform() for s in samplers]
+        ahead = 0 if pending is None else 1
+        as_float[3 * n:4 * n] = [s.next_uniform(ahead) for s in samplers]
         packed[4 * n:5 * n] = [s.config.top_k for s in samplers]
         packed[5 * n:6 * n + 1] = offsets
         if ids:
@@ -113,10 +135,27 @@ class BatchSampler:
             self._work = torch.empty(max(n, 8) * self.vocab_size, dtype=torch.float32, device=self.device)
         out = torch.empty(n, dtype=torch.int32, device=self.device)
         base = self._params_dev.data_ptr()
+        if pending is not None and (pending.dtype != torch.int32 or not pending.is_cuda or pending.numel() < n):
+            raise ValueError("pending ids must be int32 on the device, one per row")
         check(library().mx_sample(
             logits.data_ptr(), logits.stride(0), n, self.vocab_size,
             base, base + 4 * (4 * n), base + 4 * n, base + 4 * (2 * n), base + 4 * (3 * n),
-            base + 4 * (5 * n), base + 4 * (6 * n + 1), self._work.data_ptr(), out.data_ptr(),
+            base + 4 * (5 * n), base + 4 * (6 * n + 1),
+            pending.data_ptr() if pending is not None else None, self._work.data_ptr(), out.data_ptr(),
             torch.cuda.current_stream().cuda_stream), "sample")
         kernels._launched()
-        return out.cpu().tolist()
+        # two result buffers in turn: a step may be launched before the ids of the one before are read
+        self._turn ^= 1
+        slot = self._results[self._turn]
+        if slot is None or slot[0].numel() < n:
+            slot = (torch.empty(max(n, 64), dtype=torch.int32, pin_memory=True), torch.cuda.Event())
+            self._results[self._turn] = slot
+        host, done = slot
+        host[:n].copy_(out, non_blocking=True)
+        done.record()
+        self._device_ids[self._turn] = out
+        return host, done, n
+
+    def device_ids(self) -> torch.Tensor:
+        """The ids of the latest ``launch`` on the device (int32 [rows])."""
+        return self._device_ids[self._turn]

@@ -30,7 +30,7 @@ def sample_rows(logits, configs, generated=None, uniforms=None):
         for token in (generated[i] if generated else []):
             s.accept(token)
         if uniforms is not None:
-            s.next_uniform = (lambda u: (lambda: u))(uniforms[i])
+            s.next_uniform = (lambda u: (lambda ahead=0: u))(uniforms[i])
         samplers.append(s)
     batch = BatchSampler(DEV, logits.shape[1])
     return batch.sample(logits.to(DEV), samplers), samplers
@@ -208,6 +208,57 @@ def test_eos_and_cancel():
     engine.step()
     assert engine.cancel(rid) and engine.result(rid).finish_reason == "cancelled"
     assert not engine.has_unfinished() and engine.core.cache.free_pages() == [16]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_steps_queued_ahead_change_no_token(dtype):
+    """While everybody decodes, the engine queues the next step before it has read the ids of
+    the running one (they are fed on the device, and the repeat penalty counts them there). The
+    tokens must equal those of deciding step by step: with a repeat penalty, seeded
+    temperature sampling and different lengths; in 32-bit (where another batch around a request
+    cannot move a token) also with a stop token in the middle of one request, a request that
+    arrives while others decode, and one that is cancelled."""
+    from matricxon_b200 import ChatEngine, SamplingConfig
+
+    model, cfg, _ = build("B", dtype)
+    eventful = dtype == "float32"
+    prompts = [random_ids(n, cfg["vocab"], seed=90 + n) for n in (5, 17, 33, 12)]
+    configs = [
+        SamplingConfig(temperature=0.0, repeat_penalty=1.6, num_predict=40, num_ctx=256),
+        SamplingConfig(temperature=0.9, top_k=30, top_p=0.9, repeat_penalty=1.3, num_predict=25, num_ctx=256, seed=3),
+        SamplingConfig(temperature=1.2, top_k=0, top_p=1.0, repeat_penalty=1.0, num_predict=48, num_ctx=256, seed=4),
+        SamplingConfig(temperature=0.5, top_k=8, top_p=1.0, repeat_penalty=1.2, num_predict=30, num_ctx=256, seed=5),
+    ]
+
+    def run(look_ahead, eos=()):
+        engine = ChatEngine(model, eos_token_ids=eos, max_cache_tokens=1024, max_active=4, max_model_len=256,
+                            look_ahead=look_ahead)
+        ids = [engine.add_request(p, c) for p, c in zip(prompts[:3], configs[:3])]
+        if not eventful:
+            ids.append(engine.add_request(prompts[3], configs[3]))
+        while engine.has_unfinished():
+            engine.step()
+            if eventful and engine.steps == 9:
+                ids.append(engine.add_request(prompts[3], configs[3]))
+            if eventful and engine.steps == 20:
+                engine.cancel(ids[2])
+        assert engine.core.cache.free_pages() == [p.num_pages for p in engine.core.cache.pools]
+        results = [engine.result(i) for i in ids]
+        return engine, [(r.token_ids, r.finish_reason) for r in results]
+
+    plain, expected = run(False)
+    assert plain.steps_ahead == 0
+    ahead, got = run(True)
+    assert ahead.steps_ahead >= 20 and got == expected
+    assert len(set(expected[0][0])) > 8                       # the penalty did shape the greedy request
+    if eventful:
+        assert expected[2][1] == "cancelled" and len(expected[2][0]) < 48
+        # a stop token that the first request meets in mid-flight: its row of the step ahead is dropped
+        stop = expected[0][0][15]
+        _, expected_stop = run(False, eos={stop})
+        ahead, got_stop = run(True, eos={stop})
+        assert got_stop == expected_stop and ahead.steps_ahead >= 10
+        assert got_stop[0][1] == "stop" and len(got_stop[0][0]) <= 16
 
 
 def test_command_line(tmp_path):

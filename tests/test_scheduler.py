@@ -218,3 +218,71 @@ def test_uniform_stream_is_a_function_of_seed_and_index():
     assert a != [uniform_for(8, i) for i in range(50)]
     assert all(0.0 <= u < 1.0 for u in a) and len(set(a)) == 50
     assert abs(sum(uniform_for(1, i) for i in range(4000)) / 4000 - 0.5) < 0.02
+
+
+def test_plan_ahead_only_when_the_next_step_is_certain():
+    """The step planned before the tokens of the running one are known is the same requests one
+    token further, and is refused whenever ``schedule`` might decide otherwise."""
+    cache, scheduler = make(pages=6, page_size=4)
+    scheduler.add("a", [1, 2, 3], sampling(num_predict=4))
+    scheduler.add("b", [4, 5, 6, 7, 8], sampling(num_predict=9))
+    plan = scheduler.schedule()
+    assert scheduler.plan_ahead(plan) is None                  # prompts, not single decoded tokens
+    for entry in plan.entries:
+        cache.reserve(entry.sequence.request_id, entry.count)
+        cache.commit(entry.sequence.request_id, entry.count)
+    scheduler.step_done(plan, [9, 9])
+    plan = scheduler.schedule()                                # a and b decode
+    assert [(e.sequence.request_id, e.start, e.count) for e in plan.entries] == [("a", 3, 1), ("b", 5, 1)]
+    for entry in plan.entries:
+        cache.reserve(entry.sequence.request_id, entry.count)
+        cache.commit(entry.sequence.request_id, entry.count)
+    ahead = scheduler.plan_ahead(plan)
+    assert [(e.sequence.request_id, e.start, e.count, e.ahead, e.samples) for e in ahead.entries] == [
+        ("a", 4, 1, True, True), ("b", 6, 1, True, True)]
+    scheduler.add("c", [1, 2], sampling())
+    assert scheduler.plan_ahead(plan) is None                  # somebody waits: the next step may admit them
+    scheduler.cancel("c")
+    assert scheduler.plan_ahead(plan) is not None
+    # the step ahead runs; a stops at a token of the step before it: its row of the step ahead is dropped
+    for entry in ahead.entries:
+        cache.reserve(entry.sequence.request_id, entry.count)
+        cache.commit(entry.sequence.request_id, entry.count)
+    scheduler.eos_token_ids = {33}
+    assert [(s.request_id, t) for s, t in scheduler.step_done(plan, [33, 10])] == [("a", 33), ("b", 10)]
+    assert scheduler.finished["a"].finish_reason == "stop"
+    assert [(s.request_id, t) for s, t in scheduler.step_done(ahead, [11, 12])] == [("b", 12)]
+    cache.check_invariants()
+    assert scheduler.running[0].outputs == [9, 10, 12]
+    # b alone: 3 + 5 tokens hold 2 pages; length limits and the pool's end refuse the step ahead
+    while scheduler.has_work():
+        plan = scheduler.schedule()
+        for entry in plan.entries:
+            cache.reserve(entry.sequence.request_id, entry.count)
+            cache.commit(entry.sequence.request_id, entry.count)
+        sequence = plan.entries[0].sequence
+        ahead = scheduler.plan_ahead(plan)
+        assert (ahead is not None) == (len(sequence.outputs) + 2 <= 9)
+        scheduler.step_done(plan, [7])
+    assert cache.free_pages() == [6]
+
+
+def test_plan_ahead_refused_when_no_page_is_left_for_it():
+    cache, scheduler = make(pages=3, page_size=4)
+    scheduler.add("a", [1, 2, 3], sampling(num_predict=5))
+    scheduler.add("b", [4, 5, 6], sampling(num_predict=5))
+    run_step(cache, scheduler)                                 # both prompts: a page each
+    plan = scheduler.schedule()                                # the fourth token of each: same pages
+    assert [(e.start, e.count) for e in plan.entries] == [(3, 1), (3, 1)]
+    for entry in plan.entries:
+        cache.reserve(entry.sequence.request_id, 1)
+        cache.commit(entry.sequence.request_id, 1)
+    assert cache.free_pages() == [1]
+    assert scheduler.plan_ahead(plan) is None                  # both would need a new page, one is left
+    scheduler.cancel("b")
+    assert scheduler.plan_ahead(plan) is None                  # the running step holds a request that left
+    scheduler.step_done(plan, [5, 5])
+    plan = scheduler.schedule()
+    cache.reserve("a", 1)
+    cache.commit("a", 1)
+    assert scheduler.plan_ahead(plan) is not None
