@@ -26,6 +26,8 @@
 // 2 out(f32) = residual + v; 3 out(f32) = v, with v = acc + bias.
 #include <cuda.h>
 
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace {
@@ -326,6 +328,49 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
 }
 
+// One thread's row of a 128 x bn accumulator (tensor memory lane = row, columns from tbase): brought
+// out 16 columns at a time, the epilogue applied, stored. Shared by the kernels with 256-row tiles.
+__device__ __forceinline__ void drain_accumulator_row(unsigned tbase, int row, int n0, int bn,
+                                                      const float* __restrict__ bias, const float* residual,
+                                                      void* out, int ldo, int M, int N, int mode) {
+    const size_t row_base = (size_t)row * ldo;
+    for (int c0 = 0; c0 < bn; c0 += 64) {
+        // the residual of up to four pieces first, so that the loads are in flight together
+        const bool fast = mode == 2 && row < M && n0 + c0 + 64 <= N && c0 + 64 <= bn &&
+                          ((row_base + n0 + c0) % 4) == 0;
+        float4 res[16];
+        if (fast) {
+            const float4* src = reinterpret_cast<const float4*>(residual + row_base + n0 + c0);
+#pragma unroll
+            for (int q = 0; q < 16; ++q) res[q] = src[q];
+        }
+#pragma unroll
+        for (int piece = 0; piece < 4; ++piece) {
+            const int c = c0 + 16 * piece;
+            if (c >= bn) break;
+            unsigned r[16];
+            tmem_load16(tbase + (unsigned)c, r);
+            if (row >= M || n0 + c >= N) continue;
+            if (fast) {
+                float* o = reinterpret_cast<float*>(out) + row_base + n0 + c;
+#pragma unroll
+                for (int j = 0; j < 16; j += 4) {
+                    float4 v = res[4 * piece + j / 4];
+                    v.x += __uint_as_float(r[j]); v.y += __uint_as_float(r[j + 1]);
+                    v.z += __uint_as_float(r[j + 2]); v.w += __uint_as_float(r[j + 3]);
+                    if (bias) {
+                        v.x += bias[n0 + c + j]; v.y += bias[n0 + c + j + 1];
+                        v.z += bias[n0 + c + j + 2]; v.w += bias[n0 + c + j + 3];
+                    }
+                    *reinterpret_cast<float4*>(o + j) = v;
+                }
+            } else {
+                store_piece(r, bias, residual, out, row_base + n0 + c, n0 + c, N, mode);
+            }
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------------------------
 // The same product with 256-row tiles: two 128 x BN accumulators share every weight tile, so a
 // block takes in (256 + BN) x 128 bytes per 64-wide slice of K for twice the arithmetic. What a
@@ -347,6 +392,17 @@ struct TcWideShared {
     unsigned tmem_base;
 };
 
+// Tuning aid (compile with -DTC_PROFILE): cycles that the roles of the 256-row kernel spend in
+// each of their phases, summed over all blocks; read with mx_gemm_tcgen05_marks.
+#ifdef TC_PROFILE
+__device__ unsigned long long g_tc_marks[16];
+#define TC_CLOCK(var) long long var; asm volatile("mov.u64 %0, %%clock64;\n" : "=l"(var))
+#define TC_ADD(i, from, to) atomicAdd(&g_tc_marks[i], (unsigned long long)((to) - (from)))
+#else
+#define TC_CLOCK(var)
+#define TC_ADD(i, from, to)
+#endif
+
 __global__ void __launch_bounds__(TCW_THREADS)
 gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                          const float* __restrict__ bias, const float* residual, void* out, int ldo, int M,
@@ -362,6 +418,7 @@ gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     const int k_slices = (K + TC_BK - 1) / TC_BK;
     const int tiles_m = (M + TCW_BM - 1) / TCW_BM, tiles_n = (N + bn - 1) / bn;
     const int n_tiles = tiles_m * tiles_n;
+    TC_CLOCK(t_start);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < TCW_STAGES; ++s) {
@@ -383,6 +440,8 @@ gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
     const unsigned tmem_base = sh.tmem_base;
+    TC_CLOCK(t_setup);
+    if (threadIdx.x == 0) { TC_ADD(0, t_start, t_setup); }
 
     if (warp == 8) {
         // ---------------- producer
@@ -393,7 +452,10 @@ gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                 const int m0 = (tile % tiles_m) * TCW_BM, n0 = (tile / tiles_m) * bn;
                 for (int ks = 0; ks < k_slices; ++ks, ++it) {
                     const int s = it % TCW_STAGES;
+                    TC_CLOCK(p0);
                     alive = tc_mbar_wait(&sh.empty[s], ((unsigned)(it / TCW_STAGES) & 1) ^ 1, status);
+                    TC_CLOCK(p1);
+                    TC_ADD(1, p0, p1);
                     if (!alive) break;
                     tc_mbar_expect_tx(&sh.full[s], stage_bytes);
                     unsigned char* a_tile = tiles + (size_t)s * stage_bytes;
@@ -411,12 +473,19 @@ gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             int it = 0, local = 0;
             bool alive = true;
             for (int tile = blockIdx.x; tile < n_tiles && alive; tile += gridDim.x, ++local) {
+                TC_CLOCK(m0);
                 alive = tc_mbar_wait(&sh.acc_empty, ((unsigned)local & 1) ^ 1, status);
+                TC_CLOCK(m1);
+                TC_ADD(2, m0, m1);
                 if (!alive) break;
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
                 for (int ks = 0; ks < k_slices; ++ks, ++it) {
                     const int s = it % TCW_STAGES;
+                    TC_CLOCK(m2);
                     alive = tc_mbar_wait(&sh.full[s], (unsigned)(it / TCW_STAGES) & 1, status);
+                    TC_CLOCK(m3);
+                    TC_ADD(3, m2, m3);
+                    if (ks == 0) { TC_ADD(4, m2, m3); }
                     if (!alive) break;
                     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
                     const unsigned char* a_tile = tiles + (size_t)s * stage_bytes;
@@ -431,6 +500,8 @@ gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                     umma_commit(&sh.empty[s]);
                 }
                 if (alive) umma_commit(&sh.acc_full);
+                TC_CLOCK(m4);
+                TC_ADD(5, m1, m4);
             }
         }
     } else {
@@ -438,58 +509,478 @@ gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         const int half = warp >> 2, quarter = warp & 3;
         int local = 0;
         for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++local) {
+            TC_CLOCK(e0);
             if (!tc_mbar_wait(&sh.acc_full, (unsigned)local & 1, status)) break;
+            TC_CLOCK(e1);
+            if (threadIdx.x == 0) { TC_ADD(6, e0, e1); }
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
             const int m0 = (tile % tiles_m) * TCW_BM, n0 = (tile / tiles_m) * bn;
             const int row = m0 + 128 * half + 32 * quarter + lane;
             const unsigned tbase = tmem_base + (unsigned)half * 256 + ((unsigned)(32 * quarter) << 16);
-            const size_t row_base = (size_t)row * ldo;
-            for (int c0 = 0; c0 < bn; c0 += 64) {
-                // the residual of up to four pieces first, so that the loads are in flight together
-                const bool fast = mode == 2 && row < M && n0 + c0 + 64 <= N && c0 + 64 <= bn &&
-                                  ((row_base + n0 + c0) % 4) == 0;
-                float4 res[16];
-                if (fast) {
-                    const float4* src = reinterpret_cast<const float4*>(residual + row_base + n0 + c0);
-#pragma unroll
-                    for (int q = 0; q < 16; ++q) res[q] = src[q];
-                }
-#pragma unroll
-                for (int piece = 0; piece < 4; ++piece) {
-                    const int c = c0 + 16 * piece;
-                    if (c >= bn) break;
-                    unsigned r[16];
-                    tmem_load16(tbase + (unsigned)c, r);
-                    if (row >= M || n0 + c >= N) continue;
-                    if (fast) {
-                        float* o = reinterpret_cast<float*>(out) + row_base + n0 + c;
-#pragma unroll
-                        for (int j = 0; j < 16; j += 4) {
-                            float4 v = res[4 * piece + j / 4];
-                            v.x += __uint_as_float(r[j]); v.y += __uint_as_float(r[j + 1]);
-                            v.z += __uint_as_float(r[j + 2]); v.w += __uint_as_float(r[j + 3]);
-                            if (bias) {
-                                v.x += bias[n0 + c + j]; v.y += bias[n0 + c + j + 1];
-                                v.z += bias[n0 + c + j + 2]; v.w += bias[n0 + c + j + 3];
-                            }
-                            *reinterpret_cast<float4*>(o + j) = v;
-                        }
-                    } else {
-                        store_piece(r, bias, residual, out, row_base + n0 + c, n0 + c, N, mode);
-                    }
-                }
-            }
+            drain_accumulator_row(tbase, row, n0, bn, bias, residual, out, ldo, M, N, mode);
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
             __syncwarp();
+            TC_CLOCK(e2);
+            if (threadIdx.x == 0) { TC_ADD(7, e1, e2); }
             if (lane == 0) tc_mbar_arrive(&sh.acc_empty);
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
     __syncthreads();
+    TC_CLOCK(t_end);
+    if (threadIdx.x == 0) { TC_ADD(8, t_start, t_end); TC_ADD(9, 0, 1); }
     if (warp == 9) {
         __syncwarp();
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(512)
+                     : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// The same product on pairs of SMs (tcgen05 cta_group::2): a cluster of two blocks works on one
+// 512 x BN tile. Every MMA spans both SMs (M = 256: rows 0-127 accumulate in the first block's tensor
+// memory, rows 128-255 in the second's) and reads its B operand half from each block's shared
+// memory, so a block takes in 256 rows of A and only BN / 2 rows of W per slice of K: 48 KB where
+// the 256-row kernel needs 64 KB for the same arithmetic, and four stages fit where it has three.
+// That is what this product is bound by: bytes in flight per SM over the latency of a load.
+//   Both blocks run a producer (warp 8): it waits for its own "empty" barrier and issues its loads,
+//   which all announce their bytes on the FIRST block's "full" barrier (the cta_group::2 form of
+//   the TMA load may signal the peer's barrier). The first block's warp 9 issues the MMAs for the
+//   pair and commits them to the "empty" / "accumulator ready" barriers of both blocks (commit with
+//   a block mask). Warps 0-7 of each block drain that block's 128 lanes of both accumulators and
+//   arrive on the first block's "accumulator free" barrier (16 arrivals).
+// No load here is a multicast: each block fetches what it holds.
+constexpr int TCP_ROWS = 512;          // rows of a pair's tile
+constexpr int TCP_PARTS = 1;            // epilogue warps per 32 accumulator lanes and accumulator: they take 32-column pieces in turn
+constexpr int TCP_EPI_WARPS = 8 * TCP_PARTS;
+constexpr int TCP_STAGES = TCP_PARTS == 1 ? 4 : 3;
+constexpr int TCP_THREADS = 32 * (TCP_EPI_WARPS + 2);    // then the producer warp and the MMA warp
+constexpr int TCP_STAGING = TCP_EPI_WARPS * 4096;        // a 4 KB stage for each epilogue warp
+
+struct TcPairShared {
+    unsigned long long full[TCP_STAGES];       // used in the first block of the pair
+    unsigned long long empty[TCP_STAGES];      // in each block
+    unsigned long long acc_full;               // in each block
+    unsigned long long acc_empty;              // used in the first block: 16 arrivals
+    unsigned tmem_base;
+};
+
+__device__ __forceinline__ unsigned cluster_block_rank() {
+    unsigned r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
+    return r;
+}
+// The address of the same shared-memory object in block `rank` of the cluster.
+__device__ __forceinline__ unsigned shared_of_rank(const void* ptr, unsigned rank) {
+    unsigned d;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(d) : "r"(smem_u32(ptr)), "r"(rank));
+    return d;
+}
+__device__ __forceinline__ void cluster_barrier() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n"
+                 "barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+// Tile load into this block's shared memory whose bytes are counted by a barrier that may live in
+// the other block of the pair (`bar_cluster_addr`: a shared::cluster address).
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, int x, int y,
+                                                 unsigned bar_cluster_addr) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::"r"(
+            smem_u32(smem_dst)),
+        "l"(map), "r"(x), "r"(y), "r"(bar_cluster_addr)
+        : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(unsigned tmem_acc, unsigned long long adesc,
+                                               unsigned long long bdesc, unsigned idesc, bool accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_acc),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"((unsigned)accumulate)
+        : "memory");
+}
+// Arrives, once the MMAs issued so far are done, on the barrier at this offset in both blocks.
+__device__ __forceinline__ void umma_commit_pair(unsigned long long* bar) {
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;\n" ::"r"(
+            smem_u32(bar)),
+        "h"((unsigned short)3)
+        : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(unsigned bar_cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];\n" ::"r"(bar_cluster_addr) : "memory");
+}
+
+__device__ __forceinline__ void tmem_load32_nowait(unsigned taddr, unsigned* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]),
+          "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]),
+          "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+// Shared-memory accesses by 32-bit shared address: the stage pointers are computed through integers, so the
+// compiler would otherwise use generic loads and stores (slower, and ordered against the global ones).
+__device__ __forceinline__ void sts128(unsigned addr, unsigned a, unsigned b, unsigned c, unsigned d) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ float4 lds128(unsigned addr) {
+    float4 v;
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];\n" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr) : "memory");
+    return v;
+}
+
+// out[0..3] += v without reading it here: the addition happens at the memory side, nothing waits for it.
+__device__ __forceinline__ void red_add_f32x4(float* dst, float4 v) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};\n" ::"l"(dst), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
+                 : "memory");
+}
+
+// A warp's 32 rows of one accumulator leave through shared memory so that global memory sees whole
+// row pieces: 32 columns at a time, every lane writes its own row's 32 floats into the warp's stage
+// in a 16-byte XOR swizzle; then eight lanes together carry one row piece out (four rows per
+// instruction), and that is where bias, residual, GELU and the rounding are applied: a lane keeps one
+// 4-column unit for all rows. The loop hardly waits on global memory: the bias unit of a piece is
+// fetched one piece ahead (the first by `EpilogueLane::prefetch` while the products still run), the
+// residual pieces set out together with the accumulator piece they belong to, and for bfloat16
+// outputs the next accumulator piece is on its way from tensor memory while one is carried out. No bank conflicts either way. `stage`: 4 KB of this warp.
+// `free_bar`: arrived on by lane 0 as soon as the warp has read its last accumulator value.
+template <bool F32>
+struct EpilogueLane {
+    float4 bias4;             // this lane's bias unit of the coming 32-column piece
+    float4 res[8];            // residual pieces of the coming 32-column piece (rows 4 i + lane / 8)
+    int sub_row, unit_out;
+
+    __device__ __forceinline__ void load_bias(const float* __restrict__ bias, int n0, int c, int bn, int N) {
+        const int col_out = n0 + c + unit_out * 4;
+        bias4 = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (bias != nullptr && c + unit_out * 4 < bn && col_out < N) {
+            if (col_out + 4 <= N) bias4 = __ldg(reinterpret_cast<const float4*>(bias + col_out));
+            else {
+                bias4.x = bias[col_out];
+                if (col_out + 1 < N) bias4.y = bias[col_out + 1];
+                if (col_out + 2 < N) bias4.z = bias[col_out + 2];
+            }
+        }
+    }
+
+    __device__ __forceinline__ void load_residual(const float* residual, int ldo, int row0, int n0, int c,
+                                                  int bn, int M, int N) {
+        const int col_out = n0 + c + unit_out * 4;
+        const bool live = c < bn && unit_out * 4 < bn - c && col_out < N;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int row = row0 + 4 * i + sub_row;
+            res[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (live && row < M) {
+                const float* src = residual + (size_t)row * ldo + col_out;
+                if (col_out + 4 <= N) res[i] = *reinterpret_cast<const float4*>(src);
+                else {
+                    res[i].x = src[0];
+                    if (col_out + 1 < N) res[i].y = src[1];
+                    if (col_out + 2 < N) res[i].z = src[2];
+                }
+            }
+        }
+    }
+
+    // Before the accumulator is waited for: what the first piece needs from global memory.
+    __device__ __forceinline__ void prefetch(const float* __restrict__ bias, const float* residual,
+                                             const void* out, int ldo, int row0, int n0, int c_first, int bn,
+                                             int M, int N, int mode, int lane) {
+        sub_row = lane >> 3;
+        unit_out = lane & 7;
+        load_bias(bias, n0, c_first, bn, N);
+        if constexpr (F32) {
+            if (mode == 2 && residual != out) load_residual(residual, ldo, row0, n0, c_first, bn, M, N);
+        }
+    }
+
+    // One 32-column piece: `cur` holds (after the wait) the accumulator values of columns c .. c + 31 of
+    // this lane's row; the next piece is sent for into `nxt`.
+    __device__ __forceinline__ void piece(unsigned* cur, unsigned* nxt, int c, unsigned tbase, int row0, int n0,
+                                          int bn, const float* __restrict__ bias, const float* residual,
+                                          void* out, int ldo, int M, int N, int mode, unsigned char* stage,
+                                          int lane, unsigned free_bar) {
+        const int c_next = c + 32 * TCP_PARTS;
+        const bool last = c_next >= bn;
+        TC_CLOCK(d0);
+        asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+        TC_CLOCK(d1);
+        if (threadIdx.x == 0) { TC_ADD(10, d0, d1); }
+        const float4 b4 = bias4;
+        if (!last) load_bias(bias, n0, c_next, bn, N);
+        if constexpr (!F32) {
+            if (!last) tmem_load32_nowait(tbase + (unsigned)c_next, nxt);
+        }
+        if (last) {                                      // the accumulator may be overwritten from here on
+            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(free_bar);
+        }
+        if (row0 < M && n0 + c < N) {
+            const unsigned stage_addr = smem_u32(stage);
+            const unsigned row_dst = stage_addr + lane * 128;
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+                sts128(row_dst + ((u ^ (lane & 7)) << 4), cur[4 * u], cur[4 * u + 1], cur[4 * u + 2], cur[4 * u + 3]);
+            __syncwarp();
+            TC_CLOCK(d2);
+            if (threadIdx.x == 0) { TC_ADD(11, d1, d2); }
+            if (row0 + 32 <= M && n0 + c + 32 <= N && c + 32 <= bn) {
+                // every row and column of the piece exists: no predicates, vector accesses only
+                float4 v[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int local_row = 4 * i + sub_row;
+                    v[i] = lds128(stage_addr + local_row * 128 + ((unit_out ^ (local_row & 7)) << 4));
+                }
+                const size_t first = (size_t)(row0 + sub_row) * ldo + n0 + c + unit_out * 4;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    v[i].x += b4.x; v[i].y += b4.y; v[i].z += b4.z; v[i].w += b4.w;
+                    if constexpr (F32) {
+                        float* dst = reinterpret_cast<float*>(out) + first + (size_t)(4 * i) * ldo;
+                        if (mode == 2 && residual == out) {
+                            red_add_f32x4(dst, v[i]);    // the residual stream is updated in place
+                        } else {
+                            if (mode == 2) {
+                                v[i].x += res[i].x; v[i].y += res[i].y; v[i].z += res[i].z; v[i].w += res[i].w;
+                            }
+                            *reinterpret_cast<float4*>(dst) = v[i];
+                        }
+                    } else {
+                        if (mode == 1) {
+                            v[i].x = gelu_tanh_fast(v[i].x); v[i].y = gelu_tanh_fast(v[i].y);
+                            v[i].z = gelu_tanh_fast(v[i].z); v[i].w = gelu_tanh_fast(v[i].w);
+                        }
+                        __nv_bfloat162 lo = __floats2bfloat162_rn(v[i].x, v[i].y);
+                        __nv_bfloat162 hi = __floats2bfloat162_rn(v[i].z, v[i].w);
+                        uint2 pk;
+                        pk.x = *reinterpret_cast<unsigned*>(&lo); pk.y = *reinterpret_cast<unsigned*>(&hi);
+                        *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(out) + first +
+                                                  (size_t)(4 * i) * ldo) = pk;
+                    }
+                }
+            } else {
+                edge_piece(stage_addr, c, row0, n0, bn, b4, residual, out, ldo, M, N, mode);
+            }
+            __syncwarp();                                // the stage is free for the next piece
+            TC_CLOCK(d3);
+            if (threadIdx.x == 0) { TC_ADD(12, d2, d3); }
+        }
+        if constexpr (F32) {                             // the next piece and its residual set out together
+            if (!last) {
+                tmem_load32_nowait(tbase + (unsigned)c_next, nxt);
+                if (mode == 2 && residual != out) load_residual(residual, ldo, row0, n0, c_next, bn, M, N);
+            }
+        }
+    }
+
+    // The same way out for a piece that crosses the last row, the last column or the tile's width: every
+    // access is checked. Kept out of line so that the loop over interior pieces stays short.
+    __device__ __noinline__ void edge_piece(unsigned stage_addr, int c, int row0, int n0, int bn, float4 b4,
+                                            const float* residual, void* out, int ldo, int M, int N, int mode) {
+        const int width = min(32, bn - c);
+        const int col_out = n0 + c + unit_out * 4;
+        if (unit_out * 4 >= width || col_out >= N) return;
+        for (int i = 0; i < 8; ++i) {
+            const int local_row = 4 * i + sub_row, row = row0 + local_row;
+            if (row >= M) continue;
+            const float4 staged = lds128(stage_addr + local_row * 128 + ((unit_out ^ (local_row & 7)) << 4));
+            float v[4] = {staged.x + b4.x, staged.y + b4.y, staged.z + b4.z, staged.w + b4.w};
+            for (int e = 0; e < 4 && col_out + e < N; ++e) {
+                const size_t at = (size_t)row * ldo + col_out + e;
+                if constexpr (F32) {
+                    reinterpret_cast<float*>(out)[at] = (mode == 2 ? residual[at] : 0.f) + v[e];
+                } else {
+                    reinterpret_cast<__nv_bfloat16*>(out)[at] =
+                        __float2bfloat16_rn(mode == 1 ? gelu_tanh_fast(v[e]) : v[e]);
+                }
+            }
+        }
+    }
+
+    // The loops over pieces stay rolled: code that runs once per tile is fetched cold, and a block
+    // spends longer waiting for the instructions of an unrolled epilogue than executing them.
+    __device__ __forceinline__ void drain(unsigned tbase, int row0, int n0, int c_first, int bn,
+                                          const float* __restrict__ bias, const float* residual, void* out,
+                                          int ldo, int M, int N, int mode, unsigned char* stage, int lane,
+                                          unsigned free_bar) {
+        constexpr int STEP = 32 * TCP_PARTS;
+        if (c_first >= bn) {                             // a tile too narrow to give this warp a piece
+            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(free_bar);
+            return;
+        }
+        unsigned ra[32];
+        tmem_load32_nowait(tbase + (unsigned)c_first, ra);
+        if constexpr (F32) {                             // one register buffer: the others hold the residual
+#pragma unroll 1
+            for (int c = c_first; c < bn; c += STEP)
+                piece(ra, ra, c, tbase, row0, n0, bn, bias, residual, out, ldo, M, N, mode, stage, lane, free_bar);
+        } else {
+            unsigned rb[32];
+#pragma unroll 1
+            for (int c = c_first; c < bn; c += 2 * STEP) {
+                piece(ra, rb, c, tbase, row0, n0, bn, bias, residual, out, ldo, M, N, mode, stage, lane, free_bar);
+                if (c + STEP < bn)
+                    piece(rb, ra, c + STEP, tbase, row0, n0, bn, bias, residual, out, ldo, M, N, mode, stage, lane,
+                          free_bar);
+            }
+        }
+    }
+};
+
+
+template <bool F32>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TCP_THREADS)
+gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                         const float* __restrict__ bias, const float* residual, void* out, int ldo, int M,
+                         int N, int K, int bn, int mode, int* status) {
+    const unsigned a_bytes = 256 * TC_BK * 2, w_bytes = (unsigned)(bn / 2) * TC_BK * 2;
+    const unsigned stage_bytes = a_bytes + w_bytes;
+    extern __shared__ unsigned char tc_smem_raw[];
+    unsigned char* tiles = reinterpret_cast<unsigned char*>(
+        (reinterpret_cast<uintptr_t>(tc_smem_raw) + 1023) & ~(uintptr_t)1023);
+    __shared__ TcPairShared sh;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const unsigned rank = cluster_block_rank();
+    const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+    const int k_slices = (K + TC_BK - 1) / TC_BK;
+    const int tiles_m = (M + TCP_ROWS - 1) / TCP_ROWS, tiles_n = (N + bn - 1) / bn;
+    const int n_tiles = tiles_m * tiles_n;
+    TC_CLOCK(t_start);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < TCP_STAGES; ++s) {
+            tc_mbar_init(&sh.full[s], 1);
+            tc_mbar_init(&sh.empty[s], 1);
+        }
+        tc_mbar_init(&sh.acc_full, 1);
+        tc_mbar_init(&sh.acc_empty, 2 * TCP_EPI_WARPS);  // the epilogue warps of both blocks
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == TCP_EPI_WARPS + 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(
+                         smem_u32(&sh.tmem_base)),
+                     "r"(512)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;\n" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    cluster_barrier();                                  // the peer's barriers exist from here on
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    const unsigned tmem_base = sh.tmem_base;
+    TC_CLOCK(t_setup);
+    if (threadIdx.x == 0) { TC_ADD(0, t_start, t_setup); }
+
+    if (warp == TCP_EPI_WARPS) {
+        // ---------------- producer (in both blocks)
+        if (lane == 0) {
+            int it = 0;
+            bool alive = true;
+            for (int tile = pair; tile < n_tiles && alive; tile += n_pairs) {
+                const int m0 = (tile % tiles_m) * TCP_ROWS + 128 * (int)rank;
+                const int n0 = (tile / tiles_m) * bn + (bn / 2) * (int)rank;
+                for (int ks = 0; ks < k_slices; ++ks, ++it) {
+                    const int s = it % TCP_STAGES;
+                    TC_CLOCK(p0);
+                    alive = tc_mbar_wait(&sh.empty[s], ((unsigned)(it / TCP_STAGES) & 1) ^ 1, status);
+                    TC_CLOCK(p1);
+                    if (rank == 0) { TC_ADD(1, p0, p1); }
+                    if (!alive) break;
+                    if (rank == 0) tc_mbar_expect_tx(&sh.full[s], 2 * stage_bytes);
+                    const unsigned bar = shared_of_rank(&sh.full[s], 0);
+                    unsigned char* a_tile = tiles + (size_t)s * stage_bytes;
+                    tma_load_2d_pair(a_tile, &map_a, ks * TC_BK, m0, bar);
+                    tma_load_2d_pair(a_tile + 128 * TC_BK * 2, &map_a, ks * TC_BK, m0 + 256, bar);
+                    tma_load_2d_pair(a_tile + a_bytes, &map_w, ks * TC_BK, n0, bar);
+                }
+            }
+            if (rank == 0)                                // nothing stays in flight (the MMAs read both blocks' stages)
+                for (int j = max(0, it - TCP_STAGES); j < it; ++j)
+                    if (!tc_mbar_wait(&sh.full[j % TCP_STAGES], (unsigned)(j / TCP_STAGES) & 1, status)) break;
+        }
+    } else if (warp == TCP_EPI_WARPS + 1) {
+        // ---------------- MMA issuer of the pair: rows 0-255 of the tile into columns [0, bn), rows
+        // 256-511 into [256, 256 + bn) of both blocks' tensor memory
+        if (lane == 0 && rank == 0) {
+            const unsigned idesc = umma_idesc(256, bn);
+            int it = 0, local = 0;
+            bool alive = true;
+            for (int tile = pair; tile < n_tiles && alive; tile += n_pairs, ++local) {
+                TC_CLOCK(m0);
+                alive = tc_mbar_wait(&sh.acc_empty, ((unsigned)local & 1) ^ 1, status);
+                TC_CLOCK(m1);
+                TC_ADD(2, m0, m1);
+                if (!alive) break;
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                for (int ks = 0; ks < k_slices; ++ks, ++it) {
+                    const int s = it % TCP_STAGES;
+                    TC_CLOCK(m2);
+                    alive = tc_mbar_wait(&sh.full[s], (unsigned)(it / TCP_STAGES) & 1, status);
+                    TC_CLOCK(m3);
+                    TC_ADD(3, m2, m3);
+                    if (ks == 0) { TC_ADD(4, m2, m3); }
+                    if (!alive) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                    const unsigned char* a_tile = tiles + (size_t)s * stage_bytes;
+                    const unsigned long long adesc_lo = umma_desc(a_tile);
+                    const unsigned long long adesc_hi = umma_desc(a_tile + 128 * TC_BK * 2);
+                    const unsigned long long bdesc = umma_desc(a_tile + a_bytes);
+#pragma unroll
+                    for (int k = 0; k < TC_BK / 16; ++k) {
+                        umma_bf16_pair(tmem_base, adesc_lo + 2 * k, bdesc + 2 * k, idesc, (ks | k) != 0);
+                        umma_bf16_pair(tmem_base + 256, adesc_hi + 2 * k, bdesc + 2 * k, idesc, (ks | k) != 0);
+                    }
+                    umma_commit_pair(&sh.empty[s]);
+                }
+                if (alive) umma_commit_pair(&sh.acc_full);
+                TC_CLOCK(m4);
+                TC_ADD(5, m1, m4);
+            }
+        }
+    } else {
+        // ---------------- epilogue: warp w -> accumulator w / 4, lane quarter w % 4 of this block's half
+        const int half = (warp >> 2) & 1, quarter = warp & 3, c_first = 32 * (warp >> 3);
+        const unsigned free_bar = shared_of_rank(&sh.acc_empty, 0);
+        unsigned char* stage = tiles + (size_t)TCP_STAGES * stage_bytes + (size_t)warp * 4096;
+        int local = 0;
+        for (int tile = pair; tile < n_tiles; tile += n_pairs, ++local) {
+            const int m0 = (tile % tiles_m) * TCP_ROWS, n0 = (tile / tiles_m) * bn;
+            const int row0 = m0 + 256 * half + 128 * (int)rank + 32 * quarter;
+            const unsigned tbase = tmem_base + (unsigned)half * 256 + ((unsigned)(32 * quarter) << 16);
+            EpilogueLane<F32> mine;
+            mine.prefetch(bias, residual, out, ldo, row0, n0, c_first, bn, M, N, mode, lane);
+            TC_CLOCK(e0);
+            if (!tc_mbar_wait(&sh.acc_full, (unsigned)local & 1, status)) break;
+            TC_CLOCK(e1);
+            if (threadIdx.x == 0 && rank == 0) { TC_ADD(6, e0, e1); }
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            mine.drain(tbase, row0, n0, c_first, bn, bias, residual, out, ldo, M, N, mode, stage, lane, free_bar);
+            TC_CLOCK(e2);
+            if (threadIdx.x == 0 && rank == 0) { TC_ADD(7, e1, e2); }
+        }
+    }
+    // ---------------- teardown: neither block leaves while the other may still touch its memory
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    cluster_barrier();
+    TC_CLOCK(t_end);
+    if (threadIdx.x == 0 && rank == 0) { TC_ADD(8, t_start, t_end); TC_ADD(9, 0, 1); }
+    if (warp == TCP_EPI_WARPS + 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(512)
                      : "memory");
     }
 }
@@ -552,7 +1043,45 @@ int sm_count() {
     return count;
 }
 
+// How many pairs of SMs the pair kernel can hold at once with its largest tile (0: it cannot run).
+int pair_count() {
+    static int count = -1;
+    if (count < 0) {
+        const size_t most = (size_t)TCP_STAGES * (256 + 128) * TC_BK * 2 + TCP_STAGING + 1024;
+        count = 0;
+        if (cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)most) == cudaSuccess &&
+            cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)most) == cudaSuccess) {
+            cudaLaunchConfig_t config = {};
+            config.gridDim = dim3(2 * sm_count());
+            config.blockDim = dim3(TCP_THREADS);
+            config.dynamicSmemBytes = most;
+            int clusters = 0;
+            if (cudaOccupancyMaxActiveClusters(&clusters, gemm_tcgen05_pair_kernel<true>, &config) == cudaSuccess)
+                count = clusters;
+        }
+        cudaGetLastError();
+    }
+    return count;
+}
+
 }  // namespace
+
+#ifdef TC_PROFILE
+// marks: 0 setup, 1 producer waiting for a free stage, 2 issuer waiting for the accumulator, 3 issuer
+// waiting for operands (4: of which the first slice of a tile), 5 issuer per tile from accumulator free to
+// last commit, 6 epilogue waiting for the accumulator, 7 epilogue draining, 8 whole block, 9 blocks
+extern "C" int mx_gemm_tcgen05_marks(unsigned long long* out, int reset) {
+    cudaDeviceSynchronize();
+    if (out) cudaMemcpyFromSymbol(out, g_tc_marks, sizeof(unsigned long long) * 16);
+    if (reset) {
+        static unsigned long long zeros[16];
+        cudaMemcpyToSymbol(g_tc_marks, zeros, sizeof(zeros));
+    }
+    return MX_OK;
+}
+#endif
 
 extern "C" int mx_gemm_tcgen05(const void* A, const void* W, const float* bias, const float* residual,
                                void* out, int out_dtype, int M, int N, int K, int lda, int ldw, int ldo,
@@ -574,16 +1103,22 @@ extern "C" int mx_gemm_tcgen05(const void* A, const void* W, const float* bias, 
     // tile's epilogue under the next tile's products, which is worth more (c_fc at 2,048 rows: 132 us
     // against 148 us)
     const long long tiles_128 = (long long)((M + 127) / 128) * ((N + 255) / 256);
-    const bool wide = M > 256 && tiles_128 < 4LL * n_sm;
-    const int tile_rows = wide ? TCW_BM : TC_BM;
-    const int stages = wide ? TCW_STAGES : TC_STAGES;
-    const int bn = pick_tile_width(M, N, n_sm, tile_rows);
-    CUtensorMap map_a, map_w;
-    int rc = make_map(&map_a, A, M, K, lda, tile_rows);
-    if (rc != MX_OK) return rc;
-    rc = make_map(&map_w, W, N, K, ldw, bn);
-    if (rc != MX_OK) return rc;
-    const size_t smem = (size_t)stages * (tile_rows + bn) * TC_BK * 2 + 1024;
+    bool wide = M > 256 && tiles_128 < 4LL * n_sm;
+    // pairs of SMs on 512-row tiles once there are rows for them: less operand traffic per SM
+    const int n_pairs = pair_count();
+    // (its epilogue moves 16-byte units: rows of the output, the residual and the bias must allow that)
+    const bool f32_out = mode >= 2;
+    const bool pair_can = n_pairs > 0 && (ldo * (f32_out ? 4 : 2)) % (f32_out ? 16 : 8) == 0 &&
+                          reinterpret_cast<uintptr_t>(out) % 16 == 0 &&
+                          (mode != 2 || reinterpret_cast<uintptr_t>(residual) % 16 == 0) &&
+                          (bias == nullptr || reinterpret_cast<uintptr_t>(bias) % 16 == 0);
+    bool pair = M > 512 && pair_can;
+    if (const char* force = getenv("MATRICXON_GEMM_TILES")) {       // for measurements: 128, 256 or 512 rows
+        const int rows = atoi(force);
+        if (rows == 128) { wide = false; pair = false; }
+        if (rows == 256) { wide = true; pair = false; }
+        if (rows == 512) pair = pair_can;
+    }
     static bool attribute_set = false;
     if (!attribute_set) {
         const size_t most = (size_t)TC_STAGES * (TC_BM + 256) * TC_BK * 2 + 1024;
@@ -596,6 +1131,33 @@ extern "C" int mx_gemm_tcgen05(const void* A, const void* W, const float* bias, 
         if (e != cudaSuccess) MX_REFUSE("tcgen05 gemm: cannot reserve %zu bytes of shared memory", most_wide);
         attribute_set = true;
     }
+    if (pair) {
+        const int bn = pick_tile_width(M, N, n_pairs, TCP_ROWS);
+        CUtensorMap map_a, map_w;
+        int rc = make_map(&map_a, A, M, K, lda, 128);
+        if (rc != MX_OK) return rc;
+        rc = make_map(&map_w, W, N, K, ldw, bn / 2);
+        if (rc != MX_OK) return rc;
+        const size_t smem = (size_t)TCP_STAGES * (256 + bn / 2) * TC_BK * 2 + TCP_STAGING + 1024;
+        const long long tiles = (long long)((M + TCP_ROWS - 1) / TCP_ROWS) * ((N + bn - 1) / bn);
+        const int grid = 2 * (int)(tiles < n_pairs ? tiles : n_pairs);
+        if (f32_out)
+            gemm_tcgen05_pair_kernel<true><<<grid, TCP_THREADS, smem, stream>>>(map_a, map_w, bias, residual, out,
+                                                                                ldo, M, N, K, bn, mode, status);
+        else
+            gemm_tcgen05_pair_kernel<false><<<grid, TCP_THREADS, smem, stream>>>(map_a, map_w, bias, residual, out,
+                                                                                 ldo, M, N, K, bn, mode, status);
+        return mx_launch_status();
+    }
+    const int tile_rows = wide ? TCW_BM : TC_BM;
+    const int stages = wide ? TCW_STAGES : TC_STAGES;
+    const int bn = pick_tile_width(M, N, n_sm, tile_rows);
+    CUtensorMap map_a, map_w;
+    int rc = make_map(&map_a, A, M, K, lda, tile_rows);
+    if (rc != MX_OK) return rc;
+    rc = make_map(&map_w, W, N, K, ldw, bn);
+    if (rc != MX_OK) return rc;
+    const size_t smem = (size_t)stages * (tile_rows + bn) * TC_BK * 2 + 1024;
     const long long tiles = (long long)((M + tile_rows - 1) / tile_rows) * ((N + bn - 1) / bn);
     const int grid = (int)(tiles < n_sm ? tiles : n_sm);
     if (wide)

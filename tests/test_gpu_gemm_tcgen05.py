@@ -39,6 +39,36 @@ def test_tcgen05_gemm_all_epilogues(m, n, k_dim):
     assert status.item() == 0
 
 
+@pytest.mark.parametrize("rows", [128, 256, 512])
+@pytest.mark.parametrize("m,n,k_dim", [(513, 264, 64), (700, 3000, 256), (1537, 3072, 1024), (1100, 1000, 96)])
+def test_tcgen05_gemm_every_tile_height(rows, m, n, k_dim, monkeypatch):
+    """The three kernels (128-row tiles, 256-row tiles, 512-row tiles on pairs of SMs) on the same
+    products: each is forced in turn; edges in M, N and K, an N that is no multiple of 16."""
+    from matricxon_b200.ops import kernels as k
+
+    monkeypatch.setenv("MATRICXON_GEMM_TILES", str(rows))
+    torch.manual_seed(rows + m)
+    a = torch.randn(m, k_dim, device=DEV).bfloat16()
+    w = (torch.randn(n, k_dim, device=DEV) / math.sqrt(k_dim)).bfloat16()
+    bias = torch.randn(n, device=DEV)
+    residual = torch.randn(m, n, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    acc = (a.double() @ w.double().T + bias.double()).cpu()
+    out = torch.full((m + 1, n), float("nan"), dtype=torch.bfloat16, device=DEV)
+    k.gemm_tcgen05(a, w, bias, None, out[:m], k.EPILOGUE_GELU, status)
+    assert torch.allclose(out[:m].double().cpu(), plain_gelu_tanh(acc), atol=2e-2, rtol=2e-2)
+    assert torch.isnan(out[m]).all()                                   # nothing written past the last row
+    out32 = residual.clone()
+    k.gemm_tcgen05(a, w, bias, out32, out32, k.EPILOGUE_RESIDUAL, status)          # in place
+    assert torch.allclose(out32.double().cpu(), acc + residual.double().cpu(), atol=2e-3, rtol=1e-4)
+    apart = torch.full((m, n), float("nan"), device=DEV)
+    k.gemm_tcgen05(a, w, bias, residual, apart, k.EPILOGUE_RESIDUAL, status)       # residual elsewhere
+    assert torch.allclose(apart.double().cpu(), acc + residual.double().cpu(), atol=2e-3, rtol=1e-4)
+    k.gemm_tcgen05(a, w, None, None, apart, k.EPILOGUE_F32, status)
+    assert torch.allclose(apart.double().cpu(), acc - bias.double().cpu(), atol=2e-3, rtol=1e-4)
+    assert status.item() == 0
+
+
 def test_tcgen05_gemm_strided_rows_and_same_result_for_a_row_in_any_batch():
     from matricxon_b200.ops import kernels as k
 
