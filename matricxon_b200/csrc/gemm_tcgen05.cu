@@ -22,6 +22,9 @@
 // the status word and the role moves on, so the block always reaches the point where tensor
 // memory is freed.
 //
+// Three kernels share this scheme: 128-row tiles (below), 256-row tiles (two accumulators per block) and
+// 512-row tiles on pairs of SMs (cta_group::2); mx_gemm_tcgen05 picks by the number of rows.
+//
 // Epilogue modes as in gemm_simt.cu: 0 out(bf16) = v; 1 out(bf16) = gelu_tanh(v);
 // 2 out(f32) = residual + v; 3 out(f32) = v, with v = acc + bias.
 #include <cuda.h>
@@ -1071,7 +1074,9 @@ int pair_count() {
 #ifdef TC_PROFILE
 // marks: 0 setup, 1 producer waiting for a free stage, 2 issuer waiting for the accumulator, 3 issuer
 // waiting for operands (4: of which the first slice of a tile), 5 issuer per tile from accumulator free to
-// last commit, 6 epilogue waiting for the accumulator, 7 epilogue draining, 8 whole block, 9 blocks
+// last commit, 6 epilogue waiting for the accumulator, 7 epilogue draining, 8 whole block, 9 blocks (pairs
+// in the pair kernel, whose marks 10-12 - the drain's waits for tensor memory, its way into shared memory
+// and out to global memory - are added by thread 0 of both blocks: halve them)
 extern "C" int mx_gemm_tcgen05_marks(unsigned long long* out, int reset) {
     cudaDeviceSynchronize();
     if (out) cudaMemcpyFromSymbol(out, g_tc_marks, sizeof(unsigned long long) * 16);
