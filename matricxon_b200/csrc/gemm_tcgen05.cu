@@ -374,27 +374,6 @@ __device__ __forceinline__ void drain_accumulator_row(unsigned tbase, int row, i
     }
 }
 
-// ---------------------------------------------------------------------------------------------
-// The same product with 256-row tiles: two 128 x BN accumulators share every weight tile, so a
-// block takes in (256 + BN) x 128 bytes per 64-wide slice of K for twice the arithmetic. What a
-// block can keep in flight (its shared memory) divided by the latency of a TMA load is its
-// bandwidth; with 128-row tiles that bandwidth feeds the tensor pipe for about 40 % of the
-// time, with 256-row tiles for most of it. The two accumulators fill tensor memory (2 x 256
-// columns), so the epilogue of a tile does not overlap the next tile's products; eight
-// epilogue warps (two per lane quarter, one per accumulator) keep it short, and the producer
-// goes on loading the next tile's stages meanwhile.
-constexpr int TCW_BM = 256;
-constexpr int TCW_STAGES = 3;
-constexpr int TCW_THREADS = 320;      // warps 0-7 epilogue, warp 8 producer, warp 9 MMA issuer
-
-struct TcWideShared {
-    unsigned long long full[TCW_STAGES];
-    unsigned long long empty[TCW_STAGES];
-    unsigned long long acc_full;
-    unsigned long long acc_empty;
-    unsigned tmem_base;
-};
-
 // Tuning aid (compile with -DTC_PROFILE): cycles that the roles of the 256-row kernel spend in
 // each of their phases, summed over all blocks; read with mx_gemm_tcgen05_marks.
 #ifdef TC_PROFILE
@@ -406,211 +385,9 @@ __device__ unsigned long long g_tc_marks[16];
 #define TC_ADD(i, from, to)
 #endif
 
-__global__ void __launch_bounds__(TCW_THREADS)
-gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-                         const float* __restrict__ bias, const float* residual, void* out, int ldo, int M,
-                         int N, int K, int bn, int mode, int* status) {
-    const unsigned a_bytes = TCW_BM * TC_BK * 2, w_bytes = (unsigned)bn * TC_BK * 2;
-    const unsigned stage_bytes = a_bytes + w_bytes;
-    extern __shared__ unsigned char tc_smem_raw[];
-    unsigned char* tiles = reinterpret_cast<unsigned char*>(
-        (reinterpret_cast<uintptr_t>(tc_smem_raw) + 1023) & ~(uintptr_t)1023);
-    __shared__ TcWideShared sh;
+// Epilogue warps per 32 accumulator lanes and accumulator (they take 32-column pieces in turn): one.
+constexpr int TCP_PARTS = 1;
 
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int k_slices = (K + TC_BK - 1) / TC_BK;
-    const int tiles_m = (M + TCW_BM - 1) / TCW_BM, tiles_n = (N + bn - 1) / bn;
-    const int n_tiles = tiles_m * tiles_n;
-    TC_CLOCK(t_start);
-
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < TCW_STAGES; ++s) {
-            tc_mbar_init(&sh.full[s], 1);
-            tc_mbar_init(&sh.empty[s], 1);
-        }
-        tc_mbar_init(&sh.acc_full, 1);
-        tc_mbar_init(&sh.acc_empty, 8);                 // one arrival per epilogue warp
-        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
-    }
-    if (warp == 9) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(
-                         smem_u32(&sh.tmem_base)),
-                     "r"(512)
-                     : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
-    }
-    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
-    __syncthreads();
-    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-    const unsigned tmem_base = sh.tmem_base;
-    TC_CLOCK(t_setup);
-    if (threadIdx.x == 0) { TC_ADD(0, t_start, t_setup); }
-
-    if (warp == 8) {
-        // ---------------- producer
-        if (lane == 0) {
-            int it = 0;
-            bool alive = true;
-            for (int tile = blockIdx.x; tile < n_tiles && alive; tile += gridDim.x) {
-                const int m0 = (tile % tiles_m) * TCW_BM, n0 = (tile / tiles_m) * bn;
-                for (int ks = 0; ks < k_slices; ++ks, ++it) {
-                    const int s = it % TCW_STAGES;
-                    TC_CLOCK(p0);
-                    alive = tc_mbar_wait(&sh.empty[s], ((unsigned)(it / TCW_STAGES) & 1) ^ 1, status);
-                    TC_CLOCK(p1);
-                    TC_ADD(1, p0, p1);
-                    if (!alive) break;
-                    tc_mbar_expect_tx(&sh.full[s], stage_bytes);
-                    unsigned char* a_tile = tiles + (size_t)s * stage_bytes;
-                    tma_load_2d(a_tile, &map_a, ks * TC_BK, m0, &sh.full[s]);
-                    tma_load_2d(a_tile + a_bytes, &map_w, ks * TC_BK, n0, &sh.full[s]);
-                }
-            }
-            for (int j = max(0, it - TCW_STAGES); j < it; ++j)     // nothing of ours stays in flight
-                if (!tc_mbar_wait(&sh.full[j % TCW_STAGES], (unsigned)(j / TCW_STAGES) & 1, status)) break;
-        }
-    } else if (warp == 9) {
-        // ---------------- MMA issuer: rows 0-127 into columns [0, bn), rows 128-255 into [256, 256 + bn)
-        if (lane == 0) {
-            const unsigned idesc = umma_idesc(128, bn);
-            int it = 0, local = 0;
-            bool alive = true;
-            for (int tile = blockIdx.x; tile < n_tiles && alive; tile += gridDim.x, ++local) {
-                TC_CLOCK(m0);
-                alive = tc_mbar_wait(&sh.acc_empty, ((unsigned)local & 1) ^ 1, status);
-                TC_CLOCK(m1);
-                TC_ADD(2, m0, m1);
-                if (!alive) break;
-                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                for (int ks = 0; ks < k_slices; ++ks, ++it) {
-                    const int s = it % TCW_STAGES;
-                    TC_CLOCK(m2);
-                    alive = tc_mbar_wait(&sh.full[s], (unsigned)(it / TCW_STAGES) & 1, status);
-                    TC_CLOCK(m3);
-                    TC_ADD(3, m2, m3);
-                    if (ks == 0) { TC_ADD(4, m2, m3); }
-                    if (!alive) break;
-                    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                    const unsigned char* a_tile = tiles + (size_t)s * stage_bytes;
-                    const unsigned long long adesc_lo = umma_desc(a_tile);
-                    const unsigned long long adesc_hi = umma_desc(a_tile + 128 * TC_BK * 2);
-                    const unsigned long long bdesc = umma_desc(a_tile + a_bytes);
-#pragma unroll
-                    for (int k = 0; k < TC_BK / 16; ++k) {
-                        umma_bf16(tmem_base, adesc_lo + 2 * k, bdesc + 2 * k, idesc, (ks | k) != 0);
-                        umma_bf16(tmem_base + 256, adesc_hi + 2 * k, bdesc + 2 * k, idesc, (ks | k) != 0);
-                    }
-                    umma_commit(&sh.empty[s]);
-                }
-                if (alive) umma_commit(&sh.acc_full);
-                TC_CLOCK(m4);
-                TC_ADD(5, m1, m4);
-            }
-        }
-    } else {
-        // ---------------- epilogue: warp w -> accumulator w / 4, lane quarter w % 4
-        const int half = warp >> 2, quarter = warp & 3;
-        int local = 0;
-        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++local) {
-            TC_CLOCK(e0);
-            if (!tc_mbar_wait(&sh.acc_full, (unsigned)local & 1, status)) break;
-            TC_CLOCK(e1);
-            if (threadIdx.x == 0) { TC_ADD(6, e0, e1); }
-            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-            const int m0 = (tile % tiles_m) * TCW_BM, n0 = (tile / tiles_m) * bn;
-            const int row = m0 + 128 * half + 32 * quarter + lane;
-            const unsigned tbase = tmem_base + (unsigned)half * 256 + ((unsigned)(32 * quarter) << 16);
-            drain_accumulator_row(tbase, row, n0, bn, bias, residual, out, ldo, M, N, mode);
-            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
-            __syncwarp();
-            TC_CLOCK(e2);
-            if (threadIdx.x == 0) { TC_ADD(7, e1, e2); }
-            if (lane == 0) tc_mbar_arrive(&sh.acc_empty);
-        }
-    }
-    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
-    __syncthreads();
-    TC_CLOCK(t_end);
-    if (threadIdx.x == 0) { TC_ADD(8, t_start, t_end); TC_ADD(9, 0, 1); }
-    if (warp == 9) {
-        __syncwarp();
-        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(512)
-                     : "memory");
-    }
-}
-
-// ---------------------------------------------------------------------------------------------
-// The same product on pairs of SMs (tcgen05 cta_group::2): a cluster of two blocks works on one
-// 512 x BN tile. Every MMA spans both SMs (M = 256: rows 0-127 accumulate in the first block's tensor
-// memory, rows 128-255 in the second's) and reads its B operand half from each block's shared
-// memory, so a block takes in 256 rows of A and only BN / 2 rows of W per slice of K: 48 KB where
-// the 256-row kernel needs 64 KB for the same arithmetic, and four stages fit where it has three.
-// That is what this product is bound by: bytes in flight per SM over the latency of a load.
-//   Both blocks run a producer (warp 8): it waits for its own "empty" barrier and issues its loads,
-//   which all announce their bytes on the FIRST block's "full" barrier (the cta_group::2 form of
-//   the TMA load may signal the peer's barrier). The first block's warp 9 issues the MMAs for the
-//   pair and commits them to the "empty" / "accumulator ready" barriers of both blocks (commit with
-//   a block mask). Warps 0-7 of each block drain that block's 128 lanes of both accumulators and
-//   arrive on the first block's "accumulator free" barrier (16 arrivals).
-// No load here is a multicast: each block fetches what it holds.
-constexpr int TCP_ROWS = 512;          // rows of a pair's tile
-constexpr int TCP_PARTS = 1;            // epilogue warps per 32 accumulator lanes and accumulator: they take 32-column pieces in turn
-constexpr int TCP_EPI_WARPS = 8 * TCP_PARTS;
-constexpr int TCP_STAGES = TCP_PARTS == 1 ? 4 : 3;
-constexpr int TCP_THREADS = 32 * (TCP_EPI_WARPS + 2);    // then the producer warp and the MMA warp
-constexpr int TCP_STAGING = TCP_EPI_WARPS * 4096;        // a 4 KB stage for each epilogue warp
-
-struct TcPairShared {
-    unsigned long long full[TCP_STAGES];       // used in the first block of the pair
-    unsigned long long empty[TCP_STAGES];      // in each block
-    unsigned long long acc_full;               // in each block
-    unsigned long long acc_empty;              // used in the first block: 16 arrivals
-    unsigned tmem_base;
-};
-
-__device__ __forceinline__ unsigned cluster_block_rank() {
-    unsigned r;
-    asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
-    return r;
-}
-// The address of the same shared-memory object in block `rank` of the cluster.
-__device__ __forceinline__ unsigned shared_of_rank(const void* ptr, unsigned rank) {
-    unsigned d;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(d) : "r"(smem_u32(ptr)), "r"(rank));
-    return d;
-}
-__device__ __forceinline__ void cluster_barrier() {
-    asm volatile("barrier.cluster.arrive.release.aligned;\n"
-                 "barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
-}
-// Tile load into this block's shared memory whose bytes are counted by a barrier that may live in
-// the other block of the pair (`bar_cluster_addr`: a shared::cluster address).
-__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, int x, int y,
-                                                 unsigned bar_cluster_addr) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::"r"(
-            smem_u32(smem_dst)),
-        "l"(map), "r"(x), "r"(y), "r"(bar_cluster_addr)
-        : "memory");
-}
-__device__ __forceinline__ void umma_bf16_pair(unsigned tmem_acc, unsigned long long adesc,
-                                               unsigned long long bdesc, unsigned idesc, bool accumulate) {
-    asm volatile(
-        "{\n.reg .pred p;\n"
-        "setp.ne.b32 p, %4, 0;\n"
-        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_acc),
-        "l"(adesc), "l"(bdesc), "r"(idesc), "r"((unsigned)accumulate)
-        : "memory");
-}
-// Arrives, once the MMAs issued so far are done, on the barrier at this offset in both blocks.
-__device__ __forceinline__ void umma_commit_pair(unsigned long long* bar) {
-    asm volatile(
-        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;\n" ::"r"(
-            smem_u32(bar)),
-        "h"((unsigned short)3)
-        : "memory");
-}
 __device__ __forceinline__ void mbar_arrive_cluster(unsigned bar_cluster_addr) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];\n" ::"r"(bar_cluster_addr) : "memory");
 }
@@ -801,7 +578,9 @@ struct EpilogueLane {
             for (int e = 0; e < 4 && col_out + e < N; ++e) {
                 const size_t at = (size_t)row * ldo + col_out + e;
                 if constexpr (F32) {
-                    reinterpret_cast<float*>(out)[at] = (mode == 2 ? residual[at] : 0.f) + v[e];
+                    float* dst = reinterpret_cast<float*>(out) + at;
+                    if (mode == 2 && residual == out) atomicAdd(dst, v[e]);
+                    else *dst = (mode == 2 ? residual[at] : 0.f) + v[e];
                 } else {
                     reinterpret_cast<__nv_bfloat16*>(out)[at] =
                         __float2bfloat16_rn(mode == 1 ? gelu_tanh_fast(v[e]) : v[e]);
@@ -843,6 +622,247 @@ struct EpilogueLane {
 };
 
 
+// ---------------------------------------------------------------------------------------------
+// The same product with 256-row tiles (and, for a residual added in place, K shared out between
+// blocks: with few rows a product has too few tiles for 148 SMs, and what bounds a block is what it
+// loads): two 128 x BN accumulators share every weight tile, so a
+// block takes in (256 + BN) x 128 bytes per 64-wide slice of K for twice the arithmetic. What a
+// block can keep in flight (its shared memory) divided by the latency of a TMA load is its
+// bandwidth; with 128-row tiles that bandwidth feeds the tensor pipe for about 40 % of the
+// time, with 256-row tiles for most of it. The two accumulators fill tensor memory (2 x 256
+// columns), so the epilogue of a tile does not overlap the next tile's products; eight
+// epilogue warps (two per lane quarter, one per accumulator) keep it short, and the producer
+// goes on loading the next tile's stages meanwhile.
+constexpr int TCW_BM = 256;
+constexpr int TCW_STAGES = 3;
+constexpr int TCW_THREADS = 320;      // warps 0-7 epilogue, warp 8 producer, warp 9 MMA issuer
+constexpr int TCW_STAGING = 8 * 4096;  // a 4 KB stage for each epilogue warp
+
+struct TcWideShared {
+    unsigned long long full[TCW_STAGES];
+    unsigned long long empty[TCW_STAGES];
+    unsigned long long acc_full;
+    unsigned long long acc_empty;
+    unsigned tmem_base;
+};
+
+
+template <bool F32>
+__global__ void __launch_bounds__(TCW_THREADS)
+gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                         const float* __restrict__ bias, const float* residual, void* out, int ldo, int M,
+                         int N, int K, int bn, int mode, int k_splits, int* status) {
+    const unsigned a_bytes = TCW_BM * TC_BK * 2, w_bytes = (unsigned)bn * TC_BK * 2;
+    const unsigned stage_bytes = a_bytes + w_bytes;
+    extern __shared__ unsigned char tc_smem_raw[];
+    unsigned char* tiles = reinterpret_cast<unsigned char*>(
+        (reinterpret_cast<uintptr_t>(tc_smem_raw) + 1023) & ~(uintptr_t)1023);
+    __shared__ TcWideShared sh;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int k_slices = (K + TC_BK - 1) / TC_BK;
+    const int tiles_m = (M + TCW_BM - 1) / TCW_BM, tiles_n = (N + bn - 1) / bn;
+    const int n_tiles = tiles_m * tiles_n;
+    // k_splits > 1: a tile's slices of K are shared out between that many work items, each of which adds
+    // its part into the output (residual mode in place only: the additions happen at the memory side)
+    const int per_split = (k_slices + k_splits - 1) / k_splits;
+    const int n_items = n_tiles * k_splits;
+    TC_CLOCK(t_start);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < TCW_STAGES; ++s) {
+            tc_mbar_init(&sh.full[s], 1);
+            tc_mbar_init(&sh.empty[s], 1);
+        }
+        tc_mbar_init(&sh.acc_full, 1);
+        tc_mbar_init(&sh.acc_empty, 8);                 // one arrival per epilogue warp
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 9) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(
+                         smem_u32(&sh.tmem_base)),
+                     "r"(512)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    const unsigned tmem_base = sh.tmem_base;
+    TC_CLOCK(t_setup);
+    if (threadIdx.x == 0) { TC_ADD(0, t_start, t_setup); }
+
+    if (warp == 8) {
+        // ---------------- producer
+        if (lane == 0) {
+            int it = 0;
+            bool alive = true;
+            for (int item = blockIdx.x; item < n_items && alive; item += gridDim.x) {
+                const int tile = item / k_splits, split = item - tile * k_splits;
+                const int m0 = (tile % tiles_m) * TCW_BM, n0 = (tile / tiles_m) * bn;
+                const int ks_end = min(k_slices, (split + 1) * per_split);
+                for (int ks = split * per_split; ks < ks_end; ++ks, ++it) {
+                    const int s = it % TCW_STAGES;
+                    TC_CLOCK(p0);
+                    alive = tc_mbar_wait(&sh.empty[s], ((unsigned)(it / TCW_STAGES) & 1) ^ 1, status);
+                    TC_CLOCK(p1);
+                    TC_ADD(1, p0, p1);
+                    if (!alive) break;
+                    tc_mbar_expect_tx(&sh.full[s], stage_bytes);
+                    unsigned char* a_tile = tiles + (size_t)s * stage_bytes;
+                    tma_load_2d(a_tile, &map_a, ks * TC_BK, m0, &sh.full[s]);
+                    tma_load_2d(a_tile + a_bytes, &map_w, ks * TC_BK, n0, &sh.full[s]);
+                }
+            }
+            for (int j = max(0, it - TCW_STAGES); j < it; ++j)     // nothing of ours stays in flight
+                if (!tc_mbar_wait(&sh.full[j % TCW_STAGES], (unsigned)(j / TCW_STAGES) & 1, status)) break;
+        }
+    } else if (warp == 9) {
+        // ---------------- MMA issuer: rows 0-127 into columns [0, bn), rows 128-255 into [256, 256 + bn)
+        if (lane == 0) {
+            const unsigned idesc = umma_idesc(128, bn);
+            int it = 0, local = 0;
+            bool alive = true;
+            for (int item = blockIdx.x; item < n_items && alive; item += gridDim.x, ++local) {
+                const int split = item % k_splits;
+                const int ks_begin = split * per_split, ks_end = min(k_slices, ks_begin + per_split);
+                TC_CLOCK(m0);
+                alive = tc_mbar_wait(&sh.acc_empty, ((unsigned)local & 1) ^ 1, status);
+                TC_CLOCK(m1);
+                TC_ADD(2, m0, m1);
+                if (!alive) break;
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                for (int ks = ks_begin; ks < ks_end; ++ks, ++it) {
+                    const int s = it % TCW_STAGES;
+                    TC_CLOCK(m2);
+                    alive = tc_mbar_wait(&sh.full[s], (unsigned)(it / TCW_STAGES) & 1, status);
+                    TC_CLOCK(m3);
+                    TC_ADD(3, m2, m3);
+                    if (ks == ks_begin) { TC_ADD(4, m2, m3); }
+                    if (!alive) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                    const unsigned char* a_tile = tiles + (size_t)s * stage_bytes;
+                    const unsigned long long adesc_lo = umma_desc(a_tile);
+                    const unsigned long long adesc_hi = umma_desc(a_tile + 128 * TC_BK * 2);
+                    const unsigned long long bdesc = umma_desc(a_tile + a_bytes);
+#pragma unroll
+                    for (int k = 0; k < TC_BK / 16; ++k) {
+                        umma_bf16(tmem_base, adesc_lo + 2 * k, bdesc + 2 * k, idesc, ks > ks_begin || k != 0);
+                        umma_bf16(tmem_base + 256, adesc_hi + 2 * k, bdesc + 2 * k, idesc, ks > ks_begin || k != 0);
+                    }
+                    umma_commit(&sh.empty[s]);
+                }
+                if (alive) umma_commit(&sh.acc_full);
+                TC_CLOCK(m4);
+                TC_ADD(5, m1, m4);
+            }
+        }
+    } else {
+        // ---------------- epilogue: warp w -> accumulator w / 4, lane quarter w % 4
+        const int half = warp >> 2, quarter = warp & 3;
+        const unsigned free_bar = smem_u32(&sh.acc_empty);
+        unsigned char* stage = tiles + (size_t)TCW_STAGES * stage_bytes + (size_t)warp * 4096;
+        int local = 0;
+        for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++local) {
+            const int tile = item / k_splits, split = item - tile * k_splits;
+            const int m0 = (tile % tiles_m) * TCW_BM, n0 = (tile / tiles_m) * bn;
+            const int row0 = m0 + 128 * half + 32 * quarter;
+            const unsigned tbase = tmem_base + (unsigned)half * 256 + ((unsigned)(32 * quarter) << 16);
+            const float* bias_here = split == 0 ? bias : nullptr;     // one of a tile's parts brings the bias
+            EpilogueLane<F32> mine;
+            mine.prefetch(bias_here, residual, out, ldo, row0, n0, 0, bn, M, N, mode, lane);
+            TC_CLOCK(e0);
+            if (!tc_mbar_wait(&sh.acc_full, (unsigned)local & 1, status)) break;
+            TC_CLOCK(e1);
+            if (threadIdx.x == 0) { TC_ADD(6, e0, e1); }
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            mine.drain(tbase, row0, n0, 0, bn, bias_here, residual, out, ldo, M, N, mode, stage, lane, free_bar);
+            TC_CLOCK(e2);
+            if (threadIdx.x == 0) { TC_ADD(7, e1, e2); }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    TC_CLOCK(t_end);
+    if (threadIdx.x == 0) { TC_ADD(8, t_start, t_end); TC_ADD(9, 0, 1); }
+    if (warp == 9) {
+        __syncwarp();
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(512)
+                     : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// The same product on pairs of SMs (tcgen05 cta_group::2): a cluster of two blocks works on one
+// 512 x BN tile. Every MMA spans both SMs (M = 256: rows 0-127 accumulate in the first block's tensor
+// memory, rows 128-255 in the second's) and reads its B operand half from each block's shared
+// memory, so a block takes in 256 rows of A and only BN / 2 rows of W per slice of K: 48 KB where
+// the 256-row kernel needs 64 KB for the same arithmetic, and four stages fit where it has three.
+// That is what this product is bound by: bytes in flight per SM over the latency of a load.
+//   Both blocks run a producer (warp 8): it waits for its own "empty" barrier and issues its loads,
+//   which all announce their bytes on the FIRST block's "full" barrier (the cta_group::2 form of
+//   the TMA load may signal the peer's barrier). The first block's warp 9 issues the MMAs for the
+//   pair and commits them to the "empty" / "accumulator ready" barriers of both blocks (commit with
+//   a block mask). Warps 0-7 of each block drain that block's 128 lanes of both accumulators and
+//   arrive on the first block's "accumulator free" barrier (16 arrivals).
+// No load here is a multicast: each block fetches what it holds.
+constexpr int TCP_ROWS = 512;          // rows of a pair's tile
+constexpr int TCP_EPI_WARPS = 8 * TCP_PARTS;
+constexpr int TCP_STAGES = TCP_PARTS == 1 ? 4 : 3;
+constexpr int TCP_THREADS = 32 * (TCP_EPI_WARPS + 2);    // then the producer warp and the MMA warp
+constexpr int TCP_STAGING = TCP_EPI_WARPS * 4096;        // a 4 KB stage for each epilogue warp
+
+struct TcPairShared {
+    unsigned long long full[TCP_STAGES];       // used in the first block of the pair
+    unsigned long long empty[TCP_STAGES];      // in each block
+    unsigned long long acc_full;               // in each block
+    unsigned long long acc_empty;              // used in the first block: 16 arrivals
+    unsigned tmem_base;
+};
+
+__device__ __forceinline__ unsigned cluster_block_rank() {
+    unsigned r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
+    return r;
+}
+// The address of the same shared-memory object in block `rank` of the cluster.
+__device__ __forceinline__ unsigned shared_of_rank(const void* ptr, unsigned rank) {
+    unsigned d;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(d) : "r"(smem_u32(ptr)), "r"(rank));
+    return d;
+}
+__device__ __forceinline__ void cluster_barrier() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n"
+                 "barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+// Tile load into this block's shared memory whose bytes are counted by a barrier that may live in
+// the other block of the pair (`bar_cluster_addr`: a shared::cluster address).
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, int x, int y,
+                                                 unsigned bar_cluster_addr) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::"r"(
+            smem_u32(smem_dst)),
+        "l"(map), "r"(x), "r"(y), "r"(bar_cluster_addr)
+        : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(unsigned tmem_acc, unsigned long long adesc,
+                                               unsigned long long bdesc, unsigned idesc, bool accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_acc),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"((unsigned)accumulate)
+        : "memory");
+}
+// Arrives, once the MMAs issued so far are done, on the barrier at this offset in both blocks.
+__device__ __forceinline__ void umma_commit_pair(unsigned long long* bar) {
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;\n" ::"r"(
+            smem_u32(bar)),
+        "h"((unsigned short)3)
+        : "memory");
+}
 template <bool F32>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TCP_THREADS)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
@@ -1046,6 +1066,40 @@ int sm_count() {
     return count;
 }
 
+// MATRICXON_GEMM_SPLIT_K=0 keeps every tile's K in one block (the parts of a split K meet in the output
+// through additions at the memory side, whose order is not fixed: sums may differ in the last bit from
+// run to run).
+bool split_k_allowed() {
+    static int allowed = -1;
+    if (allowed < 0) {
+        const char* env = getenv("MATRICXON_GEMM_SPLIT_K");
+        allowed = (env != nullptr && env[0] == '0') ? 0 : 1;
+    }
+    return allowed == 1;
+}
+
+// Tile width and number of parts of K for the 256-row kernel when K may be split: the pair with the least
+// estimated time. A block's slice of K costs the slower of its loads ((256 + bn) x 128 bytes at about 100
+// bytes a nanosecond per SM) and its products; a work item ends with an epilogue; items run in rounds.
+void pick_width_and_split(int M, int N, int K, int n_sm, int* best_bn, int* best_splits) {
+    const long long tiles_m = (M + TCW_BM - 1) / TCW_BM;
+    const int k_slices = (K + TC_BK - 1) / TC_BK;
+    double best = -1.0;
+    for (int bn = 256; bn >= 64; bn -= 16) {
+        const long long tiles = tiles_m * ((N + bn - 1) / bn);
+        for (int splits = 1; splits <= 16; ++splits) {
+            const int per = (k_slices + splits - 1) / splits;
+            if (per < 4 && splits > 1) break;
+            if ((long long)(splits - 1) * per >= k_slices) continue;          // a part without slices
+            const long long rounds = (tiles * splits + n_sm - 1) / n_sm;
+            const double load_ns = (256.0 + bn) * 1.28, mma_ns = bn * 2.1;
+            const double item_ns = per * (load_ns > mma_ns ? load_ns : mma_ns) + 2000.0 + bn * 25.0;
+            const double cost = rounds * item_ns;
+            if (best < 0 || cost < best) { best = cost; *best_bn = bn; *best_splits = splits; }
+        }
+    }
+}
+
 // How many pairs of SMs the pair kernel can hold at once with its largest tile (0: it cannot run).
 int pair_count() {
     static int count = -1;
@@ -1103,35 +1157,52 @@ extern "C" int mx_gemm_tcgen05(const void* A, const void* W, const float* bias, 
         MX_REFUSE("tcgen05 gemm: epilogue mode %d does not write dtype %d", mode, out_dtype);
     if (status == nullptr) MX_REFUSE("tcgen05 gemm: needs a status word for its bounded waits");
     const int n_sm = sm_count();
-    // 256-row tiles once there are rows to fill them (a W tile feeds two accumulators), unless 128-row
-    // tiles give every SM four or more: then the persistent kernel's second accumulator buffer hides each
-    // tile's epilogue under the next tile's products, which is worth more (c_fc at 2,048 rows: 132 us
-    // against 148 us)
-    const long long tiles_128 = (long long)((M + 127) / 128) * ((N + 255) / 256);
-    bool wide = M > 256 && tiles_128 < 4LL * n_sm;
-    // pairs of SMs on 512-row tiles once there are rows for them: less operand traffic per SM
     const int n_pairs = pair_count();
-    // (its epilogue moves 16-byte units: rows of the output, the residual and the bias must allow that)
     const bool f32_out = mode >= 2;
-    const bool pair_can = n_pairs > 0 && (ldo * (f32_out ? 4 : 2)) % (f32_out ? 16 : 8) == 0 &&
-                          reinterpret_cast<uintptr_t>(out) % 16 == 0 &&
-                          (mode != 2 || reinterpret_cast<uintptr_t>(residual) % 16 == 0) &&
-                          (bias == nullptr || reinterpret_cast<uintptr_t>(bias) % 16 == 0);
-    bool pair = M > 512 && pair_can;
+    // the epilogue of the 256- and 512-row kernels moves 16-byte units (8 bytes of bfloat16 outputs)
+    const bool vector_ok = (ldo * (f32_out ? 4 : 2)) % (f32_out ? 16 : 8) == 0 &&
+                           reinterpret_cast<uintptr_t>(out) % 16 == 0 &&
+                           (mode != 2 || reinterpret_cast<uintptr_t>(residual) % 16 == 0) &&
+                           (bias == nullptr || reinterpret_cast<uintptr_t>(bias) % 16 == 0);
+    // a residual added in place lets K be shared out between blocks (every part adds into the output)
+    const bool may_split = mode == 2 && residual == out && vector_ok && split_k_allowed();
+    // 512-row tiles on pairs of SMs once there are rows for them; 256-row tiles (two accumulators per W
+    // tile) from 257 rows on, or from 129 when K can be split, unless 128-row tiles give every SM four or
+    // more: then the 128-row kernel's second accumulator buffer hides each tile's epilogue under the next
+    // tile's products, which is worth more (c_fc at 2,048 rows: 132 us against 148 us)
+    const long long tiles_128 = (long long)((M + 127) / 128) * ((N + 255) / 256);
+    bool pair = M > 512 && vector_ok && n_pairs > 0;
+    bool wide = false;
+    if (!pair && vector_ok && M > 128) {
+        if (may_split) {
+            wide = true;
+        } else if (M > 256 && tiles_128 < 4LL * n_sm) {
+            // both kernels are bound by what a block loads per slice of K: rounds x (tile rows + tile width)
+            const int bn_128 = pick_tile_width(M, N, n_sm, TC_BM), bn_256 = pick_tile_width(M, N, n_sm, TCW_BM);
+            const long long t_128 = (long long)((M + 127) / 128) * ((N + bn_128 - 1) / bn_128);
+            const long long t_256 = (long long)((M + 255) / 256) * ((N + bn_256 - 1) / bn_256);
+            const long long cost_128 = ((t_128 + n_sm - 1) / n_sm) * (TC_BM + bn_128 + 32);
+            const long long cost_256 = ((t_256 + n_sm - 1) / n_sm) * (TCW_BM + bn_256 + 32);
+            wide = cost_256 <= cost_128;
+        }
+    }
     if (const char* force = getenv("MATRICXON_GEMM_TILES")) {       // for measurements: 128, 256 or 512 rows
         const int rows = atoi(force);
         if (rows == 128) { wide = false; pair = false; }
-        if (rows == 256) { wide = true; pair = false; }
-        if (rows == 512) pair = pair_can;
+        if (rows == 256 && vector_ok) { wide = true; pair = false; }
+        if (rows == 512 && vector_ok && n_pairs > 0) { pair = true; wide = false; }
     }
     static bool attribute_set = false;
     if (!attribute_set) {
         const size_t most = (size_t)TC_STAGES * (TC_BM + 256) * TC_BK * 2 + 1024;
-        const size_t most_wide = (size_t)TCW_STAGES * (TCW_BM + 256) * TC_BK * 2 + 1024;
+        const size_t most_wide = (size_t)TCW_STAGES * (TCW_BM + 256) * TC_BK * 2 + TCW_STAGING + 1024;
         cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              (int)most);
         if (e == cudaSuccess)
-            e = cudaFuncSetAttribute(gemm_tcgen05_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+            e = cudaFuncSetAttribute(gemm_tcgen05_wide_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)most_wide);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(gemm_tcgen05_wide_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      (int)most_wide);
         if (e != cudaSuccess) MX_REFUSE("tcgen05 gemm: cannot reserve %zu bytes of shared memory", most_wide);
         attribute_set = true;
@@ -1154,22 +1225,35 @@ extern "C" int mx_gemm_tcgen05(const void* A, const void* W, const float* bias, 
                                                                                  ldo, M, N, K, bn, mode, status);
         return mx_launch_status();
     }
-    const int tile_rows = wide ? TCW_BM : TC_BM;
-    const int stages = wide ? TCW_STAGES : TC_STAGES;
-    const int bn = pick_tile_width(M, N, n_sm, tile_rows);
+    if (wide) {
+        int bn = pick_tile_width(M, N, n_sm, TCW_BM), k_splits = 1;
+        if (may_split) pick_width_and_split(M, N, K, n_sm, &bn, &k_splits);
+        CUtensorMap map_a, map_w;
+        int rc = make_map(&map_a, A, M, K, lda, TCW_BM);
+        if (rc != MX_OK) return rc;
+        rc = make_map(&map_w, W, N, K, ldw, bn);
+        if (rc != MX_OK) return rc;
+        const size_t smem = (size_t)TCW_STAGES * (TCW_BM + bn) * TC_BK * 2 + TCW_STAGING + 1024;
+        const long long items = (long long)((M + TCW_BM - 1) / TCW_BM) * ((N + bn - 1) / bn) * k_splits;
+        const int grid = (int)(items < n_sm ? items : n_sm);
+        if (f32_out)
+            gemm_tcgen05_wide_kernel<true><<<grid, TCW_THREADS, smem, stream>>>(map_a, map_w, bias, residual, out,
+                                                                                ldo, M, N, K, bn, mode, k_splits, status);
+        else
+            gemm_tcgen05_wide_kernel<false><<<grid, TCW_THREADS, smem, stream>>>(map_a, map_w, bias, residual, out,
+                                                                                 ldo, M, N, K, bn, mode, k_splits, status);
+        return mx_launch_status();
+    }
+    const int bn = pick_tile_width(M, N, n_sm, TC_BM);
     CUtensorMap map_a, map_w;
-    int rc = make_map(&map_a, A, M, K, lda, tile_rows);
+    int rc = make_map(&map_a, A, M, K, lda, TC_BM);
     if (rc != MX_OK) return rc;
     rc = make_map(&map_w, W, N, K, ldw, bn);
     if (rc != MX_OK) return rc;
-    const size_t smem = (size_t)stages * (tile_rows + bn) * TC_BK * 2 + 1024;
-    const long long tiles = (long long)((M + tile_rows - 1) / tile_rows) * ((N + bn - 1) / bn);
+    const size_t smem = (size_t)TC_STAGES * (TC_BM + bn) * TC_BK * 2 + 1024;
+    const long long tiles = (long long)((M + TC_BM - 1) / TC_BM) * ((N + bn - 1) / bn);
     const int grid = (int)(tiles < n_sm ? tiles : n_sm);
-    if (wide)
-        gemm_tcgen05_wide_kernel<<<grid, TCW_THREADS, smem, stream>>>(map_a, map_w, bias, residual, out, ldo, M,
-                                                                      N, K, bn, mode, status);
-    else
-        gemm_tcgen05_kernel<<<grid, TC_THREADS, smem, stream>>>(map_a, map_w, bias, residual, out, ldo, M, N, K,
-                                                                bn, mode, status);
+    gemm_tcgen05_kernel<<<grid, TC_THREADS, smem, stream>>>(map_a, map_w, bias, residual, out, ldo, M, N, K, bn, mode,
+                                                           status);
     return mx_launch_status();
 }

@@ -34,8 +34,20 @@ def dtype_code(dtype: torch.dtype) -> int:
     raise KernelLibraryError(f"kernels take float32 or bfloat16, not {dtype}")
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_device_index: int | None = None
+
+
 def _stream() -> int:
-    return torch.cuda.current_stream().cuda_stream
+    """The current stream's handle. ``torch.cuda.current_stream()`` builds a Python object and looks the
+    device up through several layers on every call (a third of a prompt step's host time when asked
+    once per launch); the raw query is one C call. One device per process."""
+    global _device_index
+    if _raw_stream is None:
+        return torch.cuda.current_stream().cuda_stream
+    if _device_index is None:
+        _device_index = torch.cuda.current_device()
+    return _raw_stream(_device_index)
 
 
 def _ptr(t: torch.Tensor | None) -> int | None:

@@ -142,7 +142,7 @@ class BatchSampler:
             base, base + 4 * (4 * n), base + 4 * n, base + 4 * (2 * n), base + 4 * (3 * n),
             base + 4 * (5 * n), base + 4 * (6 * n + 1),
             pending.data_ptr() if pending is not None else None, self._work.data_ptr(), out.data_ptr(),
-            torch.cuda.current_stream().cuda_stream), "sample")
+            kernels._stream()), "sample")
         kernels._launched()
         # two result buffers in turn: a step may be launched before the ids of the one before are read
         self._turn ^= 1
