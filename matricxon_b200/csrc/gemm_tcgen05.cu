@@ -39,6 +39,7 @@ constexpr int TC_BM = 128;
 constexpr int TC_BK = 64;              // 64 bf16 = 128 bytes = one swizzle row
 constexpr int TC_STAGES = 4;
 constexpr int TC_THREADS = 192;
+constexpr int TC_STAGING = 4 * 4096;      // a 4 KB stage for each epilogue warp
 constexpr int TC_SPIN_LIMIT = 1 << 22;
 
 __device__ __forceinline__ unsigned smem_u32(const void* ptr) {
@@ -202,132 +203,6 @@ __device__ __forceinline__ void store_piece(const unsigned (&r)[16], const float
             if (mode == 1) v = gelu_tanh_fast(v);
             o[j] = __float2bfloat16_rn(v);
         }
-    }
-}
-
-// Persistent: a block walks the tiles blockIdx.x, blockIdx.x + gridDim.x, ... (rows fastest, so
-// blocks that run together share weight tiles through L2). The accumulator is double-buffered
-// in tensor memory (2 x 256 columns): the epilogue of one tile overlaps the products of the next.
-__global__ void __launch_bounds__(TC_THREADS)
-gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-                    const float* __restrict__ bias, const float* residual, void* out, int ldo, int M,
-                    int N, int K, int bn, int mode, int* status) {
-    const unsigned a_bytes = TC_BM * TC_BK * 2, w_bytes = (unsigned)bn * TC_BK * 2;
-    const unsigned stage_bytes = a_bytes + w_bytes;
-    extern __shared__ unsigned char tc_smem_raw[];
-    // stages must start on a 1024-byte boundary for the 128-byte swizzle
-    unsigned char* tiles = reinterpret_cast<unsigned char*>(
-        (reinterpret_cast<uintptr_t>(tc_smem_raw) + 1023) & ~(uintptr_t)1023);
-    __shared__ TcShared sh;
-
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int k_slices = (K + TC_BK - 1) / TC_BK;
-    const int tiles_m = (M + TC_BM - 1) / TC_BM, tiles_n = (N + bn - 1) / bn;
-    const int n_tiles = tiles_m * tiles_n;
-
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < TC_STAGES; ++s) {
-            tc_mbar_init(&sh.full[s], 1);
-            tc_mbar_init(&sh.empty[s], 1);
-        }
-        for (int b = 0; b < 2; ++b) {
-            tc_mbar_init(&sh.acc_full[b], 1);
-            tc_mbar_init(&sh.acc_empty[b], 4);          // one arrival per epilogue warp
-        }
-        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
-    }
-    if (warp == 5) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(
-                         smem_u32(&sh.tmem_base)),
-                     "r"(512)
-                     : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
-    }
-    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
-    __syncthreads();
-    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-    const unsigned tmem_base = sh.tmem_base;
-
-    if (warp == 4) {
-        // ---------------- producer
-        if (lane == 0) {
-            int it = 0;
-            bool alive = true;
-            for (int tile = blockIdx.x; tile < n_tiles && alive; tile += gridDim.x) {
-                const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * bn;
-                for (int ks = 0; ks < k_slices; ++ks, ++it) {
-                    const int s = it % TC_STAGES;
-                    alive = tc_mbar_wait(&sh.empty[s], ((unsigned)(it / TC_STAGES) & 1) ^ 1, status);
-                    if (!alive) break;
-                    tc_mbar_expect_tx(&sh.full[s], stage_bytes);
-                    unsigned char* a_tile = tiles + (size_t)s * stage_bytes;
-                    tma_load_2d(a_tile, &map_a, ks * TC_BK, m0, &sh.full[s]);
-                    tma_load_2d(a_tile + a_bytes, &map_w, ks * TC_BK, n0, &sh.full[s]);
-                }
-            }
-            // no copy of this block may still be in flight when it ends: wait (bounded) for the
-            // loads of the last stages to land
-            for (int j = max(0, it - TC_STAGES); j < it; ++j)
-                if (!tc_mbar_wait(&sh.full[j % TC_STAGES], (unsigned)(j / TC_STAGES) & 1, status)) break;
-        }
-    } else if (warp == 5) {
-        // ---------------- MMA issuer
-        if (lane == 0) {
-            const unsigned idesc = umma_idesc(TC_BM, bn);
-            int it = 0, local = 0;
-            bool alive = true;
-            for (int tile = blockIdx.x; tile < n_tiles && alive; tile += gridDim.x, ++local) {
-                const int buf = local & 1;
-                alive = tc_mbar_wait(&sh.acc_empty[buf], ((unsigned)(local >> 1) & 1) ^ 1, status);
-                if (!alive) break;
-                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                const unsigned tmem_acc = tmem_base + (unsigned)buf * 256;
-                for (int ks = 0; ks < k_slices; ++ks, ++it) {
-                    const int s = it % TC_STAGES;
-                    alive = tc_mbar_wait(&sh.full[s], (unsigned)(it / TC_STAGES) & 1, status);
-                    if (!alive) break;
-                    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                    const unsigned char* a_tile = tiles + (size_t)s * stage_bytes;
-                    const unsigned long long adesc = umma_desc(a_tile);
-                    const unsigned long long bdesc = umma_desc(a_tile + a_bytes);
-#pragma unroll
-                    for (int k = 0; k < TC_BK / 16; ++k)   // 16 elements = 32 bytes further along K
-                        umma_bf16(tmem_acc, adesc + 2 * k, bdesc + 2 * k, idesc, (ks | k) != 0);
-                    umma_commit(&sh.empty[s]);
-                }
-                if (alive) umma_commit(&sh.acc_full[buf]);   // arrives when the tile's MMAs are done
-            }
-        }
-    } else {
-        // ---------------- epilogue: warp w owns accumulator lanes 32 w .. 32 w + 31
-        int local = 0;
-        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++local) {
-            const int buf = local & 1;
-            if (!tc_mbar_wait(&sh.acc_full[buf], (unsigned)(local >> 1) & 1, status)) break;
-            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-            const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * bn;
-            const int row = m0 + 32 * warp + lane;
-            const unsigned tbase = tmem_base + (unsigned)buf * 256 + ((unsigned)(32 * warp) << 16);
-            for (int c0 = 0; c0 < bn; c0 += 16) {
-                unsigned r[16];
-                tmem_load16(tbase + (unsigned)c0, r);
-                if (row < M && n0 + c0 < N)
-                    store_piece(r, bias, residual, out, (size_t)row * ldo + n0 + c0, n0 + c0, N, mode);
-            }
-            // the accumulator buffer may be overwritten from here on
-            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
-            __syncwarp();
-            if (lane == 0) tc_mbar_arrive(&sh.acc_empty[buf]);
-        }
-    }
-    // ---------------- teardown: every role arrives here; then tensor memory is freed
-    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
-    __syncthreads();
-    if (warp == 5) {
-        __syncwarp();
-        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(512)
-                     : "memory");
     }
 }
 
@@ -621,6 +496,145 @@ struct EpilogueLane {
     }
 };
 
+
+// Persistent: a block walks the tiles blockIdx.x, blockIdx.x + gridDim.x, ... (rows fastest, so
+// blocks that run together share weight tiles through L2). The accumulator is double-buffered
+// in tensor memory (2 x 256 columns): the epilogue of one tile overlaps the products of the next.
+// `staged`: the epilogue goes through the 4 KB stages behind the operand stages (coalesced stores; needs
+// 16-byte-aligned rows, see mx_gemm_tcgen05); otherwise every lane stores its own row's pieces.
+template <bool F32>
+__global__ void __launch_bounds__(TC_THREADS)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                    const float* __restrict__ bias, const float* residual, void* out, int ldo, int M,
+                    int N, int K, int bn, int mode, int staged, int* status) {
+    const unsigned a_bytes = TC_BM * TC_BK * 2, w_bytes = (unsigned)bn * TC_BK * 2;
+    const unsigned stage_bytes = a_bytes + w_bytes;
+    extern __shared__ unsigned char tc_smem_raw[];
+    // stages must start on a 1024-byte boundary for the 128-byte swizzle
+    unsigned char* tiles = reinterpret_cast<unsigned char*>(
+        (reinterpret_cast<uintptr_t>(tc_smem_raw) + 1023) & ~(uintptr_t)1023);
+    __shared__ TcShared sh;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int k_slices = (K + TC_BK - 1) / TC_BK;
+    const int tiles_m = (M + TC_BM - 1) / TC_BM, tiles_n = (N + bn - 1) / bn;
+    const int n_tiles = tiles_m * tiles_n;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < TC_STAGES; ++s) {
+            tc_mbar_init(&sh.full[s], 1);
+            tc_mbar_init(&sh.empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            tc_mbar_init(&sh.acc_full[b], 1);
+            tc_mbar_init(&sh.acc_empty[b], 4);          // one arrival per epilogue warp
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 5) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(
+                         smem_u32(&sh.tmem_base)),
+                     "r"(512)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    const unsigned tmem_base = sh.tmem_base;
+
+    if (warp == 4) {
+        // ---------------- producer
+        if (lane == 0) {
+            int it = 0;
+            bool alive = true;
+            for (int tile = blockIdx.x; tile < n_tiles && alive; tile += gridDim.x) {
+                const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * bn;
+                for (int ks = 0; ks < k_slices; ++ks, ++it) {
+                    const int s = it % TC_STAGES;
+                    alive = tc_mbar_wait(&sh.empty[s], ((unsigned)(it / TC_STAGES) & 1) ^ 1, status);
+                    if (!alive) break;
+                    tc_mbar_expect_tx(&sh.full[s], stage_bytes);
+                    unsigned char* a_tile = tiles + (size_t)s * stage_bytes;
+                    tma_load_2d(a_tile, &map_a, ks * TC_BK, m0, &sh.full[s]);
+                    tma_load_2d(a_tile + a_bytes, &map_w, ks * TC_BK, n0, &sh.full[s]);
+                }
+            }
+            // no copy of this block may still be in flight when it ends: wait (bounded) for the
+            // loads of the last stages to land
+            for (int j = max(0, it - TC_STAGES); j < it; ++j)
+                if (!tc_mbar_wait(&sh.full[j % TC_STAGES], (unsigned)(j / TC_STAGES) & 1, status)) break;
+        }
+    } else if (warp == 5) {
+        // ---------------- MMA issuer
+        if (lane == 0) {
+            const unsigned idesc = umma_idesc(TC_BM, bn);
+            int it = 0, local = 0;
+            bool alive = true;
+            for (int tile = blockIdx.x; tile < n_tiles && alive; tile += gridDim.x, ++local) {
+                const int buf = local & 1;
+                alive = tc_mbar_wait(&sh.acc_empty[buf], ((unsigned)(local >> 1) & 1) ^ 1, status);
+                if (!alive) break;
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                const unsigned tmem_acc = tmem_base + (unsigned)buf * 256;
+                for (int ks = 0; ks < k_slices; ++ks, ++it) {
+                    const int s = it % TC_STAGES;
+                    alive = tc_mbar_wait(&sh.full[s], (unsigned)(it / TC_STAGES) & 1, status);
+                    if (!alive) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                    const unsigned char* a_tile = tiles + (size_t)s * stage_bytes;
+                    const unsigned long long adesc = umma_desc(a_tile);
+                    const unsigned long long bdesc = umma_desc(a_tile + a_bytes);
+#pragma unroll
+                    for (int k = 0; k < TC_BK / 16; ++k)   // 16 elements = 32 bytes further along K
+                        umma_bf16(tmem_acc, adesc + 2 * k, bdesc + 2 * k, idesc, (ks | k) != 0);
+                    umma_commit(&sh.empty[s]);
+                }
+                if (alive) umma_commit(&sh.acc_full[buf]);   // arrives when the tile's MMAs are done
+            }
+        }
+    } else {
+        // ---------------- epilogue: warp w owns accumulator lanes 32 w .. 32 w + 31
+        int local = 0;
+        unsigned char* stage = tiles + (size_t)TC_STAGES * stage_bytes + (size_t)warp * 4096;
+        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++local) {
+            const int buf = local & 1;
+            const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * bn;
+            const unsigned tbase = tmem_base + (unsigned)buf * 256 + ((unsigned)(32 * warp) << 16);
+            if (staged) {
+                EpilogueLane<F32> mine;
+                mine.prefetch(bias, residual, out, ldo, m0 + 32 * warp, n0, 0, bn, M, N, mode, lane);
+                if (!tc_mbar_wait(&sh.acc_full[buf], (unsigned)(local >> 1) & 1, status)) break;
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                mine.drain(tbase, m0 + 32 * warp, n0, 0, bn, bias, residual, out, ldo, M, N, mode, stage, lane,
+                           smem_u32(&sh.acc_empty[buf]));
+                continue;
+            }
+            if (!tc_mbar_wait(&sh.acc_full[buf], (unsigned)(local >> 1) & 1, status)) break;
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            const int row = m0 + 32 * warp + lane;
+            for (int c0 = 0; c0 < bn; c0 += 16) {
+                unsigned r[16];
+                tmem_load16(tbase + (unsigned)c0, r);
+                if (row < M && n0 + c0 < N)
+                    store_piece(r, bias, residual, out, (size_t)row * ldo + n0 + c0, n0 + c0, N, mode);
+            }
+            // the accumulator buffer may be overwritten from here on
+            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+            __syncwarp();
+            if (lane == 0) tc_mbar_arrive(&sh.acc_empty[buf]);
+        }
+    }
+    // ---------------- teardown: every role arrives here; then tensor memory is freed
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    if (warp == 5) {
+        __syncwarp();
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(512)
+                     : "memory");
+    }
+}
 
 // ---------------------------------------------------------------------------------------------
 // The same product with 256-row tiles (and, for a residual added in place, K shared out between
@@ -1194,10 +1208,13 @@ extern "C" int mx_gemm_tcgen05(const void* A, const void* W, const float* bias, 
     }
     static bool attribute_set = false;
     if (!attribute_set) {
-        const size_t most = (size_t)TC_STAGES * (TC_BM + 256) * TC_BK * 2 + 1024;
+        const size_t most = (size_t)TC_STAGES * (TC_BM + 256) * TC_BK * 2 + TC_STAGING + 1024;
         const size_t most_wide = (size_t)TCW_STAGES * (TCW_BM + 256) * TC_BK * 2 + TCW_STAGING + 1024;
-        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              (int)most);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(gemm_tcgen05_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)most);
         if (e == cudaSuccess)
             e = cudaFuncSetAttribute(gemm_tcgen05_wide_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      (int)most_wide);
@@ -1250,10 +1267,14 @@ extern "C" int mx_gemm_tcgen05(const void* A, const void* W, const float* bias, 
     if (rc != MX_OK) return rc;
     rc = make_map(&map_w, W, N, K, ldw, bn);
     if (rc != MX_OK) return rc;
-    const size_t smem = (size_t)TC_STAGES * (TC_BM + bn) * TC_BK * 2 + 1024;
+    const size_t smem = (size_t)TC_STAGES * (TC_BM + bn) * TC_BK * 2 + TC_STAGING + 1024;
     const long long tiles = (long long)((M + TC_BM - 1) / TC_BM) * ((N + bn - 1) / bn);
     const int grid = (int)(tiles < n_sm ? tiles : n_sm);
-    gemm_tcgen05_kernel<<<grid, TC_THREADS, smem, stream>>>(map_a, map_w, bias, residual, out, ldo, M, N, K, bn, mode,
-                                                           status);
+    if (f32_out)
+        gemm_tcgen05_kernel<true><<<grid, TC_THREADS, smem, stream>>>(map_a, map_w, bias, residual, out, ldo, M, N, K,
+                                                                      bn, mode, vector_ok ? 1 : 0, status);
+    else
+        gemm_tcgen05_kernel<false><<<grid, TC_THREADS, smem, stream>>>(map_a, map_w, bias, residual, out, ldo, M, N, K,
+                                                                       bn, mode, vector_ok ? 1 : 0, status);
     return mx_launch_status();
 }
