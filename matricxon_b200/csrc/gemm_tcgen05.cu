@@ -1180,12 +1180,13 @@ extern "C" int mx_gemm_tcgen05(const void* A, const void* W, const float* bias, 
                            (bias == nullptr || reinterpret_cast<uintptr_t>(bias) % 16 == 0);
     // a residual added in place lets K be shared out between blocks (every part adds into the output)
     const bool may_split = mode == 2 && residual == out && vector_ok && split_k_allowed();
-    // 512-row tiles on pairs of SMs once there are rows for them; 256-row tiles (two accumulators per W
+    // 512-row tiles on pairs of SMs from 2,048 rows on (below that its tiles are too few or too narrow: at
+    // 1,024 rows the other two are a quarter faster); 256-row tiles (two accumulators per W
     // tile) from 257 rows on, or from 129 when K can be split, unless 128-row tiles give every SM four or
     // more: then the 128-row kernel's second accumulator buffer hides each tile's epilogue under the next
     // tile's products, which is worth more (c_fc at 2,048 rows: 132 us against 148 us)
     const long long tiles_128 = (long long)((M + 127) / 128) * ((N + 255) / 256);
-    bool pair = M > 512 && vector_ok && n_pairs > 0;
+    bool pair = M >= 2048 && vector_ok && n_pairs > 0;
     bool wide = false;
     if (!pair && vector_ok && M > 128) {
         if (may_split) {
@@ -1195,8 +1196,10 @@ extern "C" int mx_gemm_tcgen05(const void* A, const void* W, const float* bias, 
             const int bn_128 = pick_tile_width(M, N, n_sm, TC_BM), bn_256 = pick_tile_width(M, N, n_sm, TCW_BM);
             const long long t_128 = (long long)((M + 127) / 128) * ((N + bn_128 - 1) / bn_128);
             const long long t_256 = (long long)((M + 255) / 256) * ((N + bn_256 - 1) / bn_256);
-            const long long cost_128 = ((t_128 + n_sm - 1) / n_sm) * (TC_BM + bn_128 + 32);
-            const long long cost_256 = ((t_256 + n_sm - 1) / n_sm) * (TCW_BM + bn_256 + 32);
+            // (the 128-row kernel keeps four stages in flight and hides all epilogues but the last under the
+            // next tile's products; the 256-row kernel pays for each: measured at 512-1,536 rows)
+            const long long cost_128 = ((t_128 + n_sm - 1) / n_sm) * ((TC_BM + bn_128) * 9 / 10 + 32) + bn_128 / 4;
+            const long long cost_256 = ((t_256 + n_sm - 1) / n_sm) * (TCW_BM + bn_256 + 32 + bn_256 / 2);
             wide = cost_256 <= cost_128;
         }
     }
