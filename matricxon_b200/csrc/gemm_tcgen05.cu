@@ -16,7 +16,10 @@
 //     mbarrier of the accumulator buffer in use. Warp 5 also allocates and frees tensor memory
 //     (all 512 columns: two accumulator buffers, so one block per SM).
 //   warps 0-3: epilogue. Each owns 32 of the 128 accumulator lanes (rows): tcgen05.ld brings
-//     32 columns at a time into registers, the epilogue is applied and the row piece stored.
+//     32 columns at a time into registers; the piece crosses a swizzled 4 KB stage in shared memory
+//     so that eight lanes carry one row piece out together, and bias / GELU / residual are applied
+//     on the way (EpilogueLane below). Outputs whose rows are not 16-byte aligned take the plain
+//     way: every lane stores its own row 16 columns at a time.
 // Rows and columns beyond M, N and K are zero-filled by TMA on the way in and skipped on the
 // way out. Every mbarrier wait is bounded: a wait that runs out sets MX_STATUS_WAIT_TIMEOUT in
 // the status word and the role moves on, so the block always reaches the point where tensor
@@ -202,49 +205,6 @@ __device__ __forceinline__ void store_piece(const unsigned (&r)[16], const float
             if (bias) v += bias[nbase + j];
             if (mode == 1) v = gelu_tanh_fast(v);
             o[j] = __float2bfloat16_rn(v);
-        }
-    }
-}
-
-// One thread's row of a 128 x bn accumulator (tensor memory lane = row, columns from tbase): brought
-// out 16 columns at a time, the epilogue applied, stored. Shared by the kernels with 256-row tiles.
-__device__ __forceinline__ void drain_accumulator_row(unsigned tbase, int row, int n0, int bn,
-                                                      const float* __restrict__ bias, const float* residual,
-                                                      void* out, int ldo, int M, int N, int mode) {
-    const size_t row_base = (size_t)row * ldo;
-    for (int c0 = 0; c0 < bn; c0 += 64) {
-        // the residual of up to four pieces first, so that the loads are in flight together
-        const bool fast = mode == 2 && row < M && n0 + c0 + 64 <= N && c0 + 64 <= bn &&
-                          ((row_base + n0 + c0) % 4) == 0;
-        float4 res[16];
-        if (fast) {
-            const float4* src = reinterpret_cast<const float4*>(residual + row_base + n0 + c0);
-#pragma unroll
-            for (int q = 0; q < 16; ++q) res[q] = src[q];
-        }
-#pragma unroll
-        for (int piece = 0; piece < 4; ++piece) {
-            const int c = c0 + 16 * piece;
-            if (c >= bn) break;
-            unsigned r[16];
-            tmem_load16(tbase + (unsigned)c, r);
-            if (row >= M || n0 + c >= N) continue;
-            if (fast) {
-                float* o = reinterpret_cast<float*>(out) + row_base + n0 + c;
-#pragma unroll
-                for (int j = 0; j < 16; j += 4) {
-                    float4 v = res[4 * piece + j / 4];
-                    v.x += __uint_as_float(r[j]); v.y += __uint_as_float(r[j + 1]);
-                    v.z += __uint_as_float(r[j + 2]); v.w += __uint_as_float(r[j + 3]);
-                    if (bias) {
-                        v.x += bias[n0 + c + j]; v.y += bias[n0 + c + j + 1];
-                        v.z += bias[n0 + c + j + 2]; v.w += bias[n0 + c + j + 3];
-                    }
-                    *reinterpret_cast<float4*>(o + j) = v;
-                }
-            } else {
-                store_piece(r, bias, residual, out, row_base + n0 + c, n0 + c, N, mode);
-            }
         }
     }
 }
