@@ -466,9 +466,11 @@ template <bool F32>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     const float* __restrict__ bias, const float* residual, void* out, int ldo, int M,
-                    int N, int K, int bn, int mode, int staged, int* status) {
+                    int N, int K, int bn, int mode, int staged, int kk, int* status) {
     const unsigned a_bytes = TC_BM * TC_BK * 2, w_bytes = (unsigned)bn * TC_BK * 2;
-    const unsigned stage_bytes = a_bytes + w_bytes;
+    // kk slices of K (64 wide each) share a stage and its barrier: with narrow tiles the fixed cost of a
+    // stage (a barrier round trip in the producer and in the issuer) is what bounds the main loop
+    const unsigned stage_bytes = (unsigned)kk * (a_bytes + w_bytes);
     extern __shared__ unsigned char tc_smem_raw[];
     // stages must start on a 1024-byte boundary for the 128-byte swizzle
     unsigned char* tiles = reinterpret_cast<unsigned char*>(
@@ -476,7 +478,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     __shared__ TcShared sh;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int k_slices = (K + TC_BK - 1) / TC_BK;
+    const int k_slices = ((K + TC_BK - 1) / TC_BK + kk - 1) / kk;          // in stages
     const int tiles_m = (M + TC_BM - 1) / TC_BM, tiles_n = (N + bn - 1) / bn;
     const int n_tiles = tiles_m * tiles_n;
 
@@ -516,8 +518,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     if (!alive) break;
                     tc_mbar_expect_tx(&sh.full[s], stage_bytes);
                     unsigned char* a_tile = tiles + (size_t)s * stage_bytes;
-                    tma_load_2d(a_tile, &map_a, ks * TC_BK, m0, &sh.full[s]);
-                    tma_load_2d(a_tile + a_bytes, &map_w, ks * TC_BK, n0, &sh.full[s]);
+                    for (int h = 0; h < kk; ++h) {          // columns beyond K arrive as zeros
+                        tma_load_2d(a_tile + h * a_bytes, &map_a, (ks * kk + h) * TC_BK, m0, &sh.full[s]);
+                        tma_load_2d(a_tile + kk * a_bytes + h * w_bytes, &map_w, (ks * kk + h) * TC_BK, n0,
+                                    &sh.full[s]);
+                    }
                 }
             }
             // no copy of this block may still be in flight when it ends: wait (bounded) for the
@@ -543,11 +548,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     if (!alive) break;
                     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
                     const unsigned char* a_tile = tiles + (size_t)s * stage_bytes;
-                    const unsigned long long adesc = umma_desc(a_tile);
-                    const unsigned long long bdesc = umma_desc(a_tile + a_bytes);
+                    for (int h = 0; h < kk; ++h) {
+                        const unsigned long long adesc = umma_desc(a_tile + h * a_bytes);
+                        const unsigned long long bdesc = umma_desc(a_tile + kk * a_bytes + h * w_bytes);
 #pragma unroll
-                    for (int k = 0; k < TC_BK / 16; ++k)   // 16 elements = 32 bytes further along K
-                        umma_bf16(tmem_acc, adesc + 2 * k, bdesc + 2 * k, idesc, (ks | k) != 0);
+                        for (int k = 0; k < TC_BK / 16; ++k)   // 16 elements = 32 bytes further along K
+                            umma_bf16(tmem_acc, adesc + 2 * k, bdesc + 2 * k, idesc, (ks | h | k) != 0);
+                    }
                     umma_commit(&sh.empty[s]);
                 }
                 if (alive) umma_commit(&sh.acc_full[buf]);   // arrives when the tile's MMAs are done
@@ -1171,7 +1178,7 @@ extern "C" int mx_gemm_tcgen05(const void* A, const void* W, const float* bias, 
     }
     static bool attribute_set = false;
     if (!attribute_set) {
-        const size_t most = (size_t)TC_STAGES * (TC_BM + 256) * TC_BK * 2 + TC_STAGING + 1024;
+        const size_t most = 226 * 1024;
         const size_t most_wide = (size_t)TCW_STAGES * (TCW_BM + 256) * TC_BK * 2 + TCW_STAGING + 1024;
         cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              (int)most);
@@ -1230,14 +1237,17 @@ extern "C" int mx_gemm_tcgen05(const void* A, const void* W, const float* bias, 
     if (rc != MX_OK) return rc;
     rc = make_map(&map_w, W, N, K, ldw, bn);
     if (rc != MX_OK) return rc;
-    const size_t smem = (size_t)TC_STAGES * (TC_BM + bn) * TC_BK * 2 + TC_STAGING + 1024;
+    // two slices of K per stage where four such stages fit (tiles of up to 64 columns)
+    int kk = 2 * TC_STAGES * (TC_BM + bn) * TC_BK * 2 + TC_STAGING + 1024 <= 226 * 1024 ? 2 : 1;
+    if (const char* force = getenv("MATRICXON_GEMM_KK")) kk = atoi(force) == 2 && kk == 2 ? 2 : 1;
+    const size_t smem = (size_t)kk * TC_STAGES * (TC_BM + bn) * TC_BK * 2 + TC_STAGING + 1024;
     const long long tiles = (long long)((M + TC_BM - 1) / TC_BM) * ((N + bn - 1) / bn);
     const int grid = (int)(tiles < n_sm ? tiles : n_sm);
     if (f32_out)
         gemm_tcgen05_kernel<true><<<grid, TC_THREADS, smem, stream>>>(map_a, map_w, bias, residual, out, ldo, M, N, K,
-                                                                      bn, mode, vector_ok ? 1 : 0, status);
+                                                                      bn, mode, vector_ok ? 1 : 0, kk, status);
     else
         gemm_tcgen05_kernel<false><<<grid, TC_THREADS, smem, stream>>>(map_a, map_w, bias, residual, out, ldo, M, N, K,
-                                                                       bn, mode, vector_ok ? 1 : 0, status);
+                                                                       bn, mode, vector_ok ? 1 : 0, kk, status);
     return mx_launch_status();
 }
