@@ -47,7 +47,7 @@ def run(name, rows, n, kd, mode):
         torch.cuda.synchronize()
     us = start.elapsed_time(end) * 1000 / (5 * reps)
     mbytes = n * kd * 2 / 1e6
-    print(f"{name:7s} rows {rows} N {n:6d} K {kd:6d}: {us:7.2f} us  {mbytes / us / 1e3:5.2f} TB/s  "
+    print(f"{name:7s} rows {rows} N {n:6d} K {kd:6d}: {us:7.2f} us  {mbytes / us:5.2f} TB/s  "
           f"({copies} copies of {mbytes:.1f} MB)", flush=True)
 
 
