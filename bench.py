@@ -287,6 +287,22 @@ def main() -> int:
         engine.core.cache.free_request("prefill")
         if rep >= 2:
             prefill_ms.append(begin.elapsed_time(end))
+    # the same prompt in portions of 256 tokens, one step each (the scheduler's default portion)
+    portion_ms = []
+    for rep in range(0 if (args.skip_prefill or args.skip_points) else 3):
+        engine.core.cache.add_request("portions")
+        torch.cuda.synchronize()
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        for start in range(0, PREFILL_TOKENS, 256):
+            last = start + 256 >= PREFILL_TOKENS
+            engine.core.runner.run([StepEntry("portions", prompt[start:start + 256], [255] if last else [])])
+        end.record()
+        torch.cuda.synchronize()
+        engine.core.cache.free_request("portions")
+        portion_ms.append(begin.elapsed_time(end))
+    if portion_ms:
+        points["prefill_2048_in_256_token_steps"] = round(PREFILL_TOKENS / (min(portion_ms) * 1e-3), 1)
     pf_ms = sorted(prefill_ms)[len(prefill_ms) // 2] if prefill_ms else float("nan")
     pf_flops = prefill_flops(config, n_layers, PREFILL_TOKENS)
     pf_frac = pf_flops / (pf_ms * 1e-3) / (peaks["bf16_tflops"] * 1e12)
