@@ -93,6 +93,9 @@ struct AtParams {
     const int* context_lens;     // [seqs]
     const int* tiles;            // [n_tiles][2]: (sequence, first token of the tile within the sequence)
     __nv_bfloat16* out;          // [tokens][out_stride]
+    float* part_o;               // n_splits > 1: [tokens][heads][splits][128] unnormalised sums
+    float* part_ml;              // n_splits > 1: [tokens][heads][splits][2] (maximum in natural-log units, sum)
+    int n_splits;                // blockIdx.z takes every n_splits-th share of a tile's chunks of keys
     int* status;
     long long n_pages;
     int out_stride, bt_stride, n_heads, n_kv_heads, group, tokens_per_tile, page_size, page_shift, window;
@@ -257,8 +260,23 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
     if (n_tok <= 0) return;                                         // nothing was allocated yet
     const int hi_tile = ctx + tok0 + n_tok - 1;
     const int lo_tile = p.window > 0 ? max(0, ctx + tok0 - p.window + 1) : 0;
-    const int c_begin = lo_tile / AT_KEYS;
-    const int n_chunks = hi_tile / AT_KEYS + 1 - c_begin;
+    // the tile's chunks of 128 keys, and this block's share of them when the keys are split (few tiles, a
+    // long context: the shares are merged by mx_attention_merge_bf16); a share may be empty
+    const int first_chunk = lo_tile / AT_KEYS;
+    const int all_chunks = hi_tile / AT_KEYS + 1 - first_chunk;
+    const int per_split = (all_chunks + p.n_splits - 1) / p.n_splits;
+    const int c_begin = first_chunk + (int)blockIdx.z * per_split;
+    const int n_chunks = max(0, min(per_split, all_chunks - (int)blockIdx.z * per_split));
+    if (n_chunks == 0) {                                            // an empty share: tell the merge, touch nothing else
+        const int t_in = tid / p.group, h_in = tid - t_in * p.group;
+        if (tid < p.tokens_per_tile * p.group && t_in < n_tok) {
+            const size_t base = ((size_t)(q_start + tok0 + t_in) * p.n_heads + (size_t)(kh * p.group + h_in)) *
+                                    p.n_splits + blockIdx.z;
+            p.part_ml[base * 2] = -INFINITY;
+            p.part_ml[base * 2 + 1] = 0.f;
+        }
+        return;
+    }
     const int pages_per_chunk = AT_KEYS >> p.page_shift;
     const unsigned page_bytes = (unsigned)(p.page_size * AT_HD * 2);
 
@@ -558,7 +576,30 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
         AT_MARK(6);
         pv_consumed_through(n_chunks);
         AT_MARK(7);
-        if (alive) {
+        if (alive && p.n_splits > 1) {
+            // a share of the keys: the unnormalised sums, the reference maximum and the sum of weights
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            const size_t base = ((size_t)(q_start + tok0 + t_in) * p.n_heads + (size_t)(kh * p.group + h_in)) *
+                                    p.n_splits + blockIdx.z;
+            const bool any = n_chunks > 0 && l_run > 0.f;
+            if (valid) {
+                p.part_ml[base * 2] = any ? m_ref * 0.6931471805599453f : -INFINITY;
+                p.part_ml[base * 2 + 1] = any ? l_run : 0.f;
+            }
+            if (n_chunks > 0) {                                          // warp-uniform: tensor memory holds sums
+#pragma unroll
+                for (int piece = 0; piece < 4; ++piece) {
+                    float o[32];
+                    tmem_load32(tmem_o + lane_base + 32 * piece, o);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+                    if (valid && any) {
+                        float4* dst4 = reinterpret_cast<float4*>(p.part_o + base * AT_HD + 32 * piece);
+#pragma unroll
+                        for (int c = 0; c < 32; c += 4) dst4[c / 4] = make_float4(o[c], o[c + 1], o[c + 2], o[c + 3]);
+                    }
+                }
+            }
+        } else if (alive) {
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
             const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
             __nv_bfloat16* dst = p.out + (size_t)(q_start + tok0 + t_in) * p.out_stride +
@@ -632,12 +673,20 @@ extern "C" int mx_attention_tc_marks(unsigned long long* out, int reset) {
 // tokens_per_tile = 128 / group tokens of that sequence. q: [n_tokens][q_stride] with query head h
 // at column h * 128. cache: [n_pages][2][kv heads][page_size * 128], keys [slot][dim], values
 // [dim][slot]. Every token of every listed sequence must be covered by tiles.
-extern "C" int mx_paged_attention_tc(const void* q, int q_stride, const void* cache, long long n_pages,
-                                     int page_size, const int* block_tables, int bt_stride, const int* cu_q,
-                                     const int* context_lens, const int* tiles, int n_tiles, int n_tokens,
-                                     int n_heads, int n_kv_heads, int head_dim, int window, float scale,
-                                     void* out, int out_stride, int* status, cudaStream_t stream) {
+extern "C" int mx_attention_merge_bf16(const float* part_o, const float* part_ml, void* out, int out_stride,
+                                       int n_tokens, int n_heads, int head_dim, int n_splits, cudaStream_t stream);
+
+// n_splits > 1: every tile's keys are shared out between n_splits blocks, whose partial results go to
+// `scratch` ((tokens x heads x splits) x (128 + 2) floats) and are merged by mx_attention_merge_bf16.
+extern "C" int mx_paged_attention_tc_split(const void* q, int q_stride, const void* cache, long long n_pages,
+                                           int page_size, const int* block_tables, int bt_stride, const int* cu_q,
+                                           const int* context_lens, const int* tiles, int n_tiles, int n_tokens,
+                                           int n_heads, int n_kv_heads, int head_dim, int window, float scale,
+                                           void* out, int out_stride, int n_splits, float* scratch, int* status,
+                                           cudaStream_t stream) {
     if (n_tiles <= 0 || n_tokens <= 0) return MX_OK;
+    if (n_splits < 1 || n_splits > 64) MX_REFUSE("tcgen05 attention: %d key splits", n_splits);
+    if (n_splits > 1 && scratch == nullptr) MX_REFUSE("tcgen05 attention: key splits without scratch memory");
     if (head_dim != AT_HD) MX_REFUSE("tcgen05 attention is built for head_dim 128, not %d", head_dim);
     if (page_size != 16 && page_size != 32) MX_REFUSE("tcgen05 attention takes pages of 16 or 32 slots, not %d", page_size);
     if (n_kv_heads <= 0 || n_heads % n_kv_heads != 0)
@@ -682,6 +731,9 @@ extern "C" int mx_paged_attention_tc(const void* q, int q_stride, const void* ca
     p.bt_stride = bt_stride; p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.group = group;
     p.tokens_per_tile = tokens_per_tile; p.page_size = page_size; p.page_shift = page_size == 16 ? 4 : 5;
     p.window = window; p.scale_log2 = scale * 1.4426950408889634f;
+    p.n_splits = n_splits;
+    p.part_o = scratch;
+    p.part_ml = scratch ? scratch + (size_t)n_tokens * n_heads * n_splits * AT_HD : nullptr;
     const size_t smem = (size_t)(2 + 2 * AT_STAGES * 2) * AT_TILE + 1024;
     static bool attribute_set = false;
     if (!attribute_set) {
@@ -689,6 +741,18 @@ extern "C" int mx_paged_attention_tc(const void* q, int q_stride, const void* ca
         if (e != cudaSuccess) MX_REFUSE("tcgen05 attention: cannot reserve %zu bytes of shared memory", smem);
         attribute_set = true;
     }
-    attention_tc_kernel<<<dim3(n_tiles, n_kv_heads), AT_THREADS, smem, stream>>>(q_map, k_map, v_map, p);
-    return mx_launch_status();
+    attention_tc_kernel<<<dim3(n_tiles, n_kv_heads, n_splits), AT_THREADS, smem, stream>>>(q_map, k_map, v_map, p);
+    const int rc = mx_launch_status();
+    if (rc != MX_OK || n_splits == 1) return rc;
+    return mx_attention_merge_bf16(p.part_o, p.part_ml, out, out_stride, n_tokens, n_heads, AT_HD, n_splits, stream);
+}
+
+extern "C" int mx_paged_attention_tc(const void* q, int q_stride, const void* cache, long long n_pages,
+                                     int page_size, const int* block_tables, int bt_stride, const int* cu_q,
+                                     const int* context_lens, const int* tiles, int n_tiles, int n_tokens,
+                                     int n_heads, int n_kv_heads, int head_dim, int window, float scale,
+                                     void* out, int out_stride, int* status, cudaStream_t stream) {
+    return mx_paged_attention_tc_split(q, q_stride, cache, n_pages, page_size, block_tables, bt_stride, cu_q,
+                                       context_lens, tiles, n_tiles, n_tokens, n_heads, n_kv_heads, head_dim, window,
+                                       scale, out, out_stride, 1, nullptr, status, stream);
 }

@@ -17,6 +17,7 @@ two-phase write of the reference's cache (app/runtime/kv_cache.py:53-72).
 
 from __future__ import annotations
 
+import gc
 import os
 from dataclasses import dataclass, field
 
@@ -124,6 +125,18 @@ class StepContext:
         if self.capturing:
             return n_splits, torch.empty((need + 3) // 4, dtype=torch.float32,
                                          device=self.token_ids.device)
+        return n_splits, self._runner.scratch_buffer(need)
+
+    def tc_tile_splits(self, n_tiles: int, alone: bool, n_heads: int, n_kv_heads: int, head_dim: int,
+                       window: int | None) -> tuple[int, torch.Tensor | None]:
+        """Key splits for the tcgen05 attention (one block per SM, chunks of 128 keys): a short
+        portion after a long context has few tiles with many chunks each."""
+        items = max(n_tiles * n_kv_heads, 1)
+        span = self.max_kv_len if window is None else min(self.max_kv_len, window)
+        n_splits = min(self._runner.sm_count // items, (span // 128 + 1) // 3, 8) if alone else 1
+        if n_splits < 2:
+            return 1, None
+        need = kernels.attention_scratch_bytes(self.n_tokens, n_heads, head_dim, n_splits)
         return n_splits, self._runner.scratch_buffer(need)
 
     def attention_splits(self, n_heads: int, n_kv_heads: int, head_dim: int,
@@ -412,8 +425,16 @@ class StepRunner:
                 torch.cuda.synchronize()
                 graph = torch.cuda.CUDAGraph()
                 ctx.capturing = True
-                with torch.cuda.graph(graph, pool=self._graph_pool):
-                    static_logits = self._forward(ctx, decode_rows=True)
+                # no garbage collection inside the capture: a collected object may free pinned memory or
+                # destroy a stream-ordered resource, which invalidates a capture in progress
+                gc_was_on = gc.isenabled()
+                gc.disable()
+                try:
+                    with torch.cuda.graph(graph, pool=self._graph_pool):
+                        static_logits = self._forward(ctx, decode_rows=True)
+                finally:
+                    if gc_was_on:
+                        gc.enable()
                 ctx.capturing = False
             finally:
                 kernels.set_chained_launch(False)

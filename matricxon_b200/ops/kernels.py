@@ -351,11 +351,13 @@ def tc_attention_supported(dtype: torch.dtype, head_dim: int, page_size: int, q_
 def paged_attention_tc(q: torch.Tensor, q_stride: int, cache: torch.Tensor, block_tables: torch.Tensor,
                        cu_q: torch.Tensor, context_lens: torch.Tensor, tiles: torch.Tensor, n_tiles: int,
                        n_tokens: int, n_heads: int, n_kv_heads: int, head_dim: int, window: int | None,
-                       scale: float, out: torch.Tensor, status: torch.Tensor) -> None:
+                       scale: float, out: torch.Tensor, status: torch.Tensor, n_splits: int = 1,
+                       scratch: torch.Tensor | None = None) -> None:
     """Attention of prompt portions on tcgen05 (bfloat16, head_dim 128, pages of 16 or 32).
     ``tiles`` is int32 [n_tiles, 2]: (sequence, first token) of tiles of 128 // group tokens
     (``attention_tile_lists(..., token_tiles=True)``); ``q`` holds the step's rows, query head h
-    at column h * head_dim."""
+    at column h * head_dim. ``n_splits`` > 1 shares every tile's keys out between that many blocks
+    (few tiles, long contexts); ``scratch`` (float32, ``attention_scratch_bytes``) takes their parts."""
     _need(q, "q", torch.bfloat16, contiguous=False)
     _need(cache, "cache", torch.bfloat16)
     for name, tensor in (("block_tables", block_tables), ("cu_q", cu_q),
@@ -366,11 +368,15 @@ def paged_attention_tc(q: torch.Tensor, q_stride: int, cache: torch.Tensor, bloc
     assert tuple(cache.shape[1:]) == (2, n_kv_heads, page_size, head_dim), cache.shape
     assert out.shape[1] == n_heads * head_dim and out.shape[0] >= n_tokens and q.shape[0] >= n_tokens
     assert tiles.numel() >= 2 * n_tiles
-    check(library().mx_paged_attention_tc(
+    if n_splits > 1:
+        _need(scratch, "scratch", torch.float32)
+        assert scratch.numel() * 4 >= attention_scratch_bytes(n_tokens, n_heads, head_dim, n_splits)
+    check(library().mx_paged_attention_tc_split(
         _ptr(q), q_stride, _ptr(cache), cache.shape[0], page_size, _ptr(block_tables),
         block_tables.stride(0), _ptr(cu_q), _ptr(context_lens), _ptr(tiles), n_tiles, n_tokens,
         n_heads, n_kv_heads, head_dim, int(window or 0), float(scale), _ptr(out), out.stride(0),
-        _ptr(status), _stream()), "paged_attention_tc")
+        int(n_splits), _ptr(scratch) if n_splits > 1 else None, _ptr(status), _stream()),
+        "paged_attention_tc")
     _launched()
 
 

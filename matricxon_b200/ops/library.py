@@ -38,6 +38,7 @@ _SIGNATURES: dict[str, tuple[list, object]] = {
     "mx_attention_scratch_bytes": ([I, I, I, I], L),
     "mx_paged_attention_mma": ([P, I, P, L, I, P, I, P, P, P, I, I, I, I, I, I, I, F, P, I, I, P, P, P], I),
     "mx_paged_attention_tc": ([P, I, P, L, I, P, I, P, P, P, I, I, I, I, I, I, F, P, I, P, P], I),
+    "mx_paged_attention_tc_split": ([P, I, P, L, I, P, I, P, P, P, I, I, I, I, I, I, F, P, I, I, P, P, P], I),
     "mx_paged_attention": ([P, I, I, P, L, I, P, I, P, P, I, I, I, I, I, F, P, I, I, P, P, P], I),
 }
 

@@ -105,10 +105,13 @@ class PagedAttention(Mixer):
                 if n_tiles == 0:
                     continue
                 if on_tc and not is_narrow:
+                    n_splits, scratch = ctx.tc_tile_splits(n_tiles, n_narrow == 0, spec.num_heads,
+                                                           spec.num_kv_heads, spec.head_dim, spec.window)
                     kernels.paged_attention_tc(qkv, qkv.stride(0), binding.kv, group.block_tables, ctx.cu_q,
                                                ctx.context_lens, tiles, n_tiles, ctx.n_tokens,
                                                spec.num_heads, spec.num_kv_heads, spec.head_dim,
-                                               spec.window, spec.scale, attn, ctx.status)
+                                               spec.window, spec.scale, attn, ctx.status,
+                                               n_splits=n_splits, scratch=scratch)
                     continue
                 alone = (n_wide == 0) if is_narrow else (n_narrow == 0)
                 n_splits, scratch = ctx.tile_splits(n_tiles, is_narrow, alone, spec.num_heads,

@@ -342,8 +342,10 @@ def run_attention(k, q, cache, tables, tok_seq, positions, heads, kv_heads, dim,
         if not tiles:
             continue
         if impl == "tc" and not is_narrow:          # prompt portions on the tcgen05 kernel
+            splits = n_splits if not others else 1
             k.paged_attention_tc(q, q.stride(0), cache, tables, as_int(cu_q), as_int(context), as_int(tiles),
-                                 len(tiles) // 2, n, heads, kv_heads, dim, window, scale, out, st)
+                                 len(tiles) // 2, n, heads, kv_heads, dim, window, scale, out, st,
+                                 n_splits=splits, scratch=scratch if splits > 1 else None)
             continue
         splits = n_splits if not others else 1      # splits need a launch that covers every token
         k.paged_attention_mma(q, q.stride(0), cache, tables, as_int(cu_q), as_int(context), as_int(tiles),
@@ -425,6 +427,19 @@ def test_tcgen05_attention_prompt_portions(heads, kv_heads, page_size, window):
         assert torch.isfinite(got).all(), f"case {index}: non-finite output at rows {torch.nonzero(~torch.isfinite(got).all(dim=1)).flatten()[:8].tolist()}"
         worst = (got - ref).abs().max(dim=1).values
         assert torch.allclose(got, ref, **tol(torch.bfloat16)), (index, int(worst.argmax()), float(worst.max()))
+    # keys shared out between blocks (portions only, so that the merge covers every row): more splits than
+    # some tiles have chunks, a window that leaves shares empty
+    for index, (seq_lens, q_lens, n_splits) in enumerate([([700, 1300], [100, 130], 3), ([2100], [40], 8),
+                                                          ([300, 129], [300, 17], 5)]):
+        q, cache, tables, tok_seq, positions, dense = paged_case(
+            torch.bfloat16, heads, kv_heads, dim, page_size, seq_lens, q_lens, seed=50 + heads + index)
+        ref = reference_attention(dense, q_lens, seq_lens, scale, window)
+        out, st = run_attention(k, q, cache, tables, tok_seq, positions, heads, kv_heads, dim,
+                                window, scale, n_splits, impl="tc")
+        got = out.double().cpu()
+        assert st == 0 and torch.isfinite(got).all(), f"split case {index}"
+        worst = (got - ref).abs().max(dim=1).values
+        assert torch.allclose(got, ref, **tol(torch.bfloat16)), ("split", index, int(worst.argmax()), float(worst.max()))
 
 
 @pytest.mark.parametrize("edge", ["window_first_visible", "just_outside_window", "page_last_slot",
