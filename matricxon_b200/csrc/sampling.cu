@@ -80,12 +80,28 @@ __device__ unsigned radix_select(const float* work, int vocab, unsigned floor_ke
     for (int pass = 3; pass >= 0; --pass) {
         for (int b = threadIdx.x; b < 256; b += SAMPLE_THREADS) hist[b] = 0;
         __syncthreads();
-        for (int i = threadIdx.x; i < vocab; i += SAMPLE_THREADS) {
-            const float x = work[i];
+        // Scores of one row sit in a narrow range, so most of them share a bucket in the upper passes:
+        // the lanes of a warp that meet in a bucket add up among themselves first (integer sums: the order
+        // does not matter) and one of them does the atomic.
+        const int lane = threadIdx.x & 31;
+        for (int i0 = 0; i0 < vocab; i0 += SAMPLE_THREADS) {        // the same trip count for every lane
+            const int i = i0 + threadIdx.x;
+            const float x = i < vocab ? work[i] : 0.f;
             const unsigned key = order_key(x);
-            if (key < floor_key || (key & mask) != prefix) continue;
-            const unsigned long long add = BY_WEIGHT ? fixed_weight(x, peak) : 1ull;
-            atomicAdd(&hist[(key >> (8 * pass)) & 255u], add);
+            const bool counted = i < vocab && key >= floor_key && (key & mask) == prefix;
+            const unsigned bucket = counted ? ((key >> (8 * pass)) & 255u) : 0xffffffffu;
+            const unsigned peers = __match_any_sync(0xffffffffu, bucket);
+            unsigned long long add = 1ull;
+            if (BY_WEIGHT) {
+                const unsigned long long w = counted ? fixed_weight(x, peak) : 0ull;
+                const unsigned lo = __reduce_add_sync(peers, (unsigned)(w & 0xffffu));
+                const unsigned mid = __reduce_add_sync(peers, (unsigned)((w >> 16) & 0xffffu));
+                const unsigned hi = __reduce_add_sync(peers, (unsigned)(w >> 32));
+                add = (unsigned long long)lo + ((unsigned long long)mid << 16) + ((unsigned long long)hi << 32);
+            } else {
+                add = (unsigned long long)__popc(peers);
+            }
+            if (counted && lane == __ffs(peers) - 1) atomicAdd(&hist[bucket], add);
         }
         __syncthreads();
         if (threadIdx.x == 0) {
