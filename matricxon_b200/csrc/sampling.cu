@@ -104,15 +104,33 @@ __device__ unsigned radix_select(const float* work, int vocab, unsigned floor_ke
             if (counted && lane == __ffs(peers) - 1) atomicAdd(&hist[bucket], add);
         }
         __syncthreads();
-        if (threadIdx.x == 0) {
-            unsigned long long before = 0;
-            int chosen = -1;
-            for (int b = 255; b >= 0; --b) {
-                if (before + hist[b] >= rank) { chosen = b; break; }
-                before += hist[b];
+        if (threadIdx.x < 32) {
+            // warp 0 walks the histogram from the top: lane l owns buckets 255 - 8 l ... 248 - 8 l
+            const int top = 255 - 8 * lane;
+            unsigned long long mine = 0;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) mine += hist[top - j];
+            unsigned long long incl = mine;                  // sum over this lane and the lanes above it in rank
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const unsigned long long up = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += up;
             }
-            shared_u32[0] = (unsigned)(chosen + 1);          // 0 means: total below rank
-            shared_u64[0] = rank - before;
+            const bool here = incl >= rank && incl - mine < rank;   // the rank falls among this lane's buckets
+            if (here) {
+                unsigned long long before = incl - mine;
+                int chosen = top;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    chosen = top - j;
+                    if (before + hist[chosen] >= rank) break;
+                    before += hist[chosen];
+                }
+                shared_u32[0] = (unsigned)(chosen + 1);
+                shared_u64[0] = rank - before;
+            }
+            const unsigned long long total = __shfl_sync(0xffffffffu, incl, 31);
+            if (lane == 0 && total < rank) shared_u32[0] = 0u;   // 0 means: total below rank
         }
         __syncthreads();
         if (shared_u32[0] == 0) return 0u;
