@@ -222,37 +222,46 @@ sample_kernel(const float* __restrict__ logits, long long row_stride, int vocab,
         if (cut > floor_key) floor_key = cut;
     }
 
-    // inverse CDF in vocabulary order over what is kept
-    const int chunk = (vocab + SAMPLE_THREADS - 1) / SAMPLE_THREADS;
-    const int begin = min(vocab, tid * chunk), end = min(vocab, begin + chunk);
-    unsigned long long local = 0;
-    for (int i = begin; i < end; ++i)
-        if (order_key(work[i]) >= floor_key) local += fixed_weight(work[i], peak);
-    // exclusive scan of `local` over threads
-    unsigned long long incl = local;
+    // inverse CDF in vocabulary order over what is kept: warp w owns the contiguous segment
+    // [w * seg, (w + 1) * seg) and reads it 32 neighbours at a time
     const int lane = tid & 31, warp = tid >> 5;
+    const int seg = ((vocab + SAMPLE_THREADS / 32 - 1) / (SAMPLE_THREADS / 32) + 31) & ~31;
+    const int begin = min(vocab, warp * seg), end = min(vocab, begin + seg);
+    unsigned long long local = 0;
+    for (int i = begin + lane; i < end; i += 32)
+        if (order_key(work[i]) >= floor_key) local += fixed_weight(work[i], peak);
 #pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-        const unsigned long long up = __shfl_up_sync(0xffffffffu, incl, o);
-        if (lane >= o) incl += up;
-    }
+    for (int o = 16; o > 0; o >>= 1) local += __shfl_xor_sync(0xffffffffu, local, o);
     __syncthreads();
-    if (lane == 31) sum_scratch[warp] = incl;
+    if (lane == 0) sum_scratch[warp] = local;
     if (tid == 0) found_index = 0x7fffffff;
     __syncthreads();
-    unsigned long long warp_base = 0, total = 0;
+    unsigned long long running = 0, total = 0;
     for (int w = 0; w < SAMPLE_THREADS / 32; ++w) {
-        if (w < warp) warp_base += sum_scratch[w];
+        if (w < warp) running += sum_scratch[w];
         total += sum_scratch[w];
     }
-    unsigned long long running = warp_base + incl - local;
     const double target = (double)uniform[row] * (double)total;
     int last_kept = -1;
-    for (int i = begin; i < end; ++i) {
-        if (order_key(work[i]) < floor_key) continue;
-        last_kept = i;
-        running += fixed_weight(work[i], peak);
-        if ((double)running > target) { atomicMin(&found_index, i); break; }
+    bool found = false;
+    for (int i0 = begin; i0 < end && !found; i0 += 32) {              // a warp-uniform loop
+        const int i = i0 + lane;
+        const bool kept = i < end && order_key(work[i]) >= floor_key;
+        const unsigned any = __ballot_sync(0xffffffffu, kept);
+        if (any == 0u) continue;
+        last_kept = max(last_kept, i0 + 31 - __clz(any));
+        unsigned long long incl = kept ? fixed_weight(work[i], peak) : 0ull;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const unsigned long long up = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += up;
+        }
+        const unsigned hit = __ballot_sync(0xffffffffu, kept && (double)(running + incl) > target);
+        if (hit != 0u) {
+            if (lane == 0) atomicMin(&found_index, i0 + __ffs(hit) - 1);
+            found = true;
+        }
+        running += __shfl_sync(0xffffffffu, incl, 31);
     }
     __syncthreads();
     if (found_index == 0x7fffffff) {
