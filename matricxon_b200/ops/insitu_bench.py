@@ -23,6 +23,7 @@ def main() -> None:
 
     def timed(label: str) -> float:
         runner._graphs.clear()                      # the next step captures anew, with the patched launcher
+        runner._graph_pool = None                   # (the graphs' memory pool goes with the last of them)
         ms = bench.time_decode(engine, ids, config.vocab_size, 24, 4)
         print(f"{label:26s} {ms * 1000:9.1f} us a step", flush=True)
         return ms
@@ -45,6 +46,7 @@ def main() -> None:
     base = timed("plain step")
     cases = [("LayerNorm (both)", "layernorm", None), ("QKV + rotation", "gemm_skinny_rope", None),
              ("attention + merge", "paged_attention_mma", None), ("O", "gemm_skinny", weight_is(h, h)),
+             ("library product (17-128 rows)", "epilogue", None),
              ("c_fc", "gemm_skinny", weight_is(i, h)), ("c_proj", "gemm_skinny", weight_is(h, i)),
              ("head (once a step)", "gemm_skinny", lambda a, w, *r, **kw: w.shape[0] == config.vocab_size)]
     for label, name, condition in cases:
