@@ -230,7 +230,7 @@ def main() -> int:
 
     import torch
 
-    from matricxon_b200 import GenerationRequest, SamplingConfig
+    from matricxon_b200 import SamplingConfig
 
     if not torch.cuda.is_available():
         print("bench.py: no CUDA device")

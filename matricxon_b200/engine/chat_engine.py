@@ -15,8 +15,6 @@ import os
 from pathlib import Path
 from typing import Iterable, Iterator
 
-import torch
-
 from matricxon_b200.engine.core import EngineCore, load_model
 from matricxon_b200.engine.request import GenerationRequest, GenerationResult, as_token_list
 from matricxon_b200.engine.scheduler import FINISHED, RUNNING, Scheduler, SchedulerConfig, Sequence
