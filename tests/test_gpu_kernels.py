@@ -140,14 +140,15 @@ def test_skinny_gemm_all_epilogues(m, n, k_dim):
 
 
 @pytest.mark.parametrize("mode", [0, 1, 2, 3])
-def test_library_product_with_epilogue(mode):
+@pytest.mark.parametrize("n", [1000, 1002])                  # four columns per thread; one at a time
+def test_library_product_with_epilogue(mode, n):
     from matricxon_b200.ops.linear import linear
 
     torch.manual_seed(mode)
     a = torch.randn(33, 96, device=DEV).bfloat16()
-    w = (torch.randn(1000, 96, device=DEV) / 10).bfloat16()
-    bias = torch.randn(1000, device=DEV)
-    residual = torch.randn(33, 1000, device=DEV)
+    w = (torch.randn(n, 96, device=DEV) / 10).bfloat16()
+    bias = torch.randn(n, device=DEV)
+    residual = torch.randn(33, n, device=DEV)
     acc = a.double().cpu() @ w.double().cpu().T + bias.double().cpu()
     expected = [acc, plain_gelu_tanh(acc), acc + residual.double().cpu(), acc][mode]
     out = linear(a, w, bias, mode, residual=residual.clone() if mode == 2 else None, backend="library")
