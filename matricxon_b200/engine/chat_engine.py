@@ -17,8 +17,15 @@ from typing import Iterable, Iterator
 
 from matricxon_b200.engine.core import EngineCore, load_model
 from matricxon_b200.engine.request import GenerationRequest, GenerationResult, as_token_list
-from matricxon_b200.engine.scheduler import FINISHED, RUNNING, Scheduler, SchedulerConfig, Sequence
-from matricxon_b200.engine.step import StepEntry
+from matricxon_b200.engine.scheduler import (
+    FINISHED,
+    RUNNING,
+    RequestRefused,
+    Scheduler,
+    SchedulerConfig,
+    Sequence,
+)
+from matricxon_b200.engine.step import StepEntry, StepError
 from matricxon_b200.sampling.config import SamplingConfig
 from matricxon_b200.sampling.sampler import BatchSampler
 
@@ -61,7 +68,14 @@ class ChatEngine:
     def add_request(self, input_ids, sampling: SamplingConfig | None = None,
                     request_id: str | None = None) -> str:
         request_id = request_id if request_id is not None else f"req-{next(self._ids)}"
-        self.scheduler.add(request_id, as_token_list(input_ids), sampling or SamplingConfig())
+        tokens = as_token_list(input_ids)
+        vocab = self.model.spec.vocab_size
+        if tokens and not (0 <= min(tokens) and max(tokens) < vocab):
+            raise RequestRefused(f"the prompt holds a token id outside the vocabulary of {vocab}")
+        if request_id in self.scheduler.finished or self.core.cache.has_request(request_id) \
+                or any(s.request_id == request_id for s in self.scheduler.waiting):
+            raise RequestRefused(f"request id {request_id!r} is already in use")
+        self.scheduler.add(request_id, tokens, sampling or SamplingConfig())
         return request_id
 
     def cancel(self, request_id: str) -> bool:
@@ -93,15 +107,26 @@ class ChatEngine:
         ids = self.sampler.device_ids() if samplers else None
         return plan, handle, ids, entries
 
-    def step(self) -> list[tuple[str, int, bool]]:
-        """One scheduled step. Returns (request id, new token, finished) for every request
-        that produced a token.
+    def step(self) -> list[tuple[str, int | None, bool]]:
+        """One scheduled step. Returns (request id, new token, finished) for every request that
+        produced a token, and (request id, None, True) for a request that ended without one (a
+        faulty step, or the end of what the pool can hold).
 
         While every running request decodes, the step after this one is queued on the device
         before this one's ids are read (``Scheduler.plan_ahead``): its token ids come from this
         step's sampler on the device, so the host's work between two steps runs beside the GPU.
         A request that stops at a token of this step has a wasted row in the step ahead; nothing
-        else differs from deciding step by step."""
+        else differs from deciding step by step.
+
+        A step that fails is void for the requests at fault, and the others go on: an entry the
+        host can see to be malformed (a token id outside the vocabulary, ...) ends its own request
+        with ``finish_reason="error"`` before anything is launched, and the rest of the plan runs
+        in the next step; a fault that only a kernel saw cannot be pinned on one request, so every
+        request of that step ends with ``error`` (the reference hands the exception of a failed
+        batch to every reply in it, app/runtime/batch_decode.py:82-83,101-105) and requests outside
+        the step are untouched. Raises ``SchedulerStalled`` rather than returning nothing for ever
+        when requests are left and none can run."""
+        ended_before = set(self.scheduler.finished)
         launched = self._ahead
         self._ahead = None
         if launched is not None and all(e.sequence.status != RUNNING for e in launched[0].entries):
@@ -109,8 +134,16 @@ class ChatEngine:
         if launched is None:
             plan = self.scheduler.schedule()
             if not plan.entries:
-                return []
-            launched = self._launch(plan)
+                return self._ended_since(ended_before, [])
+            try:
+                launched = self._launch(plan)
+            except StepError as error:
+                if not error.request_ids:
+                    raise
+                for planned in plan.entries:
+                    if planned.sequence.request_id in error.request_ids:
+                        self.scheduler.fail(planned.sequence, str(error))
+                return self._ended_since(ended_before, [])
         plan, handle, _ids, entries = launched
         if self.look_ahead and handle is not None:
             ahead = self.scheduler.plan_ahead(plan)
@@ -119,20 +152,37 @@ class ChatEngine:
                 if self.core.runner.can_feed_from_device(ahead_entries):
                     self._ahead = self._launch(ahead, before=launched)
                     self.steps_ahead += 1
-        if handle is not None:
-            sampled = self.sampler.read(handle)
-            self.core.runner.check_status(synchronised=True)
-        else:
-            sampled = []
-            self.core.runner.check_status()
+        try:
+            if handle is not None:
+                sampled = self.sampler.read(handle)
+                self.core.runner.check_status(synchronised=True)
+            else:
+                sampled = []
+                self.core.runner.check_status()
+        except StepError as error:
+            # a kernel met a bad index: what the step wrote and chose is void for all its requests,
+            # and so is the step queued behind it, which holds the same requests
+            self._ahead = None
+            for planned in plan.entries:
+                if planned.sequence.status == RUNNING:
+                    self.scheduler.fail(planned.sequence, str(error))
+            self.steps += 1
+            return self._ended_since(ended_before, [])
         produced = self.scheduler.step_done(plan, sampled)
         self.steps += 1
-        return [(seq.request_id, token, seq.status == FINISHED) for seq, token in produced]
+        return self._ended_since(
+            ended_before, [(seq.request_id, token, seq.status == FINISHED) for seq, token in produced])
+
+    def _ended_since(self, before: set, produced: list) -> list:
+        """``produced`` plus (id, None, True) for requests that ended during this call without a token."""
+        with_token = {rid for rid, _, _ in produced}
+        silent = [rid for rid in self.scheduler.finished if rid not in before and rid not in with_token]
+        return produced + [(rid, None, True) for rid in silent]
 
     def result(self, request_id: str) -> GenerationResult:
         sequence: Sequence = self.scheduler.finished.pop(request_id)
         return GenerationResult(token_ids=list(sequence.outputs),
-                                finish_reason=sequence.finish_reason)
+                                finish_reason=sequence.finish_reason, error=sequence.error)
 
     # ------------------------------------------------------------------ the reference's calls
     def stream(self, request: GenerationRequest) -> Iterator[int]:
@@ -141,7 +191,7 @@ class ChatEngine:
         try:
             while request_id not in self.scheduler.finished:
                 for rid, token, _ in self.step():
-                    if rid == request_id:
+                    if rid == request_id and token is not None:
                         yield token
         finally:
             if request_id not in self.scheduler.finished:

@@ -29,4 +29,5 @@ class GenerationRequest:
 @dataclass(frozen=True)
 class GenerationResult:
     token_ids: list[int]
-    finish_reason: Literal["stop", "length", "cancelled"]
+    finish_reason: Literal["stop", "length", "cancelled", "error"]
+    error: str | None = None        # what went wrong, when ``finish_reason`` is "error"

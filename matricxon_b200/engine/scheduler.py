@@ -12,12 +12,17 @@ Here one step holds decode tokens and prompt portions together, under a token bu
   2. the rest of the budget goes to prompt portions, running requests before waiting ones,
      in arrival order, each at most ``prefill_chunk`` tokens and cut to the remaining budget;
   3. waiting requests are admitted while fewer than ``max_num_seqs`` run and pages are free.
-When pages run out: portions are skipped first (nothing is admitted or advanced); if a decode
-token cannot get its page, the most recently admitted running request is preempted: its pages
-are freed, it keeps its sampled tokens and returns to the front of the queue, and is later
-recomputed as one prompt of (prompt + sampled tokens). Its random stream is a function of
-(seed, token index), so the tokens it goes on to sample are unchanged. A request that cannot
-fit in the empty pool is refused when it is added.
+When pages run out: portions are cut (halved until they fit) or wait while something else in
+the step moves; a decode token that cannot get its page, or the oldest prompt portion when
+nothing else moves, makes the most recently admitted running request give up its pages
+(never an older one: the youngest gives way itself). A preempted request keeps its sampled
+tokens, returns to the front of the queue and is later recomputed as one prompt of
+(prompt + sampled tokens). Its random stream is a function of (seed, token index), so the
+tokens it goes on to sample are unchanged. The oldest running request therefore always
+advances, which is why every request ends (the property the reference's worker has by
+construction: tests/unit/test_batching_scheduler.py:44-60,153-176). A request alone that
+still cannot get a page ends with ``length``; one that cannot fit in the empty pool is
+refused when it is added.
 """
 
 from __future__ import annotations
@@ -34,6 +39,10 @@ WAITING, RUNNING, FINISHED = "waiting", "running", "finished"
 
 class RequestRefused(ValueError):
     """A request that can never run under the engine's limits."""
+
+
+class SchedulerStalled(RuntimeError):
+    """Requests are left, none of them can run, and nothing is in flight that would change that."""
 
 
 @dataclass
@@ -57,6 +66,7 @@ class Sequence:
     finish_reason: str | None = None
     preemptions: int = 0
     order: int = 0                         # admission order among running requests
+    error: str | None = None               # why, when ``finish_reason`` is "error"
 
     @property
     def tokens(self) -> list[int]:
@@ -94,6 +104,7 @@ class PlannedEntry:
 class StepPlan:
     entries: list[PlannedEntry] = field(default_factory=list)
     preempted: list[Sequence] = field(default_factory=list)
+    ended: int = 0             # requests that planning itself finished (``length`` at the pool's end, ``error``)
 
     @property
     def num_tokens(self) -> int:
@@ -122,10 +133,17 @@ class Scheduler:
         room = max(limit - len(prompt), 0)
         max_new = room if sampling.num_predict < 0 else min(sampling.num_predict, room)
         most_pages = (len(prompt) + max_new + self.cache.page_size - 1) // self.cache.page_size
+        page_size = self.cache.page_size
         for group, pool in enumerate(self.cache.pools):
-            if self.cache.rules[group].window is None and most_pages > pool.num_pages:
+            window = self.cache.rules[group].window
+            need = most_pages
+            if window is not None:
+                # a window of W keys spans at most ceil((W - 1) / page) + 1 pages, and the next token's
+                # page is taken before the oldest is given back
+                need = min(most_pages, (window - 1 + page_size - 1) // page_size + 2)
+            if need > pool.num_pages:
                 raise RequestRefused(
-                    f"request needs {most_pages} pages in group {group}, the pool has {pool.num_pages}")
+                    f"request needs {need} pages in group {group}, the pool has {pool.num_pages}")
         sequence = Sequence(request_id, list(prompt), sampling, max_new, RequestSampler(sampling))
         if max_new == 0:
             sequence.status, sequence.finish_reason = FINISHED, "length"
@@ -146,6 +164,15 @@ class Scheduler:
                 self._finish(sequence, "cancelled")
                 return True
         return False
+
+    def fail(self, sequence: Sequence, why: str) -> None:
+        """Ends a waiting or running request whose step was void; its pages go back at once."""
+        if sequence.status == FINISHED:
+            return
+        if sequence.status == WAITING:
+            self.waiting.remove(sequence)
+        sequence.error = why
+        self._finish(sequence, "error")
 
     def has_work(self) -> bool:
         return bool(self.waiting or self.running)
@@ -171,28 +198,58 @@ class Scheduler:
         self.waiting.appendleft(sequence)
         plan.preempted.append(sequence)
 
+    def _youngest_unplanned(self, plan: StepPlan) -> Sequence | None:
+        candidates = [s for s in self.running if all(e.sequence is not s for e in plan.entries)]
+        return max(candidates, key=lambda s: s.order) if candidates else None
+
+    def _make_room(self, sequence: Sequence, count: int, planned: list[int], plan: StepPlan) -> bool:
+        """Preempts the most recently admitted requests that are not part of ``plan`` until
+        ``sequence`` can have pages for ``count`` tokens. Older requests are never touched: when
+        ``sequence`` is itself the youngest it is the one that goes (or, alone in the pool, ends
+        with ``length``: it has reached what the pool can hold). True if the tokens fit now."""
+        while not self._fits(sequence, count, planned):
+            victim = self._youngest_unplanned(plan)
+            if victim is None:
+                return False
+            if victim is sequence:
+                if len(self.running) == 1:
+                    self._finish(sequence, "length")
+                else:
+                    self._preempt(sequence, plan)
+                return False
+            self._preempt(victim, plan)
+        return True
+
     def schedule(self) -> StepPlan:
+        """The next step. Never empty while a request can move: a plan that only preempted is
+        retried at once, and a state in which requests are left but none can run (which the rules
+        above exclude) raises instead of returning an empty plan for ever."""
+        plan = self._schedule_once()
+        preempted = list(plan.preempted)
+        while not plan.entries and self.has_work() and (plan.preempted or plan.ended):
+            plan = self._schedule_once()
+            preempted.extend(plan.preempted)
+        plan.preempted = preempted
+        if not plan.entries and self.has_work():
+            raise SchedulerStalled(
+                f"{len(self.running)} running and {len(self.waiting)} waiting requests, none can run "
+                f"(free pages per group: {self.cache.free_pages()})")
+        return plan
+
+    def _schedule_once(self) -> StepPlan:
         plan = StepPlan()
         planned = [0] * len(self.cache.pools)
         budget = self.config.max_num_batched_tokens
 
-        # 1. decode tokens, oldest request first; preempt the youngest when a page is missing
-        decodes = [s for s in self.running if s.remaining == 1]
-        for sequence in decodes:
-            if sequence.status != RUNNING or budget <= 0:
+        # 1. decode tokens, oldest request first; the youngest unplanned request goes when a page is missing
+        for sequence in sorted(self.running, key=lambda s: s.order):
+            if sequence.status != RUNNING or sequence.remaining != 1 or budget <= 0:
                 continue
-            while not self._fits(sequence, 1, planned):
-                victims = [s for s in self.running if s is not sequence
-                           and all(e.sequence is not s for e in plan.entries)]
-                if not victims:
-                    break
-                self._preempt(max(victims, key=lambda s: s.order), plan)
-            if sequence.status == RUNNING and self._fits(sequence, 1, planned):
+            finished_before = len(self.finished)
+            if self._make_room(sequence, 1, planned, plan):
                 self._plan(plan, sequence, 1, planned)
                 budget -= 1
-            elif sequence.status == RUNNING and len(self.running) == 1 and not plan.entries:
-                # alone and still no page: the request has reached what the pool can hold
-                self._finish(sequence, "length")
+            plan.ended += len(self.finished) - finished_before
 
         # 2. prompt portions of running requests, in admission order
         def portion(sequence: Sequence) -> int:
@@ -203,13 +260,21 @@ class Scheduler:
 
         blocked = False
         for sequence in sorted(self.running, key=lambda s: s.order):
-            if sequence.remaining <= 1 or any(e.sequence is sequence for e in plan.entries):
+            if sequence.status != RUNNING or sequence.remaining <= 1 \
+                    or any(e.sequence is sequence for e in plan.entries):
                 continue
             if budget <= 0:
                 break
             count = portion(sequence)
+            if count <= 0 and not plan.entries:
+                # nothing else moves in this step, so nothing will free a page by itself: the
+                # youngest requests give theirs up until the oldest portion has one
+                finished_before = len(self.finished)
+                if self._make_room(sequence, 1, planned, plan):
+                    count = portion(sequence)
+                plan.ended += len(self.finished) - finished_before
             if count <= 0:
-                blocked = True
+                blocked = True                 # older requests move; this one waits for their pages
                 break
             self._plan(plan, sequence, count, planned)
             budget -= count
@@ -227,10 +292,13 @@ class Scheduler:
             if count <= 0:
                 self.cache.free_request(sequence.request_id)
                 if not self.running:
+                    # not one token fits the empty pool: ``add`` refuses such requests, so this is
+                    # a pool smaller than a page per group; the request ends, the others go on
                     self.waiting.popleft()
-                    self._finish(sequence, "cancelled")
-                    raise RequestRefused(
-                        f"request {sequence.request_id!r} does not fit in the empty cache pool")
+                    sequence.error = "the request does not fit in the empty cache pool"
+                    self._finish(sequence, "error")
+                    plan.ended += 1
+                    continue
                 break
             self.waiting.popleft()
             sequence.status = RUNNING

@@ -31,7 +31,16 @@ from matricxon_b200.ops import kernels
 
 
 class StepError(RuntimeError):
-    """A step whose inputs were malformed or whose kernels reported a bad index."""
+    """A step whose inputs were malformed or whose kernels reported a bad index.
+
+    ``request_ids`` names the requests at fault when the host could tell (a malformed entry is
+    found before anything is reserved or launched, so the other requests of the step are
+    untouched and can run in the next one); it is empty when a kernel reported the fault, and
+    the step is then void for every request in it."""
+
+    def __init__(self, message: str, request_ids: list[str] | None = None) -> None:
+        super().__init__(message)
+        self.request_ids = list(request_ids or ())
 
 
 @dataclass
@@ -191,6 +200,10 @@ class StepRunner:
         self._graph_host_arrays: dict[int, tuple] = {}       # bucket -> (pinned tensor, its numpy view)
         self._arange = np.arange(max_graph_batch + 2, dtype=np.int32)
         self._graph_pool = None
+        # token ids are checked against the vocabulary on the host before a step is built; a caller
+        # that vouches for its ids may switch the scan off (the embedding kernel still refuses a bad
+        # id: it writes zeros and sets a status bit, which voids the step for all its requests)
+        self.check_ids_on_host = True
         self.last_upload_bytes = 0        # host-to-device bytes of the latest step's metadata
         self.launches_per_step = 0        # this library's kernel launches in the latest step
         model.bind_cache(storage.groups, storage.states)
@@ -226,21 +239,38 @@ class StepRunner:
 
     # ------------------------------------------------------------------ building a step
     def _validate(self, entries: list[StepEntry]) -> None:
+        """Everything the host can check, before a page is reserved or a kernel launched. One
+        error lists every fault and names the requests at fault."""
         if not entries:
             raise StepError("a step needs at least one entry")
+        faults: list[str] = []
+        at_fault: list[str] = []
         seen = set()
         total = 0
+        vocab = self.model.spec.vocab_size
         for entry in entries:
+            problems = []
             if entry.request_id in seen:
-                raise StepError(f"request {entry.request_id!r} appears twice in one step")
+                problems.append("appears twice in one step")
             seen.add(entry.request_id)
+            if not self.cache.has_request(entry.request_id):
+                problems.append("is not live in the cache")
             if not entry.tokens:
-                raise StepError(f"request {entry.request_id!r} brings no tokens")
+                problems.append("brings no tokens")
+            elif self.check_ids_on_host and not (0 <= min(entry.tokens) and max(entry.tokens) < vocab):
+                bad = next(t for t in entry.tokens if not 0 <= t < vocab)
+                problems.append(f"brings token id {bad}, outside the vocabulary of {vocab}")
             for index in entry.want:
                 if not 0 <= index < len(entry.tokens):
-                    raise StepError(f"request {entry.request_id!r} wants logits at {index}, "
-                                    f"but brings {len(entry.tokens)} tokens")
+                    problems.append(f"wants logits at {index}, but brings {len(entry.tokens)} tokens")
+                    break
             total += len(entry.tokens)
+            if problems:
+                faults.append(f"request {entry.request_id!r} " + " and ".join(problems))
+                if entry.request_id not in at_fault:
+                    at_fault.append(entry.request_id)
+        if faults:
+            raise StepError("; ".join(faults), at_fault)
         if total > self.max_step_tokens:
             raise StepError(f"step of {total} tokens exceeds max_step_tokens={self.max_step_tokens}")
         if len(entries) > self.max_step_seqs:
@@ -261,8 +291,6 @@ class StepRunner:
         reserved: list[str] = []
         try:
             for entry in entries:
-                if not cache.has_request(entry.request_id):
-                    raise StepError(f"request {entry.request_id!r} is not live in the cache")
                 cache.reserve(entry.request_id, len(entry.tokens))
                 reserved.append(entry.request_id)
         except Exception:
@@ -464,8 +492,6 @@ class StepRunner:
         reserved: list[str] = []
         try:
             for entry in entries:
-                if not cache.has_request(entry.request_id):
-                    raise StepError(f"request {entry.request_id!r} is not live in the cache")
                 cache.reserve(entry.request_id, 1)
                 reserved.append(entry.request_id)
         except Exception:

@@ -107,6 +107,8 @@ def test_mixed_batches_with_page_reuse(setup):
     live: dict[str, int] = {}
     collector = Collector()
     turn = 0
+    owners: dict[tuple[int, int], set] = {}     # (group, physical page) -> requests that held it
+    reused_before = None
     while waiting or live:
         while waiting and len(live) < 4:
             live[waiting.pop(0)] = 0
@@ -129,8 +131,24 @@ def test_mixed_batches_with_page_reuse(setup):
         turn += 1
         if portions:
             collector.run(setup["session"], portions, end=ended)
+            report = setup["session"].last_report["pages"]
+            if reused_before is None:
+                reused_before = report["reused"]
+            held = 0
+            for rid, state in report["requests"].items():
+                assert state["length"] == live[rid]
+                for group, table in enumerate(state["pages"]):
+                    for page in table:
+                        if page >= 0:
+                            owners.setdefault((group, page), set()).add(rid)
+                            held += 1
+            # no page lost: what is free and what the live requests hold is the pool
+            assert sum(report["free"]) + held == sum(report["total"])
         for rid in ended:
             del live[rid]
+    shared = [page for page, who in owners.items() if len(who) > 1]
+    assert shared, "no physical page served two requests: the pool was not small enough"
+    assert setup["session"].last_report["pages"]["reused"] > reused_before
     for rid, ids in tokens.items():
         base = rid.split("#")[0]
         ref = setup["reference"][base]
@@ -164,3 +182,39 @@ def test_steps_without_wanted_logits_write_no_file(setup):
     ref = setup["reference"][rid][3]
     assert out.shape == (1, setup["cfg"]["vocab"])
     assert np.abs(out[0] - ref).max() <= tolerance(setup["dtype"], ref)
+
+
+def test_a_line_that_is_no_step_ends_the_run_with_a_message(tmp_path):
+    """Host-side faults of a trace: the program says which line and why, and exits with 2;
+    nothing reaches the GPU."""
+    import json
+    import subprocess
+    import sys
+
+    from trace_utils import TRACE_RUN
+
+    folder = tmp_path / "model"
+    write_tiny_model(folder, "A", torch.float32)
+    vocab = TINY["A"][0]["vocab_size"]
+    good = {"step": 0, "entries": [{"id": "a", "tokens": [1, 2, 3], "want": [2]}], "end": []}
+    cases = {
+        "not json": ("{this is not json", "not JSON"),
+        "no tokens": (json.dumps({"step": 1, "entries": [{"id": "a", "tokens": []}]}), "non-empty list"),
+        "bad id": (json.dumps({"step": 1, "entries": [{"id": "a", "tokens": [vocab + 3], "want": [0]}]}),
+                   "outside the vocabulary"),
+        "twice": (json.dumps({"step": 1, "entries": [{"id": "a", "tokens": [1]}, {"id": "a", "tokens": [2]}]}),
+                  "appears twice"),
+        "want": (json.dumps({"step": 1, "entries": [{"id": "a", "tokens": [1, 2], "want": [2]}]}),
+                 "wants logits at 2"),
+        "unknown end": (json.dumps({"step": 1, "entries": [], "end": ["nobody"]}), "not live"),
+    }
+    for label, (line, expected) in cases.items():
+        out = tmp_path / f"out_{label.replace(' ', '_')}"
+        done = subprocess.run(
+            [sys.executable, str(TRACE_RUN), "--model", str(folder), "--dtype", "float32", "--out", str(out),
+             "--max-tokens", "128"], input=json.dumps(good) + "\n" + line + "\n",
+            capture_output=True, text=True, timeout=300)
+        assert done.returncode == 2, (label, done.returncode, done.stderr[-500:])
+        assert "input line 2" in done.stderr and expected in done.stderr, (label, done.stderr[-500:])
+        assert done.stdout.split() == ["done", "0"], (label, done.stdout)
+        assert (out / "0.f32").exists() and not (out / "1.f32").exists()

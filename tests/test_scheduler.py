@@ -286,3 +286,123 @@ def test_plan_ahead_refused_when_no_page_is_left_for_it():
     cache.reserve("a", 1)
     cache.commit("a", 1)
     assert scheduler.plan_ahead(plan) is not None
+
+
+def outputs_in_roomy_pool(prompts, num_predict, **config):
+    cache, scheduler = make(pages=4096, **config)
+    for name, prompt in prompts.items():
+        scheduler.add(name, prompt, sampling(num_predict=num_predict, num_ctx=4096))
+    run_all(cache, scheduler)
+    return {name: scheduler.finished[name].outputs for name in prompts}
+
+
+@pytest.mark.parametrize("pages, page_size, length, chunk", [(10, 16, 100, 32), (100, 16, 960, 256)])
+def test_two_prompts_that_do_not_fit_together_both_finish(pages, page_size, length, chunk):
+    """Every running request is in the middle of its prompt and the pool is empty: nothing decodes,
+    so nothing would ever free a page. The younger request gives way and both finish with the
+    tokens they produce in a roomy pool."""
+    prompts = {"a": [1 + i % 7 for i in range(length)], "b": [2 + i % 5 for i in range(length)]}
+    config = dict(page_size=page_size, max_num_batched_tokens=2 * chunk, prefill_chunk=chunk,
+                  max_model_len=4096)
+    expected = outputs_in_roomy_pool(prompts, 4, **config)
+    cache, scheduler = make(pages=pages, **config)
+    for name, prompt in prompts.items():
+        scheduler.add(name, prompt, sampling(num_predict=4, num_ctx=4096))
+    log = []
+    for _ in range(200):
+        if not scheduler.has_work():
+            break
+        plan, _ = run_step(cache, scheduler, log)
+        assert plan.entries, "an empty plan while requests are left"
+    assert not scheduler.has_work()
+    assert scheduler.num_preemptions >= 1
+    assert {n: scheduler.finished[n].outputs for n in prompts} == expected
+    assert all(scheduler.finished[n].finish_reason == "length" for n in prompts)
+    assert cache.free_pages() == [pages]
+
+
+def test_the_youngest_gives_way_never_an_older_request():
+    """A decoding request that needs a page while an older request is still in its prompt gives up
+    its own pages: the oldest running request always advances."""
+    cache, scheduler = make(pages=8, page_size=4, max_num_batched_tokens=8, prefill_chunk=4)
+    scheduler.add("old", [1] * 24, sampling(num_predict=2))        # 6 pages of prompt, slowly
+    run_step(cache, scheduler)
+    scheduler.add("young", [2] * 4, sampling(num_predict=12))      # one page, then decodes
+    log, preempted = [], []
+    for _ in range(100):
+        if not scheduler.has_work():
+            break
+        plan, _ = run_step(cache, scheduler, log)
+        preempted.extend(s.request_id for s in plan.preempted)
+        assert plan.entries
+    assert not scheduler.has_work()
+    assert preempted and set(preempted) == {"young"}
+    assert len(scheduler.finished["old"].outputs) == 2 and len(scheduler.finished["young"].outputs) == 12
+
+
+def test_random_pools_windows_and_chunks_always_make_progress():
+    """Whatever the pool, the window and the portion size: every plan moves something, every
+    request ends within a bounded number of steps with the tokens it produces in a roomy pool,
+    and no page is lost on the way."""
+    import random
+    rng = random.Random(11)
+    preemptions = 0
+    for case in range(60):
+        page_size = rng.choice([2, 4, 16])
+        window = rng.choice([None, 24])
+        chunk = rng.choice([1, 3, 8, 32])
+        budget = rng.choice([chunk, 2 * chunk + 3, 64])
+        n_requests = rng.randint(2, 6)
+        prompts = {f"r{i}": [rng.randint(1, 40) for _ in range(rng.randint(1, 90))]
+                   for i in range(n_requests)}
+        num_predict = rng.randint(1, 12)
+        longest = max(len(p) for p in prompts.values()) + num_predict
+        pages_for_one = (longest + page_size - 1) // page_size
+        if window is not None:
+            pages_for_one = min(pages_for_one, (window - 1 + page_size - 1) // page_size + 2)
+        pages = pages_for_one + rng.randint(0, pages_for_one)
+        config = dict(page_size=page_size, window=window, max_num_seqs=rng.choice([2, 4]),
+                      max_num_batched_tokens=budget, prefill_chunk=chunk, max_model_len=4096)
+        expected = outputs_in_roomy_pool(prompts, num_predict, **config)
+        cache, scheduler = make(pages=pages, **config)
+        for name, prompt in prompts.items():
+            scheduler.add(name, prompt, sampling(num_predict=num_predict, num_ctx=4096))
+        total = sum(len(p) + num_predict for p in prompts.values())
+        steps = 0
+        while scheduler.has_work():
+            plan, _ = run_step(cache, scheduler)
+            assert plan.entries, (case, "empty plan")
+            steps += 1
+            assert steps <= 40 * total, (case, "no end in sight")
+        for name in prompts:
+            done = scheduler.finished[name]
+            assert done.finish_reason == "length" and done.outputs == expected[name], (case, name)
+        assert cache.free_pages() == [pages], case
+        preemptions += scheduler.num_preemptions
+    assert preemptions > 20             # the cases do run out of pages
+
+
+def test_window_only_pool_too_small_is_refused_at_add_not_inside_a_step():
+    cache, scheduler = make(pages=2, page_size=4, window=8)
+    with pytest.raises(RequestRefused):
+        scheduler.add("a", [1] * 30, sampling(num_predict=4))      # a window of 8 spans up to 4 pages
+    scheduler.add("b", [1] * 5, sampling(num_predict=3))           # 8 tokens: 2 pages are enough
+    run_all(cache, scheduler)
+    assert len(scheduler.finished["b"].outputs) == 3
+
+
+def test_trace_lines_are_checked_before_they_reach_the_engine():
+    from matricxon_b200.engine.replay import TraceFormatError, parse_trace_line
+
+    step, entries, end = parse_trace_line(
+        '{"step": 3, "entries": [{"id": 7, "tokens": [5, 17, 3], "want": [0, 2]}], "end": ["x", 9]}')
+    assert step == 3 and entries == [{"id": "7", "tokens": [5, 17, 3], "want": [0, 2]}] and end == ["x", "9"]
+    assert parse_trace_line('{"step": 0}') == (0, [], [])
+    for line in ('{"step": 0', '[1, 2]', '{"entries": []}', '{"step": 0, "entries": {}}',
+                 '{"step": 0, "entries": [{"id": "a"}]}', '{"step": 0, "entries": [{"id": "a", "tokens": []}]}',
+                 '{"step": 0, "entries": [{"id": "a", "tokens": [1.5]}]}',
+                 '{"step": 0, "entries": [{"id": "a", "tokens": [true]}]}',
+                 '{"step": 0, "entries": [{"id": "a", "tokens": [1], "want": "all"}]}',
+                 '{"step": 0, "entries": [], "end": "a"}'):
+        with pytest.raises(TraceFormatError):
+            parse_trace_line(line)

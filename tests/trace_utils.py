@@ -19,15 +19,17 @@ class TraceSession:
     the logits file's contents (or None)."""
 
     def __init__(self, model_dir, dtype: str, max_tokens: int, out_dir, vocab: int,
-                 extra_args: tuple[str, ...] = ()) -> None:
+                 extra_args: tuple[str, ...] = (), capture_stderr: bool = False) -> None:
         self.out_dir = Path(out_dir)
         self.vocab = vocab
         self.next_step = 0
+        self.last_report: dict = {}
         env = dict(os.environ)
         self.proc = subprocess.Popen(
             [sys.executable, str(TRACE_RUN), "--model", str(model_dir), "--dtype", dtype,
              "--out", str(out_dir), "--max-tokens", str(max_tokens), *extra_args],
-            stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True, env=env)
+            stdin=subprocess.PIPE, stdout=subprocess.PIPE, stderr=subprocess.PIPE if capture_stderr else None,
+            text=True, env=env)
 
     def step(self, entries: list[dict], end: list[str] = ()) -> np.ndarray | None:
         number = self.next_step
@@ -39,6 +41,8 @@ class TraceSession:
             self.proc.kill()
             raise RuntimeError(f"trace_run answered {line!r} to step {number} "
                                f"(exit code {self.proc.poll()})")
+        with open(self.out_dir / f"{number}.json") as handle:
+            self.last_report = json.load(handle)
         path = self.out_dir / f"{number}.f32"
         wanted = sum(len(e.get("want", [])) for e in entries)
         if wanted == 0:
@@ -74,6 +78,8 @@ class Collector:
             keys.extend((request, start + i) for i in want)
             self.progress[request] = start + len(tokens)
         out = session.step(entries, end)
+        # the program's own account of its rows: (request, absolute position), in order
+        assert [tuple(row) for row in session.last_report["rows"]] == keys
         if keys:
             for key, row in zip(keys, out):
                 assert key not in self.logits
