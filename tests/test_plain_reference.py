@@ -100,3 +100,56 @@ def test_sampler_inverse_cdf_sweep():
     for i in range(n):
         counts[plain_sample(logits, [], 1.0, 0, 1.0, 1.0, (i + 0.5) / n)] += 1
     assert torch.allclose(counts / n, probs.float(), atol=2e-3)
+
+
+# ------------------------------------------------------------------ the reference's own C kernels
+def _golden_module():
+    import importlib.util
+
+    spec = importlib.util.spec_from_file_location("make_golden_native",
+                                                  os.path.join(GOLDEN, "make_golden_native.py"))
+    module = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(module)
+    return module
+
+
+def test_window_mask_and_attention_match_the_reference_c_kernel():
+    """``mx_attention`` (app/native/src/mx_attention.c:16-68) and ``_causal_mask``
+    (app/architectures/gemma4_layers.py:17-34), run on the CPU by tests/golden/make_golden_native.py:
+    the window rule of the plain implementation rests on their outputs, not on a reading."""
+    golden = _golden_module()
+    stored = np.load(os.path.join(GOLDEN, "native_attention.npz"))
+    for index, case in enumerate(golden.ATTENTION_CASES):
+        heads, kv_heads, dim, n_q, n_kv, offset, window = case
+        q, k, v = golden.attention_inputs(index, case)
+        mask = plain_mask(n_q, n_kv, offset, window or None)
+        assert np.array_equal(mask.numpy(), stored[f"mask_{index}"]), case
+        out = plain_attention_core(q.double(), k.double(), v.double(), dim ** -0.5, window or None, offset)
+        assert np.abs(out.numpy() - stored[f"out_{index}"]).max() < 1e-5, case
+        if window:
+            # the window matters in these cases: without it the result differs
+            full = plain_attention_core(q.double(), k.double(), v.double(), dim ** -0.5, None, offset)
+            if offset + 1 > window:
+                assert np.abs(full.numpy() - stored[f"out_{index}"]).max() > 1e-4, case
+
+
+def test_sampler_matches_the_reference_c_kernel():
+    """``mx_sample`` (app/native/src/mx_sample.c:51-108) over a sweep of uniforms. Without top-p
+    the kernel draws in vocabulary order and the plain sampler picks the same token for every
+    uniform (up to a boundary within rounding). With top-p below one the kernel sorts its
+    candidates and draws in descending order (mx_sample.c:88-107) where this engine keeps
+    vocabulary order, so there the kept set and each token's share of the draws are compared."""
+    golden = _golden_module()
+    stored = np.load(os.path.join(GOLDEN, "native_sampler.npz"))
+    for index, case in enumerate(golden.SAMPLER_CASES):
+        _, temperature, top_k, top_p, penalty, _ = case
+        logits, generated = golden.sampler_inputs(index, case)
+        theirs = stored[f"tokens_{index}"].tolist()
+        ours = [plain_sample(logits, generated, temperature, top_k, top_p, penalty, (i + 0.5) / golden.SWEEP)
+                for i in range(golden.SWEEP)]
+        if top_p >= 1.0:
+            assert sum(a != b for a, b in zip(ours, theirs)) <= 1, case
+        else:
+            assert set(ours) == set(theirs), case
+            for token in set(theirs):
+                assert abs(ours.count(token) - theirs.count(token)) <= 2, (case, token)
