@@ -107,13 +107,31 @@ class ClockSampler:
 
 
 def reference_arm(args) -> int:
-    """The reference arm. nesmind/matricxon cannot be installed offline: it has no package
-    metadata (pip stops at "metadata-generation-failed": flat layout with several top-level
-    packages, no [project] table), so there is nothing under baseline/_ref to run."""
-    print(json.dumps({"impl": "reference",
-                      "unavailable": "pip install --no-index --target baseline/_ref of nesmind/matricxon "
-                                     "fails at metadata generation (the tree is not an installable "
-                                     "package: flat layout, no [project] table)"}))
+    """The reference arm: nesmind/matricxon's own stock code (``baseline/reference_arm.py`` says
+    which calls) on the same configuration, with the same steps, warm-up and context. pip cannot
+    install the reference (no package metadata), so a plain copy under ``baseline/_ref`` is put on
+    the path; without it, or if its GPU path fails, the line says ``unavailable`` and why."""
+    sys.path.insert(0, os.path.join(ROOT, "baseline"))
+    import reference_arm as arm
+
+    if args.warmup < 3:
+        args.warmup = 3
+    clocks = ClockSampler()
+    try:
+        arm.import_reference()
+        clocks.start()
+        context = min(args.context, CONTEXT - args.steps - args.warmup - 8)
+        record = arm.run(args, STARCODER2_3B, context, PREFILL_TOKENS, CONTEXT, clocks)
+    except arm.ReferenceUnavailable as error:
+        print(json.dumps({"impl": "reference", "unavailable": str(error)}))
+        return 0
+    except Exception as error:                      # the reference's own code failed at these sizes
+        text = f"{type(error).__name__}: {error}".replace("\n", " ")[:300]
+        print(json.dumps({"impl": "reference", "unavailable": f"the reference's GPU path failed: {text}"}))
+        return 0
+    finally:
+        clocks.stop()
+    print(json.dumps(record))
     return 0
 
 

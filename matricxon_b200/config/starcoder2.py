@@ -54,8 +54,9 @@ class Starcoder2Config:
             raise ConfigError(
                 f"num_attention_heads ({self.num_attention_heads}) must be a multiple of "
                 f"num_key_value_heads ({self.num_key_value_heads})")
-        if self.head_dim % 2 != 0:
-            raise ConfigError(f"head_dim ({self.head_dim}) must be even for rotary halves")
+        if self.head_dim % 16 != 0 or not 16 <= self.head_dim <= 256:
+            raise ConfigError(f"head_dim ({self.head_dim}) must be a multiple of 16 between 16 and 256: "
+                              "the attention kernels take no other size")
         if self.hidden_act not in _ACTIVATIONS:
             raise ConfigError(
                 f"hidden_act {self.hidden_act!r} is not supported; StarCoder2 uses "
@@ -106,6 +107,8 @@ class Starcoder2Config:
             bias=self.use_bias,
             window=self.sliding_window,
             scale=float(self.head_dim) ** -0.5,
+            projection_names=("q_proj", "k_proj", "v_proj"),
+            output_name="o_proj",
             position=RotarySpec(rotary_dim=self.head_dim, theta=self.rope_theta),
         )
         mlp = MlpSpec(
@@ -113,8 +116,13 @@ class Starcoder2Config:
             intermediate_size=self.intermediate_size,
             bias=self.use_bias,
             activation=_ACTIVATIONS[self.hidden_act],
+            up_name="c_fc",
+            down_name="c_proj",
         )
-        layer = LayerSpec(mixer=attention, feed_forward=mlp, mixer_norm=norm, ffn_norm=norm)
+        layer = LayerSpec(mixer=attention, feed_forward=mlp, mixer_norm=norm, ffn_norm=norm,
+                          mixer_name="self_attn", feed_forward_name="mlp",
+                          mixer_norm_name="input_layernorm",
+                          ffn_norm_name="post_attention_layernorm")
         return ModelSpec(
             hidden_size=self.hidden_size,
             vocab_size=self.vocab_size,
@@ -123,6 +131,10 @@ class Starcoder2Config:
             final_norm=norm,
             tie_word_embeddings=self.tie_word_embeddings,
             max_position_embeddings=self.max_position_embeddings,
+            embedding_name="model.embed_tokens",
+            layer_prefix="model.layers",
+            final_norm_name="model.norm",
+            head_name="lm_head",
         )
 
 

@@ -26,7 +26,6 @@ import torch
 
 from matricxon_b200.cache.manager import CacheManager, OutOfPages
 from matricxon_b200.cache.storage import CacheStorage
-from matricxon_b200.engine.fused_decode import FusedDecode
 from matricxon_b200.ops import kernels
 
 
@@ -88,7 +87,7 @@ class StepContext:
         self.host: HostStep = None
         self.capturing = False        # inside a CUDA-graph capture: buffers must belong to the graph
         self.padded = False           # a fixed-size decode batch: every sequence has one row or none
-        self._tiles: dict[tuple, tuple] = {}
+        self.memo: dict = {}          # what parts derive from the step once and share (tile lists, ...)
 
     def hidden(self, hidden_size: int) -> torch.Tensor:
         if self.capturing:
@@ -96,84 +95,29 @@ class StepContext:
                                device=self.token_ids.device)
         return self._runner.hidden_buffer(self.n_tokens, hidden_size)
 
-    def attention_tiles(self, group: int, token_tiles: bool = False):
-        """Tile lists of the tensor-core attention for query groups of ``group`` heads:
-        (narrow tiles, their count, wide tiles, their count); built once per step, group and
-        kind of wide tile (64 rows, or ``token_tiles``: 128 // group tokens for the tcgen05 kernel)."""
-        key = (group, token_tiles)
-        cached = self._tiles.get(key)
-        if cached is not None:
-            return cached
-        q_lens = [1] * self.n_seqs if self.padded else self.host.q_lens
-        narrow, wide = kernels.attention_tile_lists(q_lens, group, token_tiles)
-        device = self.token_ids.device
-        both = torch.tensor(narrow + wide + [0, 0], dtype=torch.int32).to(device, non_blocking=True)
-        self._tiles[key] = (both[:len(narrow)], len(narrow) // 2,
-                            both[len(narrow):len(narrow) + len(wide)], len(wide) // 2)
-        return self._tiles[key]
+    @property
+    def device(self) -> torch.device:
+        return self.token_ids.device if self.token_ids is not None else self._runner.device
 
-    def tile_splits(self, n_tiles: int, narrow: bool, alone: bool, n_heads: int, n_kv_heads: int,
-                    head_dim: int, window: int | None) -> tuple[int, torch.Tensor | None]:
-        """Key splits for one launch of the tensor-core attention (a block per tile, KV head
-        and split). Splits only pay when the tiles alone leave SMs idle, and only a launch
-        that covers every token of the step may use them (the merge runs over all tokens)."""
-        if not alone:
-            return 1, None
-        items = max(n_tiles * n_kv_heads, 1)
-        span = self.max_kv_len if window is None else min(self.max_kv_len, window)
-        chunks = span // 32 + 1
-        # a narrow block fills an SM's shared memory with its four private pipelines: one per SM
-        target = self._runner.sm_count * (1 if narrow else 2)
-        n_splits = max(1, min(target // items, chunks // (4 if narrow else 8), 128))
-        while n_splits > 1 and kernels.attention_scratch_bytes(
-                self.n_tokens, n_heads, head_dim, n_splits) > (256 << 20):
-            n_splits //= 2
-        if n_splits == 1:
-            return 1, None
-        need = kernels.attention_scratch_bytes(self.n_tokens, n_heads, head_dim, n_splits)
+    @property
+    def sm_count(self) -> int:
+        return self._runner.sm_count
+
+    def scratch(self, nbytes: int) -> torch.Tensor:
+        """Float32 scratch memory of at least ``nbytes`` for one kernel launch of this step. Every
+        call of a step may get the same memory (launches of a step run in stream order and none
+        keeps its scratch beyond its own merge), except inside a capture, where each caller gets
+        memory that belongs to the graph."""
         if self.capturing:
-            return n_splits, torch.empty((need + 3) // 4, dtype=torch.float32,
-                                         device=self.token_ids.device)
-        return n_splits, self._runner.scratch_buffer(need)
-
-    def tc_tile_splits(self, n_tiles: int, alone: bool, n_heads: int, n_kv_heads: int, head_dim: int,
-                       window: int | None) -> tuple[int, torch.Tensor | None]:
-        """Key splits for the tcgen05 attention (one block per SM, chunks of 128 keys): a short
-        portion after a long context has few tiles with many chunks each."""
-        items = max(n_tiles * n_kv_heads, 1)
-        span = self.max_kv_len if window is None else min(self.max_kv_len, window)
-        n_splits = min(self._runner.sm_count // items, (span // 128 + 1) // 3, 8) if alone else 1
-        if n_splits < 2:
-            return 1, None
-        need = kernels.attention_scratch_bytes(self.n_tokens, n_heads, head_dim, n_splits)
-        return n_splits, self._runner.scratch_buffer(need)
-
-    def attention_splits(self, n_heads: int, n_kv_heads: int, head_dim: int,
-                         window: int | None) -> tuple[int, torch.Tensor | None]:
-        """How many key splits the attention launch should use, and its scratch memory.
-
-        Few query tokens (decoding) leave most SMs idle unless the keys are split; many
-        tokens fill the GPU by themselves."""
-        group = n_heads // n_kv_heads
-        blocks = self.n_tokens * n_kv_heads * ((group + 15) // 16)
-        span = self.max_kv_len if window is None else min(self.max_kv_len, window)
-        chunks = span // 32 + 2
-        target = self._runner.sm_count * 4
-        n_splits = max(1, min(target // max(blocks, 1), chunks // 2, 64))
-        if n_splits == 1:
-            return 1, None
-        need = kernels.attention_scratch_bytes(self.n_tokens, n_heads, head_dim, n_splits)
-        if self.capturing:
-            return n_splits, torch.empty((need + 3) // 4, dtype=torch.float32,
-                                         device=self.token_ids.device)
-        return n_splits, self._runner.scratch_buffer(need)
+            return torch.empty((nbytes + 3) // 4, dtype=torch.float32, device=self.device)
+        return self._runner.scratch_buffer(nbytes)
 
 
 class StepRunner:
     def __init__(self, model, cache: CacheManager, storage: CacheStorage,
                  max_step_tokens: int = 8192, max_step_seqs: int = 256,
                  max_model_len: int | None = None, use_graphs: bool = True,
-                 max_graph_batch: int = 64, fused_decode: bool | None = None) -> None:
+                 max_graph_batch: int = 64) -> None:
         self.model = model
         self.cache = cache
         self.storage = storage
@@ -207,15 +151,6 @@ class StepRunner:
         self.last_upload_bytes = 0        # host-to-device bytes of the latest step's metadata
         self.launches_per_step = 0        # this library's kernel launches in the latest step
         model.bind_cache(storage.groups, storage.states)
-        # decode steps of up to 16 rows can run as one persistent kernel when the model fits it.
-        # Off unless asked for (the argument, or MATRICXON_FUSED_DECODE=1): measured on a B200 at
-        # StarCoder2-3B sizes it takes about 1.8 times as long as the captured graph of separate
-        # kernels, because its consumer warps, not HBM, set the pace.
-        if fused_decode is None:
-            fused_decode = os.environ.get("MATRICXON_FUSED_DECODE", "0") == "1"
-        self.fused = None
-        if use_graphs and fused_decode and model.runtime.dtype == torch.bfloat16:
-            self.fused = FusedDecode.try_build(model, cache.page_size)
 
     # ------------------------------------------------------------------ buffers
     def hidden_buffer(self, n_tokens: int, hidden_size: int) -> torch.Tensor:
@@ -405,8 +340,6 @@ class StepRunner:
     # ------------------------------------------------------------------ running a step
     def _forward(self, ctx: StepContext, decode_rows: bool = False) -> torch.Tensor | None:
         """``decode_rows``: every row is one new token of its own sequence and wants logits."""
-        if decode_rows and self.fused is not None and self.fused.supports(ctx.n_tokens):
-            return self.fused.forward(ctx)
         hidden = self.model.forward(ctx)
         if ctx.logit_rows.numel() == 0:
             return None

@@ -157,21 +157,6 @@ class DecoderModel:
             x = self.layers[entry.layer].forward(x, ctx, self.bindings[position])
         return x
 
-    def describe(self) -> dict | None:
-        """The whole model as plain data (see ``Part.describe``): one entry per schedule position
-        with its block and its cache binding, or None if a part cannot be described."""
-        entries = []
-        for position, entry in enumerate(self.spec.schedule):
-            block = self.layers[entry.layer].describe()
-            if block is None:
-                return None
-            entries.append({"block": block, "binding": self.bindings[position]})
-        final_norm = self.final_norm.describe()
-        if final_norm is None:
-            return None
-        return {"embedding": self.embedding, "entries": entries, "final_norm": final_norm, "head": self.head,
-                "hidden_size": self.spec.hidden_size, "vocab_size": self.spec.vocab_size}
-
     def logits(self, x: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
         """Float32 logits [len(rows), vocab] of the residual-stream rows ``rows``."""
         normed = self.final_norm.forward(x, rows=rows)

@@ -8,6 +8,12 @@ feature ``head * head_dim + d`` (qwen_layers.py:72-74), position encoding on q a
 ``j > p - window`` (app/architectures/gemma4_layers.py:17-34, app/native/src/mx_attention.c:36-39);
 query head h uses KV head ``h // (heads / kv heads)`` (qwen_layers.py:90-100); then
 ``residual + o Wo^T + bo`` (qwen_layers.py:101-102, app/architectures/starcoder2_layers.py:67).
+
+Which kernel runs a step's rows, how the rows are cut into tiles and into how many pieces the
+keys of a tile are split is decided here, beside the kernels' wrappers: the step context only
+says what the step looks like (``host.q_lens``, ``max_kv_len``, ``sm_count``) and hands out
+scratch memory (``ctx.scratch``) and a per-step memo (``ctx.memo``) so that layers with the same
+geometry build their tile lists once.
 """
 
 from __future__ import annotations
@@ -27,12 +33,74 @@ from matricxon_b200.weights.loader import WeightSpec
 _TC_ATTENTION = os.environ.get("MATRICXON_TC_ATTENTION", "1") != "0"
 
 
+# ---------------------------------------------------------------------- tiling and key splits
+def attention_tiles(ctx, group: int, token_tiles: bool = False):
+    """Tile lists of the tensor-core attention for query groups of ``group`` heads:
+    (narrow tiles, their count, wide tiles, their count); built once per step, group and
+    kind of wide tile (64 rows, or ``token_tiles``: 128 // group tokens for the tcgen05 kernel)."""
+    key = ("attention_tiles", group, token_tiles)
+    cached = ctx.memo.get(key)
+    if cached is not None:
+        return cached
+    q_lens = [1] * ctx.n_seqs if ctx.padded else ctx.host.q_lens
+    narrow, wide = kernels.attention_tile_lists(q_lens, group, token_tiles)
+    both = torch.tensor(narrow + wide + [0, 0], dtype=torch.int32).to(ctx.device, non_blocking=True)
+    ctx.memo[key] = (both[:len(narrow)], len(narrow) // 2,
+                     both[len(narrow):len(narrow) + len(wide)], len(wide) // 2)
+    return ctx.memo[key]
+
+
+def _key_span(ctx, window: int | None) -> int:
+    return ctx.max_kv_len if window is None else min(ctx.max_kv_len, window)
+
+
+def mma_tile_splits(ctx, n_tiles: int, narrow: bool, alone: bool, n_heads: int, n_kv_heads: int,
+                    head_dim: int, window: int | None):
+    """Key splits for one launch of the mma.sync attention (a block per tile, KV head and
+    split). Splits only pay when the tiles alone leave SMs idle, and only a launch that covers
+    every token of the step may use them (the merge runs over all tokens)."""
+    if not alone:
+        return 1, None
+    items = max(n_tiles * n_kv_heads, 1)
+    chunks = _key_span(ctx, window) // 32 + 1
+    # a narrow block fills an SM's shared memory with its four private pipelines: one per SM
+    target = ctx.sm_count * (1 if narrow else 2)
+    n_splits = max(1, min(target // items, chunks // (4 if narrow else 8), 128))
+    while n_splits > 1 and kernels.attention_scratch_bytes(
+            ctx.n_tokens, n_heads, head_dim, n_splits) > (256 << 20):
+        n_splits //= 2
+    if n_splits == 1:
+        return 1, None
+    return n_splits, ctx.scratch(kernels.attention_scratch_bytes(ctx.n_tokens, n_heads, head_dim, n_splits))
+
+
+def tc_tile_splits(ctx, n_tiles: int, alone: bool, n_heads: int, n_kv_heads: int, head_dim: int,
+                   window: int | None):
+    """Key splits for the tcgen05 attention (one block per SM, chunks of 128 keys): a short
+    portion after a long context has few tiles with many chunks each."""
+    items = max(n_tiles * n_kv_heads, 1)
+    n_splits = min(ctx.sm_count // items, (_key_span(ctx, window) // 128 + 1) // 3, 8) if alone else 1
+    if n_splits < 2:
+        return 1, None
+    return n_splits, ctx.scratch(kernels.attention_scratch_bytes(ctx.n_tokens, n_heads, head_dim, n_splits))
+
+
+def simt_splits(ctx, n_heads: int, n_kv_heads: int, head_dim: int, window: int | None):
+    """Key splits of the generic kernel: few query tokens (decoding) leave most SMs idle unless
+    the keys are split; many tokens fill the GPU by themselves."""
+    group = n_heads // n_kv_heads
+    blocks = ctx.n_tokens * n_kv_heads * ((group + 15) // 16)
+    chunks = _key_span(ctx, window) // 32 + 2
+    n_splits = max(1, min(ctx.sm_count * 4 // max(blocks, 1), chunks // 2, 64))
+    if n_splits == 1:
+        return 1, None
+    return n_splits, ctx.scratch(kernels.attention_scratch_bytes(ctx.n_tokens, n_heads, head_dim, n_splits))
+
+
 @register_part("mixer", "attention")
 class PagedAttention(Mixer):
     def __init__(self, spec, runtime, prefix):
         super().__init__(spec, runtime, prefix)
-        if spec.num_heads % spec.num_kv_heads != 0:
-            raise ValueError("attention heads must be a multiple of kv heads")
         self.q_size = spec.num_heads * spec.head_dim
         self.kv_size = spec.num_kv_heads * spec.head_dim
         self.position = (build_part("position", spec.position, runtime, prefix)
@@ -43,8 +111,12 @@ class PagedAttention(Mixer):
     @classmethod
     def weight_specs(cls, spec, prefix):
         q_size, kv_size = spec.num_heads * spec.head_dim, spec.num_kv_heads * spec.head_dim
-        shapes = {"q_proj": (q_size, spec.hidden_size), "k_proj": (kv_size, spec.hidden_size),
-                  "v_proj": (kv_size, spec.hidden_size), "o_proj": (spec.hidden_size, q_size)}
+        if len(spec.projection_names) == 3:
+            shapes = dict(zip(spec.projection_names, ((q_size, spec.hidden_size), (kv_size, spec.hidden_size),
+                                                      (kv_size, spec.hidden_size))))
+        else:
+            shapes = {spec.projection_names[0]: (q_size + 2 * kv_size, spec.hidden_size)}
+        shapes[spec.output_name] = (spec.hidden_size, q_size)
         specs = []
         for name, shape in shapes.items():
             specs.append(WeightSpec(f"{prefix}{name}.weight", shape, role="matrix", init="weight"))
@@ -58,22 +130,19 @@ class PagedAttention(Mixer):
                               window=spec.window)
 
     def load(self, fetch):
-        p = self.prefix
-        self.qkv_weight = torch.cat([fetch(f"{p}{n}.weight") for n in ("q_proj", "k_proj", "v_proj")])
-        self.o_weight = fetch(f"{p}o_proj.weight")
+        p, names = self.prefix, self.spec.projection_names
+
+        def packed(kind: str) -> torch.Tensor:
+            parts = [fetch(f"{p}{n}.{kind}") for n in names]
+            return parts[0] if len(parts) == 1 else torch.cat(parts)
+
+        self.qkv_weight = packed("weight")
+        self.o_weight = fetch(f"{p}{self.spec.output_name}.weight")
         if self.spec.bias:
-            self.qkv_bias = torch.cat([fetch(f"{p}{n}.bias") for n in ("q_proj", "k_proj", "v_proj")])
-            self.o_bias = fetch(f"{p}o_proj.bias")
+            self.qkv_bias = packed("bias")
+            self.o_bias = fetch(f"{p}{self.spec.output_name}.bias")
         else:
             self.qkv_bias = self.o_bias = None
-
-    def describe(self):
-        spec = self.spec
-        return {"kind": "paged_attention", "qkv_weight": self.qkv_weight, "qkv_bias": self.qkv_bias,
-                "o_weight": self.o_weight, "o_bias": self.o_bias, "num_heads": spec.num_heads,
-                "num_kv_heads": spec.num_kv_heads, "head_dim": spec.head_dim, "window": spec.window,
-                "scale": float(spec.scale),
-                "position": self.position.describe() if self.position is not None else None}
 
     def forward(self, h, residual, ctx, binding):
         spec, rt = self.spec, self.runtime
@@ -100,12 +169,12 @@ class PagedAttention(Mixer):
             # prompt portions on tcgen05 when the kernel takes the geometry, else on mma.sync
             on_tc = _TC_ATTENTION and kernels.tc_attention_supported(rt.dtype, spec.head_dim, rt.page_size,
                                                                      qkv.stride(0), group_size)
-            narrow, n_narrow, wide, n_wide = ctx.attention_tiles(group_size, token_tiles=on_tc)
+            narrow, n_narrow, wide, n_wide = attention_tiles(ctx, group_size, token_tiles=on_tc)
             for tiles, n_tiles, is_narrow in ((narrow, n_narrow, True), (wide, n_wide, False)):
                 if n_tiles == 0:
                     continue
                 if on_tc and not is_narrow:
-                    n_splits, scratch = ctx.tc_tile_splits(n_tiles, n_narrow == 0, spec.num_heads,
+                    n_splits, scratch = tc_tile_splits(ctx, n_tiles, n_narrow == 0, spec.num_heads,
                                                            spec.num_kv_heads, spec.head_dim, spec.window)
                     kernels.paged_attention_tc(qkv, qkv.stride(0), binding.kv, group.block_tables, ctx.cu_q,
                                                ctx.context_lens, tiles, n_tiles, ctx.n_tokens,
@@ -114,7 +183,7 @@ class PagedAttention(Mixer):
                                                n_splits=n_splits, scratch=scratch)
                     continue
                 alone = (n_wide == 0) if is_narrow else (n_narrow == 0)
-                n_splits, scratch = ctx.tile_splits(n_tiles, is_narrow, alone, spec.num_heads,
+                n_splits, scratch = mma_tile_splits(ctx, n_tiles, is_narrow, alone, spec.num_heads,
                                                     spec.num_kv_heads, spec.head_dim, spec.window)
                 kernels.paged_attention_mma(qkv, qkv.stride(0), binding.kv, group.block_tables,
                                             ctx.cu_q, ctx.context_lens, tiles, n_tiles, is_narrow,
@@ -122,7 +191,7 @@ class PagedAttention(Mixer):
                                             spec.head_dim, spec.window, spec.scale, attn, ctx.status,
                                             n_splits=n_splits, scratch=scratch)
         else:
-            n_splits, scratch = ctx.attention_splits(spec.num_heads, spec.num_kv_heads,
+            n_splits, scratch = simt_splits(ctx, spec.num_heads, spec.num_kv_heads,
                                                      spec.head_dim, spec.window)
             kernels.paged_attention(qkv, qkv.stride(0), binding.kv, group.block_tables, ctx.tok_seq,
                                     ctx.positions, ctx.n_tokens, spec.num_heads, spec.num_kv_heads,

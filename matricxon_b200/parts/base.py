@@ -126,13 +126,6 @@ class Part:
     def load(self, fetch: Callable[[str], torch.Tensor]) -> None:
         return None
 
-    def describe(self) -> dict | None:
-        """What the part computes, as plain data: ``{"kind": ..., tensors, constants}``, or None
-        when it cannot be said that way. The engine reads it (after ``load``) to see whether a
-        whole step of the model fits one of its fused kernels; a part that returns None simply
-        keeps the step on the part-by-part path."""
-        return None
-
 
 class Norm(Part):
     def forward(self, x, out=None, rows=None):

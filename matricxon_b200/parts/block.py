@@ -40,13 +40,6 @@ class PreNormSequentialBlock(Block):
         for part in self.parts():
             part.load(fetch)
 
-    def describe(self):
-        parts = {"mixer_norm": self.mixer_norm.describe(), "mixer": self.mixer.describe(),
-                 "ffn_norm": self.ffn_norm.describe(), "feed_forward": self.feed_forward.describe()}
-        if any(value is None for value in parts.values()):
-            return None
-        return {"kind": "pre_norm_sequential", **parts}
-
     def forward(self, x, ctx, binding):
         h = self.mixer_norm.forward(x)
         x = self.mixer.forward(h, x, ctx, binding)

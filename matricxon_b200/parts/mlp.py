@@ -41,10 +41,6 @@ class Mlp(FeedForward):
         self.up_bias = fetch(f"{p}{s.up_name}.bias") if s.bias else None
         self.down_bias = fetch(f"{p}{s.down_name}.bias") if s.bias else None
 
-    def describe(self):
-        return {"kind": "mlp", "activation": self.spec.activation, "up_weight": self.up_weight,
-                "up_bias": self.up_bias, "down_weight": self.down_weight, "down_bias": self.down_bias}
-
     def forward(self, h, residual, ctx):
         backend = self.runtime.gemm_backend
         mid = linear(h, self.up_weight, self.up_bias, _ACTIVATION_MODES[self.spec.activation],

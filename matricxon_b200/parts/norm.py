@@ -30,9 +30,6 @@ class LayerNorm(Norm):
         self.weight = fetch(self.prefix + "weight")
         self.bias = fetch(self.prefix + "bias") if self.spec.bias else None
 
-    def describe(self):
-        return {"kind": "layernorm", "weight": self.weight, "bias": self.bias, "eps": float(self.spec.eps)}
-
     def forward(self, x, out=None, rows=None):
         n_rows = x.shape[0] if rows is None else rows.numel()
         if out is None:

@@ -31,9 +31,6 @@ class RotaryNeox(PositionEncoding):
         super().__init__(spec, runtime, prefix)
         self.inv_freq = inverse_frequencies(spec.rotary_dim, spec.theta).to(runtime.device)
 
-    def describe(self):
-        return {"kind": "rotary_neox", "inv_freq": self.inv_freq, "rotary_dim": int(self.spec.rotary_dim)}
-
     def project_rotate_store(self, h, weight, bias, ctx, binding, n_heads, n_kv_heads, head_dim):
         rt = self.runtime
         if (rt.dtype != torch.bfloat16 or rt.gemm_backend != "auto" or self.spec.rotary_dim != head_dim

@@ -8,7 +8,11 @@ passes the same constants as constructor arguments
 app/architectures/rope.py:16); here they are data so that a layer list can mix kinds.
 
 A spec class only needs a string attribute ``kind``; the class registered under
-that kind (parts/registry.py) is built from it. New kinds need no change here.
+that kind (``parts.base.register_part``) is built from it. New kinds need no change here.
+
+No tensor name is written in this file: what the tensors of a layer are called in a
+checkpoint is the architecture's business, so every name is a field that the
+architecture's configuration fills in (config/starcoder2.py for StarCoder2).
 """
 
 from __future__ import annotations
@@ -51,8 +55,24 @@ class AttentionSpec:
     bias: bool
     window: int | None
     scale: float
+    # tensor names under the mixer's prefix, without ".weight" / ".bias": either three names (the
+    # query, key and value projections as separate tensors, packed into one at load) or one name
+    # (a checkpoint that stores them fused: rows of q, then k, then v), and the output projection
+    projection_names: tuple[str, ...]
+    output_name: str
     position: Any | None = None
     kind: str = "attention"
+
+    def __post_init__(self) -> None:
+        if len(self.projection_names) not in (1, 3):
+            raise ValueError("projection_names holds three names (q, k, v) or one (fused qkv), "
+                             f"not {len(self.projection_names)}")
+        if self.num_heads % self.num_kv_heads != 0:
+            raise ValueError(f"{self.num_heads} attention heads are no multiple of "
+                             f"{self.num_kv_heads} kv heads")
+        if self.head_dim <= 0 or self.head_dim % 16 != 0 or self.head_dim > 256:
+            raise ValueError(f"head_dim {self.head_dim} is not a multiple of 16 up to 256: "
+                             "no attention kernel of this engine takes it")
 
 
 @dataclass(frozen=True)
@@ -62,9 +82,9 @@ class MlpSpec:
     hidden_size: int
     intermediate_size: int
     bias: bool
-    activation: str = "gelu_tanh"
-    up_name: str = "c_fc"
-    down_name: str = "c_proj"
+    activation: str
+    up_name: str                 # tensor names under the feed-forward's prefix
+    down_name: str
     kind: str = "mlp"
 
 
@@ -76,12 +96,12 @@ class LayerSpec:
     feed_forward: Any
     mixer_norm: Any
     ffn_norm: Any
+    # weight-name fragments under the layer's prefix ("<layer_prefix>.<index>.")
+    mixer_name: str
+    feed_forward_name: str
+    mixer_norm_name: str
+    ffn_norm_name: str
     block: str = "pre_norm_sequential"
-    # weight-name fragments under "model.layers.{i}."
-    mixer_name: str = "self_attn"
-    feed_forward_name: str = "mlp"
-    mixer_norm_name: str = "input_layernorm"
-    ffn_norm_name: str = "post_attention_layernorm"
 
 
 @dataclass(frozen=True)
@@ -107,10 +127,12 @@ class ModelSpec:
     final_norm: Any
     tie_word_embeddings: bool
     max_position_embeddings: int
-    embedding_name: str = "model.embed_tokens"
-    layer_prefix: str = "model.layers"
-    final_norm_name: str = "model.norm"
-    head_name: str = "lm_head"
+    # tensor names: "<embedding_name>.weight", "<layer_prefix>.<index>.", "<final_norm_name>.",
+    # "<head_name>.weight" (read only when the head is not tied to the embedding)
+    embedding_name: str
+    layer_prefix: str
+    final_norm_name: str
+    head_name: str
     extra: dict = field(default_factory=dict, compare=False, hash=False)
 
     def __post_init__(self) -> None:

@@ -2,6 +2,8 @@
 
 import json
 
+import dataclasses
+
 import pytest
 import torch
 
@@ -105,18 +107,13 @@ def test_cache_plan_groups_and_shared_cache():
     plan = plan_cache(spec)
     assert len(plan.groups) == 1 and plan.groups[0].entries == (0, 1)
     assert plan.groups[0].request.window == 32
-    shared = ModelSpec(hidden_size=spec.hidden_size, vocab_size=spec.vocab_size, layers=spec.layers,
-                       schedule=(ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(0),
-                                 ScheduleEntry(1, cache_of=1)),
-                       final_norm=spec.final_norm, tie_word_embeddings=True,
-                       max_position_embeddings=128)
+    shared = dataclasses.replace(spec, schedule=(ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(0),
+                                                 ScheduleEntry(1, cache_of=1)))
     plan = plan_cache(shared)
     assert plan.groups[0].entries == (0, 1, 2)          # layer 0 runs twice: two caches
     assert plan.kv_of_entry == ((0, 0), (0, 1), (0, 2), (0, 1)) and plan.writes[-1] is False
     with pytest.raises(ValueError):
-        ModelSpec(hidden_size=8, vocab_size=8, layers=spec.layers,
-                  schedule=(ScheduleEntry(0, cache_of=1), ScheduleEntry(1)),
-                  final_norm=spec.final_norm, tie_word_embeddings=True, max_position_embeddings=8)
+        dataclasses.replace(spec, schedule=(ScheduleEntry(0, cache_of=1), ScheduleEntry(1)))
 
 
 def test_random_folder_round_trip(tmp_path):
@@ -222,3 +219,23 @@ def test_sharded_folder(tmp_path):
     files = ModelFiles(tmp_path)
     assert set(files.names()) == set(names)
     assert torch.equal(files.read(second[0]), tensors[second[0]])
+
+
+def test_sizes_no_kernel_takes_are_refused_when_the_model_is_described():
+    """head sizes in steps of 16 up to 256: anything else is refused by the configuration (and by
+    the attention spec itself, for specs built by hand), not by the first kernel launch."""
+    from matricxon_b200.config import ConfigError
+
+    for head_dim in (8, 24, 40, 272):
+        raw = dict(TINY_A, head_dim=head_dim)
+        with pytest.raises(ConfigError, match="multiple of 16"):
+            config_from_dict(raw)
+    mixer = tiny_config("A").model_spec().layers[0].mixer
+    with pytest.raises(ValueError, match="multiple of 16"):
+        dataclasses.replace(mixer, head_dim=20)
+    with pytest.raises(ValueError, match="kv heads"):
+        dataclasses.replace(mixer, num_heads=5)
+    with pytest.raises(ValueError, match="projection_names"):
+        dataclasses.replace(mixer, projection_names=("q", "kv"))
+    for head_dim in (16, 48, 80, 256):
+        assert config_from_dict(dict(TINY_A, head_dim=head_dim)).head_dim == head_dim

@@ -1,6 +1,7 @@
 """Each part alone against the plain implementation, and a toy mixer with state of its own
 registered from the test, built and stepped without touching the framework's files."""
 
+import dataclasses
 from types import SimpleNamespace
 
 import pytest
@@ -37,7 +38,7 @@ def hand_made_context(seq_lens, page_size, pages, start=0):
     from matricxon_b200.engine.step import GroupStep, HostStep, StepContext
 
     runner = SimpleNamespace(
-        status=torch.zeros(1, dtype=torch.int32, device=DEV), sm_count=148,
+        status=torch.zeros(1, dtype=torch.int32, device=DEV), sm_count=148, device=torch.device(DEV),
         hidden_buffer=lambda n, h: torch.empty(n, h, device=DEV),
         scratch_buffer=lambda nbytes: torch.empty(nbytes // 4 + 1, device=DEV))
     ctx = StepContext(runner)
@@ -243,12 +244,9 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped():
     ToyDecaySpec = register_toy_parts()
     base = tiny_config("A").model_spec()
     attention_layer = base.layers[0]
-    toy_layer = LayerSpec(mixer=ToyDecaySpec(base.hidden_size, 0.5), feed_forward=attention_layer.feed_forward,
-                          mixer_norm=attention_layer.mixer_norm, ffn_norm=attention_layer.ffn_norm)
+    toy_layer = dataclasses.replace(attention_layer, mixer=ToyDecaySpec(base.hidden_size, 0.5))
     schedule = (ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(0), ScheduleEntry(1))
-    spec = ModelSpec(hidden_size=base.hidden_size, vocab_size=base.vocab_size,
-                     layers=(attention_layer, toy_layer), schedule=schedule, final_norm=base.final_norm,
-                     tie_word_embeddings=True, max_position_embeddings=128)
+    spec = dataclasses.replace(base, layers=(attention_layer, toy_layer), schedule=schedule)
     specs = model_weight_specs(spec)
     assert any(s.name == "model.layers.1.self_attn.mix.weight" for s in specs)
     source = RandomSource(specs, seed=11, init=RandomInit(0.05, 0.02, 0.02, 0.02))
@@ -376,12 +374,10 @@ def test_toy_position_encoding_and_routed_feed_forward_beside_the_stock_parts():
     stock = base.layers[0]
     decay_base, experts, inter = 1.01, 3, 80
     toy_attention = dataclasses.replace(stock.mixer, position=ToyDecaySpec(decay_base))
-    toy_layer = LayerSpec(mixer=toy_attention, feed_forward=ToyExpertsSpec(base.hidden_size, inter, experts),
-                          mixer_norm=stock.mixer_norm, ffn_norm=stock.ffn_norm)
+    toy_layer = dataclasses.replace(stock, mixer=toy_attention,
+                                    feed_forward=ToyExpertsSpec(base.hidden_size, inter, experts))
     schedule = (ScheduleEntry(0), ScheduleEntry(1))
-    spec = ModelSpec(hidden_size=base.hidden_size, vocab_size=base.vocab_size, layers=(toy_layer, stock),
-                     schedule=schedule, final_norm=base.final_norm, tie_word_embeddings=True,
-                     max_position_embeddings=128)
+    spec = dataclasses.replace(base, layers=(toy_layer, stock), schedule=schedule)
     specs = model_weight_specs(spec)
     assert any(s.name == "model.layers.0.mlp.experts.2.down.weight" for s in specs)
     source = RandomSource(specs, seed=5, init=RandomInit(0.08, 0.02, 0.02, 0.02))
@@ -454,3 +450,54 @@ def test_toy_position_encoding_and_routed_feed_forward_beside_the_stock_parts():
     for rid in prompts:
         worst = (torch.cat(got[rid]).double() - refs[rid]).abs().max()
         assert torch.allclose(torch.cat(got[rid]).double(), refs[rid], atol=1e-4), (rid, float(worst))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_with_a_fused_differently_named_qkv_tensor(dtype):
+    """A checkpoint that stores q, k and v as one tensor under other names is a matter of the
+    spec's name fields: the part is the stock one, nothing in the package changes, and the logits
+    equal the stock model's on the same numbers."""
+    from matricxon_b200.engine.core import EngineCore
+    from matricxon_b200.engine.step import StepEntry
+    from matricxon_b200.models.decoder import DecoderModel, model_weight_specs
+    from matricxon_b200.weights.loader import DictSource, make_fetcher
+
+    base = tiny_config("A").model_spec()
+    stock_layer = base.layers[0]
+    fused_mixer = dataclasses.replace(stock_layer.mixer, projection_names=("c_attn",), output_name="dense")
+    fused_layer = dataclasses.replace(stock_layer, mixer=fused_mixer, mixer_name="attn",
+                                      mixer_norm_name="ln_1", ffn_norm_name="ln_2")
+    spec = dataclasses.replace(base, layers=(fused_layer,) * len(base.layers), embedding_name="wte",
+                               layer_prefix="h", final_norm_name="ln_f")
+    names = {s.name for s in model_weight_specs(spec)}
+    assert "h.0.attn.c_attn.weight" in names and "h.1.attn.dense.bias" in names and "wte.weight" in names
+    assert not any("q_proj" in name or "model." in name for name in names)
+
+    stock = tiny_tensors("A", dtype)
+    renamed = {}
+    for layer in range(len(base.layers)):
+        old, new = f"model.layers.{layer}.", f"h.{layer}."
+        for kind in ("weight", "bias"):
+            renamed[f"{new}attn.c_attn.{kind}"] = torch.cat(
+                [stock[f"{old}self_attn.{n}.{kind}"] for n in ("q_proj", "k_proj", "v_proj")])
+            renamed[f"{new}attn.dense.{kind}"] = stock[f"{old}self_attn.o_proj.{kind}"]
+            renamed[f"{new}ln_1.{kind}"] = stock[f"{old}input_layernorm.{kind}"]
+            renamed[f"{new}ln_2.{kind}"] = stock[f"{old}post_attention_layernorm.{kind}"]
+            for n in ("c_fc", "c_proj"):
+                renamed[f"{new}mlp.{n}.{kind}"] = stock[f"{old}mlp.{n}.{kind}"]
+    renamed["wte.weight"] = stock["model.embed_tokens.weight"]
+    renamed["ln_f.weight"], renamed["ln_f.bias"] = stock["model.norm.weight"], stock["model.norm.bias"]
+    assert set(renamed) == names
+
+    ids = random_ids(45, TINY["A"][0]["vocab_size"], seed=4)
+    outputs = []
+    for model_spec, tensors in ((base, stock), (spec, renamed)):
+        model = DecoderModel(model_spec, make_runtime(dtype))
+        model.load(make_fetcher(model_weight_specs(model_spec), DictSource(tensors), dtype, DEV))
+        core = EngineCore(model, max_cache_tokens=128, max_requests=2)
+        core.cache.add_request("r")
+        first = core.runner.run([StepEntry("r", ids[:30], list(range(30)))]).clone()
+        rest = core.runner.run([StepEntry("r", ids[30:], list(range(15)))]).clone()
+        core.runner.check_status()
+        outputs.append(torch.cat([first, rest]))
+    assert torch.equal(outputs[0], outputs[1])
