@@ -1,10 +1,12 @@
 """Device tensors behind the cache manager's page numbers and state slots.
 
-One allocation per group: [entries, pages, 2 (k, v), kv heads, page_size * head_dim]
-in the runtime dtype (kept 6-D as [..., page_size, head_dim] for its element count). One
-page's keys for one KV head are a contiguous ``[slot][dim]`` tile; its values are stored
-transposed as ``[dim][slot]``, which lets a tensor-core kernel read the keys of one value
-dimension with one 16-byte load. ``keys_view`` / ``values_view`` give the two layouts names. Fixed-size state: one tensor [slots, *shape] per
+One allocation per group: [entries, pages, planes, kv heads, page_size * head_dim] in the
+runtime dtype (kept 6-D as [..., page_size, head_dim] for its element count), ``planes`` being
+what the group's mixers asked for (two for attention: keys and values). What lies inside a
+tile is the mixer's convention, not this file's. The attention part keeps one page's keys for
+one KV head as a contiguous ``[slot][dim]`` tile and its values transposed as ``[dim][slot]``,
+which lets a tensor-core kernel read the keys of one value dimension with one 16-byte load;
+``keys_view`` / ``values_view`` give those two layouts names. Fixed-size state: one tensor [slots, *shape] per
 schedule entry that asks for it (the reference allocates conv/ssm state per
 recurrent layer the same way, app/runtime/mamba_cache.py:63-70).
 """
@@ -24,8 +26,8 @@ class CacheStorage:
         self.page_size = page_size
         self.groups: list[torch.Tensor] = []
         for group, pages in zip(plan.groups, pages_per_group):
-            shape = (len(group.entries), pages, 2, group.request.num_kv_heads, page_size,
-                     group.request.head_dim)
+            shape = (len(group.entries), pages, group.request.planes, group.request.num_kv_heads,
+                     page_size, group.request.head_dim)
             tensor = torch.empty(shape, dtype=dtype, device=device)
             # NaN everywhere when asked: a read of a slot that was never written then shows
             tensor.fill_(float("nan")) if poison else tensor.zero_()
@@ -63,5 +65,5 @@ def values_view(entry_cache: torch.Tensor) -> torch.Tensor:
 
 def bytes_per_token(plan: CachePlan, dtype: torch.dtype) -> int:
     width = torch.empty((), dtype=dtype).element_size()
-    return sum(len(g.entries) * 2 * g.request.num_kv_heads * g.request.head_dim * width
+    return sum(len(g.entries) * g.request.planes * g.request.num_kv_heads * g.request.head_dim * width
                for g in plan.groups)

@@ -347,18 +347,22 @@ class StepRunner:
 
     def _graph_bucket(self, entries: list[StepEntry]) -> int | None:
         """The captured batch size a pure decode step can replay, or None for an eager step."""
-        if not self.use_graphs or self.model.cache_plan.state_bytes_per_request:
+        if not self.use_graphs:
             return None
         if len(entries) > self.max_graph_batch:
             return None
         if any(len(e.tokens) != 1 or e.want != [0] for e in entries):
             return None
         page_size = self.cache.page_size
+        stateful = bool(self.model.cache_plan.state_bytes_per_request)
         for entry in entries:
             if not self.cache.has_request(entry.request_id):
                 return None
-            if self.cache.record(entry.request_id).length // page_size >= self.graph_table_width:
+            record = self.cache.record(entry.request_id)
+            if record.length // page_size >= self.graph_table_width:
                 return None                      # longer than the captured block tables
+            if record.fresh_state and stateful:
+                return None                      # its state slot is zeroed on the eager path first
         bucket = 1
         while bucket < len(entries):
             bucket *= 2

@@ -84,7 +84,8 @@ def plan_cache(spec: ModelSpec) -> CachePlan:
         if entry.cache_of is not None:
             source = own[entry.cache_of]
             if request is not None and source is not None and \
-                    (request.num_kv_heads, request.head_dim) != (source.num_kv_heads, source.head_dim):
+                    (request.num_kv_heads, request.head_dim, request.planes) != \
+                    (source.num_kv_heads, source.head_dim, source.planes):
                 raise ValueError(f"schedule entry {position} cannot read the cache of entry "
                                  f"{entry.cache_of}: head geometry differs")
             own.append(None)
@@ -137,7 +138,7 @@ class DecoderModel:
                      else fetch(f"{self.spec.head_name}.weight"))
 
     def bind_cache(self, group_storage: list[torch.Tensor], state_storage: list[torch.Tensor | None]) -> None:
-        """``group_storage[g]`` is [entries, pages, 2, kv heads, page_size, head_dim];
+        """``group_storage[g]`` is [entries, pages, planes, kv heads, page_size, head_dim];
         ``state_storage[position]`` is [slots, *shape] or None."""
         plan = self.cache_plan
         self.bindings = []

@@ -78,11 +78,18 @@ class Runtime:
 
 @dataclass(frozen=True)
 class KVCacheRequest:
-    """Paged keys and values for one execution of a mixer. ``window`` None keeps every key."""
+    """Paged memory for one execution of a mixer: per page and KV head, ``planes`` tiles of
+    ``page_size x head_dim`` elements. Attention asks for two (keys and values); a mixer that
+    caches one vector per token (keys only, a shared latent) asks for one with
+    ``num_kv_heads = 1`` and its vector's width as ``head_dim``. How a tile is laid out inside is
+    the mixer's own business: the cache manager deals in pages, never in their contents.
+    ``window`` None keeps every position; otherwise pages wholly older than the last
+    ``window`` positions are given back."""
 
     num_kv_heads: int
     head_dim: int
     window: int | None
+    planes: int = 2
 
 
 @dataclass(frozen=True)
@@ -97,7 +104,7 @@ class StateRequest:
 class CacheBinding:
     """What one schedule entry's mixer may touch in the cache.
 
-    ``kv`` is [pages, 2, kv heads, page_size, head_dim] of the group ``group``; ``writes``
+    ``kv`` is [pages, planes, kv heads, page_size, head_dim] of the group ``group``; ``writes``
     is False when the entry reads another entry's cache. ``state`` is [slots, *shape].
     """
 

@@ -129,7 +129,7 @@ def test_greedy_generation_config_a(dtype):
     engine = ChatEngine(model, max_cache_tokens=512, max_active=4, max_batched_tokens=64, prefill_chunk=7,
                         max_model_len=128)
     prompts = [random_ids(n, cfg["vocab"], seed=n) for n in (5, 17, 40, 64)]
-    sampling = SamplingConfig(temperature=0.0, num_predict=16, num_ctx=128, seed=0)
+    sampling = SamplingConfig(temperature=0.0, repeat_penalty=1.0, num_predict=16, num_ctx=128, seed=0)
     alone = [engine.generate(GenerationRequest(p, sampling)) for p in prompts]
     for prompt, result in zip(prompts, alone):
         assert len(result.token_ids) == 16 and result.finish_reason == "length"

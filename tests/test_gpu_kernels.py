@@ -358,7 +358,7 @@ def run_attention(k, q, cache, tables, tok_seq, positions, heads, kv_heads, dim,
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("heads,kv_heads,dim,page_size", [
     (4, 2, 16, 16), (3, 1, 32, 16), (24, 2, 128, 16), (5, 5, 48, 8), (40, 2, 64, 32), (2, 1, 256, 16),
-    (8, 8, 64, 16), (14, 2, 128, 64)])
+    (8, 8, 64, 16), (14, 2, 128, 64), (36, 4, 128, 16)])
 @pytest.mark.parametrize("window", [None, 24, 100])
 def test_paged_attention_mixed_batch(dtype, heads, kv_heads, dim, page_size, window):
     k = kernels()
@@ -376,7 +376,7 @@ def test_paged_attention_mixed_batch(dtype, heads, kv_heads, dim, page_size, win
 
 @pytest.mark.parametrize("heads,kv_heads,dim,page_size", [
     (24, 2, 128, 16), (4, 4, 64, 16), (14, 2, 64, 8), (7, 1, 128, 32), (32, 2, 128, 16), (6, 3, 64, 32),
-    (40, 2, 64, 16)])
+    (40, 2, 64, 16), (36, 4, 128, 16)])
 @pytest.mark.parametrize("window", [None, 24, 100])
 def test_tensor_core_attention_mixed_batch(heads, kv_heads, dim, page_size, window):
     """The bfloat16 tensor-core kernel on decode rows, short portions and a long portion at
@@ -406,7 +406,7 @@ def test_tensor_core_attention_mixed_batch(heads, kv_heads, dim, page_size, wind
 
 
 @pytest.mark.parametrize("heads,kv_heads,page_size", [(24, 2, 16), (7, 1, 32), (32, 2, 16), (6, 6, 16), (16, 1, 32),
-                                                      (9, 3, 16)])
+                                                      (9, 3, 16), (36, 4, 16), (48, 4, 16)])
 @pytest.mark.parametrize("window", [None, 24, 100, 300])
 def test_tcgen05_attention_prompt_portions(heads, kv_heads, page_size, window):
     """The tcgen05 kernel on prompt portions (with decode rows beside them on the narrow kernel),

@@ -501,3 +501,115 @@ def test_attention_with_a_fused_differently_named_qkv_tensor(dtype):
         core.runner.check_status()
         outputs.append(torch.cat([first, rest]))
     assert torch.equal(outputs[0], outputs[1])
+
+
+# ------------------------------------------- a toy mixer whose paged cache is not a key/value pair
+def test_toy_mixer_with_a_one_plane_windowed_cache():
+    """``toy_latent_mean``: every token stores ONE projected vector in the paged cache (one plane,
+    one "head" as wide as the vector) and outputs the mean of the vectors of the last ``window``
+    positions, itself included. Its pages live in a pool of their own beside the attention
+    layers' (another geometry, another window), are written through the step's slots, read through
+    its block tables, and are given back as the window passes them. Defined here, registered
+    here; the package does not know it."""
+    from matricxon_b200.engine.core import EngineCore
+    from matricxon_b200.engine.step import StepEntry
+    from matricxon_b200.models.decoder import DecoderModel, model_weight_specs
+    from matricxon_b200.parts.base import KVCacheRequest, Mixer, register_part
+    from matricxon_b200.parts.spec import ScheduleEntry
+    from matricxon_b200.weights.loader import DictSource, WeightSpec, make_fetcher
+    from matricxon_b200.weights.random_init import RandomInit, RandomSource
+
+    class ToyLatentSpec:
+        kind = "toy_latent_mean"
+
+        def __init__(self, hidden_size, latent, window):
+            self.hidden_size, self.latent, self.window = hidden_size, latent, window
+
+    @register_part("mixer", "toy_latent_mean")
+    class ToyLatentMean(Mixer):
+        @classmethod
+        def weight_specs(cls, spec, prefix):
+            return [WeightSpec(prefix + "down.weight", (spec.latent, spec.hidden_size)),
+                    WeightSpec(prefix + "up.weight", (spec.hidden_size, spec.latent))]
+
+        @classmethod
+        def cache_request(cls, spec):
+            return KVCacheRequest(num_kv_heads=1, head_dim=spec.latent, window=spec.window, planes=1)
+
+        def load(self, fetch):
+            self.down, self.up = fetch(self.prefix + "down.weight"), fetch(self.prefix + "up.weight")
+
+        def forward(self, h, residual, ctx, binding):
+            pages, planes, heads, page_size, latent = binding.kv.shape
+            assert (planes, heads, latent) == (1, 1, self.spec.latent)
+            flat = binding.kv.view(pages * page_size, latent)          # slot -> vector
+            group = ctx.groups[binding.group]
+            vectors = h.float() @ self.down.float().T
+            if binding.writes:
+                flat[group.slots.long()] = vectors.to(flat.dtype)
+            tables = group.block_tables.cpu()
+            out = torch.empty_like(vectors)
+            row = 0
+            for seq, (q_len, start) in enumerate(zip(ctx.host.q_lens, ctx.host.context_lens)):
+                for position in range(start, start + q_len):
+                    seen = range(max(0, position - self.spec.window + 1), position + 1)
+                    slots = [int(tables[seq, j // page_size]) * page_size + j % page_size for j in seen]
+                    assert min(slots) >= 0, "a position inside the window has lost its page"
+                    out[row] = flat[torch.tensor(slots, device=h.device)].float().mean(dim=0)
+                    row += 1
+            return residual + out @ self.up.float().T
+
+    base = tiny_config("A").model_spec()
+    window, latent = 9, 48
+    toy_layer = dataclasses.replace(base.layers[0], mixer=ToyLatentSpec(base.hidden_size, latent, window))
+    schedule = (ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(1))
+    spec = dataclasses.replace(base, layers=(base.layers[0], toy_layer), schedule=schedule)
+    specs = model_weight_specs(spec)
+    source = RandomSource(specs, seed=3, init=RandomInit(0.05, 0.02, 0.02, 0.02))
+    weights = {name: source.read(name) for name in source.names()}
+    model = DecoderModel(spec, make_runtime(torch.float32))
+    plan = model.cache_plan
+    assert len(plan.groups) == 2 and plan.groups[1].entries == (1, 2)       # the toy layer runs twice
+    assert plan.groups[1].request == KVCacheRequest(1, latent, window, planes=1)
+    model.load(make_fetcher(specs, DictSource(weights), torch.float32, DEV))
+    core = EngineCore(model, max_cache_tokens=128, max_requests=2, poison_cache=True)
+    assert tuple(core.storage.groups[1].shape) == (2, 8, 1, 1, 16, latent)
+
+    cfg = plain_config(TINY["A"][0])
+    ids = random_ids(60, 512, 9)
+
+    def reference():
+        w = {k: v.double() for k, v in weights.items()}
+        x = w["model.embed_tokens.weight"][torch.tensor(ids)]
+        positions = torch.arange(len(ids))
+        for entry in schedule:
+            p = f"model.layers.{entry.layer}."
+            hidden = plain_layernorm(x, w[p + "input_layernorm.weight"], w[p + "input_layernorm.bias"], cfg["eps"])
+            if entry.layer == 1:
+                vectors = hidden @ w[p + "self_attn.down.weight"].T
+                means = torch.stack([vectors[max(0, t - window + 1):t + 1].mean(dim=0) for t in range(len(ids))])
+                x = x + means @ w[p + "self_attn.up.weight"].T
+            else:
+                x = x + plain_attention(hidden, w, p + "self_attn.", cfg, positions)
+            hidden = plain_layernorm(x, w[p + "post_attention_layernorm.weight"],
+                                     w[p + "post_attention_layernorm.bias"], cfg["eps"])
+            x = x + plain_mlp(hidden, w, p + "mlp.", cfg)
+        x = plain_layernorm(x, w["model.norm.weight"], w["model.norm.bias"], cfg["eps"])
+        return x @ w["model.embed_tokens.weight"].T
+
+    expected = reference()
+    core.cache.add_request("r")
+    got, done = [], 0
+    for size in [7, 2, 16, 1, 1, 5, 11, 3, 1, 13]:
+        size = min(size, len(ids) - done)
+        if size == 0:
+            break
+        got.append(core.runner.run([StepEntry("r", ids[done:done + size], list(range(size)))]).cpu())
+        core.runner.check_status()
+        done += size
+        core.cache.check_invariants()
+    assert done == len(ids)
+    assert torch.allclose(torch.cat(got).double(), expected, atol=5e-5)
+    # the toy group's window of 9 keeps at most two pages of 16; the attention group's window of 32 three
+    assert len(core.cache.held_pages("r", 1)) <= 2 and len(core.cache.held_pages("r", 0)) <= 3
+    assert core.cache.pages_reused > 0
