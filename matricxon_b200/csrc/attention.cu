@@ -439,9 +439,15 @@ extern "C" int mx_paged_attention_static(const void* q, int dtype, int q_stride,
                                          int window, float scale, void* out, int out_stride,
                                          int n_splits, int* status, cudaStream_t stream) {
     if (n_tokens <= 0) return MX_OK;
-    if (n_splits < 1) MX_REFUSE("static attention: n_splits %d", n_splits);
+    // sizes are checked before they are multiplied: a non-positive one would make `need` negative
+    // and slip under the limit
+    if (n_splits < 1 || n_splits > 65535) MX_REFUSE("static attention: n_splits %d is not in 1..65535", n_splits);
+    if (n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads != 0)
+        MX_REFUSE("static attention: %d heads over %d kv heads", n_heads, n_kv_heads);
+    if (head_dim <= 0 || head_dim % 16 != 0 || head_dim > 256)
+        MX_REFUSE("static attention: head_dim %d is not a multiple of 16 up to 256", head_dim);
     const long long need = mx_attention_scratch_bytes(n_tokens, n_heads, head_dim, n_splits);
-    if (need > MX_STATIC_ATTENTION_SCRATCH_BYTES)
+    if (need < 0 || need > MX_STATIC_ATTENTION_SCRATCH_BYTES)
         MX_REFUSE("static attention: %d tokens x %d heads x %d splits x head_dim %d need %lld bytes "
                   "of scratch, the built-in array holds %lld; use fewer splits or tokens per call",
                   n_tokens, n_heads, n_splits, head_dim, need, (long long)MX_STATIC_ATTENTION_SCRATCH_BYTES);

@@ -18,6 +18,10 @@
 //   * the first call on each device looks the array's device address up
 //     (cudaGetSymbolAddress) and remembers it; make that first call outside any stream
 //     capture. Later calls only launch kernels;
+//   * the array that is used is the one of the device that is current when the call is made:
+//     `q`, `out`, `cache`, the index arrays and `stream` must all belong to that device. A
+//     caller that holds pointers of device 1 while device 0 is current gets device 0's array,
+//     which device 1's kernels cannot be assumed to reach: set the device first;
 //   * the function calls no cudaMalloc, cudaFree or allocating library routine;
 //   * every call uses the same array and leaves its partials there. The kernels write each
 //     partial before the merge reads it, so nothing needs clearing between calls, but two

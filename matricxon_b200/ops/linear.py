@@ -90,9 +90,9 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, mod
     if backend == "tcgen05":
         kernels.gemm_tcgen05(x, weight, bias, residual, out, mode)
         return out
-    acc = None
-    if out_dtype == torch.float32:
-        acc = _mm_f32(x, weight.t())
+    # the library product keeps its float accumulator for every mode, so that bias, GELU and the
+    # residual see the same unrounded sum as in the engine's own kernels
+    acc = _mm_f32(x, weight.t())
     if acc is None:
         acc = torch.mm(x, weight.t())
     if mode == EPILOGUE_F32 and bias is None and acc.dtype == torch.float32:
