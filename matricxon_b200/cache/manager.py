@@ -262,16 +262,18 @@ class CacheManager:
             record.table_arrays[group] = array = grown
         return array[:width]
 
-    def slot_ids(self, request_id: str, group: int, start: int, count: int) -> list[int]:
-        """Physical slots (page * page_size + offset) of positions [start, start + count)."""
-        table = self.record(request_id).tables[group]
-        out = []
-        for position in range(start, start + count):
-            page = table[position // self.page_size]
-            if page < 0:
-                raise CacheError(f"position {position} of {request_id!r} has no page in group {group}")
-            out.append(page * self.page_size + position % self.page_size)
-        return out
+    def slot_ids(self, request_id: str, group: int, start: int, count: int) -> "np.ndarray":
+        """Physical slots (page * page_size + offset) of positions [start, start + count), int32."""
+        record = self.record(request_id)
+        positions = np.arange(start, start + count, dtype=np.int64)
+        logical = positions // self.page_size
+        if count > 0 and logical[-1] >= len(record.tables[group]):
+            raise CacheError(f"position {start + count - 1} of {request_id!r} has no page in group {group}")
+        pages = record.table_arrays[group][logical].astype(np.int64)
+        if count > 0 and pages.min() < 0:
+            bad = int(positions[np.argmax(pages < 0)])
+            raise CacheError(f"position {bad} of {request_id!r} has no page in group {group}")
+        return (pages * self.page_size + positions % self.page_size).astype(np.int32)
 
     # ------------------------------------------------------------------ inspection
     def free_pages(self) -> list[int]:

@@ -35,35 +35,6 @@
 
 namespace {
 
-// Tuning aid (compile with -DAT_PROFILE): thread 0 of every block adds the cycles between successive
-// marks of its softmax loop to g_at_marks[mark]; read with mx_attention_tc_marks.
-#ifdef AT_PROFILE
-#ifndef AT_MARK_TID
-#define AT_MARK_TID 0
-#endif
-__device__ unsigned long long g_at_marks[16];
-#define AT_MARK(i)                                                                        \
-    do {                                                                                  \
-        if (tid == AT_MARK_TID) {                                                         \
-            long long now_;                                                               \
-            asm volatile("mov.u64 %0, %%clock64;\n" : "=l"(now_));                        \
-            atomicAdd(&g_at_marks[i], (unsigned long long)(now_ - at_last_));             \
-            at_last_ = now_;                                                              \
-        }                                                                                 \
-    } while (0)
-// the same for the MMA-issuing thread (marks 8-15)
-#define AT_MARK_M(i)                                                                      \
-    do {                                                                                  \
-        long long now_;                                                                   \
-        asm volatile("mov.u64 %0, %%clock64;\n" : "=l"(now_));                            \
-        atomicAdd(&g_at_marks[i], (unsigned long long)(now_ - at_last_m_));               \
-        at_last_m_ = now_;                                                                \
-    } while (0)
-#else
-#define AT_MARK(i)
-#define AT_MARK_M(i)
-#endif
-
 constexpr int AT_ROWS = 128;
 constexpr int AT_KEYS = 128;
 constexpr int AT_HD = 128;
@@ -398,17 +369,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
                 v_step[kk] = (unsigned)((pg * page_bytes) >> 4) + 2u * within;
             }
             bool alive = at_wait(&sh.q_full, 0, p.status);
-#ifdef AT_PROFILE
-            long long at_last_m_;
-            asm volatile("mov.u64 %0, %%clock64;\n" : "=l"(at_last_m_));
-#endif
             // state of the chunk whose scores are issued next (qk_*) and of the chunk whose P V is next (pv_*)
             int qk_stage = 0, qk_buf = 0;
             unsigned qk_stage_parity = 0;
             auto issue_qk = [&]() -> bool {
-                AT_MARK_M(8);
                 if (!at_wait(&sh.k_full[qk_stage], qk_stage_parity, p.status)) return false;
-                AT_MARK_M(9);
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
                 const unsigned acc = tmem_base + (unsigned)qk_buf * 128;
 #pragma unroll
@@ -417,7 +382,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
                     for (int k = 0; k < 4; ++k)
                         at_mma(acc, q_desc[half] + 2 * k, k_desc[qk_stage][half] + 2 * k, idesc, (half | k) != 0);
                 at_commit(&sh.s_full[qk_buf]);
-                AT_MARK_M(10);
                 if (++qk_stage == AT_STAGES) {
                     qk_stage = 0;
                     qk_stage_parity ^= 1u;
@@ -433,11 +397,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
                     alive = issue_qk();
                     if (!alive) break;
                 }
-                AT_MARK_M(11);
                 if (!at_wait(&sh.p_full[pv_buf], pv_buf_parity, p.status)) break;
-                AT_MARK_M(12);
                 if (!at_wait(&sh.v_full[pv_stage], pv_stage_parity, p.status)) break;
-                AT_MARK_M(13);
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
                 const unsigned p_addr = tmem_base + (unsigned)pv_buf * 128;
 #pragma unroll
@@ -474,16 +435,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
                 ++consumed;
             }
         };
-#ifdef AT_PROFILE
-        long long at_last_;
-        asm volatile("mov.u64 %0, %%clock64;\n" : "=l"(at_last_));
-#endif
         for (int j = 0; j < n_chunks && alive; ++j) {
             const int b = j % AT_SBUF, s = j % AT_STAGES;
-            AT_MARK(0);
             alive = at_wait(&sh.s_full[b], (unsigned)(j / AT_SBUF) & 1, p.status);
             if (!alive) break;
-            AT_MARK(1);
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
             pv_consumed_through(j - 1);               // long completed: this only keeps the count in step
             if (!alive) break;
@@ -496,7 +451,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
 #pragma unroll
             for (int piece = 0; piece < 4; ++piece) tmem_load32(s_addr + 32 * piece, sc + 32 * piece);
             asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-            AT_MARK(2);
             if (edge) {
 #pragma unroll
                 for (int c = 0; c < AT_KEYS; ++c) {
@@ -508,7 +462,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
 #pragma unroll
             for (int c = 0; c < AT_KEYS; ++c) mx = fmaxf(mx, sc[c]);
             mx *= p.scale_log2;
-            AT_MARK(3);
             const bool jump = mx > m_ref + AT_JUMP || (m_ref == -INFINITY && mx > -INFINITY);
             const float m_new = jump ? mx : m_ref;
             // O may only be touched while no P V is running: the rare rescaling waits for the previous one
@@ -548,7 +501,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
                 tmem_store32_bits(s_addr + 32 * half, packed);
             }
             asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
-            AT_MARK(4);
             l_run += sum;
             if (j == n_chunks - 1 && c0 + AT_KEYS - 1 > hi_tile) {
                 // value slots beyond the newest key hold no data yet: zero them in the stage
@@ -571,11 +523,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
             __syncwarp();
             if (lane == 0) at_arrive(&sh.p_full[b]);
-            AT_MARK(5);
         }
-        AT_MARK(6);
         pv_consumed_through(n_chunks);
-        AT_MARK(7);
         if (alive && p.n_splits > 1) {
             // a share of the keys: the unnormalised sums, the reference maximum and the sum of weights
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
@@ -657,17 +606,6 @@ int at_make_map(CUtensorMap* map, const void* base, int rank, const cuuint64_t* 
 
 }  // namespace
 
-#ifdef AT_PROFILE
-extern "C" int mx_attention_tc_marks(unsigned long long* out, int reset) {
-    cudaDeviceSynchronize();
-    if (out) cudaMemcpyFromSymbol(out, g_at_marks, sizeof(unsigned long long) * 16);
-    if (reset) {
-        static unsigned long long zeros[16];
-        cudaMemcpyToSymbol(g_at_marks, zeros, sizeof(zeros));
-    }
-    return MX_OK;
-}
-#endif
 
 // tiles: [n_tiles][2] (sequence, first token within the sequence); a tile covers
 // tokens_per_tile = 128 / group tokens of that sequence. q: [n_tokens][q_stride] with query head h

@@ -34,6 +34,8 @@
 
 #include <cstdlib>
 
+#include <mutex>
+
 #include "common.cuh"
 
 namespace {
@@ -209,17 +211,6 @@ __device__ __forceinline__ void store_piece(const unsigned (&r)[16], const float
     }
 }
 
-// Tuning aid (compile with -DTC_PROFILE): cycles that the roles of the 256-row kernel spend in
-// each of their phases, summed over all blocks; read with mx_gemm_tcgen05_marks.
-#ifdef TC_PROFILE
-__device__ unsigned long long g_tc_marks[16];
-#define TC_CLOCK(var) long long var; asm volatile("mov.u64 %0, %%clock64;\n" : "=l"(var))
-#define TC_ADD(i, from, to) atomicAdd(&g_tc_marks[i], (unsigned long long)((to) - (from)))
-#else
-#define TC_CLOCK(var)
-#define TC_ADD(i, from, to)
-#endif
-
 // Epilogue warps per 32 accumulator lanes and accumulator (they take 32-column pieces in turn): one.
 constexpr int TCP_PARTS = 1;
 
@@ -325,10 +316,7 @@ struct EpilogueLane {
                                           int lane, unsigned free_bar) {
         const int c_next = c + 32 * TCP_PARTS;
         const bool last = c_next >= bn;
-        TC_CLOCK(d0);
         asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-        TC_CLOCK(d1);
-        if (threadIdx.x == 0) { TC_ADD(10, d0, d1); }
         const float4 b4 = bias4;
         if (!last) load_bias(bias, n0, c_next, bn, N);
         if constexpr (!F32) {
@@ -346,8 +334,6 @@ struct EpilogueLane {
             for (int u = 0; u < 8; ++u)
                 sts128(row_dst + ((u ^ (lane & 7)) << 4), cur[4 * u], cur[4 * u + 1], cur[4 * u + 2], cur[4 * u + 3]);
             __syncwarp();
-            TC_CLOCK(d2);
-            if (threadIdx.x == 0) { TC_ADD(11, d1, d2); }
             if (row0 + 32 <= M && n0 + c + 32 <= N && c + 32 <= bn) {
                 // every row and column of the piece exists: no predicates, vector accesses only
                 float4 v[8];
@@ -387,8 +373,6 @@ struct EpilogueLane {
                 edge_piece(stage_addr, c, row0, n0, bn, b4, residual, out, ldo, M, N, mode);
             }
             __syncwarp();                                // the stage is free for the next piece
-            TC_CLOCK(d3);
-            if (threadIdx.x == 0) { TC_ADD(12, d2, d3); }
         }
         if constexpr (F32) {                             // the next piece and its residual set out together
             if (!last) {
@@ -648,7 +632,6 @@ gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     // its part into the output (residual mode in place only: the additions happen at the memory side)
     const int per_split = (k_slices + k_splits - 1) / k_splits;
     const int n_items = n_tiles * k_splits;
-    TC_CLOCK(t_start);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < TCW_STAGES; ++s) {
@@ -670,8 +653,6 @@ gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
     const unsigned tmem_base = sh.tmem_base;
-    TC_CLOCK(t_setup);
-    if (threadIdx.x == 0) { TC_ADD(0, t_start, t_setup); }
 
     if (warp == 8) {
         // ---------------- producer
@@ -684,10 +665,7 @@ gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                 const int ks_end = min(k_slices, (split + 1) * per_split);
                 for (int ks = split * per_split; ks < ks_end; ++ks, ++it) {
                     const int s = it % TCW_STAGES;
-                    TC_CLOCK(p0);
                     alive = tc_mbar_wait(&sh.empty[s], ((unsigned)(it / TCW_STAGES) & 1) ^ 1, status);
-                    TC_CLOCK(p1);
-                    TC_ADD(1, p0, p1);
                     if (!alive) break;
                     tc_mbar_expect_tx(&sh.full[s], stage_bytes);
                     unsigned char* a_tile = tiles + (size_t)s * stage_bytes;
@@ -707,19 +685,12 @@ gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             for (int item = blockIdx.x; item < n_items && alive; item += gridDim.x, ++local) {
                 const int split = item % k_splits;
                 const int ks_begin = split * per_split, ks_end = min(k_slices, ks_begin + per_split);
-                TC_CLOCK(m0);
                 alive = tc_mbar_wait(&sh.acc_empty, ((unsigned)local & 1) ^ 1, status);
-                TC_CLOCK(m1);
-                TC_ADD(2, m0, m1);
                 if (!alive) break;
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
                 for (int ks = ks_begin; ks < ks_end; ++ks, ++it) {
                     const int s = it % TCW_STAGES;
-                    TC_CLOCK(m2);
                     alive = tc_mbar_wait(&sh.full[s], (unsigned)(it / TCW_STAGES) & 1, status);
-                    TC_CLOCK(m3);
-                    TC_ADD(3, m2, m3);
-                    if (ks == ks_begin) { TC_ADD(4, m2, m3); }
                     if (!alive) break;
                     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
                     const unsigned char* a_tile = tiles + (size_t)s * stage_bytes;
@@ -734,8 +705,6 @@ gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                     umma_commit(&sh.empty[s]);
                 }
                 if (alive) umma_commit(&sh.acc_full);
-                TC_CLOCK(m4);
-                TC_ADD(5, m1, m4);
             }
         }
     } else {
@@ -752,20 +721,13 @@ gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             const float* bias_here = split == 0 ? bias : nullptr;     // one of a tile's parts brings the bias
             EpilogueLane<F32> mine;
             mine.prefetch(bias_here, residual, out, ldo, row0, n0, 0, bn, M, N, mode, lane);
-            TC_CLOCK(e0);
             if (!tc_mbar_wait(&sh.acc_full, (unsigned)local & 1, status)) break;
-            TC_CLOCK(e1);
-            if (threadIdx.x == 0) { TC_ADD(6, e0, e1); }
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
             mine.drain(tbase, row0, n0, 0, bn, bias_here, residual, out, ldo, M, N, mode, stage, lane, free_bar);
-            TC_CLOCK(e2);
-            if (threadIdx.x == 0) { TC_ADD(7, e1, e2); }
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
     __syncthreads();
-    TC_CLOCK(t_end);
-    if (threadIdx.x == 0) { TC_ADD(8, t_start, t_end); TC_ADD(9, 0, 1); }
     if (warp == 9) {
         __syncwarp();
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
@@ -862,7 +824,6 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     const int k_slices = (K + TC_BK - 1) / TC_BK;
     const int tiles_m = (M + TCP_ROWS - 1) / TCP_ROWS, tiles_n = (N + bn - 1) / bn;
     const int n_tiles = tiles_m * tiles_n;
-    TC_CLOCK(t_start);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < TCP_STAGES; ++s) {
@@ -885,8 +846,6 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     cluster_barrier();                                  // the peer's barriers exist from here on
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
     const unsigned tmem_base = sh.tmem_base;
-    TC_CLOCK(t_setup);
-    if (threadIdx.x == 0) { TC_ADD(0, t_start, t_setup); }
 
     if (warp == TCP_EPI_WARPS) {
         // ---------------- producer (in both blocks)
@@ -898,10 +857,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                 const int n0 = (tile / tiles_m) * bn + (bn / 2) * (int)rank;
                 for (int ks = 0; ks < k_slices; ++ks, ++it) {
                     const int s = it % TCP_STAGES;
-                    TC_CLOCK(p0);
                     alive = tc_mbar_wait(&sh.empty[s], ((unsigned)(it / TCP_STAGES) & 1) ^ 1, status);
-                    TC_CLOCK(p1);
-                    if (rank == 0) { TC_ADD(1, p0, p1); }
                     if (!alive) break;
                     if (rank == 0) tc_mbar_expect_tx(&sh.full[s], 2 * stage_bytes);
                     const unsigned bar = shared_of_rank(&sh.full[s], 0);
@@ -923,19 +879,12 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             int it = 0, local = 0;
             bool alive = true;
             for (int tile = pair; tile < n_tiles && alive; tile += n_pairs, ++local) {
-                TC_CLOCK(m0);
                 alive = tc_mbar_wait(&sh.acc_empty, ((unsigned)local & 1) ^ 1, status);
-                TC_CLOCK(m1);
-                TC_ADD(2, m0, m1);
                 if (!alive) break;
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
                 for (int ks = 0; ks < k_slices; ++ks, ++it) {
                     const int s = it % TCP_STAGES;
-                    TC_CLOCK(m2);
                     alive = tc_mbar_wait(&sh.full[s], (unsigned)(it / TCP_STAGES) & 1, status);
-                    TC_CLOCK(m3);
-                    TC_ADD(3, m2, m3);
-                    if (ks == 0) { TC_ADD(4, m2, m3); }
                     if (!alive) break;
                     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
                     const unsigned char* a_tile = tiles + (size_t)s * stage_bytes;
@@ -950,8 +899,6 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                     umma_commit_pair(&sh.empty[s]);
                 }
                 if (alive) umma_commit_pair(&sh.acc_full);
-                TC_CLOCK(m4);
-                TC_ADD(5, m1, m4);
             }
         }
     } else {
@@ -966,22 +913,15 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             const unsigned tbase = tmem_base + (unsigned)half * 256 + ((unsigned)(32 * quarter) << 16);
             EpilogueLane<F32> mine;
             mine.prefetch(bias, residual, out, ldo, row0, n0, c_first, bn, M, N, mode, lane);
-            TC_CLOCK(e0);
             if (!tc_mbar_wait(&sh.acc_full, (unsigned)local & 1, status)) break;
-            TC_CLOCK(e1);
-            if (threadIdx.x == 0 && rank == 0) { TC_ADD(6, e0, e1); }
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
             mine.drain(tbase, row0, n0, c_first, bn, bias, residual, out, ldo, M, N, mode, stage, lane, free_bar);
-            TC_CLOCK(e2);
-            if (threadIdx.x == 0 && rank == 0) { TC_ADD(7, e1, e2); }
         }
     }
     // ---------------- teardown: neither block leaves while the other may still touch its memory
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
     __syncthreads();
     cluster_barrier();
-    TC_CLOCK(t_end);
-    if (threadIdx.x == 0 && rank == 0) { TC_ADD(8, t_start, t_end); TC_ADD(9, 0, 1); }
     if (warp == TCP_EPI_WARPS + 1) {
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(512)
@@ -1007,7 +947,42 @@ EncodeTiledFn encode_tiled_fn() {
 }
 
 // A [rows, K] bfloat16 matrix with `ld` elements between rows, cut into boxes of box_rows x 64.
+// Encoding a map costs the host a few microseconds and a step launches some hundred products, most of
+// them on the same weight matrices and the same activation buffers as the step before: maps are kept
+// by what they describe (address, extents, row stride, box) and encoded once. A map holds no reference
+// to the memory: a stale entry whose address now holds another tensor of the same extents describes
+// that tensor just as well.
+struct MapKey {
+    const void* base;
+    long long rows, K, ld;
+    int box_rows;
+    bool operator==(const MapKey& o) const {
+        return base == o.base && rows == o.rows && K == o.K && ld == o.ld && box_rows == o.box_rows;
+    }
+};
+
+struct MapSlot {
+    MapKey key;
+    CUtensorMap map;
+    bool used;
+};
+
+constexpr int MAP_CACHE_SLOTS = 4096;           // a power of two
+MapSlot g_map_cache[MAP_CACHE_SLOTS];
+std::mutex g_map_cache_lock;
+
 int make_map(CUtensorMap* map, const void* base, long long rows, long long K, long long ld, int box_rows) {
+    const MapKey key = {base, rows, K, ld, box_rows};
+    unsigned long long h = (unsigned long long)(size_t)base * 0x9E3779B97F4A7C15ull;
+    h ^= (unsigned long long)rows * 0xC2B2AE3D27D4EB4Full + (unsigned long long)K * 0x165667B19E3779F9ull +
+         (unsigned long long)ld * 0x27D4EB2F165667C5ull + (unsigned long long)box_rows;
+    h ^= h >> 29;
+    std::lock_guard<std::mutex> guard(g_map_cache_lock);
+    MapSlot& slot = g_map_cache[h & (MAP_CACHE_SLOTS - 1)];
+    if (slot.used && slot.key == key) {
+        *map = slot.map;
+        return MX_OK;
+    }
     EncodeTiledFn encode = encode_tiled_fn();
     if (encode == nullptr) MX_REFUSE("tcgen05 gemm: the driver does not offer cuTensorMapEncodeTiled");
     const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
@@ -1018,8 +993,14 @@ int make_map(CUtensorMap* map, const void* base, long long rows, long long K, lo
                                box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (rc != CUDA_SUCCESS) MX_REFUSE("tcgen05 gemm: cuTensorMapEncodeTiled failed with code %d", (int)rc);
+    slot.key = key;
+    slot.map = *map;
+    slot.used = true;
     return MX_OK;
 }
+
+// Set by mx_gemm_tcgen05_force_tiles (0: the kernel is chosen by shape).
+int g_forced_tile_rows = 0;
 
 // The tile width that needs the fewest rounds of work per SM: the time of a product is about
 // (rounds of tiles per SM) x (tile width + a fixed cost per tile).
@@ -1106,22 +1087,14 @@ int pair_count() {
 
 }  // namespace
 
-#ifdef TC_PROFILE
-// marks: 0 setup, 1 producer waiting for a free stage, 2 issuer waiting for the accumulator, 3 issuer
-// waiting for operands (4: of which the first slice of a tile), 5 issuer per tile from accumulator free to
-// last commit, 6 epilogue waiting for the accumulator, 7 epilogue draining, 8 whole block, 9 blocks (pairs
-// in the pair kernel, whose marks 10-12 - the drain's waits for tensor memory, its way into shared memory
-// and out to global memory - are added by thread 0 of both blocks: halve them)
-extern "C" int mx_gemm_tcgen05_marks(unsigned long long* out, int reset) {
-    cudaDeviceSynchronize();
-    if (out) cudaMemcpyFromSymbol(out, g_tc_marks, sizeof(unsigned long long) * 16);
-    if (reset) {
-        static unsigned long long zeros[16];
-        cudaMemcpyToSymbol(g_tc_marks, zeros, sizeof(zeros));
-    }
+// Forces the 128-, 256- or 512-row kernel where the shape allows it (0 gives the choice back to the
+// shape): tests run all three on the same product.
+extern "C" int mx_gemm_tcgen05_force_tiles(int rows) {
+    if (rows != 0 && rows != 128 && rows != 256 && rows != 512)
+        MX_REFUSE("tcgen05 gemm: tiles of %d rows do not exist (128, 256, 512, or 0 for the shape's own)", rows);
+    g_forced_tile_rows = rows;
     return MX_OK;
 }
-#endif
 
 extern "C" int mx_gemm_tcgen05(const void* A, const void* W, const float* bias, const float* residual,
                                void* out, int out_dtype, int M, int N, int K, int lda, int ldw, int ldo,
@@ -1170,8 +1143,8 @@ extern "C" int mx_gemm_tcgen05(const void* A, const void* W, const float* bias, 
             wide = cost_256 <= cost_128;
         }
     }
-    if (const char* force = getenv("MATRICXON_GEMM_TILES")) {       // for measurements: 128, 256 or 512 rows
-        const int rows = atoi(force);
+    if (g_forced_tile_rows != 0) {       // mx_gemm_tcgen05_force_tiles: tests run every kernel on the same product
+        const int rows = g_forced_tile_rows;
         if (rows == 128) { wide = false; pair = false; }
         if (rows == 256 && vector_ok) { wide = true; pair = false; }
         if (rows == 512 && vector_ok && n_pairs > 0) { pair = true; wide = false; }
@@ -1239,7 +1212,6 @@ extern "C" int mx_gemm_tcgen05(const void* A, const void* W, const float* bias, 
     if (rc != MX_OK) return rc;
     // two slices of K per stage where four such stages fit (tiles of up to 64 columns)
     int kk = 2 * TC_STAGES * (TC_BM + bn) * TC_BK * 2 + TC_STAGING + 1024 <= 226 * 1024 ? 2 : 1;
-    if (const char* force = getenv("MATRICXON_GEMM_KK")) kk = atoi(force) == 2 && kk == 2 ? 2 : 1;
     const size_t smem = (size_t)kk * TC_STAGES * (TC_BM + bn) * TC_BK * 2 + TC_STAGING + 1024;
     const long long tiles = (long long)((M + TC_BM - 1) / TC_BM) * ((N + bn - 1) / bn);
     const int grid = (int)(tiles < n_sm ? tiles : n_sm);

@@ -19,6 +19,7 @@ from __future__ import annotations
 
 import gc
 import os
+import time
 from dataclasses import dataclass, field
 
 import numpy as np
@@ -117,7 +118,7 @@ class StepRunner:
     def __init__(self, model, cache: CacheManager, storage: CacheStorage,
                  max_step_tokens: int = 8192, max_step_seqs: int = 256,
                  max_model_len: int | None = None, use_graphs: bool = True,
-                 max_graph_batch: int = 64) -> None:
+                 max_graph_batch: int = 64, max_shape_graphs: int = 24) -> None:
         self.model = model
         self.cache = cache
         self.storage = storage
@@ -139,6 +140,15 @@ class StepRunner:
         self.use_graphs = use_graphs and getattr(model, "capturable", False)
         self.max_graph_batch = max_graph_batch
         self._graphs: dict[int, tuple] = {}
+        # steps that are not pure decoding are captured too, one graph per exact shape (how many
+        # tokens each entry brings and where it wants logits), from the second time a shape is seen:
+        # a prompt cut into equal portions, or the same mix of portions and decoded tokens step
+        # after step, then costs the host one metadata copy and one replay instead of some three
+        # hundred launches. Shapes seen once (the ragged end of a prompt) run eagerly.
+        self.max_shape_graphs = max_shape_graphs
+        self._shape_graphs: dict[tuple, tuple] = {}        # shape -> record, oldest use first
+        self._shape_seen: dict[tuple, int] = {}
+        self.host_seconds = 0.0           # time the host spent inside ``run`` so far
         self._status_host: torch.Tensor | None = None
         self.chained_launch_rows = int(os.environ.get("MATRICXON_CHAINED_ROWS", "2"))
         self._graph_host_arrays: dict[int, tuple] = {}       # bucket -> (pinned tensor, its numpy view)
@@ -368,43 +378,56 @@ class StepRunner:
             bucket *= 2
         return bucket
 
+    def _graph_buffers(self, n_tokens: int, n_seqs: int, widths: list[int]):
+        """A pinned and a device buffer of a graph's own for the step's metadata, and the event
+        that says when the latest copy between them is done."""
+        layout_ints = 16 * max(n_tokens, n_seqs) + 64 + sum((n_tokens + 4) + n_seqs * (w + 4) for w in widths)
+        buffers = (torch.empty(layout_ints, dtype=torch.int32, pin_memory=True),
+                   torch.zeros(layout_ints, dtype=torch.int32, device=self.device),
+                   torch.cuda.Event())
+        buffers[2].record()
+        return buffers
+
+    def _capture(self, ctx: StepContext, decode_rows: bool, chained: bool):
+        """Runs the step of ``ctx`` once eagerly (which also builds what parts keep per step) and
+        captures it as a CUDA graph. Returns (graph, the graph's own logits, launches per step)."""
+        ctx.max_kv_len = self.graph_table_width * self.cache.page_size
+        launches_before = kernels.launch_count
+        # steps of very few rows gain from kernels that start while their predecessor drains
+        kernels.set_chained_launch(chained)
+        try:
+            self._forward(ctx, decode_rows=decode_rows)             # warm-up, outside the capture
+            launches = kernels.launch_count - launches_before
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            ctx.capturing = True
+            # no garbage collection inside the capture: a collected object may free pinned memory or
+            # destroy a stream-ordered resource, which invalidates a capture in progress
+            gc_was_on = gc.isenabled()
+            gc.disable()
+            try:
+                with torch.cuda.graph(graph, pool=self._graph_pool):
+                    static_logits = self._forward(ctx, decode_rows=decode_rows)
+            finally:
+                if gc_was_on:
+                    gc.enable()
+            ctx.capturing = False
+        finally:
+            kernels.set_chained_launch(False)
+        if self._graph_pool is None:
+            self._graph_pool = graph.pool()
+        return graph, static_logits, launches
+
     def _run_graph(self, entries: list[StepEntry], bucket: int, token_feed: torch.Tensor | None = None) -> torch.Tensor:
         record = self._graphs.get(bucket)
         if token_feed is not None and record is None:
             raise StepError("a step fed from the device needs the graph of its batch size to exist already")
         widths = [self.graph_table_width] * len(self.cache.rules)
         if record is None:
-            layout_ints = 16 * bucket + 64 + sum(bucket * (w + 4) for w in widths)
-            buffers = (torch.empty(layout_ints, dtype=torch.int32, pin_memory=True),
-                       torch.zeros(layout_ints, dtype=torch.int32, device=self.device),
-                       torch.cuda.Event())
-            buffers[2].record()
+            buffers = self._graph_buffers(bucket, bucket, widths)
             ctx = self.build(entries, pad_to=bucket, table_widths=widths, buffers=buffers)
-            ctx.max_kv_len = self.graph_table_width * self.cache.page_size
-            launches_before = kernels.launch_count
-            # steps of very few rows gain from kernels that start while their predecessor drains
-            kernels.set_chained_launch(bucket <= self.chained_launch_rows)
-            try:
-                self._forward(ctx, decode_rows=True)             # warm-up, outside the capture
-                self.launches_per_step = kernels.launch_count - launches_before
-                torch.cuda.synchronize()
-                graph = torch.cuda.CUDAGraph()
-                ctx.capturing = True
-                # no garbage collection inside the capture: a collected object may free pinned memory or
-                # destroy a stream-ordered resource, which invalidates a capture in progress
-                gc_was_on = gc.isenabled()
-                gc.disable()
-                try:
-                    with torch.cuda.graph(graph, pool=self._graph_pool):
-                        static_logits = self._forward(ctx, decode_rows=True)
-                finally:
-                    if gc_was_on:
-                        gc.enable()
-                ctx.capturing = False
-            finally:
-                kernels.set_chained_launch(False)
-            if self._graph_pool is None:
-                self._graph_pool = graph.pool()
+            graph, static_logits, launches = self._capture(ctx, True, bucket <= self.chained_launch_rows)
+            self.launches_per_step = launches
             # the captured kernels hold raw pointers into everything the context owns (the tile
             # list among them), so the context lives as long as the graph
             self._graphs[bucket] = (graph, static_logits, buffers, self.launches_per_step, ctx)
@@ -419,6 +442,54 @@ class StepRunner:
         graph.replay()
         self.launches_per_step = launches
         return static_logits[:len(entries)]
+
+    def _shape_key(self, entries: list[StepEntry]) -> tuple | None:
+        """The exact shape of a step that may run as a graph of its own, or None."""
+        if not self.use_graphs or self.max_shape_graphs <= 0:
+            return None
+        page_size = self.cache.page_size
+        stateful = bool(self.model.cache_plan.state_bytes_per_request)
+        for entry in entries:
+            if not self.cache.has_request(entry.request_id):
+                return None
+            record = self.cache.record(entry.request_id)
+            if (record.length + len(entry.tokens) - 1) // page_size >= self.graph_table_width:
+                return None                      # longer than the captured block tables
+            if record.fresh_state and stateful:
+                return None
+        return tuple((len(entry.tokens), tuple(entry.want)) for entry in entries)
+
+    def _run_shape_graph(self, entries: list[StepEntry], key: tuple) -> torch.Tensor | None:
+        """A step of a shape seen before: captured at its second appearance, replayed from then on."""
+        record = self._shape_graphs.pop(key, None)
+        widths = [self.graph_table_width] * len(self.cache.rules)
+        if record is None:
+            seen = self._shape_seen.get(key, 0) + 1
+            self._shape_seen[key] = seen
+            if len(self._shape_seen) > 4096:
+                self._shape_seen.clear()
+            if seen < 2:
+                return self._run_eager(entries)
+            n_tokens = sum(len(entry.tokens) for entry in entries)
+            buffers = self._graph_buffers(n_tokens, len(entries), widths)
+            ctx = self.build(entries, table_widths=widths, buffers=buffers)
+            graph, static_logits, launches = self._capture(ctx, False, False)
+            record = (graph, static_logits, buffers, launches, ctx)
+            while len(self._shape_graphs) >= self.max_shape_graphs:
+                self._shape_graphs.pop(next(iter(self._shape_graphs)))      # the least recently used
+        else:
+            self.build(entries, table_widths=widths, buffers=record[2])
+        self._shape_graphs[key] = record
+        record[0].replay()
+        self.launches_per_step = record[3]
+        return record[1]
+
+    def _run_eager(self, entries: list[StepEntry]) -> torch.Tensor | None:
+        ctx = self.build(entries)
+        launches_before = kernels.launch_count
+        logits = self._forward(ctx)
+        self.launches_per_step = kernels.launch_count - launches_before
+        return logits
 
     def _refill_decode(self, entries: list[StepEntry], bucket: int, widths: list[int], buffers) -> None:
         """The metadata of a captured decode step, written straight into the graph's pinned buffer
@@ -508,8 +579,10 @@ class StepRunner:
         it chose have reached the host. Only steps that replay an existing graph take it.
 
         A step of single decode tokens replays a CUDA graph captured for its batch size
-        (rounded up to a power of two with padding rows); the logits it returns live in the
-        graph's memory and are overwritten by the next step of that size."""
+        (rounded up to a power of two with padding rows); any other step replays a graph of its
+        exact shape from the second time that shape is seen. The logits a replay returns live in
+        the graph's memory and are overwritten by the next step of that shape."""
+        started = time.perf_counter()
         bucket = self._graph_bucket(entries)
         try:
             if token_feed is not None and bucket is None:
@@ -517,10 +590,8 @@ class StepRunner:
             if bucket is not None:
                 logits = self._run_graph(entries, bucket, token_feed)
             else:
-                ctx = self.build(entries)
-                launches_before = kernels.launch_count
-                logits = self._forward(ctx)
-                self.launches_per_step = kernels.launch_count - launches_before
+                key = self._shape_key(entries)
+                logits = self._run_shape_graph(entries, key) if key is not None else self._run_eager(entries)
         except OutOfPages:
             raise
         except Exception:
@@ -532,6 +603,7 @@ class StepRunner:
             self.cache.commit(entry.request_id, len(entry.tokens))
         self.steps_run += 1
         self.tokens_run += len(entries) if bucket is not None else sum(len(e.tokens) for e in entries)
+        self.host_seconds += time.perf_counter() - started
         return logits
 
     def enqueue_status_read(self) -> None:

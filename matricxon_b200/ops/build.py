@@ -26,8 +26,7 @@ LIB_NAME = "libmatricxon_b200.so"
 NVCC_ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--compiler-options", "-fPIC",
               "-Xcudafe", "--diag_suppress=177"]
-# more flags for this process's build, e.g. MATRICXON_NVCC_EXTRA=-DDF_PROFILE for the cycle
-# counters of the one-kernel decode step (they are part of the stamp: a different library)
+# more flags for this process's build (they are part of the stamp: a different library)
 NVCC_FLAGS += os.environ.get("MATRICXON_NVCC_EXTRA", "").split()
 
 

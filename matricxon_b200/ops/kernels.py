@@ -216,6 +216,12 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None,
     _launched()
 
 
+def gemm_tcgen05_force_tiles(rows: int) -> None:
+    """Makes ``gemm_tcgen05`` use its 128-, 256- or 512-row kernel wherever the shape allows it; 0
+    gives the choice back to the shape. For tests that run all three on the same product."""
+    check(library().mx_gemm_tcgen05_force_tiles(int(rows)), "gemm_tcgen05_force_tiles")
+
+
 def skinny_gemm_supported(a: torch.Tensor, w: torch.Tensor) -> bool:
     return (a.dtype == torch.bfloat16 and a.shape[0] <= 16 and a.shape[1] % 32 == 0
             and a.stride(1) == 1 and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0

@@ -51,7 +51,7 @@ def test_reserve_commit_free():
     assert cache.pages_needed("a", 5) == [2]
     cache.reserve("a", 5)
     assert cache.record("a").reserved == 5 and cache.free_pages() == [14]
-    assert cache.slot_ids("a", 0, 0, 5) == [0, 1, 2, 3, 4]
+    assert cache.slot_ids("a", 0, 0, 5).tolist() == [0, 1, 2, 3, 4]
     cache.commit("a", 5)
     assert cache.record("a").length == 5
     assert cache.pages_needed("a", 3) == [0]       # room left in the second page

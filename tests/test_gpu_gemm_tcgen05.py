@@ -39,16 +39,24 @@ def test_tcgen05_gemm_all_epilogues(m, n, k_dim):
     assert status.item() == 0
 
 
+@pytest.fixture
+def forced_tiles():
+    from matricxon_b200.ops import kernels as k
+
+    yield k.gemm_tcgen05_force_tiles
+    k.gemm_tcgen05_force_tiles(0)
+
+
 @pytest.mark.parametrize("rows", [128, 256, 512])
 @pytest.mark.parametrize("m,n,k_dim", [(513, 264, 64), (700, 3000, 256), (1537, 3072, 1024), (1100, 1000, 96),
                                        (200, 1000, 3072), (300, 3072, 12288)])
-def test_tcgen05_gemm_every_tile_height(rows, m, n, k_dim, monkeypatch):
+def test_tcgen05_gemm_every_tile_height(rows, m, n, k_dim, forced_tiles):
     """The three kernels (128-row tiles, 256-row tiles, 512-row tiles on pairs of SMs) on the same
     products: each is forced in turn; edges in M, N and K, an N that is no multiple of 16. With a
     residual added in place the 256-row kernel shares K out between blocks (the long-K cases)."""
     from matricxon_b200.ops import kernels as k
 
-    monkeypatch.setenv("MATRICXON_GEMM_TILES", str(rows))
+    forced_tiles(rows)
     torch.manual_seed(rows + m)
     a = torch.randn(m, k_dim, device=DEV).bfloat16()
     w = (torch.randn(n, k_dim, device=DEV) / math.sqrt(k_dim)).bfloat16()
