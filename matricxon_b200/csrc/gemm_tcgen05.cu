@@ -37,91 +37,14 @@
 #include <mutex>
 
 #include "common.cuh"
+#include "tcgen05_helpers.cuh"
 
 namespace {
 
 constexpr int TC_BM = 128;
-constexpr int TC_BK = 64;              // 64 bf16 = 128 bytes = one swizzle row
 constexpr int TC_STAGES = 4;
 constexpr int TC_THREADS = 192;
 constexpr int TC_STAGING = 4 * 4096;      // a 4 KB stage for each epilogue warp
-constexpr int TC_SPIN_LIMIT = 1 << 22;
-
-__device__ __forceinline__ unsigned smem_u32(const void* ptr) {
-    return (unsigned)__cvta_generic_to_shared(ptr);
-}
-__device__ __forceinline__ void tc_mbar_init(unsigned long long* bar, int count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void tc_mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes)
-                 : "memory");
-}
-__device__ __forceinline__ bool tc_mbar_try_wait(unsigned long long* bar, unsigned parity) {
-    unsigned ok;
-    asm volatile(
-        "{\n.reg .pred p;\n"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-        "selp.u32 %0, 1, 0, p;\n}\n"
-        : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-// Returns false when the wait ran out (the status word is set; the caller carries on).
-__device__ __forceinline__ bool tc_mbar_wait(unsigned long long* bar, unsigned parity, int* status) {
-    for (int spin = 0; spin < TC_SPIN_LIMIT; ++spin)
-        if (tc_mbar_try_wait(bar, parity)) return true;
-    atomicOr(status, MX_STATUS_WAIT_TIMEOUT);
-    return false;
-}
-
-__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y,
-                                            unsigned long long* bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::"r"(
-            smem_u32(smem_dst)),
-        "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
-        : "memory");
-}
-
-// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows of 128 bytes, groups of
-// eight rows 1024 bytes apart.
-__device__ __forceinline__ unsigned long long umma_desc(const void* smem_tile) {
-    unsigned long long desc = 0;
-    desc |= (unsigned long long)((smem_u32(smem_tile) & 0x3FFFF) >> 4);        // start address
-    desc |= (unsigned long long)1 << 16;                                       // leading offset (unused here)
-    desc |= (unsigned long long)(1024 >> 4) << 32;                             // stride between 8-row groups
-    desc |= (unsigned long long)1 << 46;                                       // descriptor version of sm_100
-    desc |= (unsigned long long)2 << 61;                                       // SWIZZLE_128B
-    return desc;
-}
-
-// Instruction descriptor of kind::f16: bf16 x bf16 -> f32, both operands K-major, M x N tile.
-__device__ __forceinline__ unsigned umma_idesc(int m, int n) {
-    unsigned d = 0;
-    d |= 1u << 4;                      // accumulator format: f32
-    d |= 1u << 7;                      // A format: bf16
-    d |= 1u << 10;                     // B format: bf16
-    d |= (unsigned)(n >> 3) << 17;
-    d |= (unsigned)(m >> 4) << 24;
-    return d;
-}
-
-__device__ __forceinline__ void umma_bf16(unsigned tmem_acc, unsigned long long adesc,
-                                          unsigned long long bdesc, unsigned idesc, bool accumulate) {
-    asm volatile(
-        "{\n.reg .pred p;\n"
-        "setp.ne.b32 p, %4, 0;\n"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_acc),
-        "l"(adesc), "l"(bdesc), "r"(idesc), "r"((unsigned)accumulate)
-        : "memory");
-}
-__device__ __forceinline__ void umma_commit(unsigned long long* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(
-                     smem_u32(bar))
-                 : "memory");
-}
 
 struct TcShared {
     unsigned long long full[TC_STAGES];
@@ -130,21 +53,6 @@ struct TcShared {
     unsigned long long acc_empty[2];
     unsigned tmem_base;
 };
-
-__device__ __forceinline__ void tc_mbar_arrive(unsigned long long* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
-}
-
-__device__ __forceinline__ void tmem_load16(unsigned taddr, unsigned (&r)[16]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr)
-        : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-}
 
 // Applies the epilogue to 16 accumulator values of one output row and stores them.
 __device__ __forceinline__ void store_piece(const unsigned (&r)[16], const float* __restrict__ bias,
@@ -971,7 +879,9 @@ constexpr int MAP_CACHE_SLOTS = 4096;           // a power of two
 MapSlot g_map_cache[MAP_CACHE_SLOTS];
 std::mutex g_map_cache_lock;
 
-int make_map(CUtensorMap* map, const void* base, long long rows, long long K, long long ld, int box_rows) {
+}  // namespace
+
+int mx_tensor_map_2d(CUtensorMap* map, const void* base, long long rows, long long K, long long ld, int box_rows) {
     const MapKey key = {base, rows, K, ld, box_rows};
     unsigned long long h = (unsigned long long)(size_t)base * 0x9E3779B97F4A7C15ull;
     h ^= (unsigned long long)rows * 0xC2B2AE3D27D4EB4Full + (unsigned long long)K * 0x165667B19E3779F9ull +
@@ -998,6 +908,8 @@ int make_map(CUtensorMap* map, const void* base, long long rows, long long K, lo
     slot.used = true;
     return MX_OK;
 }
+
+namespace {
 
 // Set by mx_gemm_tcgen05_force_tiles (0: the kernel is chosen by shape).
 int g_forced_tile_rows = 0;
@@ -1170,9 +1082,9 @@ extern "C" int mx_gemm_tcgen05(const void* A, const void* W, const float* bias, 
     if (pair) {
         const int bn = pick_tile_width(M, N, n_pairs, TCP_ROWS);
         CUtensorMap map_a, map_w;
-        int rc = make_map(&map_a, A, M, K, lda, 128);
+        int rc = mx_tensor_map_2d(&map_a, A, M, K, lda, 128);
         if (rc != MX_OK) return rc;
-        rc = make_map(&map_w, W, N, K, ldw, bn / 2);
+        rc = mx_tensor_map_2d(&map_w, W, N, K, ldw, bn / 2);
         if (rc != MX_OK) return rc;
         const size_t smem = (size_t)TCP_STAGES * (256 + bn / 2) * TC_BK * 2 + TCP_STAGING + 1024;
         const long long tiles = (long long)((M + TCP_ROWS - 1) / TCP_ROWS) * ((N + bn - 1) / bn);
@@ -1189,9 +1101,9 @@ extern "C" int mx_gemm_tcgen05(const void* A, const void* W, const float* bias, 
         int bn = pick_tile_width(M, N, n_sm, TCW_BM), k_splits = 1;
         if (may_split) pick_width_and_split(M, N, K, n_sm, &bn, &k_splits);
         CUtensorMap map_a, map_w;
-        int rc = make_map(&map_a, A, M, K, lda, TCW_BM);
+        int rc = mx_tensor_map_2d(&map_a, A, M, K, lda, TCW_BM);
         if (rc != MX_OK) return rc;
-        rc = make_map(&map_w, W, N, K, ldw, bn);
+        rc = mx_tensor_map_2d(&map_w, W, N, K, ldw, bn);
         if (rc != MX_OK) return rc;
         const size_t smem = (size_t)TCW_STAGES * (TCW_BM + bn) * TC_BK * 2 + TCW_STAGING + 1024;
         const long long items = (long long)((M + TCW_BM - 1) / TCW_BM) * ((N + bn - 1) / bn) * k_splits;
@@ -1206,9 +1118,9 @@ extern "C" int mx_gemm_tcgen05(const void* A, const void* W, const float* bias, 
     }
     const int bn = pick_tile_width(M, N, n_sm, TC_BM);
     CUtensorMap map_a, map_w;
-    int rc = make_map(&map_a, A, M, K, lda, TC_BM);
+    int rc = mx_tensor_map_2d(&map_a, A, M, K, lda, TC_BM);
     if (rc != MX_OK) return rc;
-    rc = make_map(&map_w, W, N, K, ldw, bn);
+    rc = mx_tensor_map_2d(&map_w, W, N, K, ldw, bn);
     if (rc != MX_OK) return rc;
     // two slices of K per stage where four such stages fit (tiles of up to 64 columns)
     int kk = 2 * TC_STAGES * (TC_BM + bn) * TC_BK * 2 + TC_STAGING + 1024 <= 226 * 1024 ? 2 : 1;

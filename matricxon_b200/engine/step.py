@@ -147,6 +147,7 @@ class StepRunner:
         # hundred launches. Shapes seen once (the ragged end of a prompt) run eagerly.
         self.max_shape_graphs = max_shape_graphs
         self._shape_graphs: dict[tuple, tuple] = {}        # shape -> record, oldest use first
+        self._shape_pool = None
         self._shape_seen: dict[tuple, int] = {}
         self.host_seconds = 0.0           # time the host spent inside ``run`` so far
         self._status_host: torch.Tensor | None = None
@@ -388,7 +389,7 @@ class StepRunner:
         buffers[2].record()
         return buffers
 
-    def _capture(self, ctx: StepContext, decode_rows: bool, chained: bool):
+    def _capture(self, ctx: StepContext, decode_rows: bool, chained: bool, pool_name: str = "_graph_pool"):
         """Runs the step of ``ctx`` once eagerly (which also builds what parts keep per step) and
         captures it as a CUDA graph. Returns (graph, the graph's own logits, launches per step)."""
         ctx.max_kv_len = self.graph_table_width * self.cache.page_size
@@ -406,7 +407,7 @@ class StepRunner:
             gc_was_on = gc.isenabled()
             gc.disable()
             try:
-                with torch.cuda.graph(graph, pool=self._graph_pool):
+                with torch.cuda.graph(graph, pool=getattr(self, pool_name)):
                     static_logits = self._forward(ctx, decode_rows=decode_rows)
             finally:
                 if gc_was_on:
@@ -414,8 +415,8 @@ class StepRunner:
             ctx.capturing = False
         finally:
             kernels.set_chained_launch(False)
-        if self._graph_pool is None:
-            self._graph_pool = graph.pool()
+        if getattr(self, pool_name) is None:
+            setattr(self, pool_name, graph.pool())
         return graph, static_logits, launches
 
     def _run_graph(self, entries: list[StepEntry], bucket: int, token_feed: torch.Tensor | None = None) -> torch.Tensor:
@@ -473,7 +474,9 @@ class StepRunner:
             n_tokens = sum(len(entry.tokens) for entry in entries)
             buffers = self._graph_buffers(n_tokens, len(entries), widths)
             ctx = self.build(entries, table_widths=widths, buffers=buffers)
-            graph, static_logits, launches = self._capture(ctx, False, False)
+            # a memory pool apart from the decode graphs': their small buffers then stay close together
+            # instead of being scattered through the blocks that prompt-sized steps leave behind
+            graph, static_logits, launches = self._capture(ctx, False, False, "_shape_pool")
             record = (graph, static_logits, buffers, launches, ctx)
             while len(self._shape_graphs) >= self.max_shape_graphs:
                 self._shape_graphs.pop(next(iter(self._shape_graphs)))      # the least recently used

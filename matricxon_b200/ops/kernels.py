@@ -222,6 +222,48 @@ def gemm_tcgen05_force_tiles(rows: int) -> None:
     check(library().mx_gemm_tcgen05_force_tiles(int(rows)), "gemm_tcgen05_force_tiles")
 
 
+_sm_counts: dict[int, int] = {}
+
+
+def sm_count(device: torch.device) -> int:
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    if index not in _sm_counts:
+        _sm_counts[index] = torch.cuda.get_device_properties(index).multi_processor_count
+    return _sm_counts[index]
+
+
+def stream_gemm_supported(a: torch.Tensor, w: torch.Tensor) -> bool:
+    return (a.dtype == torch.bfloat16 and 0 < a.shape[0] <= 128 and a.shape[1] % 8 == 0 and a.stride(1) == 1
+            and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+            and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemm_stream(a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None,
+                residual: torch.Tensor | None, out: torch.Tensor, mode: int,
+                status: torch.Tensor | None = None) -> None:
+    """The product for up to 128 rows (decoding, short prompt portions): the weight matrix is streamed
+    from HBM once, dealt out evenly over the SMs, through TMA into tcgen05 products with the tokens
+    as the narrow side; the epilogue is fused. A row's result does not depend on the other rows."""
+    _need(a, "a", torch.bfloat16, contiguous=False)
+    _need(w, "w", torch.bfloat16)
+    _need(out, "out")
+    m, k = a.shape
+    n = w.shape[0]
+    assert w.shape[1] == k and tuple(out.shape) == (m, n), (a.shape, w.shape, out.shape)
+    if bias is not None:
+        _need(bias, "bias", torch.float32)
+        assert bias.numel() == n
+    if residual is not None:
+        _need(residual, "residual", torch.float32)
+        assert tuple(residual.shape) == (m, n) and residual.stride(0) == out.stride(0)
+    if status is None:
+        status = default_status(a.device)
+    check(library().mx_gemm_stream(_ptr(a), _ptr(w), _ptr(bias), _ptr(residual), _ptr(out),
+                                   dtype_code(out.dtype), m, n, k, a.stride(0), w.stride(0),
+                                   out.stride(0), mode, _ptr(status), _stream()), "gemm_stream")
+    _launched()
+
+
 def skinny_gemm_supported(a: torch.Tensor, w: torch.Tensor) -> bool:
     return (a.dtype == torch.bfloat16 and a.shape[0] <= 16 and a.shape[1] % 32 == 0
             and a.stride(1) == 1 and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0

@@ -34,6 +34,7 @@ _SIGNATURES: dict[str, tuple[list, object]] = {
     "mx_gemm_simt": ([P, P, I, P, P, P, I, I, I, I, I, I, I, I, P], I),
     "mx_gemm_tcgen05": ([P, P, P, P, P, I, I, I, I, I, I, I, I, P, P], I),
     "mx_gemm_tcgen05_force_tiles": ([I], I),
+    "mx_gemm_stream": ([P, P, P, P, P, I, I, I, I, I, I, I, I, P, P], I),
     "mx_gemm_skinny": ([P, P, P, P, P, I, I, I, I, I, I, I, I, P], I),
     "mx_gemm_skinny_rope": ([P, P, P, P, I, I, I, I, I, P, P, P, P, L, I, I, I, I, P, P], I),
     "mx_attention_scratch_bytes": ([I, I, I, I], L),

@@ -4,14 +4,17 @@ Backends, chosen by the runtime:
   "simt"    -- the engine's own FP32-core kernel; the only backend of the 32-bit path.
   "skinny"  -- the engine's tensor-core kernel for at most 16 rows (decoding): the weight
                matrix is streamed once and the epilogue is fused.
+  "stream"  -- the engine's TMA + tcgen05 kernel for at most 128 rows with the tokens as the
+               narrow side of the product: one block per SM streams its share of the weight rows.
   "tcgen05" -- the engine's TMA + tcgen05 kernel for prompt-sized products: operands staged by
                TMA, accumulator in tensor memory, epilogue fused.
   "library" -- cuBLAS through ``torch.mm`` for bfloat16 (the reference runs its products
                through nn.Linear, i.e. the library: app/architectures/qwen_layers.py:50-53),
                followed by the engine's fused bias / GELU / residual epilogue kernel.
   "auto"    -- "simt" for float32; for bfloat16 "skinny" up to 16 rows, "tcgen05" above 128 rows,
-               and "library" between (a weight stream that 128-row tiles would leave to a few
-               SMs) and for shapes neither takes (a K that is no multiple of 8).
+               "library" between (a weight stream that 128-row tiles would leave to a few SMs) and
+               for shapes neither takes (a K that is no multiple of 8), and "stream" from 9 rows
+               on where every SM owns many weight rows (``_pick`` gives the measured thresholds).
 """
 
 from __future__ import annotations
@@ -50,9 +53,28 @@ def resolve_backend(requested: str, dtype: torch.dtype) -> str:
             raise KernelLibraryError(
                 f"the float32 path runs on the FP32-core kernel only, not {requested!r}")
         return "simt"
-    if requested not in ("auto", "simt", "skinny", "tcgen05", "library"):
+    if requested not in ("auto", "simt", "skinny", "stream", "tcgen05", "library"):
         raise KernelLibraryError(f"unknown GEMM backend {requested!r}")
     return requested
+
+
+def _pick(x: torch.Tensor, weight: torch.Tensor, m: int, n: int) -> str:
+    """The backend "auto" stands for, from measurements on B200 with weights streaming from HBM.
+    Up to 8 rows the 16-row kernel is the fastest on every shape (its many small blocks hide the
+    latencies that the streaming kernel's one pipeline per SM has to sit through). From 9 rows on that
+    kernel works on two token blocks and slows by 40 %; the streaming kernel does not, and wins where
+    every SM owns enough weight rows to keep its pipeline busy: 64 for 9 to 16 rows (the wide
+    feed-forward matrix: 17 against 23 us; the vocabulary-sized head: 53 against 71 us), 256 for 17 to
+    128 rows (the head: 59 against 66 us for the library's product plus the epilogue kernel)."""
+    if 9 <= m <= 128 and kernels.stream_gemm_supported(x, weight):
+        rows_per_block = -(-n // kernels.sm_count(x.device))
+        if rows_per_block >= (64 if m <= 16 else 256):
+            return "stream"
+    if kernels.skinny_gemm_supported(x, weight):
+        return "skinny"
+    if m > 128 and kernels.tcgen05_gemm_supported(x, weight):
+        return "tcgen05"
+    return "library"
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, mode: int,
@@ -67,12 +89,7 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, mod
     out_dtype = torch.float32 if mode in (EPILOGUE_RESIDUAL, EPILOGUE_F32) else x.dtype
     backend = resolve_backend(backend, x.dtype)
     if backend == "auto":
-        if kernels.skinny_gemm_supported(x, weight):
-            backend = "skinny"
-        elif m > 128 and kernels.tcgen05_gemm_supported(x, weight):
-            backend = "tcgen05"
-        else:
-            backend = "library"
+        backend = _pick(x, weight, m, n)
     if backend == "library" and out is None and mode == EPILOGUE_F32 and bias is None and m > 0:
         acc = _mm_f32(x, weight.t())
         if acc is not None:
@@ -87,12 +104,19 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, mod
     if backend == "skinny":
         kernels.gemm_skinny(x, weight, bias, residual, out, mode)
         return out
+    if backend == "stream":
+        kernels.gemm_stream(x, weight, bias, residual, out, mode)
+        return out
     if backend == "tcgen05":
         kernels.gemm_tcgen05(x, weight, bias, residual, out, mode)
         return out
-    # the library product keeps its float accumulator for every mode, so that bias, GELU and the
-    # residual see the same unrounded sum as in the engine's own kernels
-    acc = _mm_f32(x, weight.t())
+    # Float outputs keep the library's float accumulator. Outputs in bfloat16 (the QKV product, the
+    # feed-forward's first product) take the library's bfloat16 result and are rounded a second time
+    # after bias and GELU: keeping the accumulator there too measured 4 % of a 64-row decode step (a
+    # float pass over the widest activations), for a difference of one rounding in 2^-9.
+    acc = None
+    if out_dtype == torch.float32:
+        acc = _mm_f32(x, weight.t())
     if acc is None:
         acc = torch.mm(x, weight.t())
     if mode == EPILOGUE_F32 and bias is None and acc.dtype == torch.float32:
