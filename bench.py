@@ -16,6 +16,7 @@ time; ``points`` adds decoding at batch 1 and 64. Between timed iterations the w
 from __future__ import annotations
 
 import argparse
+import gc
 import json
 import os
 import subprocess
@@ -72,7 +73,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "25"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
             return
@@ -179,28 +180,46 @@ def fill_cache(engine, batch: int, context: int, vocab: int):
     return ids
 
 
-def time_decode(engine, ids, vocab, steps, warmup):
-    """K decode steps of the whole batch, timed on the device. Every step appends one token
-    per request, so the context grows from ``context`` by K."""
+def percentile(values, q: float) -> float:
+    ordered = sorted(values)
+    if not ordered:
+        return float("nan")
+    return ordered[min(len(ordered) - 1, int(round(q * (len(ordered) - 1))))]
+
+
+def time_decode(engine, ids, vocab, steps, warmup, detail: dict | None = None):
+    """K decode steps of the whole batch, timed on the device: one CUDA event before every step
+    and one after the last, so that the K steps are timed exactly and each step's own time is
+    known too. Every step appends one token per request, so the context grows by K."""
     import torch
 
     from matricxon_b200.engine.step import StepEntry
 
     generator = torch.Generator().manual_seed(2)
+    runner = engine.core.runner
+
     def one_step():
         tokens = torch.randint(0, vocab, (len(ids),), generator=generator).tolist()
-        return engine.core.runner.run([StepEntry(rid, [tok], [0]) for rid, tok in zip(ids, tokens)])
+        return runner.run([StepEntry(rid, [tok], [0]) for rid, tok in zip(ids, tokens)])
     for _ in range(warmup):
         one_step()
     torch.cuda.synchronize()
-    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    begin.record()
-    for _ in range(steps):
+    marks = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+    host_before = runner.host_seconds - runner.wait_seconds
+    for i in range(steps):
+        marks[i].record()
         one_step()
-    end.record()
+    marks[steps].record()
     torch.cuda.synchronize()
-    engine.core.runner.check_status()
-    return begin.elapsed_time(end) / steps
+    runner.check_status()
+    per_step = [marks[i].elapsed_time(marks[i + 1]) for i in range(steps)]
+    if detail is not None:
+        detail["step_ms_p50"] = round(percentile(per_step, 0.5), 4)
+        detail["step_ms_p99"] = round(percentile(per_step, 0.99), 4)
+        # the host's own work per step (building and uploading the metadata, replaying the graph), without
+        # the time it sat waiting for the device to release the step's metadata buffer
+        detail["host_ms_per_step"] = round((runner.host_seconds - runner.wait_seconds - host_before) / steps * 1e3, 4)
+    return marks[0].elapsed_time(marks[steps]) / steps
 
 
 def decode_bytes(config, n_layers, batch, context, model) -> float:
@@ -222,6 +241,87 @@ def prefill_flops(config, n_layers, tokens) -> float:
     return n_layers * (gemm + attention) + 2.0 * v * h               # one row of logits
 
 
+STARCODER2_7B = dict(STARCODER2_3B, num_hidden_layers=32, hidden_size=4608, num_attention_heads=36,
+                     num_key_value_heads=4, intermediate_size=18432, rope_theta=1000000.0,
+                     tie_word_embeddings=False)
+STARCODER2_15B = dict(STARCODER2_3B, num_hidden_layers=40, hidden_size=6144, num_attention_heads=48,
+                      num_key_value_heads=4, intermediate_size=24576, rope_theta=100000.0,
+                      tie_word_embeddings=False)
+
+
+def run_workload(tag: str, config_dict: dict, prompt_lens: list[int], decode_steps: int, chunk: int,
+                 temperature: float, max_len: int, peaks: dict, bias_std: float = 0.0) -> dict:
+    """A whole workload through the public entry point: every request is added at once, the scheduler
+    cuts the prompts into portions of ``chunk`` tokens beside the decoding requests, and every request
+    generates ``decode_steps`` tokens. Reports generated tokens a second (end to end, host ids in and
+    out), prompt tokens a second while prompts were running, step latencies, the most pages held at
+    once, preemptions, and for the steps in which everybody decoded the bytes they had to read over
+    their time, as a fraction of the copy peak."""
+    import torch
+
+    from matricxon_b200 import ChatEngine, SamplingConfig
+    from matricxon_b200.config.registry import config_from_dict
+    from matricxon_b200.engine.core import build_model
+    from matricxon_b200.weights.random_init import RandomInit, RandomSource, weight_specs_for
+
+    config = config_from_dict(dict(config_dict))
+    source = RandomSource(weight_specs_for(config), seed=0, init=RandomInit(weight_std=0.02, bias_std=bias_std),
+                          device="cuda:0", store_dtype=torch.bfloat16)
+    model = build_model(config, source, "bfloat16", "cuda:0", PAGE_SIZE)
+    window = config.sliding_window or max_len
+    # room for every request at its longest: pages of a window (plus the portion being written) or of the whole
+    per_request = min(max_len, window + chunk + 2 * PAGE_SIZE)
+    cache_tokens = len(prompt_lens) * per_request
+    engine = ChatEngine(model, max_cache_tokens=cache_tokens, max_active=len(prompt_lens),
+                        max_batched_tokens=max(chunk + len(prompt_lens), 2048), prefill_chunk=chunk,
+                        max_model_len=max_len)
+    generator = torch.Generator().manual_seed(11)
+    sampling = SamplingConfig(temperature=temperature, top_k=0, top_p=1.0, repeat_penalty=1.0,
+                              num_predict=decode_steps, num_ctx=max_len, seed=5)
+    for n in prompt_lens:
+        engine.add_request(torch.randint(0, config.vocab_size, (n,), generator=generator).tolist(), sampling)
+    pool = engine.core.cache.pools[0]
+    step_ms, decode_ms, prompt_ms = [], [], 0.0
+    generated = 0
+    high_water = 0
+    torch.cuda.synchronize()
+    started = time.perf_counter()
+    while engine.has_unfinished():
+        prompts_running = any(s.remaining > 1 for s in engine.scheduler.running) or bool(engine.scheduler.waiting)
+        t0 = time.perf_counter()
+        produced = engine.step()
+        dt = (time.perf_counter() - t0) * 1e3
+        step_ms.append(dt)
+        generated += sum(1 for _, token, _ in produced if token is not None)
+        high_water = max(high_water, pool.num_pages - pool.free_count)
+        if prompts_running:
+            prompt_ms += dt
+        elif len(produced) == len(prompt_lens):
+            decode_ms.append(dt)
+    torch.cuda.synchronize()
+    seconds = time.perf_counter() - started
+    engine.core.runner.check_status()
+    # bytes a step of pure decoding has to read: every weight once, and each request's visible cache
+    n_layers = config.num_hidden_layers
+    mean_ctx = sum(min(n + decode_steps / 2, window) for n in prompt_lens)
+    kv = config.num_key_value_heads * config.head_dim
+    necessary = decode_bytes(config, n_layers, 0, 0, model) + mean_ctx * n_layers * 2 * kv * 2
+    p50 = percentile(decode_ms, 0.5)
+    out = {
+        f"{tag}_tok_s": round(generated / seconds, 1),
+        f"{tag}_prompt_tok_s": round(sum(prompt_lens) / (prompt_ms * 1e-3), 1) if prompt_ms else None,
+        f"{tag}_step_ms_p50": round(percentile(step_ms, 0.5), 3),
+        f"{tag}_step_ms_p99": round(percentile(step_ms, 0.99), 3),
+        f"{tag}_decode_step_ms_p50": round(p50, 3) if decode_ms else None,
+        f"{tag}_decode_hbm_frac": round(necessary / (p50 * 1e-3) / 1e9 / peaks["hbm_gbs"], 4) if decode_ms else None,
+        f"{tag}_pages_high_water": high_water, f"{tag}_pages_total": pool.num_pages,
+        f"{tag}_preemptions": engine.scheduler.num_preemptions, f"{tag}_steps": len(step_ms),
+    }
+    del engine, model, source
+    torch.cuda.empty_cache()
+    return out
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -235,6 +335,8 @@ def main() -> int:
     parser.add_argument("--skip-points", action="store_true")
     parser.add_argument("--skip-prefill", action="store_true")
     parser.add_argument("--skip-e2e", action="store_true")
+    parser.add_argument("--skip-workloads", action="store_true",
+                        help="leave out the 7B and 15B workloads through the scheduler")
     parser.add_argument("--no-graphs", action="store_true",
                         help="launch every kernel of a decode step by itself (for profilers)")
     args = parser.parse_args()
@@ -267,8 +369,10 @@ def main() -> int:
     context = min(args.context, CONTEXT - args.steps - args.warmup - 1)
     ids = fill_cache(engine, batch, context, vocab)
     mark_a = clocks.mark()
-    ms_step = time_decode(engine, ids, vocab, args.steps, args.warmup)
+    decode_detail: dict = {}
+    ms_step = time_decode(engine, ids, vocab, args.steps, args.warmup, decode_detail)
     mark_b = clocks.mark()
+    pages_in_use = engine.core.cache.pools[0].num_pages - engine.core.cache.free_pages()[0]
     mean_context = context + args.warmup + args.steps / 2
     necessary = decode_bytes(config, n_layers, batch, mean_context, model)
     achieved_gbs = necessary / (ms_step * 1e-3) / 1e9
@@ -307,9 +411,11 @@ def main() -> int:
             prefill_ms.append(begin.elapsed_time(end))
     # the same prompt in portions of 256 tokens, one step each (the scheduler's default portion)
     portion_ms = []
-    for rep in range(0 if (args.skip_prefill or args.skip_points) else 3):
+    portion_host = 0.0
+    for rep in range(0 if (args.skip_prefill or args.skip_points) else 4):
         engine.core.cache.add_request("portions")
         torch.cuda.synchronize()
+        host_before = engine.core.runner.host_seconds - engine.core.runner.wait_seconds
         begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         begin.record()
         for start in range(0, PREFILL_TOKENS, 256):
@@ -319,8 +425,11 @@ def main() -> int:
         torch.cuda.synchronize()
         engine.core.cache.free_request("portions")
         portion_ms.append(begin.elapsed_time(end))
+        portion_host = (engine.core.runner.host_seconds - engine.core.runner.wait_seconds - host_before) / (PREFILL_TOKENS // 256)
     if portion_ms:
         points["prefill_2048_in_256_token_steps"] = round(PREFILL_TOKENS / (min(portion_ms) * 1e-3), 1)
+        points["prefill_256_token_step_ms"] = round(min(portion_ms) / (PREFILL_TOKENS // 256), 3)
+        points["prefill_256_token_step_host_ms"] = round(portion_host * 1e3, 3)
     pf_ms = sorted(prefill_ms)[len(prefill_ms) // 2] if prefill_ms else float("nan")
     pf_flops = prefill_flops(config, n_layers, PREFILL_TOKENS)
     pf_frac = pf_flops / (pf_ms * 1e-3) / (peaks["bf16_tflops"] * 1e12)
@@ -351,8 +460,19 @@ def main() -> int:
     h2d_bytes = engine.core.runner.last_upload_bytes + engine.sampler.last_upload_bytes
     d2h_bytes = batch * 4 + 4
 
-    clocks.stop()
     launches = engine.core.runner.launches_per_step
+    pool_pages = engine.core.cache.pools[0].num_pages
+    # ---- the two larger configurations, whole workloads through the scheduler (shortened where the
+    # full one would take minutes: the names say how)
+    if not (args.skip_points or args.skip_workloads):
+        del engine, model
+        gc.collect()
+        torch.cuda.empty_cache()
+        lengths = torch.randint(128, 6001, (32,), generator=torch.Generator().manual_seed(7)).tolist()
+        points.update(run_workload("w7b_32req_chunk512_256steps", STARCODER2_7B, lengths, 256, 512, 0.0, 16384, peaks))
+        points.update(run_workload("w15b_8x12288_128steps", STARCODER2_15B, [12288] * 8, 128, 512, 1.0, 16384, peaks))
+        engine = None
+    clocks.stop()
     value = batch / (ms_step * 1e-3)
     record = {
         "metric": "decode tok/s @ batch 8 (StarCoder2-3B bf16, one B200)",
@@ -379,6 +499,9 @@ def main() -> int:
                     "ms": round(pf_ms, 3), "frac": round(pf_frac, 4)},
         "roofline": {"bound": "hbm", "achieved": round(achieved_gbs, 1), "peak": peaks["hbm_gbs"],
                      "unit": "GB/s", "frac": round(achieved_gbs / peaks["hbm_gbs"], 4)},
+        "latency": {"step_ms_p50": decode_detail.get("step_ms_p50"), "step_ms_p99": decode_detail.get("step_ms_p99"),
+                    "host_ms_per_step": decode_detail.get("host_ms_per_step"), "pages_high_water": pages_in_use,
+                    "pages_total": pool_pages, "preemptions": 0},
         "points": points,
         "clocks": clocks.summary(mark_a, mark_b),
     }

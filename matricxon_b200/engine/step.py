@@ -149,7 +149,8 @@ class StepRunner:
         self._shape_graphs: dict[tuple, tuple] = {}        # shape -> record, oldest use first
         self._shape_pool = None
         self._shape_seen: dict[tuple, int] = {}
-        self.host_seconds = 0.0           # time the host spent inside ``run`` so far
+        self.host_seconds = 0.0           # time the host spent inside ``run`` so far ...
+        self.wait_seconds = 0.0           # ... of which waiting for the device to be done with a metadata buffer
         self._status_host: torch.Tensor | None = None
         self.chained_launch_rows = int(os.environ.get("MATRICXON_CHAINED_ROWS", "2"))
         self._graph_host_arrays: dict[int, tuple] = {}       # bucket -> (pinned tensor, its numpy view)
@@ -324,7 +325,9 @@ class StepRunner:
             done = self._upload_done
         else:
             host, dev, done = buffers
+        waited = time.perf_counter()
         done.synchronize()                           # the pinned buffer may still be in flight
+        self.wait_seconds += time.perf_counter() - waited
         host[:total].copy_(torch.from_numpy(flat[:total]))
         dev[:total].copy_(host[:total], non_blocking=True)
         done.record()
@@ -525,7 +528,9 @@ class StepRunner:
         flat = arrays[1]
         records = [cache.requests[entry.request_id] for entry in entries]
         lens = [record.length for record in records]
+        waited = time.perf_counter()
         done.synchronize()                           # the pinned buffer may still be in flight
+        self.wait_seconds += time.perf_counter() - waited
         try:
             def part(i: int) -> np.ndarray:
                 return flat[offsets[i]:offsets[i] + lengths[i]]
