@@ -36,7 +36,7 @@ class ChatEngine:
 
     def __init__(self, model, eos_token_ids: Iterable[int] = (), dtype: str = "bfloat16",
                  device: str = "cuda:0", max_cache_tokens: int | None = None, max_active: int = 8,
-                 max_batched_tokens: int = 2048, prefill_chunk: int = 256,
+                 max_batched_tokens: int = 2048, prefill_chunk: int = 512,
                  max_model_len: int | None = None, page_size: int = 16,
                  gemm_backend: str = "auto", use_graphs: bool = True,
                  look_ahead: bool | None = None) -> None:

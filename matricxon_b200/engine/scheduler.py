@@ -49,7 +49,11 @@ class SchedulerStalled(RuntimeError):
 class SchedulerConfig:
     max_num_seqs: int = 8                  # the reference's max_active default (app/config.py:87)
     max_num_batched_tokens: int = 2048
-    prefill_chunk: int = 256               # the reference's PLAIN_PREFILL_CHUNK
+    # The reference cuts prompts into pieces of 256 tokens (PLAIN_PREFILL_CHUNK, app/runtime/chat_engine.py:36).
+    # Here every step is a pass over all weights, so short pieces are dear: measured at StarCoder2-3B
+    # sizes a step costs 16 us a token at 256 tokens, 10 at 512 and 6 at 1,024-2,048, while the requests
+    # decoding beside a 512-token piece wait about 5 ms for their next token instead of 2.
+    prefill_chunk: int = 512
     max_model_len: int = 4096
 
 

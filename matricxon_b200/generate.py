@@ -41,7 +41,7 @@ def build_parser() -> argparse.ArgumentParser:
     parser.add_argument("--device", default="cuda:0")
     parser.add_argument("--page-size", type=int, default=16)
     parser.add_argument("--max-batched-tokens", type=int, default=2048)
-    parser.add_argument("--prefill-chunk", type=int, default=256)
+    parser.add_argument("--prefill-chunk", type=int, default=512)
     return parser
 
 

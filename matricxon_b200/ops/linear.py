@@ -11,7 +11,7 @@ Backends, chosen by the runtime:
   "library" -- cuBLAS through ``torch.mm`` for bfloat16 (the reference runs its products
                through nn.Linear, i.e. the library: app/architectures/qwen_layers.py:50-53),
                followed by the engine's fused bias / GELU / residual epilogue kernel.
-  "auto"    -- "simt" for float32; for bfloat16 "skinny" up to 16 rows, "tcgen05" above 128 rows,
+  "auto"    -- "simt" for float32; for bfloat16 "skinny" up to 16 rows, "tcgen05" above 256 rows,
                "library" between (a weight stream that 128-row tiles would leave to a few SMs) and
                for shapes neither takes (a K that is no multiple of 8), and "stream" from 9 rows
                on where every SM owns many weight rows (``_pick`` gives the measured thresholds).
@@ -72,7 +72,11 @@ def _pick(x: torch.Tensor, weight: torch.Tensor, m: int, n: int) -> str:
             return "stream"
     if kernels.skinny_gemm_supported(x, weight):
         return "skinny"
-    if m > 128 and kernels.tcgen05_gemm_supported(x, weight):
+    # up to 256 rows a product has one row of 256-row tiles and too few of them for 148 SMs (each is
+    # bound by what one SM takes in through TMA): the library is faster there (73 against 86 us for
+    # the four products of a layer at 256 rows; 104 against 114 at 512, where the long-K product
+    # already favours the engine's kernel)
+    if m > 256 and kernels.tcgen05_gemm_supported(x, weight):
         return "tcgen05"
     return "library"
 
