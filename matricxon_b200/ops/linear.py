@@ -76,7 +76,10 @@ def _pick(x: torch.Tensor, weight: torch.Tensor, m: int, n: int) -> str:
     # bound by what one SM takes in through TMA): the library is faster there (73 against 86 us for
     # the four products of a layer at 256 rows; 104 against 114 at 512, where the long-K product
     # already favours the engine's kernel)
-    if m > 256 and kernels.tcgen05_gemm_supported(x, weight):
+    # ... and up to 1,023 rows for products that are short in both N and K (the QKV and output
+    # projections: 14 against 23 and 14 against 18 us at 512 rows), which have too few tiles to fill
+    # the GPU and too little K to share out
+    if m > 256 and kernels.tcgen05_gemm_supported(x, weight) and (m >= 1024 or n >= 8192 or x.shape[1] >= 8192):
         return "tcgen05"
     return "library"
 
