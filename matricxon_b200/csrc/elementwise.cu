@@ -41,7 +41,7 @@ void mx_set_error(const char* fmt, ...) {
 // ---------------------------------------------------------------- embedding
 template <typename T>
 __global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ table,
-                             float* __restrict__ out, int hidden, int vocab, int* status) {
+                             float* __restrict__ out, int hidden, int vocab, float scale, int* status) {
     pdl_trigger();
     const int row = blockIdx.x;
     const int id = ids[row];                 // step metadata: uploaded before the step, by no kernel
@@ -53,19 +53,67 @@ __global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ 
         return;
     }
     const T* src = table + (size_t)id * hidden;
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = to_float(src[i]);
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = to_float(src[i]) * scale;
 }
 
+// bfloat16 tables whose rows are a multiple of 8 wide: 16 bytes in, two float4 out per access.
+__global__ void embed_vec_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ table,
+                                 float* __restrict__ out, int hidden, int vocab, float scale, int* status) {
+    pdl_trigger();
+    const int row = blockIdx.x;
+    const int id = ids[row];
+    float4* o = reinterpret_cast<float4*>(out + (size_t)row * hidden);
+    pdl_wait();
+    const int n_vec = hidden >> 3;
+    if (id < 0 || id >= vocab) {
+        if (threadIdx.x == 0) atomicOr(status, MX_STATUS_BAD_TOKEN_ID);
+        for (int i = threadIdx.x; i < 2 * n_vec; i += blockDim.x) o[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        return;
+    }
+    const uint4* src = reinterpret_cast<const uint4*>(table + (size_t)id * hidden);
+    for (int i = threadIdx.x; i < n_vec; i += blockDim.x) {
+        const uint4 v = __ldg(src + i);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+        const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
+        const float2 c = __bfloat1622float2(h[2]), d = __bfloat1622float2(h[3]);
+        o[2 * i] = make_float4(a.x * scale, a.y * scale, b.x * scale, b.y * scale);
+        o[2 * i + 1] = make_float4(c.x * scale, c.y * scale, d.x * scale, d.y * scale);
+    }
+}
+
+// `scale` multiplies every looked-up value (1 for the architectures that take the table as it is).
 extern "C" int mx_embed(const int* ids, const void* table, int dtype, float* out, int n_tokens,
-                        int hidden, int vocab, int* status, cudaStream_t stream) {
+                        int hidden, int vocab, float scale, int* status, cudaStream_t stream) {
     if (n_tokens <= 0) return MX_OK;
     const int threads = hidden >= 1024 ? 256 : 128;
     if (dtype == MX_DTYPE_F32)
         mx_launch_chained(embed_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, ids,
-                          (const float*)table, out, hidden, vocab, status);
+                          (const float*)table, out, hidden, vocab, scale, status);
+    else if (hidden % 8 == 0 && (reinterpret_cast<uintptr_t>(table) & 15) == 0 &&
+             (reinterpret_cast<uintptr_t>(out) & 15) == 0)
+        mx_launch_chained(embed_vec_kernel, dim3(n_tokens), dim3(hidden >= 2048 ? 128 : 64), 0, stream, ids,
+                          (const __nv_bfloat16*)table, out, hidden, vocab, scale, status);
     else
         mx_launch_chained(embed_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, stream, ids,
-                          (const __nv_bfloat16*)table, out, hidden, vocab, status);
+                          (const __nv_bfloat16*)table, out, hidden, vocab, scale, status);
+    return mx_launch_status();
+}
+
+// logits <- cap * tanh(logits / cap), in place (float32): the soft cap some architectures put on
+// their output scores.
+__global__ void softcap_kernel(float* __restrict__ values, long long count, float cap) {
+    pdl_trigger();
+    pdl_wait();
+    const float inv = 1.f / cap;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (long long)gridDim.x * blockDim.x)
+        values[i] = cap * tanhf(values[i] * inv);
+}
+
+extern "C" int mx_softcap(float* values, long long count, float cap, cudaStream_t stream) {
+    if (count <= 0) return MX_OK;
+    if (!(cap > 0.f)) MX_REFUSE("softcap: the cap must be positive, not %f", (double)cap);
+    const int blocks = (int)((count + 255) / 256 < 2048 ? (count + 255) / 256 : 2048);
+    mx_launch_chained(softcap_kernel, dim3(blocks), dim3(256), 0, stream, values, count, cap);
     return mx_launch_status();
 }
 

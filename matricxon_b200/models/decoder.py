@@ -69,6 +69,8 @@ def model_weight_specs(spec: ModelSpec) -> list[WeightSpec]:
     if not spec.tie_word_embeddings:
         specs.append(WeightSpec(f"{spec.head_name}.weight", (spec.vocab_size, spec.hidden_size),
                                 role="matrix", init="weight"))
+    if spec.head_bias:
+        specs.append(WeightSpec(f"{spec.head_name}.bias", (spec.vocab_size,), role="vector", init="bias"))
     return specs
 
 
@@ -124,6 +126,7 @@ class DecoderModel:
         self.cache_plan = plan_cache(spec)
         self.embedding: torch.Tensor | None = None
         self.head: torch.Tensor | None = None
+        self.head_bias: torch.Tensor | None = None
         self.bindings: list[CacheBinding] = [CacheBinding() for _ in spec.schedule]
 
     def weight_specs(self) -> list[WeightSpec]:
@@ -136,6 +139,7 @@ class DecoderModel:
         self.final_norm.load(fetch)
         self.head = (self.embedding if self.spec.tie_word_embeddings
                      else fetch(f"{self.spec.head_name}.weight"))
+        self.head_bias = fetch(f"{self.spec.head_name}.bias") if self.spec.head_bias else None
 
     def bind_cache(self, group_storage: list[torch.Tensor], state_storage: list[torch.Tensor | None]) -> None:
         """``group_storage[g]`` is [entries, pages, planes, kv heads, page_size, head_dim];
@@ -153,7 +157,7 @@ class DecoderModel:
     def forward(self, ctx) -> torch.Tensor:
         """Runs the step's tokens through the schedule; returns the float32 residual stream."""
         x = ctx.hidden(self.spec.hidden_size)
-        kernels.embed(ctx.token_ids, self.embedding, x, ctx.status)
+        kernels.embed(ctx.token_ids, self.embedding, x, ctx.status, self.spec.embedding_scale)
         for position, entry in enumerate(self.spec.schedule):
             x = self.layers[entry.layer].forward(x, ctx, self.bindings[position])
         return x
@@ -161,4 +165,7 @@ class DecoderModel:
     def logits(self, x: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
         """Float32 logits [len(rows), vocab] of the residual-stream rows ``rows``."""
         normed = self.final_norm.forward(x, rows=rows)
-        return linear(normed, self.head, None, EPILOGUE_F32, backend=self.runtime.gemm_backend)
+        logits = linear(normed, self.head, self.head_bias, EPILOGUE_F32, backend=self.runtime.gemm_backend)
+        if self.spec.logit_softcap is not None:
+            kernels.softcap(logits, self.spec.logit_softcap)
+        return logits

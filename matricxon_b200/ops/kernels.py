@@ -73,7 +73,8 @@ def describe_status(word: int) -> str:
     return "; ".join(text for bit, text in STATUS_BITS.items() if word & bit) or "no error"
 
 
-def embed(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, status: torch.Tensor) -> None:
+def embed(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, status: torch.Tensor,
+          scale: float = 1.0) -> None:
     _need(ids, "ids", torch.int32)
     _need(table, "table")
     _need(out, "out", torch.float32)
@@ -81,7 +82,14 @@ def embed(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, status: tor
     n, hidden = out.shape
     assert ids.numel() == n and table.shape[1] == hidden
     check(library().mx_embed(_ptr(ids), _ptr(table), dtype_code(table.dtype), _ptr(out), n, hidden,
-                             table.shape[0], _ptr(status), _stream()), "embed")
+                             table.shape[0], float(scale), _ptr(status), _stream()), "embed")
+    _launched()
+
+
+def softcap(logits: torch.Tensor, cap: float) -> None:
+    """logits <- cap * tanh(logits / cap) in place (float32)."""
+    _need(logits, "logits", torch.float32)
+    check(library().mx_softcap(_ptr(logits), logits.numel(), float(cap), _stream()), "softcap")
     _launched()
 
 

@@ -27,7 +27,8 @@ P, I, L, F = c_void_p, c_int, c_longlong, c_float
 _SIGNATURES: dict[str, tuple[list, object]] = {
     "mx_last_error_message": ([], ctypes.c_char_p),
     "mx_set_chained_launch": ([I], None),
-    "mx_embed": ([P, P, I, P, I, I, I, P, P], I),
+    "mx_embed": ([P, P, I, P, I, I, I, F, P, P], I),
+    "mx_softcap": ([P, L, F, P], I),
     "mx_layernorm": ([P, P, P, P, P, I, I, I, F, P], I),
     "mx_rope_kv_write": ([P, I, I, P, P, P, P, I, I, I, I, I, I, L, I, P, P], I),
     "mx_epilogue": ([P, I, P, P, P, I, L, I, I, P], I),

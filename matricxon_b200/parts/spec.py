@@ -133,6 +133,12 @@ class ModelSpec:
     layer_prefix: str
     final_norm_name: str
     head_name: str
+    # what some architectures do around the layers (StarCoder2 does none of it): the looked-up
+    # embeddings times a constant, a bias on the output head ("<head_name>.bias"), and scores
+    # squashed to cap * tanh(score / cap)
+    embedding_scale: float = 1.0
+    head_bias: bool = False
+    logit_softcap: float | None = None
     extra: dict = field(default_factory=dict, compare=False, hash=False)
 
     def __post_init__(self) -> None:

@@ -33,19 +33,30 @@ def tol(dtype):
 
 
 # ------------------------------------------------------------------ embedding
+@pytest.mark.parametrize("hidden", [96, 100, 3072])          # 16-byte rows (the vector kernel) and not
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_embed(dtype):
+def test_embed(dtype, hidden):
     k = kernels()
-    table = torch.randn(1000, 96, device=DEV).to(dtype)
+    table = torch.randn(1000, hidden, device=DEV).to(dtype)
     ids = torch.tensor([0, 999, 17, 17, 500], dtype=torch.int32, device=DEV)
-    out = torch.empty(5, 96, device=DEV)
+    out = torch.empty(5, hidden, device=DEV)
     st = status()
     k.embed(ids, table, out, st)
     assert torch.equal(out, table[ids.long()].float()) and st.item() == 0
+    k.embed(ids, table, out, st, scale=3.0)
+    assert torch.equal(out, table[ids.long()].float() * 3.0) and st.item() == 0
     bad = torch.tensor([3, 1000, -1], dtype=torch.int32, device=DEV)
-    out = torch.empty(3, 96, device=DEV)
+    out = torch.full((3, hidden), float("nan"), device=DEV)
     k.embed(bad, table, out, st)
     assert st.item() == 1 and torch.all(out[1:] == 0) and torch.equal(out[0], table[3].float())
+
+
+def test_softcap():
+    k = kernels()
+    logits = torch.randn(7, 1003, device=DEV) * 40
+    expected = 30.0 * torch.tanh(logits.double() / 30.0)
+    k.softcap(logits, 30.0)
+    assert torch.allclose(logits.double(), expected, atol=1e-4)
 
 
 # ------------------------------------------------------------------ LayerNorm

@@ -613,3 +613,43 @@ def test_toy_mixer_with_a_one_plane_windowed_cache():
     # the toy group's window of 9 keeps at most two pages of 16; the attention group's window of 32 three
     assert len(core.cache.held_pages("r", 1)) <= 2 and len(core.cache.held_pages("r", 0)) <= 3
     assert core.cache.pages_reused > 0
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embedding_scale_head_bias_and_logit_cap_are_spec_fields(dtype):
+    """What some architectures do around the layers is data of the model's description too: the
+    embeddings times a constant, a bias on the head, scores squashed to cap * tanh(score / cap).
+    A stock tiny model with the three switched on, against the plain parts."""
+    from matricxon_b200.engine.core import EngineCore
+    from matricxon_b200.engine.step import StepEntry
+    from matricxon_b200.models.decoder import DecoderModel, model_weight_specs
+    from matricxon_b200.weights.loader import DictSource, make_fetcher
+    from plain_reference import plain_embedding, plain_layer
+
+    scale, cap = 1.75, 0.6
+    base = tiny_config("A").model_spec()
+    spec = dataclasses.replace(base, embedding_scale=scale, head_bias=True, logit_softcap=cap)
+    names = {s.name for s in model_weight_specs(spec)}
+    assert "lm_head.bias" in names
+    tensors = dict(tiny_tensors("A", dtype))
+    torch.manual_seed(3)
+    tensors["lm_head.bias"] = torch.randn(TINY["A"][0]["vocab_size"]) * 0.3
+    model = DecoderModel(spec, make_runtime(dtype))
+    model.load(make_fetcher(model_weight_specs(spec), DictSource(tensors), dtype, DEV))
+    core = EngineCore(model, max_cache_tokens=128, max_requests=2)
+    ids = random_ids(40, TINY["A"][0]["vocab_size"], seed=8)
+    core.cache.add_request("r")
+    got = torch.cat([core.runner.run([StepEntry("r", ids[:25], list(range(25)))]).clone(),
+                     core.runner.run([StepEntry("r", ids[25:], list(range(15)))]).clone()]).double().cpu()
+    core.runner.check_status()
+
+    cfg = plain_config(TINY["A"][0])
+    w = {k: v.double() for k, v in tensors.items()}
+    x = plain_embedding(torch.tensor(ids), w["model.embed_tokens.weight"]) * scale
+    for layer in range(cfg["layers"]):
+        x = plain_layer(x, w, layer, cfg, torch.arange(len(ids)))
+    x = plain_layernorm(x, w["model.norm.weight"], w["model.norm.bias"], cfg["eps"])
+    scores = x @ w["model.embed_tokens.weight"].T + w["lm_head.bias"]
+    expected = cap * torch.tanh(scores / cap)
+    assert float(expected.abs().max()) > 0.5 * cap          # the cap bites
+    assert torch.allclose(got, expected, **(dict(atol=2e-5, rtol=1e-5) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)))
