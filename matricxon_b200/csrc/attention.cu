@@ -292,24 +292,49 @@ template <typename T>
 __global__ void attention_merge_kernel(const float* __restrict__ part_o,
                                        const float* __restrict__ part_ml, T* __restrict__ out,
                                        int out_stride, int n_heads, int head_dim, int n_splits) {
+    // One trip to memory: the maxima and sums of the splits (one per thread, into shared memory) and this
+    // thread's value of the first MERGE_AHEAD splits set out together; only then is anything combined.
+    // Splits beyond what the shared arrays hold are read where they lie.
+    constexpr int MERGE_AHEAD = 16, MERGE_KEPT = 128;
+    __shared__ float split_max[MERGE_KEPT], split_sum[MERGE_KEPT];
     pdl_trigger();
     pdl_wait();
     const int t = blockIdx.x, h = blockIdx.y;
     const size_t base = ((size_t)t * n_heads + h) * n_splits;
-    float m = -INFINITY;
-    for (int s = 0; s < n_splits; ++s) m = fmaxf(m, part_ml[(base + s) * 2]);
-    float total = 0.f;
-    for (int s = 0; s < n_splits; ++s) {
-        const float ms = part_ml[(base + s) * 2];
-        if (ms != -INFINITY) total += part_ml[(base + s) * 2 + 1] * expf(ms - m);
+    for (int s = threadIdx.x; s < min(n_splits, MERGE_KEPT); s += blockDim.x) {
+        split_max[s] = part_ml[(base + s) * 2];
+        split_sum[s] = part_ml[(base + s) * 2 + 1];
     }
-    for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
-        float o = 0.f;
-        for (int s = 0; s < n_splits; ++s) {
-            const float ms = part_ml[(base + s) * 2];
-            if (ms != -INFINITY) o += part_o[(base + s) * head_dim + d] * expf(ms - m);
+    auto max_of = [&](int s) { return s < MERGE_KEPT ? split_max[s] : part_ml[(base + s) * 2]; };
+    auto sum_of = [&](int s) { return s < MERGE_KEPT ? split_sum[s] : part_ml[(base + s) * 2 + 1]; };
+    for (int d0 = 0; d0 < head_dim; d0 += blockDim.x) {
+        const int d = d0 + threadIdx.x;
+        const bool mine = d < head_dim;
+        float ahead[MERGE_AHEAD];
+#pragma unroll
+        for (int s = 0; s < MERGE_AHEAD; ++s)
+            ahead[s] = (s < n_splits && mine) ? part_o[(base + s) * head_dim + d] : 0.f;
+        __syncthreads();
+        float m = -INFINITY;
+        for (int s = 0; s < n_splits; ++s) m = fmaxf(m, max_of(s));
+        float total = 0.f, o = 0.f;
+#pragma unroll
+        for (int s = 0; s < MERGE_AHEAD; ++s) {
+            if (s >= n_splits) break;
+            const float ms = max_of(s);
+            if (ms == -INFINITY) continue;
+            const float w = expf(ms - m);
+            total += sum_of(s) * w;
+            o += ahead[s] * w;
         }
-        out[(size_t)t * out_stride + (size_t)h * head_dim + d] = from_float<T>(o / total);
+        for (int s = MERGE_AHEAD; s < n_splits; ++s) {
+            const float ms = max_of(s);
+            if (ms == -INFINITY) continue;
+            const float w = expf(ms - m);
+            total += sum_of(s) * w;
+            if (mine) o += part_o[(base + s) * head_dim + d] * w;
+        }
+        if (mine) out[(size_t)t * out_stride + (size_t)h * head_dim + d] = from_float<T>(o / total);
     }
 }
 
