@@ -45,7 +45,7 @@ constexpr int NARROW_THREADS = NARROW_WARPS * 32;
 constexpr int CHUNK = 32;
 constexpr int WIDE_STAGES = 4;      // chunks in flight per block (two pairs), wide tiles
 constexpr int NARROW_STAGES = 1;    // chunks in flight per warp, narrow tiles
-constexpr int NARROW_TABLE = 256;   // block-table entries a warp of a narrow tile reads ahead
+constexpr int NARROW_TABLE = 1024;  // block-table entries a narrow tile's block reads ahead (16,384 positions in pages of 16)
 constexpr int SPIN_LIMIT = 1 << 22;
 
 struct MmaAttnParams {
@@ -188,13 +188,20 @@ attention_mma_kernel(const MmaAttnParams p) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     __nv_bfloat16* stages = reinterpret_cast<__nv_bfloat16*>(smem_raw);
     __shared__ __align__(8) unsigned long long bars[N_STAGES];
-    __shared__ int narrow_table[NARROW ? NARROW_WARPS : 1][NARROW ? NARROW_TABLE : 1];
+    __shared__ int narrow_table[NARROW ? NARROW_TABLE : 1];   // the sequence's first block-table entries
 
     pdl_trigger();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
     const int tile = blockIdx.x, kh = blockIdx.y, split = blockIdx.z;
-    const int seq = p.tiles[2 * tile], tile_row0 = p.tiles[2 * tile + 1];
+    // no tile list: tile i is the whole of sequence i (a batch of decoding requests), one look-up less
+    const int seq = p.tiles ? p.tiles[2 * tile] : tile, tile_row0 = p.tiles ? p.tiles[2 * tile + 1] : 0;
+    if (NARROW) {
+        // the block-table row sets out together with the sequence's lengths (it does not depend on
+        // them): one trip to memory instead of two before the first page can be asked for
+        const int* row = p.block_tables + (size_t)seq * p.bt_stride;
+        for (int e = threadIdx.x; e < min(p.bt_stride, NARROW_TABLE); e += blockDim.x) narrow_table[e] = row[e];
+    }
     const int group = p.n_heads / p.n_kv_heads;
     const int q_start = p.cu_q[seq];
     const int q_len = p.cu_q[seq + 1] - q_start;
@@ -413,17 +420,13 @@ attention_mma_kernel(const MmaAttnParams p) {
         unsigned long long* my_bars = bars + warp * NARROW_STAGES;
         const int my_first = c_begin + warp;
         const int my_count = my_first < c_end ? (c_end - my_first + NARROW_WARPS - 1) / NARROW_WARPS : 0;
-        // The block-table entries of this warp's chunks, read once and together: a lookup in front of
-        // every chunk's copies would put a round trip to L2 into each turn of the loop.
+        // This warp's chunks find their pages in the row read ahead at the top (entries beyond what was
+        // kept are looked up in global memory).
         const int pages = CHUNK >> p.page_shift;
-        int* my_table = narrow_table[warp];
-        const int n_cached = min(my_count * pages, NARROW_TABLE);
-        for (int e = lane; e < n_cached; e += 32) {
-            const int lp = (my_first + NARROW_WARPS * (e / pages)) * pages + e % pages;
-            my_table[e] = lp < p.bt_stride ? bt[lp] : -1;
-        }
-        __syncwarp();
-        auto cached_for = [&](int i) -> const int* { return (i + 1) * pages <= n_cached ? my_table + i * pages : nullptr; };
+        auto cached_for = [&](int i) -> const int* {
+            const int first = (my_first + NARROW_WARPS * i) * pages;
+            return first + pages <= min(p.bt_stride, NARROW_TABLE) ? narrow_table + first : nullptr;
+        };
         if (my_count > 0)
             issue_chunk<HD>(p, my_stages, my_stages + CHUNK * HD, &my_bars[0], my_first * CHUNK, lo_tile,
                             hi_tile, bt, kbase, vbase, page_stride, lane, 32, cached_for(0));

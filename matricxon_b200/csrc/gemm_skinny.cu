@@ -110,9 +110,11 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bflo
     const int n_blocks = SPLIT ? kb_first + K / 64 : K / 32;
     // The weights are nobody's output: start pulling this thread's first pieces towards L2 while
     // the kernel before this one is still finishing, then wait for it before touching activations.
-    pdl_trigger();
+#ifndef SK_PREFETCH_ITERS
+#define SK_PREFETCH_ITERS 4     // one to eight measured alike, none and twelve or more slower
+#endif
 #pragma unroll
-    for (int u = 0; u < 2 * UNROLL; ++u) {
+    for (int u = 0; u < SK_PREFETCH_ITERS; ++u) {
         const int kb = kb_first + warp + u * SK_WARPS;
         if (kb < n_blocks) {
 #pragma unroll
@@ -144,6 +146,11 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bflo
                 mma_bf16_16816(acc[mb], wf[u][0].z, wf[u][1].z, wf[u][0].w, wf[u][1].w, xf[u][mb].z, xf[u][mb].w);
             }
     }
+    // All of this block's weights are on their way: the next kernel may start its own preamble (its
+    // weights' first pieces towards L2) under this kernel's reduction and epilogue. Triggering at the top
+    // instead lets the whole chain of kernels pile up behind the one that runs, each asking for its
+    // weights at once (a decode step of 8 rows: 2.175 ms against 2.127 ms this way, 2.155 ms unchained).
+    pdl_trigger();
     // this thread holds features g (and g + 8) for tokens 8 mb + 2t, + 1
 #pragma unroll
     for (int mb = 0; mb < MB; ++mb) {
@@ -285,13 +292,15 @@ extern "C" int mx_gemm_skinny(const void* x, const void* W, const float* bias, c
         config.gridDim = dim3(2 * grid);
         config.blockDim = dim3(SK_THREADS);
         config.stream = stream;
-        cudaLaunchAttribute attribute[1];
+        cudaLaunchAttribute attribute[2];
         attribute[0].id = cudaLaunchAttributeClusterDimension;
         attribute[0].val.clusterDim.x = 2;
         attribute[0].val.clusterDim.y = 1;
         attribute[0].val.clusterDim.z = 1;
+        attribute[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attribute[1].val.programmaticStreamSerializationAllowed = mx_chained_launch_enabled() ? 1 : 0;
         config.attrs = attribute;
-        config.numAttrs = 1;
+        config.numAttrs = 2;
         const cudaError_t e = cudaLaunchKernelEx(&config, kernel, (const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)W,
                                                  ldw, bias, residual, out, ldo, M, N, K, mode, none);
         if (e != cudaSuccess) {

@@ -152,7 +152,7 @@ class StepRunner:
         self.host_seconds = 0.0           # time the host spent inside ``run`` so far ...
         self.wait_seconds = 0.0           # ... of which waiting for the device to be done with a metadata buffer
         self._status_host: torch.Tensor | None = None
-        self.chained_launch_rows = int(os.environ.get("MATRICXON_CHAINED_ROWS", "2"))
+        self.chained_launch_rows = int(os.environ.get("MATRICXON_CHAINED_ROWS", "1024"))
         self._graph_host_arrays: dict[int, tuple] = {}       # bucket -> (pinned tensor, its numpy view)
         self._arange = np.arange(max_graph_batch + 2, dtype=np.int32)
         self._graph_pool = None

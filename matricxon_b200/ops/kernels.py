@@ -448,13 +448,18 @@ def paged_attention_mma(q: torch.Tensor, q_stride: int, cache: torch.Tensor,
     _need(q, "q", torch.bfloat16, contiguous=False)
     _need(cache, "cache", torch.bfloat16)
     for name, tensor in (("block_tables", block_tables), ("cu_q", cu_q),
-                         ("context_lens", context_lens), ("tiles", tiles), ("status", status)):
+                         ("context_lens", context_lens), ("status", status)):
         _need(tensor, name, torch.int32)
     _need(out, "out", torch.bfloat16)
     page_size = cache.shape[3]
     assert tuple(cache.shape[1:]) == (2, n_kv_heads, page_size, head_dim), cache.shape
     assert out.shape[1] == n_heads * head_dim and out.shape[0] >= n_tokens
-    assert tiles.numel() >= 2 * n_tiles
+    if tiles is None:
+        # no list: tile i is the whole of sequence i (narrow tiles only: every sequence brings at most 16 rows)
+        assert narrow and n_tiles <= context_lens.numel()
+    else:
+        _need(tiles, "tiles", torch.int32)
+        assert tiles.numel() >= 2 * n_tiles
     if n_splits > 1:
         need = attention_scratch_bytes(n_tokens, n_heads, head_dim, n_splits)
         if scratch is None or scratch.numel() * scratch.element_size() < need:
@@ -462,7 +467,7 @@ def paged_attention_mma(q: torch.Tensor, q_stride: int, cache: torch.Tensor,
         _need(scratch, "scratch", torch.float32)
     check(library().mx_paged_attention_mma(
         _ptr(q), q_stride, _ptr(cache), cache.shape[0], page_size, _ptr(block_tables),
-        block_tables.stride(0), _ptr(cu_q), _ptr(context_lens), _ptr(tiles), n_tiles,
+        block_tables.stride(0), _ptr(cu_q), _ptr(context_lens), _ptr(tiles) if tiles is not None else None, n_tiles,
         1 if narrow else 0, n_tokens, n_heads, n_kv_heads, head_dim, int(window or 0), float(scale),
         _ptr(out), out.stride(0), n_splits, _ptr(scratch), _ptr(status), _stream()),
         "paged_attention_mma")

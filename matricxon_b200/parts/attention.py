@@ -183,6 +183,8 @@ class PagedAttention(Mixer):
                                                n_splits=n_splits, scratch=scratch)
                     continue
                 alone = (n_wide == 0) if is_narrow else (n_narrow == 0)
+                if is_narrow and ctx.padded:
+                    tiles, n_tiles = None, ctx.n_seqs      # a batch of decoding requests: tile i is sequence i
                 n_splits, scratch = mma_tile_splits(ctx, n_tiles, is_narrow, alone, spec.num_heads,
                                                     spec.num_kv_heads, spec.head_dim, spec.window)
                 kernels.paged_attention_mma(qkv, qkv.stride(0), binding.kv, group.block_tables,
