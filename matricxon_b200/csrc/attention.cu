@@ -294,9 +294,11 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_o,
                                        int out_stride, int n_heads, int head_dim, int n_splits) {
     // One trip to memory: the maxima and sums of the splits (one per thread, into shared memory) and this
     // thread's value of the first MERGE_AHEAD splits set out together; only then is anything combined.
+    // Each split's weight exp(max_s - max) is computed once, by the thread that fetched its maximum.
     // Splits beyond what the shared arrays hold are read where they lie.
     constexpr int MERGE_AHEAD = 16, MERGE_KEPT = 128;
-    __shared__ float split_max[MERGE_KEPT], split_sum[MERGE_KEPT];
+    __shared__ float split_max[MERGE_KEPT], split_sum[MERGE_KEPT], split_weight[MERGE_KEPT];
+    __shared__ float total_max, total_sum;
     pdl_trigger();
     pdl_wait();
     const int t = blockIdx.x, h = blockIdx.y;
@@ -305,36 +307,55 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_o,
         split_max[s] = part_ml[(base + s) * 2];
         split_sum[s] = part_ml[(base + s) * 2 + 1];
     }
-    auto max_of = [&](int s) { return s < MERGE_KEPT ? split_max[s] : part_ml[(base + s) * 2]; };
-    auto sum_of = [&](int s) { return s < MERGE_KEPT ? split_sum[s] : part_ml[(base + s) * 2 + 1]; };
+    const bool mine0 = (int)threadIdx.x < head_dim;
+    float ahead[MERGE_AHEAD];
+#pragma unroll
+    for (int s = 0; s < MERGE_AHEAD; ++s)
+        ahead[s] = (s < n_splits && mine0) ? part_o[(base + s) * head_dim + threadIdx.x] : 0.f;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        // one warp: the maximum over all splits, then every kept split's weight and the weighted sum
+        const int lane = threadIdx.x;
+        float m = -INFINITY;
+        for (int s = lane; s < n_splits; s += 32) m = fmaxf(m, s < MERGE_KEPT ? split_max[s] : part_ml[(base + s) * 2]);
+        m = warp_max(m);
+        float total = 0.f;
+        for (int s = lane; s < n_splits; s += 32) {
+            const float ms = s < MERGE_KEPT ? split_max[s] : part_ml[(base + s) * 2];
+            const float w = ms == -INFINITY ? 0.f : expf(ms - m);
+            if (s < MERGE_KEPT) split_weight[s] = w;
+            total += (s < MERGE_KEPT ? split_sum[s] : part_ml[(base + s) * 2 + 1]) * w;
+        }
+        total = warp_sum(total);
+        if (lane == 0) { total_max = m; total_sum = total; }
+    }
+    __syncthreads();
+    const float m = total_max, inv = 1.f / total_sum;
+    auto weight_of = [&](int s) {
+        if (s < MERGE_KEPT) return split_weight[s];
+        const float ms = part_ml[(base + s) * 2];
+        return ms == -INFINITY ? 0.f : expf(ms - m);
+    };
     for (int d0 = 0; d0 < head_dim; d0 += blockDim.x) {
         const int d = d0 + threadIdx.x;
         const bool mine = d < head_dim;
-        float ahead[MERGE_AHEAD];
+        float o = 0.f;
+        if (d0 == 0) {
 #pragma unroll
-        for (int s = 0; s < MERGE_AHEAD; ++s)
-            ahead[s] = (s < n_splits && mine) ? part_o[(base + s) * head_dim + d] : 0.f;
-        __syncthreads();
-        float m = -INFINITY;
-        for (int s = 0; s < n_splits; ++s) m = fmaxf(m, max_of(s));
-        float total = 0.f, o = 0.f;
-#pragma unroll
-        for (int s = 0; s < MERGE_AHEAD; ++s) {
-            if (s >= n_splits) break;
-            const float ms = max_of(s);
-            if (ms == -INFINITY) continue;
-            const float w = expf(ms - m);
-            total += sum_of(s) * w;
-            o += ahead[s] * w;
+            // a split without keys has weight 0 and values nobody wrote: it is skipped, not multiplied
+            for (int s = 0; s < MERGE_AHEAD; ++s)
+                if (s < n_splits && split_weight[s] != 0.f) o += ahead[s] * split_weight[s];
+            for (int s = MERGE_AHEAD; s < n_splits; ++s) {
+                const float w = weight_of(s);
+                if (mine && w != 0.f) o += part_o[(base + s) * head_dim + d] * w;
+            }
+        } else {
+            for (int s = 0; s < n_splits; ++s) {
+                const float w = weight_of(s);
+                if (mine && w != 0.f) o += part_o[(base + s) * head_dim + d] * w;
+            }
         }
-        for (int s = MERGE_AHEAD; s < n_splits; ++s) {
-            const float ms = max_of(s);
-            if (ms == -INFINITY) continue;
-            const float w = expf(ms - m);
-            total += sum_of(s) * w;
-            if (mine) o += part_o[(base + s) * head_dim + d] * w;
-        }
-        if (mine) out[(size_t)t * out_stride + (size_t)h * head_dim + d] = from_float<T>(o / total);
+        if (mine) out[(size_t)t * out_stride + (size_t)h * head_dim + d] = from_float<T>(o * inv);
     }
 }
 

@@ -40,12 +40,12 @@ namespace {
 
 constexpr int MMA_WARPS = 4;        // wide tiles: 16 rows each
 constexpr int MMA_THREADS = MMA_WARPS * 32;
-constexpr int NARROW_WARPS = 8;     // narrow tiles: all warps hold the same rows and share the chunks
+constexpr int NARROW_WARPS = 8;  // narrow tiles: all warps hold the same rows and share the chunks
 constexpr int NARROW_THREADS = NARROW_WARPS * 32;
 constexpr int CHUNK = 32;
 constexpr int WIDE_STAGES = 4;      // chunks in flight per block (two pairs), wide tiles
 constexpr int NARROW_STAGES = 1;    // chunks in flight per warp, narrow tiles
-constexpr int NARROW_TABLE = 1024;  // block-table entries a narrow tile's block reads ahead (16,384 positions in pages of 16)
+constexpr int NARROW_TABLE = 512;   // block-table entries a narrow tile's block reads ahead (16,384 positions in pages of 16)
 constexpr int SPIN_LIMIT = 1 << 22;
 
 struct MmaAttnParams {
@@ -67,8 +67,8 @@ struct MmaAttnParams {
 
 __device__ __forceinline__ void mma_bf16(float (&d)[4], unsigned a0, unsigned a1, unsigned a2,
                                          unsigned a3, unsigned b0, unsigned b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+    // not volatile: a pure function of its operands, which the compiler may schedule among the loads
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
         "{%0,%1,%2,%3};\n"
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
@@ -215,9 +215,6 @@ attention_mma_kernel(const MmaAttnParams p) {
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     __syncthreads();
-    // up to here only step metadata was read (uploaded before the step, written by no kernel);
-    // queries and the newest keys and values come from the kernels before this one
-    pdl_wait();
 
     // rows of this block and of this warp
     const int tile_last = min(tile_row0 + TILE_ROWS - 1, n_rows - 1);
@@ -257,17 +254,37 @@ attention_mma_kernel(const MmaAttnParams p) {
     const size_t page_stride = 2 * (size_t)p.n_kv_heads * head_stride;
     const __nv_bfloat16* kbase = p.cache + (size_t)kh * head_stride;
     const __nv_bfloat16* vbase = p.cache + (size_t)(p.n_kv_heads + kh) * head_stride;
-
-    // Q fragments: 16 bytes of each owned row per 32-wide block
+    // Narrow tiles: up to here only step metadata was read (uploaded before the step, written by no
+    // kernel), and the keys and values of positions before this step are in the cache since earlier
+    // steps. So this warp's first chunk, if it holds none of this step's positions, sets out now, under
+    // the tail of the kernel that computes the queries and the newest keys.
+    __nv_bfloat16* my_stages = stages + (size_t)(NARROW ? warp : 0) * NARROW_STAGES * STAGE_ELEMS;
+    unsigned long long* my_bars = bars + (NARROW ? warp : 0) * NARROW_STAGES;
+    const int my_first = c_begin + warp;
+    const int my_count = NARROW && my_first < c_end ? (c_end - my_first + NARROW_WARPS - 1) / NARROW_WARPS : 0;
+    // This warp's chunks find their pages in the row read ahead at the top (entries beyond what was
+    // kept are looked up in global memory).
+    auto cached_for = [&](int i) -> const int* {
+        const int pages = CHUNK >> p.page_shift;
+        const int first = (my_first + NARROW_WARPS * i) * pages;
+        return first + pages <= min(p.bt_stride, NARROW_TABLE) ? narrow_table + first : nullptr;
+    };
+    const bool first_is_old = (my_first + 1) * CHUNK <= ctx;
+    if (NARROW && my_count > 0 && first_is_old)
+        issue_chunk<HD>(p, my_stages, my_stages + CHUNK * HD, &my_bars[0], my_first * CHUNK, lo_tile,
+                        hi_tile, bt, kbase, vbase, page_stride, lane, 32, cached_for(0));
+    // queries and the newest keys and values come from the kernels before this one
+    pdl_wait();
+    // Q fragments: 16 bytes of each owned row per 32-wide block. A row beyond the tile reads the
+    // tile's last row (r_tok, r_head point there): its scores are masked and it is never written, and
+    // a load that is not conditional is not waited for here.
     uint4 qf[2][KB];
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
         const __nv_bfloat16* qrow = p.q + (size_t)(q_start + r_tok[i]) * p.q_stride +
                                     (size_t)(kh * group + r_head[i]) * HD;
 #pragma unroll
-        for (int b = 0; b < KB; ++b)
-            qf[i][b] = r_valid[i] ? *reinterpret_cast<const uint4*>(qrow + 32 * b + 8 * t)
-                                  : make_uint4(0, 0, 0, 0);
+        for (int b = 0; b < KB; ++b) qf[i][b] = *reinterpret_cast<const uint4*>(qrow + 32 * b + 8 * t);
     }
 
     float o[NB][4];
@@ -294,12 +311,16 @@ attention_mma_kernel(const MmaAttnParams p) {
 #pragma unroll
             for (int ch = 0; ch < NCH; ++ch) {
                 const __nv_bfloat16* kcol = ksv[ch] + (size_t)(8 * (g >> 1) + (g & 1)) * HD + 8 * t + 32 * kb;
+                // the two MMAs into one accumulator depend on one another: four accumulators between them
+                uint4 kf[4];
 #pragma unroll
-                for (int b = 0; b < 4; ++b) {
-                    const uint4 kf = *reinterpret_cast<const uint4*>(kcol + 2 * b * HD);
-                    mma_bf16(s[ch][b], qf[0][kb].x, qf[1][kb].x, qf[0][kb].y, qf[1][kb].y, kf.x, kf.y);
-                    mma_bf16(s[ch][b], qf[0][kb].z, qf[1][kb].z, qf[0][kb].w, qf[1][kb].w, kf.z, kf.w);
-                }
+                for (int b = 0; b < 4; ++b) kf[b] = *reinterpret_cast<const uint4*>(kcol + 2 * b * HD);
+#pragma unroll
+                for (int b = 0; b < 4; ++b)
+                    mma_bf16(s[ch][b], qf[0][kb].x, qf[1][kb].x, qf[0][kb].y, qf[1][kb].y, kf[b].x, kf[b].y);
+#pragma unroll
+                for (int b = 0; b < 4; ++b)
+                    mma_bf16(s[ch][b], qf[0][kb].z, qf[1][kb].z, qf[0][kb].w, qf[1][kb].w, kf[b].z, kf[b].w);
             }
         // mask (only where the chunks cross an edge), running max and sum for rows g, g + 8
         float m_new[2] = {m_run[0], m_run[1]};
@@ -382,12 +403,19 @@ attention_mma_kernel(const MmaAttnParams p) {
         }
         if (c0 + NCH * CHUNK - 1 <= hi_tile) {
 #pragma unroll
-            for (int nb = 0; nb < NB; ++nb)
+            for (int nb0 = 0; nb0 < NB; nb0 += 4)
 #pragma unroll
                 for (int ch = 0; ch < NCH; ++ch) {
-                    const uint4 vf = *reinterpret_cast<const uint4*>(vsv[ch] + voff + (size_t)(8 * nb) * p.page_size);
-                    mma_bf16(o[nb], pa[ch][0][0], pa[ch][0][1], pa[ch][0][2], pa[ch][0][3], vf.x, vf.y);
-                    mma_bf16(o[nb], pa[ch][1][0], pa[ch][1][1], pa[ch][1][2], pa[ch][1][3], vf.z, vf.w);
+                    uint4 vf[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        vf[j] = *reinterpret_cast<const uint4*>(vsv[ch] + voff + (size_t)(8 * (nb0 + j)) * p.page_size);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        mma_bf16(o[nb0 + j], pa[ch][0][0], pa[ch][0][1], pa[ch][0][2], pa[ch][0][3], vf[j].x, vf[j].y);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        mma_bf16(o[nb0 + j], pa[ch][1][0], pa[ch][1][1], pa[ch][1][2], pa[ch][1][3], vf[j].z, vf[j].w);
                 }
         } else {
             // slots beyond the newest key hold no data yet: keep them out of the product
@@ -416,18 +444,7 @@ attention_mma_kernel(const MmaAttnParams p) {
         // ---- each warp streams chunks c_begin + warp, + 8, ... through a stage of its own: with eight
         // warps a block has eight chunks in flight, and a warp fetches its next chunk when it is done with
         // the one before (more warps hide the copies' latency better than deeper per-warp pipelines did)
-        __nv_bfloat16* my_stages = stages + (size_t)warp * NARROW_STAGES * STAGE_ELEMS;
-        unsigned long long* my_bars = bars + warp * NARROW_STAGES;
-        const int my_first = c_begin + warp;
-        const int my_count = my_first < c_end ? (c_end - my_first + NARROW_WARPS - 1) / NARROW_WARPS : 0;
-        // This warp's chunks find their pages in the row read ahead at the top (entries beyond what was
-        // kept are looked up in global memory).
-        const int pages = CHUNK >> p.page_shift;
-        auto cached_for = [&](int i) -> const int* {
-            const int first = (my_first + NARROW_WARPS * i) * pages;
-            return first + pages <= min(p.bt_stride, NARROW_TABLE) ? narrow_table + first : nullptr;
-        };
-        if (my_count > 0)
+        if (my_count > 0 && !first_is_old)
             issue_chunk<HD>(p, my_stages, my_stages + CHUNK * HD, &my_bars[0], my_first * CHUNK, lo_tile,
                             hi_tile, bt, kbase, vbase, page_stride, lane, 32, cached_for(0));
         for (int i = 0; i < my_count; ++i) {
@@ -450,51 +467,71 @@ attention_mma_kernel(const MmaAttnParams p) {
         }
         // ---- combine the warps' partial results through shared memory (stages are free)
         __syncthreads();
-        float* red_o = reinterpret_cast<float*>(smem_raw);              // [warp][16][HD]
-        float* red_ml = red_o + NARROW_WARPS * 16 * HD;                    // [warp][16][2]
+        constexpr int RS = HD + 8;                                      // row stride: the warps' stores hit every bank once
+        float* red_o = reinterpret_cast<float*>(smem_raw);              // [warp][16][RS]
+        float* red_ml = red_o + NARROW_WARPS * 16 * RS;                 // [warp][16][2]
+        __shared__ float weight_of[NARROW_WARPS][16], sum_of[16], max_of[16];
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
             const int r = g + 8 * i;
-            float* dst = red_o + ((size_t)warp * 16 + r) * HD;
+            float* dst = red_o + ((size_t)warp * 16 + r) * RS;
 #pragma unroll
-            for (int nb = 0; nb < NB; ++nb) {
-                dst[8 * nb + 2 * t] = o[nb][2 * i];
-                dst[8 * nb + 2 * t + 1] = o[nb][2 * i + 1];
-            }
+            for (int nb = 0; nb < NB; ++nb)
+                *reinterpret_cast<float2*>(dst + 8 * nb + 2 * t) = make_float2(o[nb][2 * i], o[nb][2 * i + 1]);
             if (t == 0) {
                 red_ml[((size_t)warp * 16 + r) * 2] = m_run[i];
                 red_ml[((size_t)warp * 16 + r) * 2 + 1] = l_run[i];
             }
         }
         __syncthreads();
-        const int rows_here = min(16, n_rows - tile_row0);
-        const float ln2 = 0.6931471805599453f;
-        for (int idx = tid; idx < rows_here * HD; idx += NARROW_THREADS) {
-            const int r = idx / HD, d = idx - r * HD;
+        // each warp's weight for each row, once (one thread per pair), and each row's maximum and sum
+        if (tid < NARROW_WARPS * 16) {
+            const int r = tid & 15, w = tid >> 4;
             float m = -INFINITY;
 #pragma unroll
-            for (int w = 0; w < NARROW_WARPS; ++w) m = fmaxf(m, red_ml[((size_t)w * 16 + r) * 2]);
-            float l = 0.f, acc = 0.f;
+            for (int w2 = 0; w2 < NARROW_WARPS; ++w2) m = fmaxf(m, red_ml[((size_t)w2 * 16 + r) * 2]);
+            const float mw = red_ml[((size_t)w * 16 + r) * 2];
+            weight_of[w][r] = (mw == -INFINITY) ? 0.f : fast_exp2(mw - m);
+            if (w == 0) max_of[r] = m;
+        }
+        __syncthreads();
+        if (tid < 16) {
+            float l = 0.f;
+#pragma unroll
+            for (int w = 0; w < NARROW_WARPS; ++w) l += red_ml[((size_t)w * 16 + tid) * 2 + 1] * weight_of[w][tid];
+            sum_of[tid] = l;
+        }
+        if (p.n_splits == 1) __syncthreads();      // the only reader of sum_of among other threads
+        const int rows_here = min(16, n_rows - tile_row0);
+        const float ln2 = 0.6931471805599453f;
+        for (int idx = tid; idx < rows_here * (HD / 4); idx += NARROW_THREADS) {
+            const int r = idx / (HD / 4), d = 4 * (idx - r * (HD / 4));
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
             for (int w = 0; w < NARROW_WARPS; ++w) {
-                const float mw = red_ml[((size_t)w * 16 + r) * 2];
-                const float wgt = (mw == -INFINITY) ? 0.f : exp2f(mw - m);
-                l += red_ml[((size_t)w * 16 + r) * 2 + 1] * wgt;
-                acc += red_o[((size_t)w * 16 + r) * HD + d] * wgt;
+                const float4 v = *reinterpret_cast<const float4*>(red_o + ((size_t)w * 16 + r) * RS + d);
+                const float wgt = weight_of[w][r];
+                acc.x += v.x * wgt; acc.y += v.y * wgt; acc.z += v.z * wgt; acc.w += v.w * wgt;
             }
             const int row = tile_row0 + r;
             const int tok = row / group, head = kh * group + (row - tok * group);
             if (p.n_splits == 1) {
-                p.out[(size_t)(q_start + tok) * p.out_stride + (size_t)head * HD + d] =
-                    __float2bfloat16_rn(acc / l);
+                const float inv = 1.f / sum_of[r];
+                uint2 packed;
+                packed.x = pack_bf16(acc.x * inv, acc.y * inv);
+                packed.y = pack_bf16(acc.z * inv, acc.w * inv);
+                *reinterpret_cast<uint2*>(p.out + (size_t)(q_start + tok) * p.out_stride + (size_t)head * HD + d) = packed;
             } else {
                 const size_t base = ((size_t)(q_start + tok) * p.n_heads + head) * p.n_splits + split;
-                p.part_o[base * HD + d] = acc;
-                if (d == 0) {
-                    p.part_ml[base * 2] = m * ln2;     // the merge kernel works with natural logs
-                    p.part_ml[base * 2 + 1] = l;
-                }
+                *reinterpret_cast<float4*>(p.part_o + base * HD + d) = acc;
             }
+        }
+        if (p.n_splits > 1 && tid < rows_here) {
+            const int row = tile_row0 + tid;
+            const int tok = row / group, head = kh * group + (row - tok * group);
+            const size_t base = ((size_t)(q_start + tok) * p.n_heads + head) * p.n_splits + split;
+            p.part_ml[base * 2] = max_of[tid] * ln2;     // the merge kernel works with natural logs
+            p.part_ml[base * 2 + 1] = sum_of[tid];
         }
         return;
     }
@@ -569,7 +606,7 @@ int launch_mma(const MmaAttnParams& p, cudaStream_t stream) {
     const size_t stage_bytes = 2 * (size_t)CHUNK * HD * sizeof(__nv_bfloat16);
     size_t smem = stage_bytes * (NARROW ? NARROW_STAGES * NARROW_WARPS : WIDE_STAGES);
     if (NARROW) {
-        const size_t reduce = (size_t)NARROW_WARPS * 16 * (HD + 2) * sizeof(float);
+        const size_t reduce = (size_t)NARROW_WARPS * 16 * (HD + 8 + 2) * sizeof(float);
         if (reduce > smem) smem = reduce;
     }
     if (smem + 1024 > 48 * 1024) {   // the kernel also has a little static shared memory
