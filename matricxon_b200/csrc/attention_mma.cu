@@ -40,12 +40,12 @@ namespace {
 
 constexpr int MMA_WARPS = 4;        // wide tiles: 16 rows each
 constexpr int MMA_THREADS = MMA_WARPS * 32;
-constexpr int NARROW_WARPS = 8;  // narrow tiles: all warps hold the same rows and share the chunks
+constexpr int NARROW_WARPS = 8;     // narrow tiles: all warps hold the same rows and share the chunks
 constexpr int NARROW_THREADS = NARROW_WARPS * 32;
 constexpr int CHUNK = 32;
 constexpr int WIDE_STAGES = 4;      // chunks in flight per block (two pairs), wide tiles
 constexpr int NARROW_STAGES = 1;    // chunks in flight per warp, narrow tiles
-constexpr int NARROW_TABLE = 512;   // block-table entries a narrow tile's block reads ahead (16,384 positions in pages of 16)
+constexpr int NARROW_TABLE = 512;   // block-table entries a narrow tile's block reads ahead (8,192 positions in pages of 16)
 constexpr int SPIN_LIMIT = 1 << 22;
 
 struct MmaAttnParams {
