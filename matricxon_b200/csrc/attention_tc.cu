@@ -9,21 +9,27 @@
 // A block owns, for one sequence and one KV head, T = 128 / group consecutive query tokens: the
 // 128 rows of an MMA tile are the pairs (token, head in group), token-major, so all rows share
 // every key. It walks the keys in chunks of 128 positions:
-//   warps 4 and 6      producers: warp 4 brings the query tile once (one 4-D TMA box per half of the
-//                      head dim) and per chunk the keys, warp 6 the values: TMA boxes straight out
+//   warps 8 and 10     producers: warp 8 brings the query tile once (one 4-D TMA box per half of the
+//                      head dim) and per chunk the keys, warp 10 the values: TMA boxes straight out
 //                      of the paged cache, one page per lane, page numbers from the block table
 //                      (read once per tile into shared memory), two stages each. A key stage is
 //                      free as soon as its Q K^T has run, a value stage when its P V has;
-//   warp 5 (one lane)  issues S = Q K^T (tcgen05.mma, operands in swizzled shared memory,
+//   warp 9 (one lane)  issues S = Q K^T (tcgen05.mma, operands in swizzled shared memory,
 //                      accumulator in tensor memory, three S buffers so that the scores of the
 //                      next chunk exist before the softmax of this one ends) and O += P V (P read
 //                      from tensor memory, V^T pages as the K-major B operand, O in tensor memory);
-//   warps 0-3          softmax: thread r owns row r. It reads its 128 scores from tensor memory
-//                      (tcgen05.ld), masks the chunks that cross an edge, keeps a running
+//   warps 0-7          softmax: two threads per row (warps w and w + 4 reach the same quarter of
+//                      tensor memory), each with 64 of the chunk's 128 keys. A thread reads its
+//                      scores from tensor memory (tcgen05.ld), masks the chunks that cross an edge,
+//                      exchanges its maximum with its partner through shared memory, keeps a running
 //                      reference maximum that only moves when the new maximum exceeds it by 2^8
 //                      (then O is rescaled in tensor memory), writes P as bfloat16 over the first
 //                      64 columns of the same score buffer (tcgen05.st), and at the end
-//                      normalises O and stores it.
+//                      normalises its 64 columns of O and stores them. (One thread per row took
+//                      82 us for the 2,048-token portion of the 3B sizes, two take 75: a scheduler
+//                      with two softmax warps runs one's tensor-memory loads under the other's
+//                      exponentials. The chunk's 16,384 exponentials alone are 1,024 cycles of the
+//                      SM's special-function units, as long as its MMAs.)
 // Keys beyond the newest one of the tile are not data yet: their scores are masked by selection and
 // their value columns are zeroed in shared memory before the last P V (0 x NaN must not happen).
 // Every mbarrier wait is bounded: a wait that runs out sets MX_STATUS_WAIT_TIMEOUT and the role
@@ -39,7 +45,10 @@ constexpr int AT_ROWS = 128;
 constexpr int AT_KEYS = 128;
 constexpr int AT_HD = 128;
 constexpr int AT_STAGES = 2;
-constexpr int AT_THREADS = 224;                       // warps 0-3 softmax, 4 keys, 5 MMA, 6 values
+constexpr int AT_SOFTMAX_WARPS = 8;                    // two per quarter of tensor memory: each takes half of a row's keys
+constexpr int AT_SOFTMAX_THREADS = AT_SOFTMAX_WARPS * 32;
+constexpr int AT_KEY_WARP = 8, AT_MMA_WARP = 9, AT_VALUE_WARP = 10;
+constexpr int AT_THREADS = 352;                       // warps 0-7 softmax, 8 keys, 9 MMA, 10 values
 constexpr unsigned AT_SPIN = 1u << 18;
 constexpr int AT_TILE = AT_ROWS * 64 * 2;            // bytes of a [128][64] bfloat16 half tile
 constexpr int AT_SBUF = 3;                            // score buffers in tensor memory: 3 x 128 columns, then O
@@ -56,6 +65,7 @@ struct AtShared {
     // chunk j - 2, and the softmax threads wait on it; with two barriers neither can fall two phases behind
     unsigned long long pv_done[2];
     unsigned tmem_base;
+    int abort;                   // a softmax thread's wait ran out: all of them leave at the next exchange
 };
 
 struct AtParams {
@@ -259,17 +269,18 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
         }
         for (int b = 0; b < AT_SBUF; ++b) {
             at_mbar_init(&sh.s_full[b], 1);
-            at_mbar_init(&sh.p_full[b], 4);
+            at_mbar_init(&sh.p_full[b], AT_SOFTMAX_WARPS);
         }
         at_mbar_init(&sh.pv_done[0], 1);
         at_mbar_init(&sh.pv_done[1], 1);
+        sh.abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     // value stages start as zeros: a page that is never fetched must not hold NaN bit patterns
     for (int i = tid; i < AT_STAGES * 2 * AT_TILE / 16; i += AT_THREADS)
         reinterpret_cast<uint4*>(v_stage)[i] = make_uint4(0u, 0u, 0u, 0u);
     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-    if (warp == 5) {
+    if (warp == AT_MMA_WARP) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&sh.tmem_base)),
                      "r"(512)
                      : "memory");
@@ -281,11 +292,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
     const unsigned tmem_base = sh.tmem_base;
     const unsigned tmem_o = tmem_base + AT_SBUF * 128;
 
-    if (warp == 4 || warp == 6) {
+    if (warp == AT_KEY_WARP || warp == AT_VALUE_WARP) {
         // ---------------- producers: warp 4 brings the query tile and the keys, warp 6 the values, each
         // at its own pace (a key stage is free once its Q K^T is done, a value stage once its P V is);
         // lane pg owns page pg of every chunk
-        const bool keys = warp == 4;
+        const bool keys = warp == AT_KEY_WARP;
         int* table = keys ? table_k : table_v;
         const int* bt = p.block_tables + (size_t)seq * p.bt_stride;
         if (keys && lane == 0) {
@@ -343,7 +354,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
                 }
             }
         }
-    } else if (warp == 5) {
+    } else if (warp == AT_MMA_WARP) {
         // ---------------- MMA issuer. One thread; everything it can know before the loop is computed
         // there, and a chunk costs it two commits: tcgen05.mma of one thread run in issue order, so the
         // Q K^T that overwrites a score buffer needs no barrier against the P V that read P from it.
@@ -416,13 +427,18 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
             }
         }
     } else {
-        // ---------------- softmax and epilogue: thread `row` owns tile row `row`
-        const int row = tid;
+        // ---------------- softmax and epilogue: two threads per tile row. Warps w and w + 4 reach the same
+        // quarter of tensor memory; thread `row` of half `part` owns keys 64 part .. 64 part + 63 of its row
+        // in every chunk and columns 64 part .. 64 part + 63 of O. The halves exchange their maxima through
+        // shared memory once a chunk (a barrier of the 256 softmax threads) and their sums once at the end.
+        // With two warps per scheduler one's tensor-memory loads and exponentials run under the other's.
+        __shared__ float half_max[2][2][AT_ROWS], half_sum[2][AT_ROWS];
+        const int part = warp >> 2, row = tid & (AT_ROWS - 1);
         const int t_in = row / p.group, h_in = row - t_in * p.group;
         const bool valid = row < p.tokens_per_tile * p.group && t_in < n_tok;
         const int pos = valid ? ctx + tok0 + t_in : -1;                 // -1: every key is masked
         const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
-        const unsigned lane_base = (unsigned)(32 * warp) << 16;
+        const unsigned lane_base = (unsigned)(32 * (warp & 3)) << 16;
         float m_ref = -INFINITY, l_run = 0.f;
         bool alive = true;
         // Phases of the "P V done" barrier are consumed strictly in order (phase j completes when the
@@ -435,80 +451,98 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
                 ++consumed;
             }
         };
-        for (int j = 0; j < n_chunks && alive; ++j) {
+        // A thread whose wait ran out keeps walking the loop without touching anything, so that every
+        // barrier below is reached by all 256 threads; they leave together after the next exchange.
+        for (int j = 0; j < n_chunks; ++j) {
             const int b = j % AT_SBUF, s = j % AT_STAGES;
-            alive = at_wait(&sh.s_full[b], (unsigned)(j / AT_SBUF) & 1, p.status);
-            if (!alive) break;
+            if (alive) alive = at_wait(&sh.s_full[b], (unsigned)(j / AT_SBUF) & 1, p.status);
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
             pv_consumed_through(j - 1);               // long completed: this only keeps the count in step
-            if (!alive) break;
-            const int c0 = (c_begin + j) * AT_KEYS;
+            alive = __all_sync(0xffffffffu, alive);   // the tensor-memory accesses below are warp-wide
+            if (!alive) *reinterpret_cast<volatile int*>(&sh.abort) = 1;
+            const int c0 = (c_begin + j) * AT_KEYS, k0 = c0 + 64 * part;
             // rows that belong to no token of the tile need no mask: whatever they compute is never stored,
             // and a row's output depends on that row alone
-            const bool edge = __any_sync(0xffffffffu, valid && (c0 + AT_KEYS - 1 > pos || c0 < lo));
+            const bool edge = __any_sync(0xffffffffu, valid && (k0 + 63 > pos || k0 < lo));
             const unsigned s_addr = tmem_base + (unsigned)b * 128 + lane_base;
-            float sc[AT_KEYS];
-#pragma unroll
-            for (int piece = 0; piece < 4; ++piece) tmem_load32(s_addr + 32 * piece, sc + 32 * piece);
-            asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-            if (edge) {
-#pragma unroll
-                for (int c = 0; c < AT_KEYS; ++c) {
-                    const int key = c0 + c;
-                    sc[c] = (key <= pos && key >= lo) ? sc[c] : -INFINITY;
-                }
-            }
+            float sc[64];
             float mx = -INFINITY;
+            if (alive) {
+                tmem_load32(s_addr + 64 * part, sc);
+                tmem_load32(s_addr + 64 * part + 32, sc + 32);
+                asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+                if (edge) {
 #pragma unroll
-            for (int c = 0; c < AT_KEYS; ++c) mx = fmaxf(mx, sc[c]);
-            mx *= p.scale_log2;
+                    for (int c = 0; c < 64; ++c) {
+                        const int key = k0 + c;
+                        sc[c] = (key <= pos && key >= lo) ? sc[c] : -INFINITY;
+                    }
+                }
+                // four chains, so that the maximum is not one chain of 64 dependent instructions
+                float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+                for (int c = 0; c < 64; c += 4) {
+                    m4[0] = fmaxf(m4[0], sc[c]); m4[1] = fmaxf(m4[1], sc[c + 1]);
+                    m4[2] = fmaxf(m4[2], sc[c + 2]); m4[3] = fmaxf(m4[3], sc[c + 3]);
+                }
+                mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+            }
+            half_max[j & 1][part][row] = mx;
+            // both halves have their scores in registers from here on: P may overwrite the other half's columns
+            asm volatile("bar.sync 3, 256;\n" ::: "memory");
+            if (*reinterpret_cast<volatile int*>(&sh.abort)) {
+                alive = false;
+                break;                                  // all 256 threads see the flag after the barrier
+            }
+            mx = fmaxf(mx, half_max[j & 1][part ^ 1][row]) * p.scale_log2;
             const bool jump = mx > m_ref + AT_JUMP || (m_ref == -INFINITY && mx > -INFINITY);
             const float m_new = jump ? mx : m_ref;
             // O may only be touched while no P V is running: the rare rescaling waits for the previous one
             if (j > 0 && __any_sync(0xffffffffu, jump)) {
                 pv_consumed_through(j);
-                if (!alive) break;
-                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-                {
+                alive = __all_sync(0xffffffffu, alive);
+                if (alive) {
+                    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
                     const float alpha = jump ? at_exp2(m_ref - m_new) : 1.f;     // exp2(-inf) = 0: O was 0 anyway
                     l_run *= alpha;
 #pragma unroll
-                    for (int piece = 0; piece < 4; ++piece) {
+                    for (int piece = 0; piece < 2; ++piece) {
                         float o[32];
-                        tmem_load32(tmem_o + lane_base + 32 * piece, o);
+                        tmem_load32(tmem_o + lane_base + 64 * part + 32 * piece, o);
                         asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 #pragma unroll
                         for (int c = 0; c < 32; ++c) o[c] *= alpha;
-                        tmem_store32(tmem_o + lane_base + 32 * piece, o);
+                        tmem_store32(tmem_o + lane_base + 64 * part + 32 * piece, o);
                     }
                     asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
                 }
             }
-            m_ref = m_new;
-            const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
-            float sum = 0.f;
-            // P as bfloat16 pairs over the first 64 columns of this chunk's S buffer (its scores are in registers)
-#pragma unroll
-            for (int half = 0; half < 2; ++half) {
+            if (alive) {
+                m_ref = m_new;
+                const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
+                float sum0 = 0.f, sum1 = 0.f;
+                // P as bfloat16 pairs over the first 64 columns of this chunk's S buffer: this half's 64 keys
+                // are columns 32 part .. 32 part + 31
                 unsigned packed[32];
 #pragma unroll
                 for (int c = 0; c < 32; ++c) {
-                    const float e0 = at_exp2(fmaf(sc[64 * half + 2 * c], p.scale_log2, -m_use));
-                    const float e1 = at_exp2(fmaf(sc[64 * half + 2 * c + 1], p.scale_log2, -m_use));
-                    sum += e0 + e1;
+                    const float e0 = at_exp2(fmaf(sc[2 * c], p.scale_log2, -m_use));
+                    const float e1 = at_exp2(fmaf(sc[2 * c + 1], p.scale_log2, -m_use));
+                    sum0 += e0;
+                    sum1 += e1;
                     packed[c] = at_pack(e0, e1);
                 }
-                tmem_store32_bits(s_addr + 32 * half, packed);
+                tmem_store32_bits(s_addr + 32 * part, packed);
+                asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+                l_run += sum0 + sum1;
             }
-            asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
-            l_run += sum;
             if (j == n_chunks - 1 && c0 + AT_KEYS - 1 > hi_tile) {
                 // value slots beyond the newest key hold no data yet: zero them in the stage
-                alive = at_wait(&sh.v_full[s], (unsigned)(j / AT_STAGES) & 1, p.status);
+                if (alive) alive = at_wait(&sh.v_full[s], (unsigned)(j / AT_STAGES) & 1, p.status);
                 unsigned char* vs = v_stage + (size_t)s * 2 * AT_TILE;
                 const int first_bad = hi_tile + 1 - c0;                     // first key column without data
                 const int row_bytes = p.page_size * 2;
-                for (int item = tid; alive && item < AT_HD * (AT_KEYS - first_bad); item += 128) {
+                for (int item = tid; alive && item < AT_HD * (AT_KEYS - first_bad); item += AT_SOFTMAX_THREADS) {
                     const int d = item / (AT_KEYS - first_bad), col = first_bad + item % (AT_KEYS - first_bad);
                     const int pg = col >> p.page_shift, kcol = col & (p.page_size - 1);
                     // 16-byte chunk kcol / 8 of row d, moved by the 32- or 64-byte swizzle of the tile
@@ -517,32 +551,36 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
                                                       (kcol & 7) * 2) = __float2bfloat16_rn(0.f);
                 }
                 asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // ordinary stores, read by the MMA
-                asm volatile("bar.sync 2, 128;\n" ::: "memory");            // all four softmax warps zeroed their part
-                if (!alive) break;
+                asm volatile("bar.sync 2, 256;\n" ::: "memory");            // all eight softmax warps zeroed their part
             }
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
             __syncwarp();
-            if (lane == 0) at_arrive(&sh.p_full[b]);
+            if (lane == 0 && alive) at_arrive(&sh.p_full[b]);
         }
         pv_consumed_through(n_chunks);
+        // the row's sum of weights: both halves hold a part
+        half_sum[part][row] = l_run;
+        asm volatile("bar.sync 3, 256;\n" ::: "memory");
+        l_run += half_sum[part ^ 1][row];
+        alive = __all_sync(0xffffffffu, alive);
         if (alive && p.n_splits > 1) {
             // a share of the keys: the unnormalised sums, the reference maximum and the sum of weights
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
             const size_t base = ((size_t)(q_start + tok0 + t_in) * p.n_heads + (size_t)(kh * p.group + h_in)) *
                                     p.n_splits + blockIdx.z;
             const bool any = n_chunks > 0 && l_run > 0.f;
-            if (valid) {
+            if (valid && part == 0) {
                 p.part_ml[base * 2] = any ? m_ref * 0.6931471805599453f : -INFINITY;
                 p.part_ml[base * 2 + 1] = any ? l_run : 0.f;
             }
             if (n_chunks > 0) {                                          // warp-uniform: tensor memory holds sums
 #pragma unroll
-                for (int piece = 0; piece < 4; ++piece) {
+                for (int piece = 0; piece < 2; ++piece) {
                     float o[32];
-                    tmem_load32(tmem_o + lane_base + 32 * piece, o);
+                    tmem_load32(tmem_o + lane_base + 64 * part + 32 * piece, o);
                     asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
                     if (valid && any) {
-                        float4* dst4 = reinterpret_cast<float4*>(p.part_o + base * AT_HD + 32 * piece);
+                        float4* dst4 = reinterpret_cast<float4*>(p.part_o + base * AT_HD + 64 * part + 32 * piece);
 #pragma unroll
                         for (int c = 0; c < 32; c += 4) dst4[c / 4] = make_float4(o[c], o[c + 1], o[c + 2], o[c + 3]);
                     }
@@ -552,11 +590,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
             const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
             __nv_bfloat16* dst = p.out + (size_t)(q_start + tok0 + t_in) * p.out_stride +
-                                 (size_t)(kh * p.group + h_in) * AT_HD;
+                                 (size_t)(kh * p.group + h_in) * AT_HD + 64 * part;
 #pragma unroll
-            for (int piece = 0; piece < 4; ++piece) {
+            for (int piece = 0; piece < 2; ++piece) {
                 float o[32];
-                tmem_load32(tmem_o + lane_base + 32 * piece, o);
+                tmem_load32(tmem_o + lane_base + 64 * part + 32 * piece, o);
                 asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
                 if (valid) {
 #pragma unroll
@@ -571,7 +609,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
     // ---------------- teardown: every role arrives here; then tensor memory is freed
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
     __syncthreads();
-    if (warp == 5) {
+    if (warp == AT_MMA_WARP) {
         __syncwarp();
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(512) : "memory");
