@@ -359,6 +359,73 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_o,
     }
 }
 
+// The merge for steps with many rows (prompt portions whose keys were shared out): a warp per (token, head),
+// eight a block, each lane four neighbouring dims; no shared memory and no barrier. The kernel above, a block
+// per pair, is built for the few rows of a decode step and spends 15 us on 6,144 pairs where this one reads
+// its 8 MB at the memory's rate. At most MERGE_ROW_SPLITS splits; head_dim a multiple of 4.
+constexpr int MERGE_ROW_SPLITS = 8, MERGE_ROW_WARPS = 8;
+template <typename T>
+__global__ void __launch_bounds__(MERGE_ROW_WARPS * 32)
+attention_merge_rows_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, T* __restrict__ out,
+                            int out_stride, int n_heads, int head_dim, int n_splits, int n_pairs) {
+    pdl_trigger();
+    pdl_wait();
+    const int pair = blockIdx.x * MERGE_ROW_WARPS + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (pair >= n_pairs) return;
+    const int t = pair / n_heads, h = pair - t * n_heads;
+    const size_t base = (size_t)pair * n_splits;
+    float weight[MERGE_ROW_SPLITS], sums[MERGE_ROW_SPLITS];
+    float m = -INFINITY;
+#pragma unroll
+    for (int s = 0; s < MERGE_ROW_SPLITS; ++s) {
+        const float2 ml = s < n_splits ? *reinterpret_cast<const float2*>(part_ml + (base + s) * 2)
+                                       : make_float2(-INFINITY, 0.f);
+        weight[s] = ml.x;
+        sums[s] = ml.y;
+        m = fmaxf(m, ml.x);
+    }
+    float total = 0.f;
+#pragma unroll
+    for (int s = 0; s < MERGE_ROW_SPLITS; ++s) {
+        weight[s] = weight[s] == -INFINITY ? 0.f : expf(weight[s] - m);
+        total += sums[s] * weight[s];
+    }
+    const float inv = 1.f / total;
+    for (int d = 4 * lane; d < head_dim; d += 128) {
+        float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int s = 0; s < MERGE_ROW_SPLITS; ++s) {
+            // a split without keys has weight 0 and values nobody wrote: it is skipped, not multiplied
+            if (s < n_splits && weight[s] != 0.f) {
+                const float4 v = *reinterpret_cast<const float4*>(part_o + (base + s) * head_dim + d);
+                o.x += v.x * weight[s]; o.y += v.y * weight[s]; o.z += v.z * weight[s]; o.w += v.w * weight[s];
+            }
+        }
+        T* dst = out + (size_t)t * out_stride + (size_t)h * head_dim + d;
+        dst[0] = from_float<T>(o.x * inv);
+        dst[1] = from_float<T>(o.y * inv);
+        dst[2] = from_float<T>(o.z * inv);
+        dst[3] = from_float<T>(o.w * inv);
+    }
+}
+
+// Which of the two merges a step takes: the many-row one from 1,024 (token, head) pairs on, where it fits.
+template <typename T>
+int launch_merge(const float* part_o, const float* part_ml, T* out, int out_stride, int n_tokens, int n_heads,
+                 int head_dim, int n_splits, cudaStream_t stream) {
+    const long long pairs = (long long)n_tokens * n_heads;
+    if (pairs >= 1024 && pairs < (1LL << 31) && n_splits <= MERGE_ROW_SPLITS && head_dim % 4 == 0 &&
+        reinterpret_cast<uintptr_t>(part_o) % 16 == 0) {
+        const int blocks = (int)((pairs + MERGE_ROW_WARPS - 1) / MERGE_ROW_WARPS);
+        mx_launch_chained(attention_merge_rows_kernel<T>, dim3(blocks), dim3(MERGE_ROW_WARPS * 32), 0, stream, part_o,
+                          part_ml, out, out_stride, n_heads, head_dim, n_splits, (int)pairs);
+        return mx_launch_status();
+    }
+    mx_launch_chained(attention_merge_kernel<T>, dim3(n_tokens, n_heads), dim3(128), 0, stream, part_o, part_ml, out,
+                      out_stride, n_heads, head_dim, n_splits);
+    return mx_launch_status();
+}
+
 template <typename T>
 size_t attention_smem_bytes(int head_dim) {
     return (size_t)GH * head_dim * 4 + (size_t)GH * KEYS * 4 + 3 * GH * 4 +
@@ -379,10 +446,8 @@ int launch_attention(const AttnParams& p, int n_tokens, cudaStream_t stream) {
     paged_attention_kernel<T, HD_SLOTS><<<grid, ATT_THREADS, smem, stream>>>(p);
     int rc = mx_launch_status();
     if (rc != MX_OK || p.n_splits == 1) return rc;
-    dim3 mgrid(n_tokens, p.n_heads);
-    attention_merge_kernel<T><<<mgrid, 128, 0, stream>>>(p.part_o, p.part_ml, (T*)p.out, p.out_stride,
-                                                        p.n_heads, p.head_dim, p.n_splits);
-    return mx_launch_status();
+    return launch_merge<T>(p.part_o, p.part_ml, (T*)p.out, p.out_stride, n_tokens, p.n_heads, p.head_dim, p.n_splits,
+                           stream);
 }
 
 }  // namespace
@@ -429,10 +494,8 @@ extern "C" int mx_attention_merge_bf16(const float* part_o, const float* part_ml
                                        int out_stride, int n_tokens, int n_heads, int head_dim,
                                        int n_splits, cudaStream_t stream) {
     if (n_tokens <= 0) return MX_OK;
-    dim3 mgrid(n_tokens, n_heads);
-    mx_launch_chained(attention_merge_kernel<__nv_bfloat16>, mgrid, dim3(128), 0, stream, part_o, part_ml,
-                      (__nv_bfloat16*)out, out_stride, n_heads, head_dim, n_splits);
-    return mx_launch_status();
+    return launch_merge<__nv_bfloat16>(part_o, part_ml, (__nv_bfloat16*)out, out_stride, n_tokens, n_heads, head_dim,
+                                       n_splits, stream);
 }
 
 // ---------------------------------------------------------------------------------------------

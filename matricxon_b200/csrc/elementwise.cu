@@ -486,45 +486,55 @@ __global__ void epilogue_kernel(const TAcc* __restrict__ acc, const float* __res
     }
 }
 
-// The same, four neighbouring columns per thread (rows whose length is a multiple of 4, 16-byte aligned
-// tensors, fewer than 2^31 elements): vector accesses, one 32-bit division per thread.
+// The same, four neighbouring columns per item (rows whose length is a multiple of 4, 16-byte aligned
+// tensors, fewer than 2^31 elements) and EPI_ITEMS items per thread, a grid apart: every item's loads are
+// issued before the first is used, so that a thread has 64 to 128 bytes on their way instead of 8 to 32
+// (the first product of the feed-forward at 256 rows: 7.7 us with one item a thread).
+constexpr int EPI_ITEMS = 4;
 template <typename TAcc, typename TOut>
 __global__ void epilogue_vec_kernel(const TAcc* __restrict__ acc, const float* __restrict__ bias,
                                     const float* residual, TOut* out, int total4, int cols4, int mode) {
-    const int i4 = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i4 >= total4) return;
-    const int col = (i4 % cols4) * 4;
-    const size_t at = (size_t)i4 * 4;
-    float v[4];
-    if (sizeof(TAcc) == 4) {
-        const float4 a = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(acc) + at);
-        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
-    } else {
-        const uint2 a = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(acc) + at);
-        const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&a.x);
-        const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(&a.y);
-        v[0] = __low2float(lo); v[1] = __high2float(lo); v[2] = __low2float(hi); v[3] = __high2float(hi);
-    }
-    if (bias) {
-        const float4 b = __ldg(reinterpret_cast<const float4*>(bias + col));
-        v[0] += b.x; v[1] += b.y; v[2] += b.z; v[3] += b.w;
-    }
-    if (mode == 1) {
+    const int first = blockIdx.x * blockDim.x + threadIdx.x, stride = gridDim.x * blockDim.x;
+    float v[EPI_ITEMS][4];
+    float4 r[EPI_ITEMS], b[EPI_ITEMS];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) v[e] = gelu_tanh(v[e]);
+    for (int k = 0; k < EPI_ITEMS; ++k) {
+        const int i4 = first + k * stride;
+        if (i4 >= total4) continue;
+        const size_t at = (size_t)i4 * 4;
+        if (sizeof(TAcc) == 4) {
+            const float4 a = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(acc) + at);
+            v[k][0] = a.x; v[k][1] = a.y; v[k][2] = a.z; v[k][3] = a.w;
+        } else {
+            const uint2 a = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(acc) + at);
+            const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&a.x);
+            const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(&a.y);
+            v[k][0] = __low2float(lo); v[k][1] = __high2float(lo); v[k][2] = __low2float(hi); v[k][3] = __high2float(hi);
+        }
+        if (bias) b[k] = __ldg(reinterpret_cast<const float4*>(bias + (i4 % cols4) * 4));
+        if (mode == 2) r[k] = *reinterpret_cast<const float4*>(residual + at);
     }
-    if (mode == 2) {
-        const float4 r = *reinterpret_cast<const float4*>(residual + at);
-        v[0] += r.x; v[1] += r.y; v[2] += r.z; v[3] += r.w;
-    }
-    if (sizeof(TOut) == 4) {
-        *reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + at) = make_float4(v[0], v[1], v[2], v[3]);
-    } else {
-        __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[2], v[3]);
-        uint2 packed;
-        packed.x = *reinterpret_cast<unsigned*>(&lo);
-        packed.y = *reinterpret_cast<unsigned*>(&hi);
-        *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(out) + at) = packed;
+#pragma unroll
+    for (int k = 0; k < EPI_ITEMS; ++k) {
+        const int i4 = first + k * stride;
+        if (i4 >= total4) continue;
+        const size_t at = (size_t)i4 * 4;
+        if (bias) { v[k][0] += b[k].x; v[k][1] += b[k].y; v[k][2] += b[k].z; v[k][3] += b[k].w; }
+        if (mode == 1) {
+            // a result that is rounded to bfloat16 takes the hardware tanh, as in the engine's own products
+#pragma unroll
+            for (int e = 0; e < 4; ++e) v[k][e] = sizeof(TOut) == 4 ? gelu_tanh(v[k][e]) : gelu_tanh_fast(v[k][e]);
+        }
+        if (mode == 2) { v[k][0] += r[k].x; v[k][1] += r[k].y; v[k][2] += r[k].z; v[k][3] += r[k].w; }
+        if (sizeof(TOut) == 4) {
+            *reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + at) = make_float4(v[k][0], v[k][1], v[k][2], v[k][3]);
+        } else {
+            __nv_bfloat162 lo = __floats2bfloat162_rn(v[k][0], v[k][1]), hi = __floats2bfloat162_rn(v[k][2], v[k][3]);
+            uint2 packed;
+            packed.x = *reinterpret_cast<unsigned*>(&lo);
+            packed.y = *reinterpret_cast<unsigned*>(&hi);
+            *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(out) + at) = packed;
+        }
     }
 }
 
@@ -540,7 +550,7 @@ extern "C" int mx_epilogue(const void* acc, int acc_dtype, const float* bias, co
                            reinterpret_cast<uintptr_t>(residual) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
     if (n_cols % 4 == 0 && aligned && total < (1LL << 31)) {
         const int total4 = (int)(total / 4), cols4 = n_cols / 4;
-        const int vblocks = (total4 + threads - 1) / threads;
+        const int vblocks = (total4 + threads * EPI_ITEMS - 1) / (threads * EPI_ITEMS);
 #define MX_EPI_VEC(TA, TO) \
     epilogue_vec_kernel<TA, TO><<<vblocks, threads, 0, stream>>>((const TA*)acc, bias, residual, (TO*)out, total4, cols4, mode)
         if (acc_dtype == MX_DTYPE_F32 && out_dtype == MX_DTYPE_F32) MX_EPI_VEC(float, float);
