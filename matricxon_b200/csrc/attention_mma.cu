@@ -20,8 +20,10 @@
 //     for 64 rows (four stages a block);
 //   * "narrow" tiles (at most 16 rows, decode tokens): all eight warps hold the same rows,
 //     each streams every eighth chunk through a stage of its own (its block-table entries read
-//     ahead into shared memory), and their
-//     partial results are combined in shared memory.
+//     ahead into shared memory), and their partial results are combined in shared memory
+//     (each warp's weight per row computed once, then float4 sums). A warp's first chunk, if
+//     all its keys were cached by earlier steps, is asked for before the kernel waits for its
+//     predecessor in the stream (the one that computes the queries and this step's keys).
 // Every wait on an mbarrier is bounded: after SPIN_LIMIT polls the kernel sets
 // MX_STATUS_WAIT_TIMEOUT in the step's status word and goes on, so it always ends.
 // Per chunk and warp: S = Q K^T with mma.sync.m16n8k16 (bf16 in, float out), float online
