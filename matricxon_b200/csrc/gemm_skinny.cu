@@ -25,6 +25,7 @@ namespace {
 constexpr int SK_WARPS = 8;
 constexpr int SK_THREADS = SK_WARPS * 32;
 constexpr int SK_UNROLL = 4;
+constexpr int SK_DEEP = 6;      // K = 3,072 is then two trips to memory per warp instead of three
 
 __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], unsigned a0, unsigned a1, unsigned a2,
                                                unsigned a3, unsigned b0, unsigned b1) {
@@ -33,6 +34,14 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], unsigned a0, unsig
         "{%0,%1,%2,%3};\n"
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// 32 bytes at once (sm_100 has 256-bit loads): four lanes then cover a whole 128-byte line of a weight row,
+// and a warp's load is eight whole lines instead of eight halves. The address must be 32-byte aligned.
+__device__ __forceinline__ void load_stream32(const __nv_bfloat16* p, uint4& lo, uint4& hi) {
+    asm volatile("ld.global.nc.L1::no_allocate.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];\n"
+                 : "=r"(lo.x), "=r"(lo.y), "=r"(lo.z), "=r"(lo.w), "=r"(hi.x), "=r"(hi.y), "=r"(hi.z), "=r"(hi.w)
+                 : "l"(p));
 }
 
 __device__ __forceinline__ uint4 load_stream(const __nv_bfloat16* p) {
@@ -64,12 +73,13 @@ struct SkinnyRope {
 // the second hands its sums to the first through distributed shared memory, which adds them after its
 // own (a fixed order) and runs the epilogue. For matrices with so few output features that one block
 // per tile leaves most of the GPU's warp slots, and so most of the loads it could have in flight, unused.
-template <int MB, bool ROPE, bool SPLIT>
+template <int MB, bool ROPE, bool SPLIT, int UNROLL = SK_UNROLL, bool WIDE = false>
 __global__ void __launch_bounds__(SK_THREADS)
 gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bfloat16* __restrict__ W,
                    int ldw, const float* __restrict__ bias, const float* residual, void* out,
                    int ldo, int M, int N, int K, int mode, const SkinnyRope rope) {
-    constexpr int UNROLL = SK_UNROLL;   // eight weight loads in flight per thread; sixteen measured slower
+    // UNROLL: weight loads in flight per thread = 2 UNROLL. Eight (the default) is best where an SM has three
+    // blocks to run (sixteen measured slower there); products with at most two blocks an SM take SK_DEEP.
     constexpr int ROWS = 16, NR = 2;                   // a block owns 16 output features: rows g and g + 8 per thread
     __shared__ float red[SK_WARPS][ROWS][8 * MB];
     __shared__ float peer[SPLIT ? ROWS : 1][8 * MB];   // SPLIT: the other block's sums, written by it
@@ -93,21 +103,23 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bflo
 #pragma unroll
     for (int i = 0; i < NR; ++i) {
         row_ok[i] = n_row[i] < N;
-        wrow[i] = W + (size_t)min(n_row[i], N - 1) * ldw + 8 * t;
+        wrow[i] = W + (size_t)min(n_row[i], N - 1) * ldw + (WIDE ? 16 : 8) * t;
     }
     const __nv_bfloat16* xrow[MB];
     bool tok_ok[MB];
 #pragma unroll
     for (int mb = 0; mb < MB; ++mb) {
         tok_ok[mb] = 8 * mb + g < M;
-        xrow[mb] = x + (size_t)min(8 * mb + g, M - 1) * ldx + 8 * t;
+        xrow[mb] = x + (size_t)min(8 * mb + g, M - 1) * ldx + (WIDE ? 16 : 8) * t;
     }
     float acc[MB][4];
 #pragma unroll
     for (int mb = 0; mb < MB; ++mb) acc[mb][0] = acc[mb][1] = acc[mb][2] = acc[mb][3] = 0.f;
 
+    // a piece of K is 32 elements per row (16 bytes a thread), or 64 with 32-byte loads (WIDE, never with SPLIT)
+    constexpr int PIECE = WIDE ? 64 : 32, HALVES = WIDE ? 2 : 1;
     const int kb_first = SPLIT ? half * (K / 64) : 0;          // SPLIT needs K to be a multiple of 64
-    const int n_blocks = SPLIT ? kb_first + K / 64 : K / 32;
+    const int n_blocks = SPLIT ? kb_first + K / 64 : K / PIECE;
     // The weights are nobody's output: start pulling this thread's first pieces towards L2 while
     // the kernel before this one is still finishing, then wait for it before touching activations.
 #ifndef SK_PREFETCH_ITERS
@@ -119,32 +131,43 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bflo
         if (kb < n_blocks) {
 #pragma unroll
             for (int i = 0; i < NR; ++i)
-                if (row_ok[i]) prefetch_l2(wrow[i] + 32 * kb);
+                if (row_ok[i]) prefetch_l2(wrow[i] + PIECE * kb);
         }
     }
     pdl_wait();
     for (int kb0 = kb_first + warp; kb0 < n_blocks; kb0 += SK_WARPS * UNROLL) {
-        uint4 wf[UNROLL][2], xf[UNROLL][MB];
+        uint4 wf[UNROLL][2][HALVES], xf[UNROLL][MB][HALVES];
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
             const int kb = kb0 + u * SK_WARPS;
             const bool in = kb < n_blocks;
-            wf[u][1] = make_uint4(0, 0, 0, 0);
 #pragma unroll
-            for (int i = 0; i < NR; ++i)
-                wf[u][i] = (in && row_ok[i]) ? load_stream(wrow[i] + 32 * kb) : make_uint4(0, 0, 0, 0);
+            for (int i = 0; i < NR; ++i) {
+#pragma unroll
+                for (int h = 0; h < HALVES; ++h) wf[u][i][h] = make_uint4(0, 0, 0, 0);
+                if (in && row_ok[i]) {
+                    if constexpr (WIDE) load_stream32(wrow[i] + PIECE * kb, wf[u][i][0], wf[u][i][HALVES - 1]);
+                    else wf[u][i][0] = load_stream(wrow[i] + PIECE * kb);
+                }
+            }
 #pragma unroll
             for (int mb = 0; mb < MB; ++mb)
-                xf[u][mb] = (in && tok_ok[mb]) ? *reinterpret_cast<const uint4*>(xrow[mb] + 32 * kb)
-                                               : make_uint4(0, 0, 0, 0);
+#pragma unroll
+                for (int h = 0; h < HALVES; ++h)
+                    xf[u][mb][h] = (in && tok_ok[mb]) ? *reinterpret_cast<const uint4*>(xrow[mb] + PIECE * kb + 8 * h)
+                                                      : make_uint4(0, 0, 0, 0);
         }
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u)
 #pragma unroll
-            for (int mb = 0; mb < MB; ++mb) {
-                mma_bf16_16816(acc[mb], wf[u][0].x, wf[u][1].x, wf[u][0].y, wf[u][1].y, xf[u][mb].x, xf[u][mb].y);
-                mma_bf16_16816(acc[mb], wf[u][0].z, wf[u][1].z, wf[u][0].w, wf[u][1].w, xf[u][mb].z, xf[u][mb].w);
-            }
+            for (int h = 0; h < HALVES; ++h)
+#pragma unroll
+                for (int mb = 0; mb < MB; ++mb) {
+                    mma_bf16_16816(acc[mb], wf[u][0][h].x, wf[u][1][h].x, wf[u][0][h].y, wf[u][1][h].y, xf[u][mb][h].x,
+                                   xf[u][mb][h].y);
+                    mma_bf16_16816(acc[mb], wf[u][0][h].z, wf[u][1][h].z, wf[u][0][h].w, wf[u][1][h].w, xf[u][mb][h].z,
+                                   xf[u][mb][h].w);
+                }
     }
     // All of this block's weights are on their way: the next kernel may start its own preamble (its
     // weights' first pieces towards L2) under this kernel's reduction and epilogue. Triggering at the top
@@ -263,6 +286,17 @@ int skinny_sm_count() {
     return count;
 }
 
+// Few blocks (at most two an SM) with more than one trip to memory each: more loads in flight per thread,
+// at the price of registers that such a product does not need for a third block.
+bool skinny_deep(int grid, int K) {
+    return grid <= 2 * skinny_sm_count() && K / 32 > SK_WARPS * SK_UNROLL;
+}
+
+// 32-byte loads want pieces of 64 and rows that start on 32-byte boundaries
+bool skinny_wide_ok(const void* W, int K, int ldw) {
+    return K % 64 == 0 && ldw % 16 == 0 && reinterpret_cast<uintptr_t>(W) % 32 == 0;
+}
+
 int check_skinny(int M, int K, int ldx, int ldw) {
     if (M > 16) MX_REFUSE("skinny gemm: %d rows, this kernel takes at most 16", M);
     if (K <= 0 || K % 32 != 0) MX_REFUSE("skinny gemm: K = %d is not a positive multiple of 32", K);
@@ -310,6 +344,14 @@ extern "C" int mx_gemm_skinny(const void* x, const void* W, const float* bias, c
         return MX_OK;
     }
     auto kernel = M <= 8 ? gemm_skinny_kernel<1, false, false> : gemm_skinny_kernel<2, false, false>;
+    if (skinny_deep(grid, K)) {
+        // (both row counts: a row's sum is then formed in the same order whatever the batch)
+        if (skinny_wide_ok(W, K, ldw))
+            kernel = M <= 8 ? gemm_skinny_kernel<1, false, false, SK_DEEP / 2, true>
+                            : gemm_skinny_kernel<2, false, false, SK_DEEP / 2, true>;
+        else
+            kernel = M <= 8 ? gemm_skinny_kernel<1, false, false, SK_DEEP> : gemm_skinny_kernel<2, false, false, SK_DEEP>;
+    }
     mx_launch_chained(kernel, dim3(grid), dim3(SK_THREADS), 0, stream, (const __nv_bfloat16*)x, ldx,
                       (const __nv_bfloat16*)W, ldw, bias, residual, out, ldo, M, N, K, mode, none);
     return mx_launch_status();
@@ -336,6 +378,13 @@ extern "C" int mx_gemm_skinny_rope(const void* x, const void* W, const float* bi
     rope.n_heads = n_heads; rope.n_kv_heads = n_kv_heads; rope.head_dim = head_dim; rope.page_size = page_size;
     const int N = (n_heads + 2 * n_kv_heads) * head_dim;
     auto kernel = M <= 8 ? gemm_skinny_kernel<1, true, false> : gemm_skinny_kernel<2, true, false>;
+    if (skinny_deep(N / 16, K)) {
+        if (skinny_wide_ok(W, K, ldw))
+            kernel = M <= 8 ? gemm_skinny_kernel<1, true, false, SK_DEEP / 2, true>
+                            : gemm_skinny_kernel<2, true, false, SK_DEEP / 2, true>;
+        else
+            kernel = M <= 8 ? gemm_skinny_kernel<1, true, false, SK_DEEP> : gemm_skinny_kernel<2, true, false, SK_DEEP>;
+    }
     mx_launch_chained(kernel, dim3(N / 16), dim3(SK_THREADS), 0, stream, (const __nv_bfloat16*)x, ldx,
                       (const __nv_bfloat16*)W, ldw, bias, (const float*)nullptr, qkv, ldo, M, N, K, 0, rope);
     return mx_launch_status();

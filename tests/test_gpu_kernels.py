@@ -115,7 +115,9 @@ def test_gemm_simt_row_result_does_not_depend_on_the_batch():
 
 
 @pytest.mark.parametrize("m", [1, 3, 8, 9, 16])
-@pytest.mark.parametrize("n,k_dim", [(3584, 3072), (1000, 96), (50, 352), (17, 32)])
+# (3584, 3072) and (160, 1088) take the kernel with more loads in flight (few blocks, a long K); the second
+# leaves its warps with five and four pieces of K
+@pytest.mark.parametrize("n,k_dim", [(3584, 3072), (160, 1088), (1000, 96), (50, 352), (17, 32)])
 def test_skinny_gemm_all_epilogues(m, n, k_dim):
     """The decode product against float64, all epilogues, rows and columns that fill no tile."""
     k = kernels()
@@ -217,7 +219,8 @@ def test_rope_kv_write(dtype, heads, kv_heads, dim, rot):
 
 @pytest.mark.parametrize("m", [1, 5, 8, 13, 16])
 @pytest.mark.parametrize("heads,kv_heads,dim,k_dim,with_bias", [(6, 2, 64, 192, True), (3, 1, 16, 96, False),
-                                                               (4, 4, 128, 256, True), (5, 1, 48, 160, True)])
+                                                               (4, 4, 128, 256, True), (5, 1, 48, 160, True),
+                                                               (24, 2, 128, 3072, True), (2, 1, 128, 1536, False)])
 def test_skinny_gemm_with_rotation_equals_product_then_rope(m, heads, kv_heads, dim, k_dim, with_bias):
     """The QKV product with rotation and cache write in its epilogue against the plain product
     followed by the rotary kernel (each checked against float64 above): same queries, same cache."""
