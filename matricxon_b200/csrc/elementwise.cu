@@ -166,8 +166,17 @@ layernorm_vec_kernel(const float* __restrict__ x, const int* __restrict__ rows,
     pdl_trigger();
     const int r = blockIdx.x;
     const int src_row = rows ? rows[r] : r;
-    pdl_wait();
     const int n_vec = hidden >> 2;
+    const float4* w4 = reinterpret_cast<const float4*>(weight);
+    const float4* b4 = reinterpret_cast<const float4*>(bias);
+    // the norm's own constants are nobody's output: this thread's first vector of them sets out before the
+    // wait on the kernel that writes x, instead of after the second reduction (a trip to L2 off the chain)
+    float4 w_first = make_float4(0.f, 0.f, 0.f, 0.f), b_first = w_first;
+    if ((int)threadIdx.x < n_vec) {
+        w_first = w4[threadIdx.x];
+        if (bias) b_first = b4[threadIdx.x];
+    }
+    pdl_wait();
     const float4* xr = reinterpret_cast<const float4*>(x + (size_t)src_row * hidden);
     float4 v[LN_VPT];
     float s = 0.f;
@@ -189,18 +198,16 @@ layernorm_vec_kernel(const float* __restrict__ x, const int* __restrict__ rows,
     }
     const float var = block_sum(q, scratch) / (float)hidden;
     const float rstd = 1.0f / sqrtf(var + eps);
-    const float4* w4 = reinterpret_cast<const float4*>(weight);
-    const float4* b4 = reinterpret_cast<const float4*>(bias);
 #pragma unroll
     for (int k = 0; k < LN_VPT; ++k) {
         const int i = threadIdx.x + k * LN_THREADS;
         if (i >= n_vec) continue;
-        const float4 w = w4[i];
+        const float4 w = k == 0 ? w_first : w4[i];
         float4 y;
         y.x = (v[k].x - mean) * rstd * w.x; y.y = (v[k].y - mean) * rstd * w.y;
         y.z = (v[k].z - mean) * rstd * w.z; y.w = (v[k].w - mean) * rstd * w.w;
         if (bias) {
-            const float4 b = b4[i];
+            const float4 b = k == 0 ? b_first : b4[i];
             y.x += b.x; y.y += b.y; y.z += b.z; y.w += b.w;
         }
         if (sizeof(TOut) == 4) {
