@@ -301,6 +301,8 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_o,
     __shared__ float total_max, total_sum;
     pdl_trigger();
     pdl_wait();
+    part_o = after_wait(part_o);
+    part_ml = after_wait(part_ml);
     const int t = blockIdx.x, h = blockIdx.y;
     const size_t base = ((size_t)t * n_heads + h) * n_splits;
     for (int s = threadIdx.x; s < min(n_splits, MERGE_KEPT); s += blockDim.x) {
@@ -370,6 +372,8 @@ attention_merge_rows_kernel(const float* __restrict__ part_o, const float* __res
                             int out_stride, int n_heads, int head_dim, int n_splits, int n_pairs) {
     pdl_trigger();
     pdl_wait();
+    part_o = after_wait(part_o);
+    part_ml = after_wait(part_ml);
     const int pair = blockIdx.x * MERGE_ROW_WARPS + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (pair >= n_pairs) return;
     const int t = pair / n_heads, h = pair - t * n_heads;

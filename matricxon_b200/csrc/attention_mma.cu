@@ -283,7 +283,7 @@ attention_mma_kernel(const MmaAttnParams p) {
     uint4 qf[2][KB];
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
-        const __nv_bfloat16* qrow = p.q + (size_t)(q_start + r_tok[i]) * p.q_stride +
+        const __nv_bfloat16* qrow = after_wait(p.q) + (size_t)(q_start + r_tok[i]) * p.q_stride +
                                     (size_t)(kh * group + r_head[i]) * HD;
 #pragma unroll
         for (int b = 0; b < KB; ++b) qf[i][b] = *reinterpret_cast<const uint4*>(qrow + 32 * b + 8 * t);

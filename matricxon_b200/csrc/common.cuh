@@ -49,6 +49,16 @@ static inline int mx_launch_status() {
 // the NEXT kernel in the stream begin its own preamble.
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;\n" ::); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+// A pointer to what the kernel before wrote, as it may be used after pdl_wait(): the compiler is told that it
+// no longer knows the pointer, so no load through it can be moved above the wait. Without this a load through
+// a `const __restrict__` parameter is fair game for the scheduler (the qualifiers promise that nothing writes
+// the data while the kernel runs, which is not true of the time before the wait): LayerNorm read rows that
+// the product before it had not finished when other loads were placed ahead of its wait.
+template <typename T>
+__device__ __forceinline__ T* after_wait(T* p) {
+    asm volatile("" : "+l"(p)::"memory");
+    return p;
+}
 __device__ __forceinline__ void prefetch_l2(const void* p) {
     asm volatile("prefetch.global.L2 [%0];\n" ::"l"(p));
 }

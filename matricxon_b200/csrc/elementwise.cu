@@ -130,7 +130,7 @@ __global__ void layernorm_kernel(const float* __restrict__ x, const int* __restr
     const int r = blockIdx.x;
     const int src_row = rows ? rows[r] : r;
     pdl_wait();
-    const float* xr = x + (size_t)src_row * hidden;
+    const float* xr = after_wait(x) + (size_t)src_row * hidden;
     float s = 0.f;
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
         const float v = xr[i];
@@ -177,7 +177,7 @@ layernorm_vec_kernel(const float* __restrict__ x, const int* __restrict__ rows,
         if (bias) b_first = b4[threadIdx.x];
     }
     pdl_wait();
-    const float4* xr = reinterpret_cast<const float4*>(x + (size_t)src_row * hidden);
+    const float4* xr = reinterpret_cast<const float4*>(after_wait(x) + (size_t)src_row * hidden);
     float4 v[LN_VPT];
     float s = 0.f;
 #pragma unroll

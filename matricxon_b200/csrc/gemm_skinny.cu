@@ -135,6 +135,10 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bflo
         }
     }
     pdl_wait();
+    // the activations (and the residual) are what the kernels before wrote: their pointers are taken anew
+#pragma unroll
+    for (int mb = 0; mb < MB; ++mb) xrow[mb] = after_wait(xrow[mb]);
+    residual = after_wait(residual);
     for (int kb0 = kb_first + warp; kb0 < n_blocks; kb0 += SK_WARPS * UNROLL) {
         uint4 wf[UNROLL][2][HALVES], xf[UNROLL][MB][HALVES];
 #pragma unroll
