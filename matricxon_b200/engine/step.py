@@ -118,7 +118,8 @@ class StepRunner:
     def __init__(self, model, cache: CacheManager, storage: CacheStorage,
                  max_step_tokens: int = 8192, max_step_seqs: int = 256,
                  max_model_len: int | None = None, use_graphs: bool = True,
-                 max_graph_batch: int = 64, max_shape_graphs: int = 24) -> None:
+                 max_graph_batch: int = 64, max_shape_graphs: int = 24,
+                 shape_graph_max_tokens: int = 1024) -> None:
         self.model = model
         self.cache = cache
         self.storage = storage
@@ -146,6 +147,10 @@ class StepRunner:
         # after step, then costs the host one metadata copy and one replay instead of some three
         # hundred launches. Shapes seen once (the ragged end of a prompt) run eagerly.
         self.max_shape_graphs = max_shape_graphs
+        # A graph saves the host's launch time (about 5 us a kernel), which only matters for steps that the
+        # device finishes about as fast; a capture costs the step twice over. Larger steps run eagerly
+        # (32 requests of 7B sizes: 14 captures of 2,048-token steps, 27 ms each, were replayed once).
+        self.shape_graph_max_tokens = shape_graph_max_tokens
         self._shape_graphs: dict[tuple, tuple] = {}        # shape -> record, oldest use first
         self._shape_pool = None
         self._shape_seen: dict[tuple, int] = {}
@@ -450,6 +455,8 @@ class StepRunner:
     def _shape_key(self, entries: list[StepEntry]) -> tuple | None:
         """The exact shape of a step that may run as a graph of its own, or None."""
         if not self.use_graphs or self.max_shape_graphs <= 0:
+            return None
+        if sum(len(entry.tokens) for entry in entries) > self.shape_graph_max_tokens:
             return None
         page_size = self.cache.page_size
         stateful = bool(self.model.cache_plan.state_bytes_per_request)
