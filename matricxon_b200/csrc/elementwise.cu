@@ -296,7 +296,7 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int row_stride,
                                      const int* __restrict__ slots, T* __restrict__ cache,
                                      int n_heads, int n_kv_heads, int head_dim, int rotary_dim,
                                      int page_size, long long n_slots, int write_cache,
-                                     int* status) {
+                                     int* status, const float* __restrict__ col_bias) {
     extern __shared__ float cs[];  // cos[half], sin[half]
     pdl_trigger();
     const int t = blockIdx.x;
@@ -309,17 +309,28 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int row_stride,
     }
     __syncthreads();
     pdl_wait();
-    T* row = qkv + (size_t)t * row_stride;
+    T* row = after_wait(qkv) + (size_t)t * row_stride;
+    // col_bias: the product's bias, still to be added (the product came from the library without an
+    // epilogue). The sum is rounded to T first, as the epilogue kernel would have left it.
+    auto value = [&](const T* p, int col) {
+        return col_bias ? to_float(from_float<T>(to_float(*p) + col_bias[col])) : to_float(*p);
+    };
 
     // q heads: rotate in place
     for (int item = threadIdx.x; item < n_heads * half; item += blockDim.x) {
         const int h = item / half, i = item - h * half;
         T* p = row + (size_t)h * head_dim;
-        const float x1 = to_float(p[i]), x2 = to_float(p[i + half]);
+        const float x1 = value(p + i, h * head_dim + i), x2 = value(p + i + half, h * head_dim + i + half);
         const float c = cs[i], s = cs[half + i];
         p[i] = from_float<T>(x1 * c - x2 * s);
         p[i + half] = from_float<T>(x2 * c + x1 * s);
     }
+    if (col_bias)                                 // q dims beyond the rotary width still want their bias
+        for (int item = threadIdx.x; item < n_heads * (head_dim - rotary_dim); item += blockDim.x) {
+            const int h = item / (head_dim - rotary_dim), i = rotary_dim + item - h * (head_dim - rotary_dim);
+            T* p = row + (size_t)h * head_dim + i;
+            *p = from_float<T>(value(p, h * head_dim + i));
+        }
     if (!write_cache) return;
 
     const long long slot = slots[t];
@@ -337,10 +348,11 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int row_stride,
     const T* krow = row + (size_t)n_heads * head_dim;
     const T* vrow = krow + (size_t)n_kv_heads * head_dim;
 
+    const int kcol = n_heads * head_dim, vcol = (n_heads + n_kv_heads) * head_dim;
     for (int item = threadIdx.x; item < n_kv_heads * half; item += blockDim.x) {
         const int h = item / half, i = item - h * half;
         const T* p = krow + (size_t)h * head_dim;
-        const float x1 = to_float(p[i]), x2 = to_float(p[i + half]);
+        const float x1 = value(p + i, kcol + h * head_dim + i), x2 = value(p + i + half, kcol + h * head_dim + i + half);
         const float c = cs[i], s = cs[half + i];
         T* dst = kbase + (size_t)h * head_stride;
         dst[i] = from_float<T>(x1 * c - x2 * s);
@@ -350,11 +362,12 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int row_stride,
     const int tail = head_dim - rotary_dim;
     for (int item = threadIdx.x; item < n_kv_heads * tail; item += blockDim.x) {
         const int h = item / tail, i = rotary_dim + (item - h * tail);
-        kbase[(size_t)h * head_stride + i] = krow[(size_t)h * head_dim + i];
+        kbase[(size_t)h * head_stride + i] = from_float<T>(value(krow + (size_t)h * head_dim + i, kcol + h * head_dim + i));
     }
     for (int item = threadIdx.x; item < n_kv_heads * head_dim; item += blockDim.x) {
         const int h = item / head_dim, i = item - h * head_dim;
-        vbase[(size_t)h * head_stride + (size_t)i * page_size] = vrow[(size_t)h * head_dim + i];
+        vbase[(size_t)h * head_stride + (size_t)i * page_size] =
+            from_float<T>(value(vrow + (size_t)h * head_dim + i, vcol + h * head_dim + i));
     }
 }
 
@@ -367,7 +380,7 @@ __global__ void rope_kv_write_vec_kernel(T* __restrict__ qkv, int row_stride,
                                          const int* __restrict__ slots, T* __restrict__ cache,
                                          int n_heads, int n_kv_heads, int head_dim, int rotary_dim,
                                          int page_size, long long n_slots, int write_cache,
-                                         int* status) {
+                                         int* status, const float* __restrict__ col_bias) {
     constexpr int E = 16 / sizeof(T);
     extern __shared__ float cs[];  // cos[half], sin[half]
     pdl_trigger();
@@ -381,8 +394,12 @@ __global__ void rope_kv_write_vec_kernel(T* __restrict__ qkv, int row_stride,
     }
     __syncthreads();
     pdl_wait();
-    T* row = qkv + (size_t)t * row_stride;
+    T* row = after_wait(qkv) + (size_t)t * row_stride;
     const int per_head = half / E;
+    // col_bias: see rope_kv_write_kernel
+    auto value = [&](T v, int col) {
+        return col_bias ? to_float(from_float<T>(to_float(v) + col_bias[col])) : to_float(v);
+    };
 
     long long slot = -1;
     if (write_cache) {
@@ -409,7 +426,7 @@ __global__ void rope_kv_write_vec_kernel(T* __restrict__ qkv, int row_stride,
         T* hi = reinterpret_cast<T*>(&hi_raw);
 #pragma unroll
         for (int e = 0; e < E; ++e) {
-            const float x1 = to_float(lo[e]), x2 = to_float(hi[e]);
+            const float x1 = value(lo[e], h * head_dim + i + e), x2 = value(hi[e], h * head_dim + i + half + e);
             const float c = cs[i + e], sn = cs[half + i + e];
             lo[e] = from_float<T>(x1 * c - x2 * sn);
             hi[e] = from_float<T>(x2 * c + x1 * sn);
@@ -419,25 +436,36 @@ __global__ void rope_kv_write_vec_kernel(T* __restrict__ qkv, int row_stride,
         *reinterpret_cast<uint4*>(dst + i) = lo_raw;
         *reinterpret_cast<uint4*>(dst + i + half) = hi_raw;
     }
+    const int tail = head_dim - rotary_dim;          // dims beyond the rotary width pass through
+    if (col_bias)                                    // ... with their bias, for q in place
+        for (int item = threadIdx.x; item < n_heads * tail; item += blockDim.x) {
+            const int h = item / tail, i = rotary_dim + (item - h * tail);
+            T* p = row + (size_t)h * head_dim + i;
+            *p = from_float<T>(value(*p, h * head_dim + i));
+        }
     if (slot < 0) return;
     const T* krow = row + (size_t)n_heads * head_dim;
     const T* vrow = krow + (size_t)n_kv_heads * head_dim;
-    const int tail = head_dim - rotary_dim;          // dims beyond the rotary width pass through
+    const int kcol = n_heads * head_dim, vcol = (n_heads + n_kv_heads) * head_dim;
     for (int item = threadIdx.x; item < n_kv_heads * tail; item += blockDim.x) {
         const int h = item / tail, i = rotary_dim + (item - h * tail);
-        kbase[(size_t)h * head_stride + i] = krow[(size_t)h * head_dim + i];
+        kbase[(size_t)h * head_stride + i] = from_float<T>(value(krow[(size_t)h * head_dim + i], kcol + h * head_dim + i));
     }
     for (int item = threadIdx.x; item < n_kv_heads * head_dim; item += blockDim.x) {
         const int h = item / head_dim, i = item - h * head_dim;
-        vbase[(size_t)h * head_stride + (size_t)i * page_size] = vrow[(size_t)h * head_dim + i];
+        vbase[(size_t)h * head_stride + (size_t)i * page_size] =
+            from_float<T>(value(vrow[(size_t)h * head_dim + i], vcol + h * head_dim + i));
     }
 }
 
-extern "C" int mx_rope_kv_write(void* qkv, int dtype, int row_stride, const int* positions,
+// col_bias (may be null): the bias of the product that made qkv, when that product ran without its epilogue
+// (the library's, for 17 or more rows): it is added here, rounded as the epilogue would have rounded it,
+// and the epilogue's pass over qkv is saved.
+extern "C" int mx_rope_kv_write_bias(void* qkv, int dtype, int row_stride, const int* positions,
                                 const float* inv_freq, const int* slots, void* cache, int n_tokens,
                                 int n_heads, int n_kv_heads, int head_dim, int rotary_dim,
                                 int page_size, long long n_pages, int write_cache, int* status,
-                                cudaStream_t stream) {
+                                const float* col_bias, cudaStream_t stream) {
     if (n_tokens <= 0) return MX_OK;
     if (rotary_dim % 2 != 0 || rotary_dim > head_dim || rotary_dim < 0)
         MX_REFUSE("rope: rotary width %d must be even and at most head_dim %d", rotary_dim, head_dim);
@@ -454,24 +482,33 @@ extern "C" int mx_rope_kv_write(void* qkv, int dtype, int row_stride, const int*
         if (dtype == MX_DTYPE_F32)
             mx_launch_chained(rope_kv_write_vec_kernel<float>, dim3(n_tokens), dim3(threads), smem, stream,
                               (float*)qkv, row_stride, positions, inv_freq, slots, (float*)cache, n_heads,
-                              n_kv_heads, head_dim, rotary_dim, page_size, n_slots, write_cache, status);
+                              n_kv_heads, head_dim, rotary_dim, page_size, n_slots, write_cache, status, col_bias);
         else
             mx_launch_chained(rope_kv_write_vec_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), smem,
                               stream, (__nv_bfloat16*)qkv, row_stride, positions, inv_freq, slots,
                               (__nv_bfloat16*)cache, n_heads, n_kv_heads, head_dim, rotary_dim, page_size,
-                              n_slots, write_cache, status);
+                              n_slots, write_cache, status, col_bias);
         return mx_launch_status();
     }
     if (dtype == MX_DTYPE_F32)
         mx_launch_chained(rope_kv_write_kernel<float>, dim3(n_tokens), dim3(threads), smem, stream,
                           (float*)qkv, row_stride, positions, inv_freq, slots, (float*)cache, n_heads,
-                          n_kv_heads, head_dim, rotary_dim, page_size, n_slots, write_cache, status);
+                          n_kv_heads, head_dim, rotary_dim, page_size, n_slots, write_cache, status, col_bias);
     else
         mx_launch_chained(rope_kv_write_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), smem, stream,
                           (__nv_bfloat16*)qkv, row_stride, positions, inv_freq, slots,
                           (__nv_bfloat16*)cache, n_heads, n_kv_heads, head_dim, rotary_dim, page_size,
-                          n_slots, write_cache, status);
+                          n_slots, write_cache, status, col_bias);
     return mx_launch_status();
+}
+
+extern "C" int mx_rope_kv_write(void* qkv, int dtype, int row_stride, const int* positions,
+                                const float* inv_freq, const int* slots, void* cache, int n_tokens,
+                                int n_heads, int n_kv_heads, int head_dim, int rotary_dim,
+                                int page_size, long long n_pages, int write_cache, int* status,
+                                cudaStream_t stream) {
+    return mx_rope_kv_write_bias(qkv, dtype, row_stride, positions, inv_freq, slots, cache, n_tokens, n_heads, n_kv_heads,
+                                 head_dim, rotary_dim, page_size, n_pages, write_cache, status, nullptr, stream);
 }
 
 // ---------------------------------------------------------------- epilogue behind a library GEMM

@@ -116,10 +116,12 @@ def layernorm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, 
 def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor,
                   slots: torch.Tensor | None, cache: torch.Tensor | None, n_heads: int,
                   n_kv_heads: int, head_dim: int, rotary_dim: int, page_size: int,
-                  status: torch.Tensor) -> None:
+                  status: torch.Tensor, bias: torch.Tensor | None = None) -> None:
     """Rotates q (and k) of each row of ``qkv`` in float; writes k and v to the cache pages.
 
-    ``cache`` is [pages, 2, kv heads, page_size, head_dim]; None rotates q only."""
+    ``cache`` is [pages, 2, kv heads, page_size, head_dim]; None rotates q only. ``bias`` (float32,
+    one per column of ``qkv``): the bias of the product that made ``qkv``, still to be added; each
+    sum is rounded to the dtype of ``qkv`` before it is used, as a separate epilogue would."""
     _need(qkv, "qkv")
     _need(positions, "positions", torch.int32)
     _need(inv_freq, "inv_freq", torch.float32)
@@ -134,10 +136,14 @@ def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Te
         _need(slots, "slots", torch.int32)
         assert tuple(cache.shape[1:]) == (2, n_kv_heads, page_size, head_dim), cache.shape
         n_pages = cache.shape[0]
-    check(library().mx_rope_kv_write(_ptr(qkv), dtype_code(qkv.dtype), qkv.stride(0),
-                                     _ptr(positions), _ptr(inv_freq), _ptr(slots), _ptr(cache), n,
-                                     n_heads, n_kv_heads, head_dim, rotary_dim, page_size, n_pages,
-                                     1 if write else 0, _ptr(status), _stream()), "rope_kv_write")
+    if bias is not None:
+        _need(bias, "bias", torch.float32)
+        assert bias.numel() == qkv.shape[1]
+    check(library().mx_rope_kv_write_bias(_ptr(qkv), dtype_code(qkv.dtype), qkv.stride(0),
+                                          _ptr(positions), _ptr(inv_freq), _ptr(slots), _ptr(cache), n,
+                                          n_heads, n_kv_heads, head_dim, rotary_dim, page_size, n_pages,
+                                          1 if write else 0, _ptr(status), _ptr(bias), _stream()),
+          "rope_kv_write")
     _launched()
 
 

@@ -31,6 +31,7 @@ _SIGNATURES: dict[str, tuple[list, object]] = {
     "mx_softcap": ([P, L, F, P], I),
     "mx_layernorm": ([P, P, P, P, P, I, I, I, F, P], I),
     "mx_rope_kv_write": ([P, I, I, P, P, P, P, I, I, I, I, I, I, L, I, P, P], I),
+    "mx_rope_kv_write_bias": ([P, I, I, P, P, P, P, I, I, I, I, I, I, L, I, P, P, P], I),
     "mx_epilogue": ([P, I, P, P, P, I, L, I, I, P], I),
     "mx_gemm_simt": ([P, P, I, P, P, P, I, I, I, I, I, I, I, I, P], I),
     "mx_gemm_tcgen05": ([P, P, P, P, P, I, I, I, I, I, I, I, I, P, P], I),

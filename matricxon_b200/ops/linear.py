@@ -84,6 +84,12 @@ def _pick(x: torch.Tensor, weight: torch.Tensor, m: int, n: int) -> str:
     return "library"
 
 
+def chosen_backend(x: torch.Tensor, weight: torch.Tensor, requested: str = "auto") -> str:
+    """The backend ``linear`` would run this product on."""
+    backend = resolve_backend(requested, x.dtype)
+    return _pick(x, weight, x.shape[0], weight.shape[0]) if backend == "auto" else backend
+
+
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, mode: int,
            residual: torch.Tensor | None = None, out: torch.Tensor | None = None,
            backend: str = "auto") -> torch.Tensor:
@@ -101,6 +107,8 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, mod
         acc = _mm_f32(x, weight.t())
         if acc is not None:
             return acc
+    if backend == "library" and out is None and mode == EPILOGUE_NONE and bias is None and m > 0:
+        return torch.mm(x, weight.t())        # nothing to add: the library's result is the result
     if out is None:
         out = torch.empty((m, n), dtype=out_dtype, device=x.device)
     if m == 0:
@@ -133,5 +141,5 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, mod
     return out
 
 
-__all__ = ["linear", "resolve_backend", "EPILOGUE_NONE", "EPILOGUE_GELU", "EPILOGUE_RESIDUAL",
+__all__ = ["linear", "chosen_backend", "resolve_backend", "EPILOGUE_NONE", "EPILOGUE_GELU", "EPILOGUE_RESIDUAL",
            "EPILOGUE_F32"]

@@ -23,7 +23,7 @@ import os
 import torch
 
 from matricxon_b200.ops import kernels
-from matricxon_b200.ops.linear import EPILOGUE_NONE, EPILOGUE_RESIDUAL, linear
+from matricxon_b200.ops.linear import EPILOGUE_NONE, EPILOGUE_RESIDUAL, chosen_backend, linear
 from matricxon_b200.parts.base import KVCacheRequest, Mixer, build_part, register_part
 from matricxon_b200.parts.rotary import store_without_rotation
 from matricxon_b200.weights.loader import WeightSpec
@@ -154,6 +154,12 @@ class PagedAttention(Mixer):
                                                      spec.num_heads, spec.num_kv_heads, spec.head_dim)
         if qkv is not None:
             pass                                        # product, rotation and cache write were one kernel
+        elif (self.position is not None and self.position.adds_bias and self.qkv_bias is not None
+              and chosen_backend(h, self.qkv_weight, rt.gemm_backend) == "library"):
+            # the library's product has no epilogue of its own: the rotation kernel adds the bias on its way
+            qkv = linear(h, self.qkv_weight, None, EPILOGUE_NONE, backend=rt.gemm_backend)
+            self.position.rotate_and_store(qkv, ctx, binding, spec.num_heads, spec.num_kv_heads,
+                                           spec.head_dim, bias=self.qkv_bias)
         elif self.position is not None:
             qkv = linear(h, self.qkv_weight, self.qkv_bias, EPILOGUE_NONE, backend=rt.gemm_backend)
             self.position.rotate_and_store(qkv, ctx, binding, spec.num_heads, spec.num_kv_heads,

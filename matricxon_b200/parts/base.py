@@ -140,6 +140,10 @@ class Norm(Part):
 
 
 class PositionEncoding(Part):
+    # True: rotate_and_store takes ``bias=`` (the QKV product's bias, not yet added) and adds it itself,
+    # which saves the product's epilogue pass where the product is the library's
+    adds_bias = False
+
     def rotate_and_store(self, qkv, ctx, binding, n_heads, n_kv_heads, head_dim):
         raise NotImplementedError
 

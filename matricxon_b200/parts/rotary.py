@@ -26,6 +26,7 @@ def inverse_frequencies(rotary_dim: int, theta: float) -> torch.Tensor:
 @register_part("position", "rotary_neox")
 class RotaryNeox(PositionEncoding):
     capturable = True
+    adds_bias = True
 
     def __init__(self, spec, runtime, prefix):
         super().__init__(spec, runtime, prefix)
@@ -44,13 +45,13 @@ class RotaryNeox(PositionEncoding):
                                  rt.page_size, ctx.status)
         return qkv
 
-    def rotate_and_store(self, qkv, ctx, binding, n_heads, n_kv_heads, head_dim):
+    def rotate_and_store(self, qkv, ctx, binding, n_heads, n_kv_heads, head_dim, bias=None):
         group = ctx.groups[binding.group] if binding.group is not None else None
         writes = binding.writes and binding.kv is not None
         kernels.rope_kv_write(
             qkv, ctx.positions, self.inv_freq,
             group.slots if writes else None, binding.kv if writes else None,
-            n_heads, n_kv_heads, head_dim, self.spec.rotary_dim, self.runtime.page_size, ctx.status)
+            n_heads, n_kv_heads, head_dim, self.spec.rotary_dim, self.runtime.page_size, ctx.status, bias=bias)
 
 
 def store_without_rotation(qkv, ctx, binding, n_heads, n_kv_heads, head_dim, page_size):

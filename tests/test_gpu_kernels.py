@@ -262,6 +262,39 @@ def test_skinny_gemm_with_rotation_equals_product_then_rope(m, heads, kv_heads, 
     assert st.item() == 2
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads,kv_heads,dim,rot", [(4, 2, 16, 16), (6, 3, 48, 32), (3, 1, 20, 12), (24, 2, 128, 128)])
+def test_rope_kv_write_adds_the_products_bias_like_an_epilogue_before_it(dtype, heads, kv_heads, dim, rot):
+    """``bias=`` (the product ran without its epilogue) against the epilogue kernel followed by the
+    rotation: the same rounding, so the same bits, in the queries and in the cache; with a rotary width
+    below the head size (the tails need their bias too) and sizes that leave the 16-byte path."""
+    k = kernels()
+    torch.manual_seed(dim + rot)
+    n, page_size, pages = 9, 4, 7
+    cols = (heads + 2 * kv_heads) * dim
+    raw = torch.randn(n, cols, device=DEV).to(dtype)
+    bias = torch.randn(cols, device=DEV)
+    positions = torch.tensor([0, 1, 2, 3, 500, 4095, 16000, 7, 8], dtype=torch.int32, device=DEV)
+    slots = torch.tensor([5, 6, 7, 0, 27, 13, -1, 1, 2], dtype=torch.int32, device=DEV)
+    inv_freq = (1.0 / (10000.0 ** (torch.arange(0, rot, 2, dtype=torch.float32) / rot))).to(DEV)
+    st = status()
+    two = torch.empty_like(raw)
+    k.epilogue(raw, bias, None, two, k.EPILOGUE_NONE)
+    cache_two = torch.full((pages, 2, kv_heads, page_size, dim), float("nan"), dtype=dtype, device=DEV)
+    k.rope_kv_write(two, positions, inv_freq, slots, cache_two, heads, kv_heads, dim, rot, page_size, st)
+    one = raw.clone()
+    cache_one = torch.full((pages, 2, kv_heads, page_size, dim), float("nan"), dtype=dtype, device=DEV)
+    k.rope_kv_write(one, positions, inv_freq, slots, cache_one, heads, kv_heads, dim, rot, page_size, st, bias=bias)
+    assert st.item() == 0
+    assert torch.equal(one[:, :heads * dim], two[:, :heads * dim])              # the queries, tails included
+    assert torch.equal(torch.isnan(cache_one), torch.isnan(cache_two))
+    assert torch.equal(torch.nan_to_num(cache_one), torch.nan_to_num(cache_two))
+    # without a cache: queries only
+    q_only = raw.clone()
+    k.rope_kv_write(q_only, positions, inv_freq, None, None, heads, kv_heads, dim, rot, page_size, st, bias=bias)
+    assert torch.equal(q_only[:, :heads * dim], two[:, :heads * dim])
+
+
 def test_rope_bad_slot_sets_status_and_padding_slot_is_silent():
     k = kernels()
     qkv = torch.randn(3, 4 * 16, device=DEV)
