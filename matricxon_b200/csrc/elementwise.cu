@@ -159,9 +159,10 @@ constexpr int LN_VPT = 8;
 
 template <typename TOut, int LN_THREADS>
 __global__ void __launch_bounds__(LN_THREADS)
-layernorm_vec_kernel(const float* __restrict__ x, const int* __restrict__ rows,
+layernorm_vec_kernel(const float* x, const int* __restrict__ rows,
                      const float* __restrict__ weight, const float* __restrict__ bias,
-                     TOut* __restrict__ out, int hidden, float eps) {
+                     TOut* __restrict__ out, int hidden, float eps, const float* acc, const float* col_bias,
+                     float* x_sum) {
     __shared__ float scratch[32];
     pdl_trigger();
     const int r = blockIdx.x;
@@ -180,11 +181,35 @@ layernorm_vec_kernel(const float* __restrict__ x, const int* __restrict__ rows,
     const float4* xr = reinterpret_cast<const float4*>(after_wait(x) + (size_t)src_row * hidden);
     float4 v[LN_VPT];
     float s = 0.f;
+    if (acc != nullptr) {
+        // the row is still a sum to be formed: x + (acc + col_bias), the residual epilogue of the product
+        // before this norm (in that kernel's order of additions), written back to x on the way
+        const float4* ar = reinterpret_cast<const float4*>(after_wait(acc) + (size_t)src_row * hidden);
+        const float4* cb = reinterpret_cast<const float4*>(col_bias);
+        float4* xw = reinterpret_cast<float4*>(after_wait(x_sum) + (size_t)src_row * hidden);
 #pragma unroll
-    for (int k = 0; k < LN_VPT; ++k) {
-        const int i = threadIdx.x + k * LN_THREADS;
-        v[k] = i < n_vec ? xr[i] : make_float4(0.f, 0.f, 0.f, 0.f);
-        s += (v[k].x + v[k].y) + (v[k].z + v[k].w);
+        for (int k = 0; k < LN_VPT; ++k) {
+            const int i = threadIdx.x + k * LN_THREADS;
+            v[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (i < n_vec) {
+                float4 a = ar[i];
+                const float4 r = xr[i];
+                if (col_bias) {
+                    const float4 b = cb[i];
+                    a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+                }
+                v[k] = make_float4(a.x + r.x, a.y + r.y, a.z + r.z, a.w + r.w);
+                xw[i] = v[k];
+            }
+            s += (v[k].x + v[k].y) + (v[k].z + v[k].w);
+        }
+    } else {
+#pragma unroll
+        for (int k = 0; k < LN_VPT; ++k) {
+            const int i = threadIdx.x + k * LN_THREADS;
+            v[k] = i < n_vec ? xr[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+            s += (v[k].x + v[k].y) + (v[k].z + v[k].w);
+        }
     }
     const float mean = block_sum(s, scratch) / (float)hidden;
     float q = 0.f;
@@ -222,12 +247,19 @@ layernorm_vec_kernel(const float* __restrict__ x, const int* __restrict__ rows,
     }
 }
 
-extern "C" int mx_layernorm(const float* x, const int* rows, const float* weight, const float* bias,
-                            void* out, int out_dtype, int n_rows, int hidden, float eps,
-                            cudaStream_t stream) {
+extern "C" int mx_epilogue(const void* acc, int acc_dtype, const float* bias, const float* residual, void* out,
+                           int out_dtype, long long n_rows, int n_cols, int mode, cudaStream_t stream);
+
+// acc != null: x (float, written) first becomes x + acc + col_bias (the residual epilogue of the product
+// whose float accumulator acc is), in the same launch where the rows allow 16-byte accesses, else by the
+// epilogue kernel ahead of the norm. rows must be null then.
+static int layernorm_launch(float* x_sum, const float* x, const int* rows, const float* weight, const float* bias,
+                            void* out, int out_dtype, int n_rows, int hidden, float eps, const float* acc,
+                            const float* col_bias, cudaStream_t stream) {
     if (n_rows <= 0) return MX_OK;
     const bool aligned = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(weight) |
-                           reinterpret_cast<uintptr_t>(bias) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+                           reinterpret_cast<uintptr_t>(bias) | reinterpret_cast<uintptr_t>(out) |
+                           reinterpret_cast<uintptr_t>(acc) | reinterpret_cast<uintptr_t>(col_bias)) & 15) == 0;
     if (hidden % 4 == 0 && hidden <= 4 * 256 * LN_VPT && aligned) {
         // about six vectors a thread: each thread then has six loads in flight, more blocks share an SM and
         // the two block-wide sums cross fewer warps (2,048 rows of 3,072: 9.8 us with 128 threads, 10.6
@@ -241,7 +273,7 @@ extern "C" int mx_layernorm(const float* x, const int* rows, const float* weight
         if (n_rows <= 256) threads = n_vec <= 256 ? 256 : (n_vec <= 512 ? 512 : (n_vec <= 768 ? 768 : 1024));
 #define MX_LN_LAUNCH(T, N)                                                                                       \
     mx_launch_chained(layernorm_vec_kernel<T, N>, dim3(n_rows), dim3(N), 0, stream, x, rows, weight, bias, (T*)out, \
-                      hidden, eps)
+                      hidden, eps, acc, col_bias, x_sum)
         if (out_dtype == MX_DTYPE_F32) {
             if (threads == 64) MX_LN_LAUNCH(float, 64);
             else if (threads == 96) MX_LN_LAUNCH(float, 96);
@@ -264,6 +296,10 @@ extern "C" int mx_layernorm(const float* x, const int* rows, const float* weight
 #undef MX_LN_LAUNCH
         return mx_launch_status();
     }
+    if (acc != nullptr) {       // the general kernel takes a finished row: the sum is formed by the epilogue kernel
+        const int rc = mx_epilogue(acc, MX_DTYPE_F32, col_bias, x, x_sum, MX_DTYPE_F32, n_rows, hidden, 2, stream);
+        if (rc != MX_OK) return rc;
+    }
     const size_t smem = (size_t)hidden * sizeof(float);
     if (smem > 200 * 1024) MX_REFUSE("layernorm: hidden size %d exceeds the 51200 this kernel stages", hidden);
     const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
@@ -279,6 +315,22 @@ extern "C" int mx_layernorm(const float* x, const int* rows, const float* weight
                           weight, bias, (__nv_bfloat16*)out, hidden, eps);
     }
     return mx_launch_status();
+}
+
+extern "C" int mx_layernorm(const float* x, const int* rows, const float* weight, const float* bias,
+                            void* out, int out_dtype, int n_rows, int hidden, float eps,
+                            cudaStream_t stream) {
+    return layernorm_launch(nullptr, x, rows, weight, bias, out, out_dtype, n_rows, hidden, eps, nullptr, nullptr,
+                            stream);
+}
+
+// x <- x + acc + col_bias (col_bias may be null), then out <- LayerNorm(x): the residual epilogue of a
+// product and the norm after it in one pass over the rows.
+extern "C" int mx_layernorm_sum(float* x, const float* acc, const float* col_bias, const float* weight,
+                                const float* bias, void* out, int out_dtype, int n_rows, int hidden, float eps,
+                                cudaStream_t stream) {
+    if (acc == nullptr) MX_REFUSE("layernorm with sum: no accumulator");
+    return layernorm_launch(x, x, nullptr, weight, bias, out, out_dtype, n_rows, hidden, eps, acc, col_bias, stream);
 }
 
 // ---------------------------------------------------------------- rotary + cache write

@@ -89,6 +89,10 @@ class StepContext:
         self.capturing = False        # inside a CUDA-graph capture: buffers must belong to the graph
         self.padded = False           # a fixed-size decode batch: every sequence has one row or none
         self.memo: dict = {}          # what parts derive from the step once and share (tile lists, ...)
+        # ops.linear.PendingSum: a block lets its parts leave a residual sum to the next norm (sums_may_pend);
+        # the model lets a block hand such a sum on to the next block (pending_sum_wanted)
+        self.sums_may_pend = False
+        self.pending_sum_wanted = False
 
     def hidden(self, hidden_size: int) -> torch.Tensor:
         if self.capturing:

@@ -15,7 +15,7 @@ from dataclasses import dataclass
 import torch
 
 from matricxon_b200.ops import kernels
-from matricxon_b200.ops.linear import EPILOGUE_F32, linear
+from matricxon_b200.ops.linear import EPILOGUE_F32, PendingSum, linear
 from matricxon_b200.parts.base import (
     CacheBinding,
     KVCacheRequest,
@@ -158,9 +158,17 @@ class DecoderModel:
         """Runs the step's tokens through the schedule; returns the float32 residual stream."""
         x = ctx.hidden(self.spec.hidden_size)
         kernels.embed(ctx.token_ids, self.embedding, x, ctx.status, self.spec.embedding_scale)
-        for position, entry in enumerate(self.spec.schedule):
-            x = self.layers[entry.layer].forward(x, ctx, self.bindings[position])
-        return x
+        # a block may hand the next one a residual sum still to be added up (the next norm adds as it reads)
+        ctx.pending_sum_wanted = True
+        try:
+            for position, entry in enumerate(self.spec.schedule):
+                layer = self.layers[entry.layer]
+                if isinstance(x, PendingSum) and not layer.takes_pending_sum:
+                    x = x.tensor()
+                x = layer.forward(x, ctx, self.bindings[position])
+        finally:
+            ctx.pending_sum_wanted = False
+        return x.tensor() if isinstance(x, PendingSum) else x      # the last block's sum, added up here
 
     def logits(self, x: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
         """Float32 logits [len(rows), vocab] of the residual-stream rows ``rows``."""

@@ -113,6 +113,26 @@ def layernorm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, 
     _launched()
 
 
+def layernorm_sum(x: torch.Tensor, acc: torch.Tensor, col_bias: torch.Tensor | None, weight: torch.Tensor,
+                  bias: torch.Tensor | None, eps: float, out: torch.Tensor) -> None:
+    """``x += acc + col_bias`` (the residual epilogue of a product whose float accumulator is ``acc``),
+    then ``out = LayerNorm(x)``, in one pass over the rows."""
+    _need(x, "x", torch.float32)
+    _need(acc, "acc", torch.float32)
+    _need(weight, "weight", torch.float32)
+    _need(out, "out")
+    assert acc.shape == x.shape and out.shape == x.shape, (x.shape, acc.shape, out.shape)
+    if col_bias is not None:
+        _need(col_bias, "col_bias", torch.float32)
+        assert col_bias.numel() == x.shape[1]
+    if bias is not None:
+        _need(bias, "bias", torch.float32)
+    check(library().mx_layernorm_sum(_ptr(x), _ptr(acc), _ptr(col_bias), _ptr(weight), _ptr(bias), _ptr(out),
+                                     dtype_code(out.dtype), x.shape[0], x.shape[1], float(eps), _stream()),
+          "layernorm_sum")
+    _launched()
+
+
 def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor,
                   slots: torch.Tensor | None, cache: torch.Tensor | None, n_heads: int,
                   n_kv_heads: int, head_dim: int, rotary_dim: int, page_size: int,

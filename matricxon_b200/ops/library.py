@@ -30,6 +30,7 @@ _SIGNATURES: dict[str, tuple[list, object]] = {
     "mx_embed": ([P, P, I, P, I, I, I, F, P, P], I),
     "mx_softcap": ([P, L, F, P], I),
     "mx_layernorm": ([P, P, P, P, P, I, I, I, F, P], I),
+    "mx_layernorm_sum": ([P, P, P, P, P, P, I, I, I, F, P], I),
     "mx_rope_kv_write": ([P, I, I, P, P, P, P, I, I, I, I, I, I, L, I, P, P], I),
     "mx_rope_kv_write_bias": ([P, I, I, P, P, P, P, I, I, I, I, I, I, L, I, P, P, P], I),
     "mx_epilogue": ([P, I, P, P, P, I, L, I, I, P], I),

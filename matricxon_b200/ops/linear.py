@@ -84,6 +84,40 @@ def _pick(x: torch.Tensor, weight: torch.Tensor, m: int, n: int) -> str:
     return "library"
 
 
+class PendingSum:
+    """``residual + x @ W.T + bias`` not yet added up: the library's float product of a step with 17 or
+    more rows, handed to the norm that follows, which forms the sum on its way through the rows
+    (``kernels.layernorm_sum``) instead of an epilogue pass of its own. ``tensor()`` adds it up for
+    anybody else."""
+
+    def __init__(self, acc: torch.Tensor, bias: torch.Tensor | None, residual: torch.Tensor) -> None:
+        self.acc, self.bias, self.residual = acc, bias, residual
+        self._done = False
+
+    @property
+    def shape(self):
+        return self.residual.shape
+
+    @property
+    def device(self):
+        return self.residual.device
+
+    @property
+    def dtype(self):
+        return self.residual.dtype
+
+    def added_by_kernel(self) -> torch.Tensor:
+        """For the kernel that adds the sum itself: the residual, which then holds it."""
+        self._done = True
+        return self.residual
+
+    def tensor(self) -> torch.Tensor:
+        if not self._done:
+            kernels.epilogue(self.acc, self.bias, self.residual, self.residual, EPILOGUE_RESIDUAL)
+            self._done = True
+        return self.residual
+
+
 def chosen_backend(x: torch.Tensor, weight: torch.Tensor, requested: str = "auto") -> str:
     """The backend ``linear`` would run this product on."""
     backend = resolve_backend(requested, x.dtype)
@@ -92,11 +126,14 @@ def chosen_backend(x: torch.Tensor, weight: torch.Tensor, requested: str = "auto
 
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, mode: int,
            residual: torch.Tensor | None = None, out: torch.Tensor | None = None,
-           backend: str = "auto") -> torch.Tensor:
+           backend: str = "auto", defer_sum: bool = False) -> "torch.Tensor | PendingSum":
     """x [M, K], weight [N, K] in the compute dtype; bias float32 [N] or None.
 
     mode EPILOGUE_NONE / EPILOGUE_GELU give the compute dtype; EPILOGUE_RESIDUAL
     (``residual + x @ W.T + bias``) and EPILOGUE_F32 give float32.
+
+    ``defer_sum`` (EPILOGUE_RESIDUAL into the residual itself): where the product is the library's, the
+    caller gets a ``PendingSum`` instead of the sum and hands it to a norm that adds as it reads.
     """
     m, n = x.shape[0], weight.shape[0]
     out_dtype = torch.float32 if mode in (EPILOGUE_RESIDUAL, EPILOGUE_F32) else x.dtype
@@ -107,6 +144,11 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, mod
         acc = _mm_f32(x, weight.t())
         if acc is not None:
             return acc
+    if (defer_sum and backend == "library" and mode == EPILOGUE_RESIDUAL and out is residual
+            and residual is not None and m > 0):
+        acc = _mm_f32(x, weight.t())
+        if acc is not None:
+            return PendingSum(acc, bias, residual)
     if backend == "library" and out is None and mode == EPILOGUE_NONE and bias is None and m > 0:
         return torch.mm(x, weight.t())        # nothing to add: the library's result is the result
     if out is None:
@@ -141,5 +183,5 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, mod
     return out
 
 
-__all__ = ["linear", "chosen_backend", "resolve_backend", "EPILOGUE_NONE", "EPILOGUE_GELU", "EPILOGUE_RESIDUAL",
+__all__ = ["linear", "chosen_backend", "PendingSum", "resolve_backend", "EPILOGUE_NONE", "EPILOGUE_GELU", "EPILOGUE_RESIDUAL",
            "EPILOGUE_F32"]

@@ -206,4 +206,4 @@ class PagedAttention(Mixer):
                                     spec.head_dim, spec.window, spec.scale, attn, ctx.status,
                                     n_splits=n_splits, scratch=scratch)
         return linear(attn, self.o_weight, self.o_bias, EPILOGUE_RESIDUAL, residual=residual,
-                      out=residual, backend=rt.gemm_backend)
+                      out=residual, backend=rt.gemm_backend, defer_sum=getattr(ctx, "sums_may_pend", False))

@@ -135,6 +135,9 @@ class Part:
 
 
 class Norm(Part):
+    # True: forward_sum(pending) takes an ``ops.linear.PendingSum`` and returns (x, norm(x))
+    adds_pending_sum = False
+
     def forward(self, x, out=None, rows=None):
         raise NotImplementedError
 
@@ -174,4 +177,6 @@ class FeedForward(Part):
 
 
 class Block(Part):
-    pass
+    # True: forward() takes ``x`` as an ``ops.linear.PendingSum`` too, and returns one where
+    # ``ctx.pending_sum_wanted`` says that the caller takes it (the model does, between such blocks)
+    takes_pending_sum = False

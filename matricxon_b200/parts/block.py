@@ -7,11 +7,14 @@ and each sub-layer adds into it in float.
 
 from __future__ import annotations
 
+from matricxon_b200.ops.linear import PendingSum
 from matricxon_b200.parts.base import Block, build_part, register_part
 
 
 @register_part("block", "pre_norm_sequential")
 class PreNormSequentialBlock(Block):
+    takes_pending_sum = True
+
     def __init__(self, spec, runtime, prefix):
         super().__init__(spec, runtime, prefix)
         self.mixer_norm = build_part("norm", spec.mixer_norm, runtime, f"{prefix}{spec.mixer_norm_name}.")
@@ -40,8 +43,28 @@ class PreNormSequentialBlock(Block):
         for part in self.parts():
             part.load(fetch)
 
+    @staticmethod
+    def _normed(norm, x):
+        """(x, norm(x)); ``x`` may arrive as a sum that the part before left to the norm to add up."""
+        if isinstance(x, PendingSum):
+            if norm.adds_pending_sum:
+                return norm.forward_sum(x)
+            x = x.tensor()
+        return x, norm.forward(x)
+
     def forward(self, x, ctx, binding):
-        h = self.mixer_norm.forward(x)
-        x = self.mixer.forward(h, x, ctx, binding)
-        h = self.ffn_norm.forward(x)
-        return self.feed_forward.forward(h, x, ctx)
+        """``x`` is the float residual stream or a ``PendingSum`` that stands for it; so is the result when
+        the caller has said (``ctx.pending_sum_wanted``) that it takes one, else the result is the stream."""
+        # this block knows what to do with a sum that one of its parts leaves pending; the parts only do so
+        # on this say-so, which is withdrawn when the block is done
+        ctx.sums_may_pend = True
+        try:
+            x, h = self._normed(self.mixer_norm, x)
+            x = self.mixer.forward(h, x, ctx, binding)
+            x, h = self._normed(self.ffn_norm, x)
+            x = self.feed_forward.forward(h, x, ctx)
+        finally:
+            ctx.sums_may_pend = False
+        if isinstance(x, PendingSum) and not getattr(ctx, "pending_sum_wanted", False):
+            return x.tensor()
+        return x

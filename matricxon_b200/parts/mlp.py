@@ -47,4 +47,4 @@ class Mlp(FeedForward):
         mid = linear(h, self.up_weight, self.up_bias, _ACTIVATION_MODES[self.spec.activation],
                      backend=backend)
         return linear(mid, self.down_weight, self.down_bias, EPILOGUE_RESIDUAL, residual=residual,
-                      out=residual, backend=backend)
+                      out=residual, backend=backend, defer_sum=getattr(ctx, "sums_may_pend", False))

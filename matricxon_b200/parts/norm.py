@@ -18,6 +18,7 @@ from matricxon_b200.weights.loader import WeightSpec
 @register_part("norm", "layernorm")
 class LayerNorm(Norm):
     capturable = True
+    adds_pending_sum = True
 
     @classmethod
     def weight_specs(cls, spec, prefix):
@@ -36,3 +37,11 @@ class LayerNorm(Norm):
             out = torch.empty((n_rows, self.spec.size), dtype=self.runtime.dtype, device=x.device)
         kernels.layernorm(x, self.weight, self.bias, self.spec.eps, out, rows)
         return out
+
+    def forward_sum(self, pending):
+        """The norm of a residual sum that has not been added up yet (``ops.linear.PendingSum``): one
+        kernel forms the sum, writes it to the residual stream and normalises it. Returns (x, norm(x))."""
+        x = pending.added_by_kernel()
+        out = torch.empty(tuple(x.shape), dtype=self.runtime.dtype, device=x.device)
+        kernels.layernorm_sum(x, pending.acc, pending.bias, self.weight, self.bias, self.spec.eps, out)
+        return x, out

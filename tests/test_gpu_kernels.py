@@ -80,6 +80,34 @@ def test_layernorm(hidden, dtype):
     assert torch.allclose(out.double().cpu(), ref, **tol(dtype))
 
 
+@pytest.mark.parametrize("hidden,rows", [(64, 37), (3072, 64), (3072, 300), (1002, 33), (96, 1)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("with_bias", [True, False])
+def test_layernorm_that_adds_up_the_residual_sum_first(hidden, rows, dtype, with_bias):
+    """``x += acc + col_bias; out = LayerNorm(x)`` in one launch against the epilogue kernel followed by the
+    norm: the same x and the same out, bit for bit (1002 columns take the general kernels)."""
+    k = kernels()
+    torch.manual_seed(hidden + rows)
+    x = torch.randn(rows, hidden, device=DEV) * 3 + 5
+    acc = torch.randn(rows, hidden, device=DEV)
+    col_bias = torch.randn(hidden, device=DEV) if with_bias else None
+    w = 1 + 0.1 * torch.randn(hidden, device=DEV)
+    b = 0.1 * torch.randn(hidden, device=DEV)
+    x_two = x.clone()
+    k.epilogue(acc, col_bias, x_two, x_two, k.EPILOGUE_RESIDUAL)
+    out_two = torch.empty(rows, hidden, dtype=dtype, device=DEV)
+    k.layernorm(x_two, w, b, 1e-5, out_two)
+    x_one = x.clone()
+    out_one = torch.full((rows, hidden), float("nan"), dtype=dtype, device=DEV)
+    k.layernorm_sum(x_one, acc, col_bias, w, b, 1e-5, out_one)
+    assert torch.equal(x_one, x_two)
+    assert torch.equal(out_one, out_two)
+    total = x.double().cpu() + acc.double().cpu() + (col_bias.double().cpu() if with_bias else 0)
+    assert torch.allclose(x_one.double().cpu(), total, atol=1e-5, rtol=1e-6)
+    ref = plain_layernorm(total, w.double().cpu(), b.double().cpu(), 1e-5)
+    assert torch.allclose(out_one.double().cpu(), ref, **tol(dtype))
+
+
 # ------------------------------------------------------------------ FP32-core GEMM
 @pytest.mark.parametrize("m,n,k_dim", [(1, 1000, 96), (7, 130, 352), (65, 64, 17), (200, 3584, 300)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])

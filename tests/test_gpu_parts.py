@@ -140,6 +140,49 @@ def test_norm_mlp_attention_block_alone(name, dtype):
     assert torch.allclose(out.double().cpu(), torch.cat(refs), **tol(dtype))
 
 
+def test_a_block_leaves_its_last_residual_sum_to_the_next_blocks_norm():
+    """With 17 or more rows in bfloat16 the residual products are the library's, and the sum
+    ``residual + product + bias`` is formed by the norm that follows (one launch instead of an epilogue
+    and a norm). A block returns such a pending sum only to a caller that says it takes one; two blocks
+    chained that way give the bits of two blocks run one after the other with the sums added up in between."""
+    import matricxon_b200.parts  # noqa: F401
+    from matricxon_b200.ops.linear import PendingSum
+    from matricxon_b200.parts.base import CacheBinding, part_class
+
+    config = tiny_config("A")
+    spec = config.model_spec()
+    cfg = plain_config(TINY["A"][0])
+    tensors = tiny_tensors("A", torch.bfloat16)
+    rt = make_runtime(torch.bfloat16)
+    fetch = fetcher(tensors, torch.bfloat16)
+    blocks = []
+    for layer in (0, 1):
+        block = part_class("block", spec.layers[layer].block)(spec.layers[layer], rt, f"model.layers.{layer}.")
+        block.load(fetch)
+        blocks.append(block)
+    seq_lens = [50, 7]
+    torch.manual_seed(5)
+    x = torch.randn(sum(seq_lens), cfg["hidden"], device=DEV)
+
+    def run(wanted):
+        ctx = hand_made_context(seq_lens, 16, 16)
+        ctx.pending_sum_wanted = wanted
+        stream = x.clone()
+        kinds = []
+        for block in blocks:
+            kv = torch.full((16, 2, cfg["kv_heads"], 16, cfg["head_dim"]), float("nan"), dtype=torch.bfloat16, device=DEV)
+            stream = block.forward(stream, ctx, CacheBinding(group=0, kv=kv, writes=True))
+            kinds.append(type(stream))
+        assert int(ctx.status.item()) == 0
+        return (stream.tensor() if isinstance(stream, PendingSum) else stream), kinds
+
+    plain, kinds = run(False)
+    assert kinds == [torch.Tensor, torch.Tensor]
+    chained, kinds = run(True)
+    assert kinds == [PendingSum, PendingSum]
+    assert torch.equal(chained, plain)
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_rotary_part_alone(dtype):
     import matricxon_b200.parts  # noqa: F401
