@@ -148,7 +148,7 @@ sample_kernel(const float* __restrict__ logits, long long row_stride, int vocab,
               const float* __restrict__ top_p, const float* __restrict__ repeat_penalty,
               const float* __restrict__ uniform, const int* __restrict__ penalty_offsets,
               const int* __restrict__ penalty_ids, const int* __restrict__ pending_ids,
-              float* __restrict__ work_all, int* __restrict__ out_tokens) {
+              float* __restrict__ work_all, int* __restrict__ out_tokens, int mark_words) {
     __shared__ ArgMax arg_scratch[SAMPLE_THREADS / 32];
     __shared__ unsigned long long sum_scratch[SAMPLE_THREADS / 32];
     __shared__ unsigned long long hist[256];
@@ -160,6 +160,44 @@ sample_kernel(const float* __restrict__ logits, long long row_stride, int vocab,
     const float* src = logits + (size_t)row * row_stride;
     float* work = work_all + (size_t)row * vocab;
     const int tid = threadIdx.x;
+
+    if (temperature[row] <= 0.f && mark_words > 0) {
+        // Greedy: one pass over the logits where they lie. The penalised ids are marked in a bitmap in
+        // shared memory and left out of the pass; their adjusted scores are candidates of their own (each
+        // from the raw score, so an id that is both listed and pending is penalised once).
+        extern __shared__ unsigned marked[];
+        const float penalty = repeat_penalty[row];
+        const int first = penalty_offsets[row], last = penalty_offsets[row + 1];
+        const int pending = pending_ids != nullptr ? pending_ids[row] : -1;
+        const bool penalised = penalty != 1.0f && (last > first || pending >= 0);
+        ArgMax best = {-INFINITY, 0x7fffffff};
+        if (penalised) {
+            for (int w = tid; w < mark_words; w += SAMPLE_THREADS) marked[w] = 0u;
+            __syncthreads();
+            for (int j = first + tid; j <= last; j += SAMPLE_THREADS) {
+                const int id = j < last ? penalty_ids[j] : pending;
+                if (id >= 0 && id < vocab) {
+                    atomicOr(&marked[id >> 5], 1u << (id & 31));
+                    const float x = src[id];
+                    best = better(best, ArgMax{x > 0.f ? x / penalty : x * penalty, id});
+                }
+            }
+            __syncthreads();
+            // every score is loaded whatever the bitmap says (loads that wait for a test cannot overlap)
+#pragma unroll 8
+            for (int i = tid; i < vocab; i += SAMPLE_THREADS) {
+                const float x = src[i];
+                const bool out_of_it = (marked[i >> 5] >> (i & 31)) & 1u;
+                best = better(best, ArgMax{out_of_it ? -INFINITY : x, i});
+            }
+        } else {
+#pragma unroll 8
+            for (int i = tid; i < vocab; i += SAMPLE_THREADS) best = better(best, ArgMax{src[i], i});
+        }
+        best = block_argmax(best, arg_scratch);
+        if (tid == 0) out_tokens[row] = best.index;
+        return;
+    }
 
     for (int i = tid; i < vocab; i += SAMPLE_THREADS) work[i] = src[i];
     __syncthreads();
@@ -288,9 +326,11 @@ extern "C" int mx_sample(const float* logits, long long row_stride, int n_rows, 
     if (n_rows <= 0) return MX_OK;
     if (vocab <= 0) MX_REFUSE("sample: vocabulary of %d", vocab);
     if (work == nullptr) MX_REFUSE("sample: needs a work buffer of rows x vocab floats");
-    sample_kernel<<<n_rows, SAMPLE_THREADS, 0, stream>>>(logits, row_stride, vocab, temperature,
-                                                         top_k, top_p, repeat_penalty, uniform,
-                                                         penalty_offsets, penalty_ids, pending_ids,
-                                                         work, out_tokens);
+    // greedy rows mark their penalised ids in a bitmap in shared memory, where the vocabulary fits in 32 KB of it
+    const int words = (vocab + 31) / 32;
+    const int mark_words = words * 4 <= 32 * 1024 ? words : 0;
+    sample_kernel<<<n_rows, SAMPLE_THREADS, (size_t)mark_words * 4, stream>>>(
+        logits, row_stride, vocab, temperature, top_k, top_p, repeat_penalty, uniform, penalty_offsets, penalty_ids,
+        pending_ids, work, out_tokens, mark_words);
     return mx_launch_status();
 }
