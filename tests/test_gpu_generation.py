@@ -50,6 +50,43 @@ def test_greedy_takes_the_first_of_equal_maxima_and_ignores_other_options():
     assert tokens == [int(torch.argmax(row)) for row in logits]
 
 
+@pytest.mark.parametrize("vocab", [1000, 49152, 300000])
+def test_greedy_with_a_repeat_penalty_judges_penalised_ids_by_their_adjusted_scores(vocab):
+    """Greedy rows take a path of their own (one pass, penalised ids marked in a bitmap; vocabularies
+    whose bitmap does not fit keep the general path): the best id is penalised below the second, a
+    negative best score gets more negative, an id that is generated and still pending on the device is
+    penalised once, a penalty below one can lift a generated id to the top."""
+    from matricxon_b200 import SamplingConfig
+    from matricxon_b200.sampling.sampler import BatchSampler, RequestSampler
+
+    torch.manual_seed(vocab)
+    logits = torch.randn(6, vocab)
+    logits[0, 7], logits[0, 900] = 10.0, 9.5          # 7 is generated: 10 / 1.5 < 9.5
+    logits[1] = -torch.rand(vocab) - 1.0
+    logits[1, 33], logits[1, 34] = -0.5, -0.6         # 33 is generated: -0.5 * 1.5 < -0.6
+    logits[2, 5], logits[2, 6] = 10.0, 9.0            # 5 is pending only: penalised
+    logits[3, 5], logits[3, 6] = 10.0, 7.0            # 5 is generated and pending: once (10 / 1.3 > 7), not twice (10 / 1.69 < 7)
+    logits[4, 8], logits[4, 9] = 4.0, 5.0             # penalty 0.5 lifts the generated 8 above 9
+    configs = [SamplingConfig(temperature=0.0, repeat_penalty=p) for p in (1.5, 1.5, 1.5, 1.3, 0.5, 1.0)]
+    generated = [[7, 1, 2], [33], [], [5], [8], [int(torch.argmax(logits[5]))]]
+    pending = [-1, -1, 5, 5, -1, -1]
+    samplers = []
+    for config, ids in zip(configs, generated):
+        sampler = RequestSampler(config)
+        for token in ids:
+            sampler.accept(token)
+        samplers.append(sampler)
+    batch = BatchSampler(DEV, vocab)
+    feed = torch.tensor(pending, dtype=torch.int32, device=DEV)
+    tokens = batch.read(batch.launch(logits.to(DEV), samplers, pending=feed))
+    expected = []
+    for row, config, ids, extra in zip(logits, configs, generated, pending):
+        seen = ids + ([extra] if extra >= 0 else [])
+        expected.append(plain_sample(row, seen, 0.0, 0, 1.0, config.repeat_penalty, 0.5))
+    assert tokens == expected
+    assert tokens[:5] == [900, 34, 6, 5, 8] and tokens[5] == int(torch.argmax(logits[5]))
+
+
 @pytest.mark.parametrize("top_k,top_p,penalty,temperature", [
     (0, 1.0, 1.0, 1.0), (40, 0.9, 1.1, 0.8), (5, 1.0, 1.0, 0.7), (0, 0.6, 1.0, 1.3), (3, 0.5, 1.5, 0.5)])
 def test_sampling_matches_plain_sampler_over_a_quantile_sweep(top_k, top_p, penalty, temperature):
