@@ -63,9 +63,11 @@ def mma_tile_splits(ctx, n_tiles: int, narrow: bool, alone: bool, n_heads: int, 
         return 1, None
     items = max(n_tiles * n_kv_heads, 1)
     chunks = _key_span(ctx, window) // 32 + 1
-    # a narrow block fills an SM's shared memory with its four private pipelines: one per SM
+    # a narrow block fills an SM's shared memory with its eight private stages: one per SM. A share of at
+    # least eight chunks gives every warp of a narrow block one (a lone request at 3,100 tokens: 12 shares
+    # of 8 chunks decode at 585 tok/s, 24 of 4 at 570, 48 of 2 at 520: more blocks, more to merge)
     target = ctx.sm_count * (1 if narrow else 2)
-    n_splits = max(1, min(target // items, chunks // (4 if narrow else 8), 128))
+    n_splits = max(1, min(target // items, chunks // 8, 128))
     while n_splits > 1 and kernels.attention_scratch_bytes(
             ctx.n_tokens, n_heads, head_dim, n_splits) > (256 << 20):
         n_splits //= 2
